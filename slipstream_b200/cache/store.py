@@ -1,0 +1,56 @@
+"""Device memory behind the cache manager: one page tensor per cache group and one
+tensor per fixed-size state a part declared.
+
+Page tensor of a group: ``[entries, pages, 2, kv_heads, page_size, head_dim]`` in
+the compute dtype: an entry is one place in the execution order that writes
+pages; keys are index 0 and values index 1 of the third axis; one (page, head)
+tile of ``page_size x head_dim`` is contiguous so that a kernel can fetch it with
+one bulk copy.  The reference keeps ``[layers, 2, blocks, block_size, kv_heads,
+head_dim]`` (slipstream/core/types.py:25-29).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from slipstream_b200.parts.base import StateSpec
+
+from .manager import GroupLayout
+
+
+class PagedStore:
+    def __init__(self, layouts: list[GroupLayout], num_pages: int, page_size: int, dtype: torch.dtype,
+                 device: torch.device, state_specs: list[list[StateSpec]], max_num_seqs: int) -> None:
+        self.num_pages = num_pages
+        self.page_size = page_size
+        self.dtype = dtype
+        self.kv: list[torch.Tensor] = []
+        for layout in layouts:
+            spec = layout.spec
+            self.kv.append(torch.zeros(
+                (max(layout.num_entries, 1), num_pages, 2, spec.num_kv_heads, page_size, spec.head_dim),
+                dtype=dtype, device=device))
+        self.state: list[dict[str, torch.Tensor]] = []
+        for specs in state_specs:
+            self.state.append({s.name: torch.zeros((max_num_seqs, *s.shape), dtype=s.dtype, device=device)
+                               for s in specs})
+
+    def kv_bytes_per_token(self) -> int:
+        """Bytes one cached token takes over all groups and entries
+        (slipstream/core/config.py:10-22 for a single group)."""
+        total = 0
+        for t in self.kv:
+            entries, _, _, heads, _, dim = t.shape
+            total += entries * 2 * heads * dim * t.element_size()
+        return total
+
+    @staticmethod
+    def bytes_per_page(layouts: list[GroupLayout], page_size: int, dtype: torch.dtype) -> int:
+        size = torch.empty((), dtype=dtype).element_size()
+        return sum(max(l.num_entries, 1) * 2 * l.spec.num_kv_heads * page_size * l.spec.head_dim * size
+                   for l in layouts)
+
+    def zero_state(self, slot: int) -> None:
+        for entry in self.state:
+            for tensor in entry.values():
+                tensor[slot].zero_()

@@ -1,0 +1,65 @@
+// Shared helpers for the sm_100a kernels: element types, loads and stores that
+// widen to float, block reductions with a fixed order, and the error word.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+// Element type codes passed through the C interface.
+#define SS_F32 0
+#define SS_BF16 1
+
+// Bits of the device error word that kernels set instead of trapping.
+#define SS_ERR_TOKEN_RANGE 1   // a token id outside [0, vocab)
+#define SS_ERR_SLOT_RANGE 2    // a cache slot outside the pool
+#define SS_ERR_PAGE_RANGE 4    // a block-table entry outside the pool
+#define SS_ERR_WAIT_LIMIT 8    // a bounded wait gave up
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// A vector weight may be stored in 32-bit even when activations are bfloat16.
+template <typename T>
+__device__ __forceinline__ float load_vec(const void* base, int64_t i, int is_f32) {
+    return is_f32 ? reinterpret_cast<const float*>(base)[i]
+                  : to_float(reinterpret_cast<const T*>(base)[i]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the block; every thread gets the result.  The order of additions
+// depends on blockDim only, never on what else is in the batch.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+#define SS_LAUNCH_CHECK() (int)cudaGetLastError()

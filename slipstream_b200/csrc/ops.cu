@@ -1,0 +1,265 @@
+// Element-wise and row-wise kernels of the decoder for sm_100a: embedding gather
+// into the float32 residual stream, residual add fused with RMSNorm, rotary
+// encoding fused with the key/value page write, SwiGLU, and a float32 SIMT
+// matrix product for the true 32-bit path.  All sizes are run-time parameters.
+//
+// Formulas restate slipstream/models/layers/rmsnorm.py:28-34,
+// slipstream/models/layers/rope.py:13-36,89-106, slipstream/models/layers/mlp.py:39
+// and slipstream/kernels/attention_ref.py:21-39 (the page write); they replace the
+// reference's Triton kernels slipstream/kernels/fused_rmsnorm.py:38-70,
+// fused_rope.py:39-85, fused_swiglu.py:32-46 and triton_paged.py:39-95.
+
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+
+template <typename T>
+__global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table,
+                                 float* __restrict__ out, int hidden, int vocab, int* err) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicOr(err, SS_ERR_TOKEN_RANGE);
+        id = 0;
+    }
+    const T* row = table + (int64_t)id * hidden;
+    float* dst = out + (int64_t)t * hidden;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) dst[j] = to_float(row[j]);
+}
+
+extern "C" int ss_embedding(const int32_t* ids, const void* table, float* out, int n_tokens,
+                            int hidden, int vocab, int dtype, int* err, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (dtype == SS_BF16)
+        embedding_kernel<bf16><<<n_tokens, threads, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab, err);
+    else
+        embedding_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, err);
+    return SS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- add + RMSNorm
+
+// One block per output row.  residual (float32) += delta, y = weight * round(x_hat).
+// With `rows`, output row i reads input row rows[i] and the residual stays as it is.
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                   const void* __restrict__ weight, int w_f32, T* __restrict__ y,
+                                   const int32_t* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[33];
+    const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* res = residual + src * hidden;
+    const T* del = delta ? delta + src * hidden : nullptr;
+    T* out = y + (int64_t)blockIdx.x * hidden;
+    const bool write_back = (rows == nullptr) && (del != nullptr);
+
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        float v = res[j];
+        if (del) v = __fadd_rn(v, to_float(del[j]));
+        if (write_back) res[j] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(ss / (float)hidden + eps);
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        float v = res[j];
+        if (del && !write_back) v = __fadd_rn(v, to_float(del[j]));
+        const float xh = to_float(from_float<T>(v * rstd));
+        out[j] = from_float<T>(load_vec<T>(weight, j, w_f32) * xh);
+    }
+}
+
+extern "C" int ss_add_rmsnorm(float* residual, const void* delta, const void* weight, int w_f32,
+                              void* y, const int32_t* rows, int n_rows, int hidden, float eps,
+                              int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    if (dtype == SS_BF16)
+        add_rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(residual, (const bf16*)delta, weight, w_f32, (bf16*)y, rows, hidden, eps);
+    else
+        add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(residual, (const float*)delta, weight, w_f32, (float*)y, rows, hidden, eps);
+    return SS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- rotary + page write
+
+// One block per token.  qkv row = [n_q heads | n_kv key heads | n_kv value heads] x D.
+// Queries are rotated in place; keys are rotated and written to their page, values
+// are copied to theirs.  kv layout: [page][2][kv head][offset in page][D].
+// A slot of -1 (or write_cache == 0) skips the write; keys are then rotated in place.
+template <typename T>
+__global__ void rope_cache_kernel(T* __restrict__ qkv, const int32_t* __restrict__ positions,
+                                  const int32_t* __restrict__ slots, const float* __restrict__ inv_freq,
+                                  T* __restrict__ kv, int n_q, int n_kv, int D, int rot_dim,
+                                  int page_size, int64_t pool_slots, int write_cache, int* err) {
+    const int t = blockIdx.x;
+    T* row = qkv + (int64_t)t * (n_q + 2 * n_kv) * D;
+    const float pos = (float)positions[t];
+    int64_t slot = (write_cache && slots) ? (int64_t)slots[t] : -1;
+    if (slot >= pool_slots) {
+        if (threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
+        slot = -1;
+    }
+    const int64_t page = slot >= 0 ? slot / page_size : 0;
+    const int off = slot >= 0 ? (int)(slot % page_size) : 0;
+    const int half = rot_dim / 2;
+
+    // rotated pairs of queries and keys
+    const int n_rot = (n_q + n_kv) * half;
+    for (int idx = threadIdx.x; idx < n_rot; idx += blockDim.x) {
+        const int h = idx / half, i = idx - h * half;
+        T* head = row + (int64_t)h * D;
+        const float x1 = to_float(head[i]), x2 = to_float(head[i + half]);
+        const float angle = __fmul_rn(pos, inv_freq[i]);
+        const float c = cosf(angle), s = sinf(angle);
+        // q*cos + rotate_half(q)*sin, each product and the sum rounded as written
+        const T o1 = from_float<T>(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(-x2, s)));
+        const T o2 = from_float<T>(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s)));
+        if (h < n_q || slot < 0) {
+            head[i] = o1;
+            head[i + half] = o2;
+        } else {
+            T* dst = kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
+            dst[i] = o1;
+            dst[i + half] = o2;
+        }
+    }
+    if (slot < 0) return;
+    // key dims beyond the rotary part, and the values
+    const int tail = D - rot_dim;
+    for (int idx = threadIdx.x; idx < n_kv * tail; idx += blockDim.x) {
+        const int h = idx / tail, d = rot_dim + (idx - h * tail);
+        kv[(((page * 2 + 0) * n_kv + h) * page_size + off) * (int64_t)D + d] = row[(int64_t)(n_q + h) * D + d];
+    }
+    for (int idx = threadIdx.x; idx < n_kv * D; idx += blockDim.x) {
+        const int h = idx / D, d = idx - h * D;
+        kv[(((page * 2 + 1) * n_kv + h) * page_size + off) * (int64_t)D + d] = row[(int64_t)(n_q + n_kv + h) * D + d];
+    }
+}
+
+extern "C" int ss_rope_cache(void* qkv, const int32_t* positions, const int32_t* slots,
+                             const float* inv_freq, void* kv, int n_tokens, int n_q, int n_kv, int D,
+                             int rot_dim, int page_size, int64_t num_pages, int write_cache, int dtype,
+                             int* err, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const int threads = 128;
+    const int64_t pool = num_pages * page_size;
+    if (dtype == SS_BF16)
+        rope_cache_kernel<bf16><<<n_tokens, threads, 0, stream>>>((bf16*)qkv, positions, slots, inv_freq, (bf16*)kv, n_q, n_kv, D, rot_dim, page_size, pool, write_cache, err);
+    else
+        rope_cache_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, positions, slots, inv_freq, (float*)kv, n_q, n_kv, D, rot_dim, page_size, pool, write_cache, err);
+    return SS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- SwiGLU
+
+// in: [n, 2*inter] = [gate | up];  out[n, inter] = silu(gate) * up, formed in float32.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t n, int inter) {
+    const int64_t total = n * inter;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / inter;
+        const int c = (int)(idx - r * inter);
+        const float g = to_float(in[r * 2 * inter + c]);
+        const float u = to_float(in[r * 2 * inter + inter + c]);
+        const float silu = g / (1.0f + expf(-g));
+        out[idx] = from_float<T>(silu * u);
+    }
+}
+
+extern "C" int ss_swiglu(const void* in, void* out, int64_t n, int inter, int dtype, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int threads = 256;
+    int64_t blocks = (n * inter + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == SS_BF16)
+        swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)in, (bf16*)out, n, inter);
+    else
+        swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)in, (float*)out, n, inter);
+    return SS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- SIMT matrix product
+
+// C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]); float32 accumulation with FFMA, one
+// sequential pass over K per output element, so a row's result does not depend on
+// how many other rows are in the batch.  No tensor cores: this is the true 32-bit
+// path (and a slow stand-in for any dtype mix).
+#define GB_M 64
+#define GB_N 64
+#define GB_K 16
+
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W,
+                                                        const void* __restrict__ bias, int bias_f32,
+                                                        TC* __restrict__ C, int M, int N, int K,
+                                                        int64_t lda, int64_t ldc) {
+    __shared__ float As[GB_K][GB_M + 4];
+    __shared__ float Ws[GB_K][GB_N + 4];
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.y * GB_M, n0 = blockIdx.x * GB_N;
+    const int tx = tid & 15, ty = tid >> 4;  // 16 x 16 threads, 4 x 4 outputs each
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+    const int lr = tid >> 2;        // 0..63: tile row loaded by this thread
+    const int lk = (tid & 3) * 4;   // 0,4,8,12: first of its 4 k
+    for (int k0 = 0; k0 < K; k0 += GB_K) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int k = k0 + lk + q;
+            const int am = m0 + lr, wn = n0 + lr;
+            As[lk + q][lr] = (am < M && k < K) ? to_float(A[(int64_t)am * lda + k]) : 0.f;
+            Ws[lk + q][lr] = (wn < N && k < K) ? to_float(W[(int64_t)wn * K + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GB_K; ++kk) {
+            float a[4], w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (bias) v += bias_f32 ? ((const float*)bias)[n] : to_float(((const TW*)bias)[n]);
+            C[(int64_t)m * ldc + n] = from_float<TC>(v);
+        }
+    }
+}
+
+// dtype_in: element type of A, W (and of bias unless bias_f32); dtype_out: of C.
+extern "C" int ss_gemm_simt(const void* A, const void* W, const void* bias, int bias_f32, void* C,
+                            int M, int N, int K, int64_t lda, int64_t ldc, int dtype_in,
+                            int dtype_out, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    dim3 grid((N + GB_N - 1) / GB_N, (M + GB_M - 1) / GB_M);
+    if (dtype_in == SS_F32 && dtype_out == SS_F32)
+        gemm_simt_kernel<float, float, float><<<grid, 256, 0, stream>>>((const float*)A, (const float*)W, bias, bias_f32, (float*)C, M, N, K, lda, ldc);
+    else if (dtype_in == SS_BF16 && dtype_out == SS_F32)
+        gemm_simt_kernel<bf16, bf16, float><<<grid, 256, 0, stream>>>((const bf16*)A, (const bf16*)W, bias, bias_f32, (float*)C, M, N, K, lda, ldc);
+    else if (dtype_in == SS_BF16 && dtype_out == SS_BF16)
+        gemm_simt_kernel<bf16, bf16, bf16><<<grid, 256, 0, stream>>>((const bf16*)A, (const bf16*)W, bias, bias_f32, (bf16*)C, M, N, K, lda, ldc);
+    else
+        return (int)cudaErrorInvalidValue;
+    return SS_LAUNCH_CHECK();
+}

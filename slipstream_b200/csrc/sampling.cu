@@ -1,0 +1,286 @@
+// Token selection on the device from float32 logits: arg-max, and the reference's
+// sampling chain (slipstream/engine/sampler.py:36-146): repetition penalty, then
+// temperature, top-k, top-p, min-p, then a draw from the softmax of what is left.
+//
+// One block per row; every row carries its own parameters, so greedy and sampled
+// requests share a launch.  Differences from the reference, by design:
+//  * the draw is a Gumbel-max race (token = argmax(x_i + g_i), g_i = -log(-log u_i))
+//    over counter-based Philox4x32-10 uniforms keyed by (seed, draw index, token),
+//    which has the distribution of multinomial(softmax(x)) but needs no sort, no
+//    prefix sum and no host state; the same (seed, draw index) gives the same
+//    token whatever else is in the batch;
+//  * top-k and top-p find their threshold by radix selection on the value bits
+//    (top-p on fixed-point sums, so the result does not depend on the order of
+//    atomics); tokens that tie with the threshold value are all kept;
+//  * rows with temperature 0 take the arg-max of the raw logits (filters skipped,
+//    as sampler.py:55-56); the lowest index wins ties.
+#include "common.cuh"
+
+#define SAMPLE_THREADS 1024
+
+struct ArgMax {
+    float v;
+    int i;
+};
+
+__device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
+    // larger value wins; on equal values the lower index wins; NaN never wins
+    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+    return a;
+}
+
+__device__ __forceinline__ ArgMax block_argmax(ArgMax a, ArgMax* scratch /* >= 33 */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgMax b;
+        b.v = __shfl_xor_sync(0xffffffffu, a.v, o);
+        b.i = __shfl_xor_sync(0xffffffffu, a.i, o);
+        a = better(a, b);
+    }
+    __syncthreads();
+    if (lane == 0) scratch[warp] = a;
+    __syncthreads();
+    if (warp == 0) {
+        ArgMax t = lane < nwarps ? scratch[lane] : ArgMax{-INFINITY, 0x7fffffff};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ArgMax b;
+            b.v = __shfl_xor_sync(0xffffffffu, t.v, o);
+            b.i = __shfl_xor_sync(0xffffffffu, t.i, o);
+            t = better(t, b);
+        }
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int vocab, int64_t stride) {
+    __shared__ ArgMax scratch[33];
+    const float* row = logits + (int64_t)blockIdx.x * stride;
+    ArgMax a{-INFINITY, 0x7fffffff};
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) a = better(a, ArgMax{row[i], i});
+    a = block_argmax(a, scratch);
+    if (threadIdx.x == 0) out[blockIdx.x] = a.i == 0x7fffffff ? 0 : a.i;
+}
+
+extern "C" int ss_argmax(const float* logits, int32_t* out, int rows, int vocab, int64_t stride,
+                         cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    argmax_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, out, vocab, stride);
+    return SS_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- Philox4x32-10
+
+__device__ __forceinline__ void philox4x32_10(uint32_t k0, uint32_t k1, uint32_t c[4]) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+        const uint32_t n0 = hi1 ^ c[1] ^ k0, n2 = hi0 ^ c[3] ^ k1;
+        c[0] = n0; c[1] = lo1; c[2] = n2; c[3] = lo0;
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+}
+
+// Gumbel noise of token i for draw number `draw` of the stream `seed`.
+__device__ __forceinline__ float gumbel(uint64_t seed, uint64_t draw, int i) {
+    uint32_t c[4] = {(uint32_t)(i >> 2), (uint32_t)draw, (uint32_t)(draw >> 32), 0x51195u};
+    philox4x32_10((uint32_t)seed, (uint32_t)(seed >> 32), c);
+    const uint32_t x = c[i & 3];
+    const float u = ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f);  // in (0, 1), exact
+    return -logf(-logf(u));
+}
+
+__device__ __forceinline__ uint32_t order_key(float v) {
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);  // monotone: larger float, larger key
+}
+
+struct SampleShared {
+    ArgMax arg[33];
+    float red[33];
+    unsigned long long hist[256];
+    uint32_t pick_digit;
+    unsigned long long pick_above;
+};
+
+// value of token i after penalty and temperature
+__device__ __forceinline__ float tempered(const float* row, int i, const uint32_t* seen, float penalty,
+                                          float inv_t_unused, float temperature) {
+    float x = row[i];
+    if (seen && ((seen[i >> 5] >> (i & 31)) & 1u)) x = x < 0.f ? x * penalty : x / penalty;
+    return x / temperature;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, int64_t stride, int32_t* __restrict__ out,
+              const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
+              const float* __restrict__ top_p, const float* __restrict__ min_p,
+              const float* __restrict__ penalty, const int64_t* __restrict__ seeds,
+              const int64_t* __restrict__ draws, uint32_t* __restrict__ seen_all,
+              int seen_words, const int32_t* __restrict__ slots, int vocab) {
+    __shared__ SampleShared sh;
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const float* row = logits + (int64_t)r * stride;
+    const float temp = temperature[r];
+    uint32_t* seen_row = (seen_all && slots && slots[r] >= 0) ? seen_all + (int64_t)slots[r] * seen_words : nullptr;
+
+    if (temp == 0.f || top_k[r] == 1) {  // greedy: raw logits, no filters
+        ArgMax a{-INFINITY, 0x7fffffff};
+        for (int i = tid; i < vocab; i += blockDim.x) a = better(a, ArgMax{row[i], i});
+        a = block_argmax(a, sh.arg);
+        if (tid == 0) {
+            const int tok = a.i == 0x7fffffff ? 0 : a.i;
+            out[r] = tok;
+            if (seen_row) atomicOr(&seen_row[tok >> 5], 1u << (tok & 31));
+        }
+        return;
+    }
+
+    const float pen = penalty[r];
+    const uint32_t* seen = (seen_row && pen != 1.0f) ? seen_row : nullptr;
+    const int k = top_k[r];
+    const float tp = top_p[r], mp = min_p[r];
+    uint32_t floor_key = 0;  // tokens with order_key(value) < floor_key are removed
+
+    // ---- top-k: key of the k-th largest value
+    if (k > 0 && k < vocab) {
+        uint32_t prefix = 0, mask = 0;
+        unsigned long long want = (unsigned long long)k;  // rank still to find inside the prefix
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            for (int b = tid; b < 256; b += blockDim.x) sh.hist[b] = 0ull;
+            __syncthreads();
+            for (int i = tid; i < vocab; i += blockDim.x) {
+                const uint32_t key = order_key(tempered(row, i, seen, pen, 0.f, temp));
+                if ((key & mask) == prefix) atomicAdd(&sh.hist[(key >> shift) & 255u], 1ull);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned long long above = 0;
+                int d = 255;
+                for (; d > 0; --d) {
+                    if (above + sh.hist[d] >= want) break;
+                    above += sh.hist[d];
+                }
+                sh.pick_digit = (uint32_t)d;
+                sh.pick_above = above;
+            }
+            __syncthreads();
+            prefix |= sh.pick_digit << shift;
+            mask |= 255u << shift;
+            want -= sh.pick_above;
+            __syncthreads();
+        }
+        floor_key = prefix;
+    }
+
+    // ---- maximum of what is left (needed by top-p and min-p)
+    float vmax = -INFINITY;
+    if (tp < 1.0f || mp > 0.0f) {
+        ArgMax a{-INFINITY, 0x7fffffff};
+        for (int i = tid; i < vocab; i += blockDim.x) {
+            const float v = tempered(row, i, seen, pen, 0.f, temp);
+            if (order_key(v) >= floor_key) a = better(a, ArgMax{v, i});
+        }
+        vmax = block_argmax(a, sh.arg).v;
+    }
+
+    // ---- top-p: keep a token iff the mass of strictly larger values is below top_p
+    if (tp < 1.0f) {
+        const float FIX = 1099511627776.0f;  // 2^40: exp() in (0,1] as fixed point
+        // total mass
+        for (int b = tid; b < 256; b += blockDim.x) sh.hist[b] = 0ull;
+        __syncthreads();
+        unsigned long long local = 0;
+        for (int i = tid; i < vocab; i += blockDim.x) {
+            const float v = tempered(row, i, seen, pen, 0.f, temp);
+            if (order_key(v) >= floor_key) local += (unsigned long long)(expf(v - vmax) * FIX);
+        }
+        atomicAdd(&sh.hist[0], local);
+        __syncthreads();
+        const unsigned long long total = sh.hist[0];
+        const unsigned long long limit = (unsigned long long)((double)tp * (double)total);
+        __syncthreads();
+        uint32_t prefix = 0, mask = 0;
+        unsigned long long above = 0;  // mass of values whose key exceeds every key under the prefix
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            for (int b = tid; b < 256; b += blockDim.x) sh.hist[b] = 0ull;
+            __syncthreads();
+            for (int i = tid; i < vocab; i += blockDim.x) {
+                const float v = tempered(row, i, seen, pen, 0.f, temp);
+                const uint32_t key = order_key(v);
+                if (key >= floor_key && (key & mask) == prefix)
+                    atomicAdd(&sh.hist[(key >> shift) & 255u], (unsigned long long)(expf(v - vmax) * FIX));
+            }
+            __syncthreads();
+            if (tid == 0) {
+                // lowest digit whose bin still starts below the limit
+                unsigned long long acc = above;
+                int d = 255;
+                for (; d > 0; --d) {
+                    const unsigned long long next = acc + sh.hist[d];
+                    if (next >= limit) break;
+                    acc = next;
+                }
+                sh.pick_digit = (uint32_t)d;
+                sh.pick_above = acc;
+            }
+            __syncthreads();
+            prefix |= sh.pick_digit << shift;
+            mask |= 255u << shift;
+            above = sh.pick_above;
+            __syncthreads();
+        }
+        if (prefix > floor_key) floor_key = prefix;
+    }
+
+    // ---- min-p: p_i / p_max = exp(x_i - x_max) >= min_p
+    float floor_val = -INFINITY;
+    if (mp > 0.0f) floor_val = vmax + logf(mp);
+
+    // ---- Gumbel-max draw over what is left
+    const uint64_t seed = (uint64_t)seeds[r], draw = (uint64_t)draws[r];
+    ArgMax a{-INFINITY, 0x7fffffff};
+    for (int i = tid; i < vocab; i += blockDim.x) {
+        const float v = tempered(row, i, seen, pen, 0.f, temp);
+        if (order_key(v) >= floor_key && v >= floor_val) a = better(a, ArgMax{v + gumbel(seed, draw, i), i});
+    }
+    a = block_argmax(a, sh.arg);
+    if (tid == 0) {
+        const int tok = a.i == 0x7fffffff ? 0 : a.i;
+        out[r] = tok;
+        if (seen_row) atomicOr(&seen_row[tok >> 5], 1u << (tok & 31));
+    }
+}
+
+extern "C" int ss_sample(const float* logits, int64_t stride, int32_t* out, const float* temperature,
+                         const int32_t* top_k, const float* top_p, const float* min_p,
+                         const float* penalty, const int64_t* seeds, const int64_t* draws,
+                         uint32_t* seen, int seen_words, const int32_t* slots, int rows, int vocab,
+                         cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, stride, out, temperature, top_k, top_p,
+                                                       min_p, penalty, seeds, draws, seen, seen_words,
+                                                       slots, vocab);
+    return SS_LAUNCH_CHECK();
+}
+
+// Set the history bits of `n` token ids in one request's row of the seen-token table.
+__global__ void mark_seen_kernel(uint32_t* __restrict__ seen_row, const int32_t* __restrict__ ids, int n,
+                                 int vocab) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int t = ids[i];
+        if (t >= 0 && t < vocab) atomicOr(&seen_row[t >> 5], 1u << (t & 31));
+    }
+}
+
+extern "C" int ss_mark_seen(uint32_t* seen_row, const int32_t* ids, int n, int vocab, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    mark_seen_kernel<<<(n + 255) / 256 > 64 ? 64 : (n + 255) / 256, 256, 0, stream>>>(seen_row, ids, n, vocab);
+    return SS_LAUNCH_CHECK();
+}

@@ -1,0 +1,162 @@
+"""What one step hands to the model: a token-major ragged batch and its metadata.
+
+``StepEntry`` is (request, its next tokens, the places among them whose logits
+are wanted).  ``build_context`` reserves pages for every entry, lays all step
+metadata out in one host buffer (token ids, positions, row ranges, lengths, and
+per cache group the block tables and slot mapping) and moves it to the device
+with one copy.  The reference rebuilds five small device tensors per forward
+from Python lists instead (slipstream/memory/paged_cache.py:71-109) and needs the
+same number of new tokens for every row of a forward.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from slipstream_b200.cache import CacheManager
+
+ATTN_TILE_ROWS = 16  # query tokens per tile of the SIMT attention kernel
+
+
+@dataclass
+class StepEntry:
+    request_id: object
+    tokens: list[int]
+    want: list[int] = field(default_factory=list)
+
+
+@dataclass
+class GroupMeta:
+    block_tables: torch.Tensor  # int32 [R, max_blocks] on the device, -1 where no page
+    slot_mapping: torch.Tensor  # int32 [N]: page * page_size + offset of each new token
+    page_size: int
+    max_blocks: int
+
+
+@dataclass
+class StepContext:
+    num_tokens: int
+    num_requests: int
+    token_ids: torch.Tensor  # int32 [N]
+    positions: torch.Tensor  # int32 [N]
+    q_start: torch.Tensor  # int32 [R + 1]: rows of request r are q_start[r] .. q_start[r+1]
+    seq_lens: torch.Tensor  # int32 [R]: tokens of the request in the cache after this step
+    state_slots: torch.Tensor  # int32 [R]: row of the state pool
+    first_chunk: torch.Tensor  # int32 [R]: 1 when the request had nothing cached before this step
+    logit_rows: torch.Tensor  # int32 [M]: rows whose logits are wanted
+    groups: list[GroupMeta]
+    q_lens_host: np.ndarray
+    seq_lens_host: np.ndarray
+    request_ids: list[object]
+    device: torch.device
+    num_logits: int = 0
+    _tiles: dict[int, tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
+    extras: dict[str, object] = field(default_factory=dict)
+
+    @property
+    def max_q_len(self) -> int:
+        return int(self.q_lens_host.max()) if self.num_requests else 0
+
+    @property
+    def max_seq_len(self) -> int:
+        return int(self.seq_lens_host.max()) if self.num_requests else 0
+
+    @property
+    def is_decode_only(self) -> bool:
+        return self.num_requests > 0 and self.max_q_len == 1
+
+    def query_tiles(self, rows: int = ATTN_TILE_ROWS) -> tuple[torch.Tensor, torch.Tensor]:
+        """(request index, first row within the request) of every tile of ``rows``
+        consecutive query tokens, as int32 device tensors."""
+        cached = self._tiles.get(rows)
+        if cached is None:
+            req, q0 = query_tiles_host(self.q_lens_host, rows)
+            both = torch.from_numpy(np.concatenate([req, q0])).to(self.device, non_blocking=True)
+            cached = (both[: req.size], both[req.size:])
+            self._tiles[rows] = cached
+        return cached
+
+
+def query_tiles_host(q_lens: np.ndarray, rows: int) -> tuple[np.ndarray, np.ndarray]:
+    counts = (q_lens + rows - 1) // rows
+    req = np.repeat(np.arange(q_lens.size, dtype=np.int32), counts)
+    first = np.cumsum(counts) - counts
+    q0 = (np.arange(int(counts.sum()), dtype=np.int32) - np.repeat(first, counts).astype(np.int32)) * rows
+    return req.astype(np.int32), q0.astype(np.int32)
+
+
+class StepInputError(ValueError):
+    """A step was asked for something it cannot run (checked on the host before any launch)."""
+
+
+def build_context(entries: list[StepEntry], cache: CacheManager, vocab_size: int, device: torch.device,
+                  reserve: bool = True) -> StepContext:
+    if not entries:
+        raise StepInputError("a step needs at least one entry")
+    seen: set[object] = set()
+    for e in entries:
+        if e.request_id in seen:
+            raise StepInputError(f"request {e.request_id!r} appears twice in one step")
+        seen.add(e.request_id)
+        if len(e.tokens) < 1:
+            raise StepInputError(f"request {e.request_id!r} brings no tokens")
+        for w in e.want:
+            if not 0 <= w < len(e.tokens):
+                raise StepInputError(f"request {e.request_id!r}: wanted place {w} is outside its "
+                                     f"{len(e.tokens)} tokens")
+    R = len(entries)
+    q_lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=R)
+    N = int(q_lens.sum())
+    token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+    if token_ids.min() < 0 or token_ids.max() >= vocab_size:
+        raise StepInputError(f"a token id is outside [0, {vocab_size})")
+    if reserve:
+        for e in entries:
+            cache.reserve(e.request_id, len(e.tokens))
+    reqs = [cache.get(e.request_id) for e in entries]
+    before = np.fromiter((r.length for r in reqs), dtype=np.int32, count=R)
+    seq_lens = before + q_lens
+    q_start = np.zeros(R + 1, dtype=np.int32)
+    np.cumsum(q_lens, out=q_start[1:])
+    row_req = np.repeat(np.arange(R, dtype=np.int32), q_lens)
+    positions = (np.arange(N, dtype=np.int32) - q_start[:-1][row_req] + before[row_req]).astype(np.int32)
+    logit_rows = np.fromiter((q_start[i] + w for i, e in enumerate(entries) for w in e.want), dtype=np.int32)
+    slots = np.fromiter((r.slot for r in reqs), dtype=np.int32, count=R)
+    first = (before == 0).astype(np.int32)
+
+    ps = cache.page_size
+    n_groups = len(cache.groups)
+    max_blocks = max(1, int((int(seq_lens.max()) + ps - 1) // ps))
+    tables = np.full((n_groups, R, max_blocks), -1, dtype=np.int32)
+    slot_maps = np.empty((n_groups, N), dtype=np.int32)
+    for g in range(n_groups):
+        for i, r in enumerate(reqs):
+            t = r.tables[g]
+            tables[g, i, : len(t)] = t
+        pages = tables[g][row_req, positions // ps]
+        if (pages < 0).any():
+            raise StepInputError("a new token falls on a block without a page")
+        slot_maps[g] = pages * ps + positions % ps
+
+    parts = [token_ids.astype(np.int32), positions, q_start, seq_lens.astype(np.int32), slots, first,
+             logit_rows, tables.reshape(-1), slot_maps.reshape(-1)]
+    sizes = [p.size for p in parts]
+    host = torch.empty(int(sum(sizes)), dtype=torch.int32, pin_memory=torch.cuda.is_available())
+    np.concatenate(parts, out=host.numpy())
+    dev = host.to(device, non_blocking=True)
+    offs = np.concatenate([[0], np.cumsum(sizes)])
+    cut = [dev[offs[i]: offs[i + 1]] for i in range(len(parts))]
+    groups = []
+    for g in range(n_groups):
+        groups.append(GroupMeta(
+            block_tables=cut[7][g * R * max_blocks: (g + 1) * R * max_blocks].view(R, max_blocks),
+            slot_mapping=cut[8][g * N: (g + 1) * N], page_size=ps, max_blocks=max_blocks))
+    ctx = StepContext(num_tokens=N, num_requests=R, token_ids=cut[0], positions=cut[1], q_start=cut[2],
+                      seq_lens=cut[3], state_slots=cut[4], first_chunk=cut[5], logit_rows=cut[6],
+                      groups=groups, q_lens_host=q_lens, seq_lens_host=seq_lens.astype(np.int32),
+                      request_ids=[e.request_id for e in entries], device=device, num_logits=logit_rows.size)
+    ctx.extras["host_buffer"] = host  # keep the pinned buffer alive until the copy has run
+    return ctx

@@ -1,0 +1,117 @@
+"""The model runner: a loaded model, its cache, and the one step function.
+
+``ModelRunner.step(entries)`` takes a batch of (request, its next tokens, wanted
+places): portions of prompts beside single decoded tokens, cut anywhere.  It runs
+only those tokens, as one ragged batch, against the pages earlier steps left,
+and returns float32 logits at the wanted places.  The reference runs decodes as
+one dense ``[B, 1]`` forward and every prompt portion as its own ``[1, take]``
+forward (slipstream/engine/llm_engine.py:476-484,508-567) and returns logits for
+every position (slipstream/models/causal_lm.py:140).
+
+Generation (``LLMEngine``) and trace replay (``bin/trace_run``) both drive this
+class; neither has a forward pass, cache or loader of its own.
+"""
+
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from slipstream_b200 import ops
+from slipstream_b200.cache import CacheManager, PagedStore
+from slipstream_b200.parts.base import Runtime
+from slipstream_b200.registry import load_config
+from slipstream_b200.weights.loader import load_weights
+from slipstream_b200.weights.random_init import random_weights_on_device
+
+from .context import StepContext, StepEntry, StepInputError, build_context
+
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class ModelRunner:
+    def __init__(self, model_dir: str | Path, *, dtype: str | None = None, page_size: int = 16,
+                 num_pages: int | None = None, gpu_memory_utilization: float = 0.9, max_num_seqs: int = 256,
+                 max_model_len: int | None = None, load_format: str = "safetensors", seed: int = 0,
+                 device: str | torch.device = "cuda:0") -> None:
+        ops.require_cuda()
+        self.device = torch.device(device)
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        self.architecture, self.config = load_config(model_dir)
+        dtype_name = dtype or self.config.torch_dtype
+        if dtype_name not in _DTYPES:
+            raise ValueError(f"unsupported dtype: {dtype_name} (bfloat16 or float32)")
+        self.dtype_name = dtype_name
+        self.runtime = Runtime(self.device, _DTYPES[dtype_name])
+        self.max_model_len = max_model_len or self.config.max_position_embeddings
+        self.page_size = page_size
+        self.max_num_seqs = max_num_seqs
+
+        self.model = self.architecture.build(self.config)
+        specs = self.model.weight_specs()
+        if load_format == "random":
+            weights = random_weights_on_device(specs, self.runtime, seed)
+        else:
+            weights = load_weights(model_dir, specs, self.runtime)
+        self.model.bind(weights, self.runtime)
+        del weights
+
+        layouts = self.model.group_layouts
+        if num_pages is None:
+            torch.cuda.synchronize(self.device)
+            torch.cuda.empty_cache()
+            free, _total = torch.cuda.mem_get_info(self.device)
+            per_page = max(1, PagedStore.bytes_per_page(layouts, page_size, self.runtime.dtype))
+            # leave room for activations of the largest step beside the pages
+            num_pages = max(1, int(free * gpu_memory_utilization * 0.9) // per_page)
+            cap = max_num_seqs * ((self.max_model_len + page_size - 1) // page_size)
+            num_pages = min(num_pages, cap)
+        self.num_pages = num_pages
+        self.cache = CacheManager(layouts, num_pages, page_size, max_num_seqs, self.max_model_len)
+        self.store = PagedStore(layouts, num_pages, page_size, self.runtime.dtype, self.device,
+                                self.model.entry_state, max_num_seqs)
+        self.model.attach_store(self.store)
+        self.has_state = any(self.model.entry_state)
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ requests
+    def admit(self, request_id: object) -> None:
+        """Give a new request its state slot (zeroed) and empty block tables."""
+        req = self.cache.admit(request_id)
+        if self.has_state:
+            self.store.zero_state(req.slot)
+
+    def release(self, request_id: object) -> None:
+        self.cache.release(request_id)
+
+    # ------------------------------------------------------------------ the step function
+    @torch.inference_mode()
+    def step(self, entries: list[StepEntry]) -> torch.Tensor:
+        for e in entries:
+            if e.request_id not in self.cache:
+                self.admit(e.request_id)
+        ctx = build_context(entries, self.cache, self.config.vocab_size, self.device)
+        logits = self.run(ctx)
+        for e in entries:
+            self.cache.commit(e.request_id, len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    def run(self, ctx: StepContext) -> torch.Tensor:
+        return self.model.forward(ctx)
+
+    def check(self) -> None:
+        """Raise if a kernel flagged an out-of-range id, slot or page (synchronises)."""
+        ops.check_errors(self.device)
+
+    # ------------------------------------------------------------------ accounting
+    def weight_bytes_per_step(self) -> int:
+        return self.model.weight_bytes_per_step()
+
+    def kv_bytes_per_token(self) -> int:
+        return self.store.kv_bytes_per_token()
+
+
+__all__ = ["ModelRunner", "StepEntry", "StepInputError"]

@@ -1,0 +1,305 @@
+"""Python entry points of the CUDA kernels.
+
+Each function takes torch tensors that live on the CUDA device, checks what the
+kernel cannot check cheaply (dtype, contiguity, sizes), and launches on torch's
+current stream.  Nothing here computes on the CPU or falls back to a library
+implementation; a failed launch raises ``KernelError``.
+
+Kernels record out-of-range token ids, cache slots and block-table entries in a
+device error word instead of trapping; ``check_errors`` reads it (one
+synchronising copy) and raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_void_p
+
+import torch
+
+from .library import KernelBuildError, load_library, require_cuda
+
+SS_F32, SS_BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return SS_F32
+    if dtype == torch.bfloat16:
+        return SS_BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, not {dtype}")
+
+
+_OPS_SIGNATURES = {
+    "ss_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "ss_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                       c_float, c_int, c_void_p],
+    "ss_rope_cache": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                      c_int, c_int, c_int64, c_int, c_int, c_void_p, c_void_p],
+    "ss_swiglu": [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p],
+    "ss_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64,
+                     c_int64, c_int, c_int, c_void_p],
+    "ss_argmax": [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p],
+    "ss_sample": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+    "ss_mark_seen": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+}
+
+_ATTN_SIGNATURES = {
+    "ss_attn_simt": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
+                     c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float,
+                     c_int, c_int, c_void_p, c_void_p],
+}
+
+_state: dict[str, object] = {}
+
+
+def _declare(lib: ctypes.CDLL, table: dict[str, list]) -> None:
+    for name, argtypes in table.items():
+        fn = getattr(lib, name, None)
+        if fn is None:
+            continue
+        fn.argtypes = argtypes
+        fn.restype = c_int
+
+
+def ops_library() -> ctypes.CDLL:
+    lib = _state.get("ops")
+    if lib is None:
+        require_cuda()
+        lib = load_library("slipstream_ops", ["ops.cu", "sampling.cu"])
+        _declare(lib, _OPS_SIGNATURES)
+        _state["ops"] = lib
+    return lib  # type: ignore[return-value]
+
+
+def attention_library(head_dim: int) -> ctypes.CDLL:
+    key = f"attn{head_dim}"
+    lib = _state.get(key)
+    if lib is None:
+        require_cuda()
+        if head_dim % 16 != 0 or not (16 <= head_dim <= 256):
+            raise KernelError(
+                f"attention kernels take head sizes that are multiples of 16 up to 256, not {head_dim}")
+        lib = load_library("slipstream_attn", ["attention.cu"], {"HEAD_DIM": head_dim})
+        _declare(lib, _ATTN_SIGNATURES)
+        _state[key] = lib
+    return lib  # type: ignore[return-value]
+
+
+def error_word(device: torch.device) -> torch.Tensor:
+    key = f"err{device}"
+    word = _state.get(key)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=device)
+        _state[key] = word
+    return word  # type: ignore[return-value]
+
+
+_ERR_NAMES = {1: "a token id outside the vocabulary", 2: "a cache slot outside the pool",
+              4: "a block-table entry outside the pool", 8: "a bounded wait gave up"}
+
+
+def check_errors(device: torch.device) -> None:
+    word = error_word(device)
+    value = int(word.item())
+    if value:
+        word.zero_()
+        what = "; ".join(text for bit, text in _ERR_NAMES.items() if value & bit)
+        raise KernelError(f"a kernel reported: {what}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, dtype: torch.dtype | None, what: str) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{what} must be a CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{what} must be contiguous")
+
+
+# --------------------------------------------------------------------------- model ops
+
+def embedding(token_ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Rows of ``table`` [vocab, hidden] at ``token_ids`` (int32 [N]) as float32 [N, hidden]."""
+    _need(token_ids, torch.int32, "token_ids")
+    _need(table, None, "embedding table")
+    n, (vocab, hidden) = token_ids.numel(), table.shape
+    if out is None:
+        out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    _need(out, torch.float32, "embedding output")
+    _check(ops_library().ss_embedding(token_ids.data_ptr(), table.data_ptr(), out.data_ptr(), n, hidden,
+                                      vocab, _code(table.dtype), error_word(table.device).data_ptr(),
+                                      _stream()), "embedding")
+    return out
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: torch.Tensor | None = None,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """``residual`` (float32 [N, H]) += ``delta`` in place, then RMSNorm times ``weight``.
+
+    With ``rows`` (int32 [M]) only those rows are produced and ``residual`` is not changed.
+    ``weight`` is in ``out_dtype`` or float32."""
+    _need(residual, torch.float32, "residual")
+    hidden = residual.shape[-1]
+    n_out = residual.shape[0] if rows is None else rows.numel()
+    if delta is not None:
+        _need(delta, out_dtype, "delta")
+        if delta.shape != residual.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} does not match residual {tuple(residual.shape)}")
+    _need(weight, None, "norm weight")
+    if weight.numel() != hidden or weight.dtype not in (out_dtype, torch.float32):
+        raise KernelError("norm weight has the wrong size or dtype")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    if out is None:
+        out = torch.empty((n_out, hidden), dtype=out_dtype, device=residual.device)
+    _need(out, out_dtype, "norm output")
+    w_f32 = int(weight.dtype == torch.float32 and out_dtype != torch.float32)
+    _check(ops_library().ss_add_rmsnorm(residual.data_ptr(), _ptr(delta), weight.data_ptr(), w_f32,
+                                        out.data_ptr(), _ptr(rows), n_out, hidden, float(eps),
+                                        _code(out_dtype), _stream()), "add_rmsnorm")
+    return out
+
+
+def rope_and_cache(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor | None,
+                   inv_freq: torch.Tensor | None, kv: torch.Tensor | None, n_q: int, n_kv: int,
+                   head_dim: int, rotary_dim: int, write_cache: bool = True) -> None:
+    """Rotate queries (in place) and keys of ``qkv`` [N, (n_q + 2 n_kv) * D] by their positions and
+    write keys and values to their pages: ``kv`` is [pages, 2, n_kv, page_size, D], ``slots`` int32 [N]
+    = page * page_size + offset (-1 skips a token).  ``rotary_dim`` 0 copies without rotating."""
+    _need(qkv, None, "qkv")
+    _need(positions, torch.int32, "positions")
+    n = qkv.shape[0]
+    if qkv.shape[1] != (n_q + 2 * n_kv) * head_dim:
+        raise KernelError("qkv has the wrong width")
+    if rotary_dim % 2 or rotary_dim > head_dim:
+        raise KernelError("rotary_dim must be even and at most head_dim")
+    if rotary_dim:
+        _need(inv_freq, torch.float32, "inv_freq")
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("inv_freq must hold rotary_dim / 2 values")
+    write = bool(write_cache and kv is not None and slots is not None)
+    pages = page_size = 0
+    if write:
+        _need(kv, qkv.dtype, "kv pages")
+        _need(slots, torch.int32, "slots")
+        if kv.dim() != 5 or kv.shape[1] != 2 or kv.shape[2] != n_kv or kv.shape[4] != head_dim:
+            raise KernelError(f"kv pages have shape {tuple(kv.shape)}, expected [pages, 2, {n_kv}, page, {head_dim}]")
+        pages, page_size = kv.shape[0], kv.shape[3]
+    _check(ops_library().ss_rope_cache(qkv.data_ptr(), positions.data_ptr(), _ptr(slots) if write else None,
+                                       _ptr(inv_freq), _ptr(kv) if write else None, n, n_q, n_kv, head_dim,
+                                       rotary_dim, max(page_size, 1), pages, int(write), _code(qkv.dtype),
+                                       error_word(qkv.device).data_ptr(), _stream()), "rope_and_cache")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gate_up`` = [N, 2 * I] holding [gate | up]."""
+    _need(gate_up, None, "gate_up")
+    n, two_i = gate_up.shape
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
+    _need(out, gate_up.dtype, "swiglu output")
+    _check(ops_library().ss_swiglu(gate_up.data_ptr(), out.data_ptr(), n, inter, _code(gate_up.dtype),
+                                   _stream()), "swiglu")
+    return out
+
+
+def gemm_simt(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+              out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ weight.T + bias`` on CUDA cores with float32 accumulation (no tensor cores):
+    x [M, K], weight [N, K].  The float32 path of every projection."""
+    _need(x, None, "x")
+    _need(weight, x.dtype, "weight")
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k:
+        raise KernelError(f"weight {tuple(weight.shape)} does not match x {tuple(x.shape)}")
+    out_dtype = out_dtype or x.dtype
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    _need(out, out_dtype, "gemm output")
+    bias_f32 = 0
+    if bias is not None:
+        _need(bias, None, "bias")
+        bias_f32 = int(bias.dtype == torch.float32)
+        if bias.numel() != n or (not bias_f32 and bias.dtype != x.dtype):
+            raise KernelError("bias has the wrong size or dtype")
+    _check(ops_library().ss_gemm_simt(x.data_ptr(), weight.data_ptr(), _ptr(bias), bias_f32, out.data_ptr(),
+                                      m, n, k, k, n, _code(x.dtype), _code(out_dtype), _stream()), "gemm_simt")
+    return out
+
+
+def paged_attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
+                         block_tables: torch.Tensor, tile_req: torch.Tensor, tile_q0: torch.Tensor,
+                         q_start: torch.Tensor, seq_lens: torch.Tensor, n_q: int, n_kv: int,
+                         head_dim: int, scale: float, window: int = 0) -> None:
+    """Causal grouped-query attention of the step's query rows over the pages.
+
+    ``q`` points at the first query head of row 0; rows are ``q_stride`` elements apart.
+    ``out`` is [N, n_q * D].  ``tile_req`` / ``tile_q0`` list tiles of 16 consecutive query tokens
+    of one request (request index, first token within the request's rows of this step)."""
+    _need(out, q.dtype, "attention output")
+    _need(kv, q.dtype, "kv pages")
+    for name, t in (("block_tables", block_tables), ("tile_req", tile_req), ("tile_q0", tile_q0),
+                    ("q_start", q_start), ("seq_lens", seq_lens)):
+        _need(t, torch.int32, name)
+    lib = attention_library(head_dim)
+    _check(lib.ss_attn_simt(q.data_ptr(), q_stride, out.data_ptr(), out.shape[1], kv.data_ptr(),
+                            block_tables.data_ptr(), block_tables.shape[1], tile_req.data_ptr(),
+                            tile_q0.data_ptr(), tile_req.numel(), q_start.data_ptr(), seq_lens.data_ptr(),
+                            n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), int(window or 0),
+                            _code(q.dtype), error_word(q.device).data_ptr(), _stream()), "paged_attention_simt")
+
+
+def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, block_tables: torch.Tensor,
+                    ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0) -> None:
+    """Attention of the step's rows over the pages, choosing the kernel for the batch.
+
+    ``qkv`` is the stacked projection output [N, (n_q + 2 n_kv) * D] whose first n_q heads are the
+    rotated queries; ``ctx`` gives the rows of each request (``q_start``), the cached lengths after
+    this step (``seq_lens``) and the list of query tiles."""
+    tile_req, tile_q0 = ctx.query_tiles(16)
+    paged_attention_simt(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_q0, ctx.q_start,
+                         ctx.seq_lens, n_q, n_kv, head_dim, scale, window)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+           out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """A projection ``x @ weight.T + bias``.  float32 runs the SIMT kernel (no reduced-precision
+    matrix mode); bfloat16 runs the library matrix product, as the reference's nn.Linear does
+    (slipstream/models/layers/attention.py:132-135)."""
+    if x.dtype == torch.float32:
+        return gemm_simt(x, weight, bias, out_dtype)
+    if out_dtype is None or out_dtype == x.dtype:
+        if bias is not None:
+            return torch.addmm(bias, x, weight.t())
+        return torch.mm(x, weight.t())
+    out = torch.mm(x, weight.t(), out_dtype=out_dtype)
+    if bias is not None:
+        out += bias
+    return out
+
+
+__all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "require_cuda", "linear", "check_errors", "error_word", "ops_library",
+           "attention_library"]

@@ -1,0 +1,83 @@
+"""Grouped-query attention over the paged key/value cache.
+
+Biased q/k/v projections (stacked into one product at load), rotary encoding of
+queries and keys, the write of keys and values to their pages, causal attention
+of the step's rows over each request's pages, and the output projection
+(slipstream/models/layers/attention.py:98-191).  ``window`` None attends over all
+earlier keys; an integer W over the last W.  Every size is a constructor
+parameter; the part does not know which model it is in.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from slipstream_b200 import ops
+
+from .base import MIXERS, CacheSpec, LayerBinding, Mixer, PositionEncoding, Runtime, WeightSpec
+
+
+@MIXERS.register("paged_attention")
+class PagedAttention(Mixer):
+    def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 position_encoding: PositionEncoding, qkv_bias: bool = True, out_bias: bool = False,
+                 window: int | None = None, scale: float | None = None) -> None:
+        if num_heads % num_kv_heads != 0:
+            raise ValueError(f"num_heads ({num_heads}) must be divisible by num_kv_heads ({num_kv_heads})")
+        if head_dim % 16 != 0 or not 16 <= head_dim <= 256:
+            raise ValueError(f"the attention kernels take head sizes that are multiples of 16 up to 256, not {head_dim}")
+        if window is not None and window < 1:
+            raise ValueError("window must be >= 1")
+        self.name = name
+        self.hidden_size = hidden_size
+        self.num_heads = num_heads
+        self.num_kv_heads = num_kv_heads
+        self.head_dim = head_dim
+        self.position_encoding = position_encoding
+        self.qkv_bias = qkv_bias
+        self.out_bias = out_bias
+        self.window = window
+        self.scale = head_dim ** -0.5 if scale is None else float(scale)
+
+    def weight_specs(self) -> list[WeightSpec]:
+        h, d, n = self.hidden_size, self.head_dim, self.name
+        specs = [WeightSpec(f"{n}.q_proj.weight", (self.num_heads * d, h)),
+                 WeightSpec(f"{n}.k_proj.weight", (self.num_kv_heads * d, h)),
+                 WeightSpec(f"{n}.v_proj.weight", (self.num_kv_heads * d, h)),
+                 WeightSpec(f"{n}.o_proj.weight", (h, self.num_heads * d))]
+        if self.qkv_bias:
+            specs += [WeightSpec(f"{n}.q_proj.bias", (self.num_heads * d,), kind="vector"),
+                      WeightSpec(f"{n}.k_proj.bias", (self.num_kv_heads * d,), kind="vector"),
+                      WeightSpec(f"{n}.v_proj.bias", (self.num_kv_heads * d,), kind="vector")]
+        if self.out_bias:
+            specs.append(WeightSpec(f"{n}.o_proj.bias", (h,), kind="vector"))
+        return specs
+
+    def cache_spec(self) -> CacheSpec:
+        return CacheSpec(self.num_kv_heads, self.head_dim, self.window)
+
+    def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
+        super().bind(weights, runtime)
+        n = self.name
+        self.qkv_weight = torch.cat([weights[f"{n}.{p}_proj.weight"] for p in "qkv"], dim=0).contiguous()
+        self.qkv_b = None
+        if self.qkv_bias:
+            self.qkv_b = torch.cat([weights[f"{n}.{p}_proj.bias"] for p in "qkv"]).to(runtime.dtype).contiguous()
+        self.o_weight = weights[f"{n}.o_proj.weight"]
+        self.o_b = weights[f"{n}.o_proj.bias"].to(runtime.dtype) if self.out_bias else None
+        self.position_encoding.bind(weights, runtime)
+        ops.attention_library(self.head_dim)  # compile now, not inside the first step
+
+    def weight_bytes(self) -> int:
+        return (self.qkv_weight.numel() + self.o_weight.numel()) * self.o_weight.element_size()
+
+    def forward(self, x: torch.Tensor, ctx, layer: LayerBinding) -> torch.Tensor:
+        meta = ctx.groups[layer.group]
+        qkv = ops.linear(x, self.qkv_weight, self.qkv_b)
+        inv_freq, rotary_dim = self.position_encoding.rotary_table()
+        ops.rope_and_cache(qkv, ctx.positions, meta.slot_mapping, inv_freq, layer.kv, self.num_heads,
+                           self.num_kv_heads, self.head_dim, rotary_dim, write_cache=layer.writes_cache)
+        out = torch.empty((x.shape[0], self.num_heads * self.head_dim), dtype=x.dtype, device=x.device)
+        ops.paged_attention(qkv, out, layer.kv, meta.block_tables, ctx, self.num_heads, self.num_kv_heads,
+                            self.head_dim, self.scale, self.window or 0)
+        return ops.linear(out, self.o_weight, self.o_b)

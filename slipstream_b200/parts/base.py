@@ -1,0 +1,205 @@
+"""Interfaces of the parts a model is put together from, and their registries.
+
+A part knows its own sizes and constants (constructor parameters), the
+checkpoint tensors it owns (``weight_specs``), what it needs from the cache
+manager (``cache_spec`` for pages of keys and values, ``state_specs`` for
+fixed-size per-request state), and how to run on a token-major batch.  No part
+knows which model it is in: a model builder picks parts layer by layer from the
+configuration and hands them their tensor-name prefixes.
+
+Token-major means activations are ``[num_tokens, width]`` for all tokens of the
+step, whatever request they belong to; ``StepContext`` says which rows belong to
+which request.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import TYPE_CHECKING, Any, Callable
+
+import torch
+
+if TYPE_CHECKING:
+    from slipstream_b200.engine.context import StepContext
+
+
+# --------------------------------------------------------------------------- specs
+
+@dataclass(frozen=True)
+class WeightSpec:
+    """One checkpoint tensor a part reads.
+
+    ``kind`` decides the dtype it is kept in: ``matrix`` tensors go to the compute
+    dtype (bfloat16 or float32); ``vector`` tensors do too unless the checkpoint
+    stores them in 32-bit, which is kept; ``index`` tensors become int32.
+    ``init`` is used by the random-weights mode: ("normal", std) or
+    ("one_plus_normal", std).  ``alias_of`` names the tensor that stands in when
+    this one is absent (tied embeddings).
+    """
+
+    name: str
+    shape: tuple[int, ...]
+    kind: str = "matrix"
+    init: tuple[str, float] = ("normal", 0.02)
+    alias_of: str | None = None
+
+
+@dataclass(frozen=True)
+class CacheSpec:
+    """Pages of keys and values one mixer needs per token.  ``window`` None means
+    every earlier key stays visible; an integer W means only the last W keys are,
+    so pages wholly before the window are given back."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Fixed-size per-request state a part keeps in the slot pool (one row per
+    live request); zeroed when a request is admitted."""
+
+    name: str
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class Runtime:
+    """Device and precision the parts are bound to."""
+
+    device: torch.device
+    dtype: torch.dtype  # torch.bfloat16 or torch.float32
+
+    @property
+    def is_fp32(self) -> bool:
+        return self.dtype == torch.float32
+
+
+# --------------------------------------------------------------------------- parts
+
+class Part:
+    """Base of all parts.  ``bind`` receives the loaded tensors by full name."""
+
+    def weight_specs(self) -> list[WeightSpec]:
+        return []
+
+    def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
+        self.runtime = runtime
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights one step reads from this part (for the roofline)."""
+        return 0
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_norm(self, residual: torch.Tensor, delta: torch.Tensor | None,
+                 rows: torch.Tensor | None = None) -> torch.Tensor:
+        """``residual += delta`` (float32, in place) and return ``norm(residual)``
+        in the compute dtype.  With ``rows`` only those rows are normalised and
+        returned, and ``residual`` is left untouched."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Where positions enter.  ``on_embedding`` may add to the residual stream;
+    ``on_query_key`` rotates (or otherwise marks) queries and keys inside a mixer.
+    Both default to doing nothing."""
+
+    def on_embedding(self, residual: torch.Tensor, ctx: "StepContext") -> None:
+        return None
+
+    def rotary_table(self) -> tuple[torch.Tensor | None, int]:
+        """(inverse frequencies float32 [rotary_dim/2] on the device, rotary_dim),
+        or (None, 0) when queries and keys are not rotated."""
+        return None, 0
+
+
+class Mixer(Part):
+    """Mixes information across the tokens of a request (attention here)."""
+
+    def cache_spec(self) -> CacheSpec | None:
+        return None
+
+    def state_specs(self) -> list[StateSpec]:
+        return []
+
+    def forward(self, x: torch.Tensor, ctx: "StepContext", layer: "LayerBinding") -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: "StepContext") -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """Arrangement of a mixer, a feed-forward and their norms around the float32
+    residual stream.  ``forward`` takes the stream and a branch output that has
+    not been added yet, and returns the same pair, so that the add fuses with the
+    next norm wherever it stands."""
+
+    mixer: Mixer
+
+    def forward(self, residual: torch.Tensor, pending: torch.Tensor | None,
+                ctx: "StepContext", layer: "LayerBinding") -> tuple[torch.Tensor, torch.Tensor | None]:
+        raise NotImplementedError
+
+
+@dataclass
+class LayerBinding:
+    """What one entry of the execution order hands to the mixer: which pages and
+    which state rows are its own.  ``kv`` is this entry's page tensor
+    ``[num_pages, 2, num_kv_heads, page_size, head_dim]`` (or None), ``group`` the
+    index of the cache group whose block tables address it, ``writes_cache``
+    False when the entry only reads pages that another entry wrote."""
+
+    kv: torch.Tensor | None = None
+    group: int = -1
+    writes_cache: bool = True
+    state: dict[str, torch.Tensor] = field(default_factory=dict)
+
+
+# --------------------------------------------------------------------------- registries
+
+class Registry:
+    """Name -> class (or builder) table with a decorator to add entries."""
+
+    def __init__(self, what: str) -> None:
+        self.what = what
+        self._entries: dict[str, Any] = {}
+
+    def register(self, name: str) -> Callable[[Any], Any]:
+        def add(obj: Any) -> Any:
+            if name in self._entries and self._entries[name] is not obj:
+                raise KeyError(f"{self.what} {name!r} is already registered")
+            self._entries[name] = obj
+            return obj
+        return add
+
+    def unregister(self, name: str) -> None:
+        self._entries.pop(name, None)
+
+    def get(self, name: str) -> Any:
+        try:
+            return self._entries[name]
+        except KeyError:
+            known = ", ".join(sorted(self._entries)) or "none"
+            raise KeyError(f"unknown {self.what} {name!r} (registered: {known})") from None
+
+    def names(self) -> list[str]:
+        return sorted(self._entries)
+
+    def __contains__(self, name: str) -> bool:
+        return name in self._entries
+
+
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+BLOCKS = Registry("block arrangement")
