@@ -1,0 +1,275 @@
+"""The Python entry point, in the reference's manner:
+
+    engine = LLMEngine(EngineConfig.for_model(folder))
+    tokens = engine.generate(Request("r0", None, [1, 2, 3], SamplingParams(max_tokens=8), 0.0))
+    outs   = engine.generate_batch([...])         # continuous batching
+    for t in engine.stream(request): ...
+
+(slipstream/engine/llm_engine.py:66-127).  ``generate`` and ``stream`` are
+``generate_batch`` with one request.  Every step is ONE call of the step function
+with whatever the scheduler chose: decoded tokens beside prompt portions.
+``LLM`` is a thin convenience wrapper that returns ``RequestOutput`` records.
+
+Token ids in, token ids out; text prompts need a ``tokenizer.json`` in the model
+folder (slipstream/models/tokenizer.py:11-57), which random-weight folders lack.
+"""
+
+from __future__ import annotations
+
+import time
+from collections.abc import Iterator
+from dataclasses import dataclass, field
+from pathlib import Path
+
+import torch
+
+from slipstream_b200.config.engine_config import CacheConfig, EngineConfig, SchedulerConfig
+from slipstream_b200.config.sampling_params import SamplingParams
+from slipstream_b200.sampling.sampler import SampleRow, Sampler
+
+from .context import StepEntry
+from .runner import ModelRunner
+from .scheduler import ScheduledSeq, Scheduler, Sequence, SequenceStatus
+
+
+@dataclass
+class Request:
+    """slipstream/core/types.py:73-87 without the SLO fields."""
+
+    request_id: str
+    prompt: str | None
+    prompt_token_ids: list[int] | None
+    sampling_params: SamplingParams = field(default_factory=SamplingParams)
+    arrival_ts: float = 0.0
+
+    def __post_init__(self) -> None:
+        if self.prompt is None and self.prompt_token_ids is None:
+            raise ValueError("Request needs prompt or prompt_token_ids")
+
+
+@dataclass
+class RequestOutput:
+    request_id: str
+    prompt_token_ids: list[int]
+    output_token_ids: list[int]
+    finish_reason: str  # stop | length | abort
+    text: str | None = None
+
+
+@dataclass
+class StepStats:
+    """Counters of the last step (slipstream/observability/metrics.py:29-95, reduced)."""
+
+    step: int = 0
+    num_running: int = 0
+    num_waiting: int = 0
+    num_batched_tokens: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    free_pages: int = 0
+    preemptions: int = 0
+    step_time_ms: float = 0.0
+
+
+def capped_new_tokens(prompt_len: int, max_tokens: int, max_model_len: int) -> int:
+    """New tokens that fit under the context window (slipstream/engine/llm_engine.py:56-63)."""
+    if max_tokens < 1:
+        return 0
+    return max(0, min(max_tokens, max_model_len - prompt_len))
+
+
+_FINISH = {SequenceStatus.FINISHED_STOPPED: "stop", SequenceStatus.FINISHED_LENGTH: "length",
+           SequenceStatus.FINISHED_ABORTED: "abort"}
+
+
+class LLMEngine:
+    def __init__(self, config: EngineConfig) -> None:
+        self.config = config
+        m, c, s = config.model, config.cache, config.scheduler
+        self.runner = ModelRunner(
+            m.model_id, dtype=m.dtype, page_size=c.block_size, num_pages=c.num_gpu_blocks,
+            gpu_memory_utilization=c.gpu_memory_utilization, max_num_seqs=s.max_num_seqs,
+            max_model_len=m.max_model_len, load_format=m.load_format, seed=config.seed,
+            use_cuda_graphs=config.use_cuda_graphs)
+        self.model_config = self.runner.config
+        self.max_model_len = self.runner.max_model_len
+        self.scheduler = Scheduler(s, self.runner.cache)
+        self.sampler = Sampler(self.model_config.vocab_size, self.runner.device, s.max_num_seqs)
+        self.tokenizer = None
+        folder = Path(m.model_id)
+        if (folder / "tokenizer.json").is_file():
+            from tokenizers import Tokenizer
+
+            self.tokenizer = Tokenizer.from_file(str(folder / "tokenizer.json"))
+        self.stats = StepStats()
+        self._requests_seen = 0
+
+    # ------------------------------------------------------------------ public calls
+    def generate(self, request: Request) -> list[int]:
+        """Blocking generation of one request; returns the output token ids only."""
+        return self.generate_batch([request])[0]
+
+    def stream(self, request: Request) -> Iterator[int]:
+        """Token iterator with the same tokens as ``generate``."""
+        seq = self._make_sequence(request)
+        self.scheduler.add_seq(seq)
+        emitted = 0
+        while self.scheduler.has_work():
+            if not self._step():
+                break
+            while emitted < seq.num_output_tokens:
+                yield seq.output_token_ids[emitted]
+                emitted += 1
+
+    def generate_batch(self, requests: list[Request]) -> list[list[int]]:
+        """Continuous batching of several requests (slipstream/engine/llm_engine.py:107-119)."""
+        seqs = [self._make_sequence(r) for r in requests]
+        for seq in seqs:
+            self.scheduler.add_seq(seq)
+        self.run_until_done(seqs)
+        return [list(s.output_token_ids) for s in seqs]
+
+    def run_until_done(self, seqs: list[Sequence]) -> None:
+        # the reference's bound on replay storms (slipstream/engine/llm_engine.py:423-429)
+        limit = 1 + 8 * sum(s.num_prompt_tokens + s.max_new_tokens for s in seqs)
+        steps = 0
+        while self.scheduler.has_work() and steps < limit:
+            steps += 1
+            if not self._step():
+                break
+        for seq in seqs:
+            if not seq.is_finished:
+                seq.status = SequenceStatus.FINISHED_ABORTED
+                self.scheduler.finish(seq)
+
+    def tokenize(self, request: Request) -> list[int]:
+        if request.prompt_token_ids is not None:
+            return [int(t) for t in request.prompt_token_ids]
+        if self.tokenizer is None:
+            raise ValueError("a text prompt needs tokenizer.json in the model folder; pass prompt_token_ids")
+        return list(self.tokenizer.encode(request.prompt, add_special_tokens=False).ids)
+
+    # ------------------------------------------------------------------ internals
+    def _make_sequence(self, request: Request) -> Sequence:
+        ids = self.tokenize(request)
+        if not ids:
+            raise ValueError("empty prompt")
+        if len(ids) >= self.max_model_len:
+            raise ValueError(f"prompt length {len(ids)} exceeds max_model_len {self.max_model_len}")
+        vocab = self.model_config.vocab_size
+        if min(ids) < 0 or max(ids) >= vocab:
+            raise ValueError(f"a prompt token id is outside [0, {vocab})")
+        params = request.sampling_params
+        if params.stop_strings and self.tokenizer is None:
+            raise ValueError("stop_strings need tokenizer.json in the model folder")
+        max_new = capped_new_tokens(len(ids), params.max_tokens, self.max_model_len)
+        self._requests_seen += 1
+        seed = params.seed if params.seed is not None else (self.config.seed * 1000003 + self._requests_seen)
+        return Sequence(seq_id=self.scheduler.next_seq_id(), prompt_token_ids=ids, sampling_params=params,
+                        arrival_ts=request.arrival_ts, request_id=request.request_id, max_new_tokens=max_new,
+                        seed=seed)
+
+    def _is_stop(self, seq: Sequence, token: int) -> bool:
+        """slipstream/engine/llm_engine.py:223-234; the stop token stays in the output."""
+        params = seq.sampling_params
+        if token in params.stop_token_ids:
+            return True
+        eos = self.model_config.eos_token_id
+        if not params.ignore_eos and eos is not None and token == eos:
+            return True
+        if params.stop_strings and self.tokenizer is not None:
+            text = self.tokenizer.decode(seq.output_token_ids)
+            return any(stop and stop in text for stop in params.stop_strings)
+        return False
+
+    def _step(self) -> bool:
+        """Schedule, run one step-function call, sample, finish.  False when nothing can run."""
+        started = time.perf_counter()
+        plan = self.scheduler.schedule()
+        if not plan.scheduled:
+            # nothing fits: whoever is still waiting can never run (slipstream/engine/llm_engine.py:467-474)
+            for stuck in list(self.scheduler.waiting):
+                stuck.status = SequenceStatus.FINISHED_ABORTED
+                self.scheduler.finish(stuck)
+            return False
+        entries: list[StepEntry] = []
+        sampling: list[ScheduledSeq] = []
+        for item in plan.scheduled:
+            seq = item.seq
+            if seq.num_computed_tokens == 0:
+                slot = self.runner.cache.get(seq.seq_id).slot
+                self.runner.reset_state(slot)
+                self.sampler.begin_request(slot, seq.sampling_params,
+                                           seq.prompt_token_ids + seq.output_token_ids)
+            want = [item.take - 1] if item.samples else []
+            entries.append(StepEntry(seq.seq_id, seq.tokens_to_feed(item.take), want))
+            if item.samples:
+                sampling.append(item)
+        decode_tokens = plan.num_decode_tokens
+        logits = self.runner.step(entries)
+        tokens: list[int] = []
+        if sampling:
+            rows = [SampleRow(i.seq.sampling_params, i.seq.seed, i.seq.num_output_tokens,
+                              self.runner.cache.get(i.seq.seq_id).slot) for i in sampling]
+            tokens = self.sampler.sample(logits, rows).tolist()  # the step's one device-to-host copy
+        for item in plan.scheduled:
+            item.seq.num_computed_tokens += item.take
+        for item, token in zip(sampling, tokens):
+            seq = item.seq
+            seq.output_token_ids.append(int(token))
+            if self._is_stop(seq, int(token)):
+                seq.status = SequenceStatus.FINISHED_STOPPED
+            elif seq.num_output_tokens >= seq.max_new_tokens or seq.num_tokens >= self.max_model_len:
+                seq.status = SequenceStatus.FINISHED_LENGTH
+            if seq.is_finished:
+                self.scheduler.finish(seq)
+        st = self.stats
+        st.step += 1
+        st.num_running, st.num_waiting = len(self.scheduler.running), len(self.scheduler.waiting)
+        st.num_batched_tokens = plan.num_batched_tokens
+        st.decode_tokens = decode_tokens
+        st.prefill_tokens = plan.num_batched_tokens - st.decode_tokens
+        st.free_pages = self.runner.cache.min_free_pages()
+        st.preemptions = self.scheduler.preemptions
+        st.step_time_ms = (time.perf_counter() - started) * 1e3
+        return True
+
+
+class LLM:
+    """Convenience wrapper: keyword options instead of an ``EngineConfig``; lists in, records out."""
+
+    def __init__(self, model: str, *, dtype: str | None = None, max_model_len: int | None = None,
+                 block_size: int = 16, num_gpu_blocks: int | None = None, gpu_memory_utilization: float = 0.9,
+                 max_num_seqs: int = 256, max_num_batched_tokens: int = 8192, prefill_chunk_size: int = 256,
+                 enable_chunked_prefill: bool = True, seed: int = 0, load_format: str = "safetensors",
+                 use_cuda_graphs: bool = True) -> None:
+        self.engine = LLMEngine(EngineConfig.for_model(
+            model, dtype=dtype, max_model_len=max_model_len, load_format=load_format,
+            cache=CacheConfig(block_size=block_size, gpu_memory_utilization=gpu_memory_utilization,
+                              num_gpu_blocks=num_gpu_blocks),
+            scheduler=SchedulerConfig(max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
+                                      enable_chunked_prefill=enable_chunked_prefill,
+                                      prefill_chunk_size=prefill_chunk_size),
+            seed=seed, use_cuda_graphs=use_cuda_graphs))
+
+    def generate(self, prompts: list[str] | None = None, sampling_params: SamplingParams | list[SamplingParams] | None = None,
+                 *, prompt_token_ids: list[list[int]] | None = None) -> list[RequestOutput]:
+        n = len(prompt_token_ids) if prompt_token_ids is not None else len(prompts or [])
+        if isinstance(sampling_params, list):
+            params = sampling_params
+        else:
+            params = [sampling_params or SamplingParams()] * n
+        requests = [Request(f"req-{i}", None if prompts is None else prompts[i],
+                            None if prompt_token_ids is None else prompt_token_ids[i], params[i], float(i) * 1e-6)
+                    for i in range(n)]
+        engine = self.engine
+        seqs = [engine._make_sequence(r) for r in requests]
+        for seq in seqs:
+            engine.scheduler.add_seq(seq)
+        engine.run_until_done(seqs)
+        outs = []
+        for seq in seqs:
+            text = engine.tokenizer.decode(seq.output_token_ids) if engine.tokenizer is not None else None
+            outs.append(RequestOutput(seq.request_id, seq.prompt_token_ids, list(seq.output_token_ids),
+                                      _FINISH.get(seq.status, "abort"), text))
+        return outs

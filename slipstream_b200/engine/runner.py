@@ -34,7 +34,7 @@ class ModelRunner:
     def __init__(self, model_dir: str | Path, *, dtype: str | None = None, page_size: int = 16,
                  num_pages: int | None = None, gpu_memory_utilization: float = 0.9, max_num_seqs: int = 256,
                  max_model_len: int | None = None, load_format: str = "safetensors", seed: int = 0,
-                 device: str | torch.device = "cuda:0") -> None:
+                 device: str | torch.device = "cuda:0", use_cuda_graphs: bool = True) -> None:
         ops.require_cuda()
         self.device = torch.device(device)
         if self.device.type == "cuda":
@@ -75,6 +75,7 @@ class ModelRunner:
         self.model.attach_store(self.store)
         self.has_state = any(self.model.entry_state)
         self.steps_run = 0
+        self.use_cuda_graphs = use_cuda_graphs
 
     # ------------------------------------------------------------------ requests
     def admit(self, request_id: object) -> None:
@@ -82,6 +83,11 @@ class ModelRunner:
         req = self.cache.admit(request_id)
         if self.has_state:
             self.store.zero_state(req.slot)
+
+    def reset_state(self, slot: int) -> None:
+        """Zero the fixed-size state rows of a slot (a request starts, or restarts after a preemption)."""
+        if self.has_state:
+            self.store.zero_state(slot)
 
     def release(self, request_id: object) -> None:
         self.cache.release(request_id)

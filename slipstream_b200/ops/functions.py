@@ -283,6 +283,55 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
                          ctx.seq_lens, n_q, n_kv, head_dim, scale, window)
 
 
+# --------------------------------------------------------------------------- sampling
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """Index of the largest value of each row of float32 ``logits`` [M, V]; the lowest index wins ties."""
+    _need(logits, torch.float32, "logits")
+    m, v = logits.shape
+    out = torch.empty(m, dtype=torch.int32, device=logits.device)
+    _check(ops_library().ss_argmax(logits.data_ptr(), out.data_ptr(), m, v, logits.stride(0), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, *, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           min_p: torch.Tensor, penalty: torch.Tensor, seeds: torch.Tensor, draws: torch.Tensor,
+           slots: torch.Tensor | None = None, seen: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row of float32 ``logits`` [M, V] with per-row parameters (device tensors [M]):
+    repetition penalty (needs ``seen`` int32 [slots, ceil(V/32)] and ``slots``), temperature (0 = arg-max),
+    top-k (-1 off), top-p, min-p, then a Gumbel-max draw keyed by (seed, draw index)."""
+    _need(logits, torch.float32, "logits")
+    m, v = logits.shape
+    for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+                        ("top_p", top_p, torch.float32), ("min_p", min_p, torch.float32),
+                        ("penalty", penalty, torch.float32), ("seeds", seeds, torch.int64),
+                        ("draws", draws, torch.int64)):
+        _need(t, dt, name)
+        if t.numel() != m:
+            raise KernelError(f"{name} must hold one value per row")
+    seen_words = 0
+    if seen is not None:
+        _need(seen, torch.int32, "seen")
+        _need(slots, torch.int32, "slots")
+        seen_words = seen.shape[1]
+        if seen_words * 32 < v:
+            raise KernelError("the seen-token mask is narrower than the vocabulary")
+    out = torch.empty(m, dtype=torch.int32, device=logits.device)
+    _check(ops_library().ss_sample(logits.data_ptr(), logits.stride(0), out.data_ptr(), temperature.data_ptr(),
+                                   top_k.data_ptr(), top_p.data_ptr(), min_p.data_ptr(), penalty.data_ptr(),
+                                   seeds.data_ptr(), draws.data_ptr(), _ptr(seen), seen_words,
+                                   _ptr(slots) if seen is not None else None, m, v, _stream()), "sample")
+    return out
+
+
+def mark_seen(seen_row: torch.Tensor, token_ids: torch.Tensor, vocab: int) -> None:
+    """Set the bits of ``token_ids`` (int32) in one request's row of the seen-token mask."""
+    _need(seen_row, torch.int32, "seen row")
+    _need(token_ids, torch.int32, "token_ids")
+    _check(ops_library().ss_mark_seen(seen_row.data_ptr(), token_ids.data_ptr(), token_ids.numel(), vocab,
+                                      _stream()), "mark_seen")
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
            out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """A projection ``x @ weight.T + bias``.  float32 runs the SIMT kernel (no reduced-precision
@@ -301,5 +350,5 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "require_cuda", "linear", "check_errors", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "require_cuda", "argmax", "sample", "mark_seen", "linear", "check_errors", "error_word", "ops_library",
            "attention_library"]

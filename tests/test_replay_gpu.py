@@ -1,0 +1,126 @@
+"""Replays the same requests whole, with the last 32 tokens one by one, in portions of changing
+size, and mixed with other requests under a small pool, in float32 and bfloat16, through the
+framework's runner and through bin/trace_run, and compares every logit row with the plain
+implementation."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+import replay_plans as plans
+from conftest import ROOT, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+# Largest |difference| allowed, as a fraction of the largest |logit| of the oracle.  float32: sums of
+# a few hundred products rounded at 6e-8, through a few layers.  bfloat16: activations are rounded to
+# 8 bits of mantissa (4e-3) after every product and norm.
+TOLERANCE = {"float32": 2e-5, "bfloat16": 3e-2}
+LENGTHS = {"r0": 70, "r1": 45, "r2": 97, "r3": 33, "r4": 64, "r5": 21}
+
+
+def oracle(folder, requests, dtype):
+    config, weights = plain.read_model_folder(folder, torch.float64)
+    if dtype == "bfloat16":  # the engine keeps matrices in bfloat16: give the oracle the same values
+        weights = {k: v.to(torch.bfloat16).to(torch.float64) if v.dim() == 2 else v for k, v in weights.items()}
+    return {rid: plain.forward_logits(config, weights, toks).float().numpy() for rid, toks in requests.items()}
+
+
+def run_plan(runner, steps):
+    from slipstream_b200.engine.runner import StepEntry
+
+    outs = []
+    for step in steps:
+        logits = runner.step([StepEntry(e["id"], e["tokens"], e["want"]) for e in step["entries"]])
+        outs.append(logits.cpu().numpy())
+        for rid in step["end"]:
+            runner.release(rid)
+        runner.cache.check_invariants()
+    runner.check()
+    return outs
+
+
+def compare(rows, want, dtype, what):
+    for rid, ref in want.items():
+        got = np.stack(rows[rid])
+        assert got.shape == ref.shape, (what, rid, got.shape, ref.shape)
+        err = np.abs(got - ref).max(axis=1)
+        bound = TOLERANCE[dtype] * np.abs(ref).max()
+        worst = int(err.argmax())
+        assert err[worst] <= bound, (f"{what}: request {rid}, first wrong token "
+                                     f"{int(np.argmax(err > bound))}, worst token {worst}: {err[worst]:.3e} > {bound:.3e}")
+
+
+@pytest.fixture(scope="module")
+def requests_for():
+    def make(config):
+        return {rid: random_tokens(config.vocab_size, n, 100 + i) for i, (rid, n) in enumerate(LENGTHS.items())}
+    return make
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_every_way_of_cutting_gives_the_plain_logits(model_folders, requests_for, name, dtype):
+    from slipstream_b200.engine.runner import ModelRunner
+
+    folder, config, page = model_folders[name]
+    requests = requests_for(config)
+    want = oracle(folder, requests, dtype)
+    max_tokens = 256  # fewer than the 330 tokens of all requests together: pages are used again
+    runner = ModelRunner(folder, dtype=dtype, page_size=page, num_pages=max_tokens // page, max_num_seqs=4)
+    results = {}
+    for what, steps in (("whole", plans.whole(requests)),
+                        ("tail one by one", plans.tail_one_by_one(requests)),
+                        ("changing portions", plans.changing_portions(requests)),
+                        ("mixed", plans.mixed(requests, max_tokens, page, seed=5)),
+                        ("mixed again", plans.mixed(requests, max_tokens, page, seed=6))):
+        rows = plans.collect(steps, run_plan(runner, steps))
+        compare(rows, want, dtype, f"{name} {dtype} {what}")
+        results[what] = rows
+        assert runner.cache.num_free_pages() == max_tokens // page
+    assert max(len(s["entries"]) for s in plans.mixed(requests, max_tokens, page, seed=5)) >= 3
+    # the cut changes nothing beyond rounding: compare the ways with one another, tighter than with the oracle
+    for what in ("tail one by one", "changing portions", "mixed"):
+        for rid in requests:
+            a, b = np.stack(results["whole"][rid]), np.stack(results[what][rid])
+            assert np.abs(a - b).max() <= 0.5 * TOLERANCE[dtype] * np.abs(a).max(), (what, rid)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(model_folders, requests_for, tmp_path, dtype):
+    folder, config, page = model_folders["B"]
+    requests = {k: v for k, v in requests_for(config).items() if k in ("r0", "r1", "r3", "r5")}
+    want = oracle(folder, requests, dtype)
+    steps = plans.mixed(requests, 192, 16, seed=2) + plans.tail_one_by_one({"r3": requests["r3"]})
+    steps.insert(3, {"entries": [], "end": []})  # a step may be empty
+    steps[0]["entries"][0]["want"] = steps[0]["entries"][0]["want"]  # keep all
+    lines = "".join(json.dumps({"step": i, **s}) + "\n" for i, s in enumerate(steps))
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", folder, "--dtype", dtype,
+                           "--out", str(out), "--max-tokens", "192"], input=lines, capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split("\n")[:-1] == [f"done {i}" for i in range(len(steps))]
+    outputs = []
+    for i, s in enumerate(steps):
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        path = out / f"{i}.f32"
+        if wanted == 0:
+            assert not path.exists()
+            outputs.append(None)
+            continue
+        data = np.fromfile(path, dtype="<f4")
+        assert data.size == wanted * config.vocab_size
+        outputs.append(data.reshape(wanted, config.vocab_size))
+    rows = plans.collect(steps, outputs)
+    # r3 was replayed twice: once mixed, once alone
+    n3 = len(requests["r3"])
+    again = {"r3": rows["r3"][n3:]}
+    rows["r3"] = rows["r3"][:n3]
+    compare(rows, want, dtype, f"trace_run {dtype} mixed")
+    compare(again, {"r3": want["r3"]}, dtype, f"trace_run {dtype} tail")

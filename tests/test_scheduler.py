@@ -1,0 +1,141 @@
+"""The scheduler's decisions, on the host, against a cache manager without a device."""
+import pytest
+
+from slipstream_b200.cache import CacheManager, GroupLayout
+from slipstream_b200.config.engine_config import SchedulerConfig
+from slipstream_b200.config.sampling_params import SamplingParams
+from slipstream_b200.engine.scheduler import Scheduler, Sequence, SequenceStatus
+from slipstream_b200.parts.base import CacheSpec
+
+
+def make(pages=16, page=4, seqs=4, budget=16, chunk=8, max_len=256):
+    cache = CacheManager([GroupLayout(CacheSpec(2, 16, None), 2)], pages, page, seqs, max_len)
+    sched = Scheduler(SchedulerConfig(max_num_seqs=seqs, max_num_batched_tokens=budget, prefill_chunk_size=chunk), cache)
+    return sched, cache
+
+
+def seq(sched, n_prompt, max_new=4, arrival=0.0):
+    s = Sequence(seq_id=sched.next_seq_id(), prompt_token_ids=list(range(n_prompt)),
+                 sampling_params=SamplingParams(max_tokens=max_new), arrival_ts=arrival, max_new_tokens=max_new)
+    sched.add_seq(s)
+    return s
+
+
+def run_step(sched, plan, token=7):
+    """What the engine does after a step: advance, append a token where the portion reached the end."""
+    for item in plan.scheduled:
+        reached_end = item.samples
+        item.seq.num_computed_tokens += item.take
+        sched.cache.commit(item.seq.seq_id, item.take)
+        if reached_end:
+            item.seq.output_token_ids.append(token)
+            if item.seq.num_output_tokens >= item.seq.max_new_tokens:
+                item.seq.status = SequenceStatus.FINISHED_LENGTH
+                sched.finish(item.seq)
+
+
+def test_prompts_are_cut_under_chunk_and_budget_and_decodes_go_first():
+    sched, cache = make(budget=12, chunk=8)
+    a, b = seq(sched, 20, arrival=0.0), seq(sched, 5, arrival=1.0)
+    plan = sched.schedule()
+    assert [(i.seq.seq_id, i.take) for i in plan.scheduled] == [(a.seq_id, 8), (b.seq_id, 4)]
+    assert plan.num_batched_tokens == 12 and not plan.scheduled[0].samples
+    run_step(sched, plan)
+    plan = sched.schedule()  # both still have prompt left; a is first in the running list
+    assert [(i.seq.seq_id, i.take, i.samples) for i in plan.scheduled] == [(a.seq_id, 8, False), (b.seq_id, 1, True)]
+    run_step(sched, plan)
+    plan = sched.schedule()  # b decodes (first), a takes its last 4 prompt tokens
+    assert [(i.seq.seq_id, i.take, i.samples) for i in plan.scheduled] == [(b.seq_id, 1, True), (a.seq_id, 4, True)]
+    assert a.tokens_to_feed(4) == [16, 17, 18, 19] and b.tokens_to_feed(1) == [7]
+    run_step(sched, plan)
+    assert a.is_decoding and b.is_decoding
+    cache.check_invariants()
+
+
+def test_no_chunking_takes_whole_prompts():
+    cache = CacheManager([GroupLayout(CacheSpec(2, 16, None), 2)], 64, 4, 4, 256)
+    sched = Scheduler(SchedulerConfig(max_num_batched_tokens=100, enable_chunked_prefill=False, prefill_chunk_size=8), cache)
+    a = seq(sched, 50)
+    assert sched.schedule().scheduled[0].take == 50
+
+
+def test_max_num_seqs_and_fcfs_order():
+    sched, _ = make(seqs=2, budget=64, chunk=64)
+    late, early, third = seq(sched, 3, arrival=5.0), seq(sched, 3, arrival=1.0), seq(sched, 3, arrival=9.0)
+    plan = sched.schedule()
+    assert [i.seq.seq_id for i in plan.scheduled] == [early.seq_id, late.seq_id]
+    assert third.status is SequenceStatus.WAITING and len(sched.running) == 2
+
+
+def test_request_that_can_never_fit_is_aborted_and_others_go_on():
+    sched, _ = make(pages=4, page=4)
+    big, ok = seq(sched, 30, max_new=4, arrival=0.0), seq(sched, 6, max_new=2, arrival=1.0)
+    plan = sched.schedule()
+    assert plan.aborted == [big] and big.status is SequenceStatus.FINISHED_ABORTED
+    assert [i.seq.seq_id for i in plan.scheduled] == [ok.seq_id]
+
+
+def test_waiting_for_pages_keeps_arrival_order():
+    sched, cache = make(pages=6, page=4, budget=64, chunk=64)
+    a = seq(sched, 16, arrival=0.0)
+    run_step(sched, sched.schedule())  # a holds 4 pages
+    b, c = seq(sched, 12, arrival=1.0), seq(sched, 3, arrival=2.0)
+    plan = sched.schedule()  # b needs 3 pages, 2 are free: it waits, and c does not overtake it
+    assert [i.seq.seq_id for i in plan.scheduled] == [a.seq_id]
+    assert b.status is SequenceStatus.WAITING and c.status is SequenceStatus.WAITING
+
+
+def test_growth_preempts_the_newest_and_replays_it():
+    sched, cache = make(pages=4, page=4, budget=64, chunk=64)
+    a, b = seq(sched, 8, max_new=8, arrival=0.0), seq(sched, 7, max_new=8, arrival=1.0)
+    run_step(sched, sched.schedule())  # a: 2 pages (full), b: 2 pages (7 of 8 slots)
+    assert cache.num_free_pages() == 0
+    plan = sched.schedule()  # a needs a third page: b (newest) is preempted; b's decode had a free slot
+    assert plan.preempted == [b] and b.status is SequenceStatus.WAITING and b.num_computed_tokens == 0
+    assert sched.waiting[0] is b and b.preemptions == 1 and sched.preemptions == 1
+    assert [i.seq.seq_id for i in plan.scheduled] == [a.seq_id]
+    run_step(sched, plan)
+    # b comes back when pages allow and replays prompt + outputs before it decodes again
+    outputs_before = list(b.output_token_ids)
+    plan = sched.schedule()
+    ids = {i.seq.seq_id: i for i in plan.scheduled}
+    if b.seq_id in ids:
+        assert ids[b.seq_id].take == b.num_tokens and ids[b.seq_id].samples
+        assert b.tokens_to_feed(b.num_tokens) == b.prompt_token_ids + outputs_before
+    cache.check_invariants()
+
+
+def test_lone_request_without_pages_skips_the_step():
+    sched, cache = make(pages=2, page=4, budget=64, chunk=64)
+    a = seq(sched, 8, max_new=1)
+    run_step(sched, sched.schedule())
+    assert a.is_finished  # max_new 1: done after the prompt
+    b = seq(sched, 8, max_new=8)  # passes the NEVER test only if 16 tokens fit: they do not
+    plan = sched.schedule()
+    assert plan.aborted == [b]
+
+
+def test_everything_finishes_under_pressure_and_pages_come_back():
+    sched, cache = make(pages=6, page=4, seqs=3, budget=10, chunk=6)
+    seqs = [seq(sched, n, max_new=5, arrival=float(i)) for i, n in enumerate([9, 4, 11, 2, 7])]
+    steps = 0
+    while sched.has_work():
+        plan = sched.schedule()
+        assert plan.scheduled, "the scheduler stalled"
+        assert plan.num_batched_tokens <= 10
+        assert len({i.seq.seq_id for i in plan.scheduled}) == len(plan.scheduled)
+        run_step(sched, plan)
+        cache.check_invariants()
+        steps += 1
+        assert steps < 500
+    assert all(s.status is SequenceStatus.FINISHED_LENGTH and s.num_output_tokens == 5 for s in seqs)
+    assert cache.num_free_pages() == 6 and cache.num_free_slots() == 3
+    assert sched.preemptions > 0
+
+
+def test_abort():
+    sched, cache = make()
+    a = seq(sched, 5)
+    run_step(sched, sched.schedule())
+    sched.abort(a.seq_id)
+    assert a.status is SequenceStatus.FINISHED_ABORTED and not sched.has_work() and cache.num_free_pages() == 16
