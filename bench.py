@@ -1,0 +1,265 @@
+"""Decode and prefill throughput of the Qwen2.5-7B shape (random weights, bfloat16) on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens a second at the given batch (a step = one decode
+step of the whole batch through the step function, timed on the device with CUDA events); ``e2e`` is
+the same through the public engine calls (``add_request`` / ``step``) with host token ids in and
+out every step; ``prefill`` is one 2,048-token prompt in one step; ``roofline`` compares the bytes a
+decode step must read (every weight once, plus the cache of the live requests) with the measured
+copy bandwidth; ``points`` holds decode at batch 1 and 64.  Peaks come from MEASURED_PEAKS.json
+beside this file when present.  One GPU only: for --gpus above 1 it says so and exits with 2.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Qwen2.5-7B layer sizes (BASELINE.json configs[2])
+SHAPE_7B = dict(vocab_size=152064, hidden_size=3584, num_hidden_layers=28, intermediate_size=18944,
+                num_attention_heads=28, num_key_value_heads=4, head_dim=128, rms_norm_eps=1e-6,
+                rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=8192,
+                torch_dtype="bfloat16")
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.samples: list[list[str]] = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc) -> None:
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        mhz = sorted(int(float(s[0])) for s in self.samples)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(float(self.samples[0][1])), "reasons": reasons,
+                "samples": len(mhz)}
+
+
+def reference_arm(args) -> int:
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "slipstream")):
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is not installed under baseline/_ref (see DESIGN.md)"}))
+        return 0
+    from baseline.reference_bench import run_reference  # noqa: E402
+
+    print(json.dumps(run_reference(args, SHAPE_7B, ref)))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--layers", type=int, default=SHAPE_7B["num_hidden_layers"])
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    ap.add_argument("--no-graphs", action="store_true")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU only (this engine uses a single device); got --gpus {args.gpus}")
+        return 2
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+
+    from slipstream_b200 import CacheConfig, EngineConfig, SamplingParams, SchedulerConfig, ops
+    from slipstream_b200.engine.llm_engine import LLMEngine, Request
+    from slipstream_b200.engine.runner import StepEntry
+
+    pk, pk_kind = peaks()
+    shape = dict(SHAPE_7B, num_hidden_layers=args.layers)
+    folder = tempfile.mkdtemp(prefix="bench_qwen7b_")
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(dict(shape, architectures=["Qwen2ForCausalLM"], model_type="qwen2"), f)
+    ctx_len, page = shape["max_position_embeddings"], 16
+    max_batch = max(64, args.batch)
+    pages = max_batch * (args.prompt_len + args.steps + args.warmup + 64) // page + 4096 // page + 64
+    engine = LLMEngine(EngineConfig.for_model(
+        folder, dtype="bfloat16", load_format="random", max_model_len=ctx_len,
+        cache=CacheConfig(block_size=page, num_gpu_blocks=pages),
+        scheduler=SchedulerConfig(max_num_seqs=max_batch, max_num_batched_tokens=8192, prefill_chunk_size=2048),
+        seed=0, use_cuda_graphs=not args.no_graphs))
+    runner = engine.runner
+    vocab = shape["vocab_size"]
+    rng = np.random.default_rng(0)
+    torch.cuda.synchronize()
+
+    def fill(batch: int, tag: str) -> list[str]:
+        """Prefill ``batch`` requests of prompt_len random tokens (untimed)."""
+        ids = [f"{tag}{i}" for i in range(batch)]
+        per_step = max(1, 4096 // args.prompt_len)
+        for i in range(0, batch, per_step):
+            runner.step([StepEntry(r, rng.integers(0, vocab, args.prompt_len).tolist(), [])
+                         for r in ids[i:i + per_step]])
+        return ids
+
+    def decode_device(batch: int, steps: int, warmup: int, tag: str) -> tuple[float, float, int]:
+        """(tokens/s, ms per step, own kernel launches) of ``steps`` decode steps timed on the device."""
+        ids = fill(batch, tag)
+        feeds = rng.integers(0, vocab, (steps + warmup, batch)).tolist()
+        for w in range(warmup):
+            engine.sampler.greedy(runner.step([StepEntry(r, [feeds[w][j]], [0]) for j, r in enumerate(ids)]))
+        torch.cuda.synchronize()
+        launches0 = ops.launch_count()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for s in range(steps):
+            engine.sampler.greedy(runner.step([StepEntry(r, [feeds[warmup + s][j]], [0]) for j, r in enumerate(ids)]))
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / steps
+        launches = ops.launch_count() - launches0
+        for r in ids:
+            runner.release(r)
+        return batch * 1000.0 / ms, ms, launches
+
+    def decode_bytes(batch: int, steps: int, warmup: int) -> float:
+        mean_ctx = args.prompt_len + warmup + (steps + 1) / 2
+        return runner.weight_bytes_per_step() + batch * mean_ctx * runner.kv_bytes_per_token()
+
+    # ---- headline: decode at --batch, device-timed, with clocks sampled
+    with ClockSampler() as clocks:
+        value, ms_step, launches = decode_device(args.batch, args.steps, args.warmup, "d")
+    clock_summary = clocks.summary()
+    achieved = decode_bytes(args.batch, args.steps, args.warmup) / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end through the public engine calls: host tokens in, host tokens out, every step
+    for j in range(args.batch):
+        engine.add_request(Request(f"e{j}", None, rng.integers(0, vocab, args.prompt_len).tolist(),
+                                   SamplingParams(max_tokens=args.steps + args.warmup + 1, temperature=0.0,
+                                                  ignore_eos=True), float(j)))
+    while any(s.num_output_tokens == 0 for s in engine.scheduler.running) or engine.scheduler.waiting:
+        engine.step()
+    for _ in range(args.warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        engine.step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    h2d = engine.runner.last_h2d_bytes
+    while engine.scheduler.has_work():
+        engine.step()
+
+    # ---- prefill of one 2,048-token prompt in one step
+    T = 2048
+    for w in range(3):
+        runner.step([StepEntry(f"pw{w}", rng.integers(0, vocab, T).tolist(), [T - 1])])
+        runner.release(f"pw{w}")
+    torch.cuda.synchronize()
+    times = []
+    for w in range(5):
+        toks = rng.integers(0, vocab, T).tolist()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step([StepEntry(f"p{w}", toks, [T - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(stop))
+        runner.release(f"p{w}")
+    prefill_ms = sorted(times)[len(times) // 2]
+    c = runner.config
+    per_token_matmul = sum(e for e in [
+        2 * c.hidden_size * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim,
+        2 * c.num_attention_heads * c.head_dim * c.hidden_size,
+        2 * c.hidden_size * 2 * c.intermediate_size,
+        2 * c.intermediate_size * c.hidden_size]) * c.num_hidden_layers
+    attn_flops = 4 * c.num_attention_heads * c.head_dim * (T * (T + 1) // 2) * c.num_hidden_layers
+    flops = T * per_token_matmul + attn_flops + 2 * c.hidden_size * c.vocab_size
+    prefill = {"value": round(T * 1000.0 / prefill_ms, 1), "tokens": T, "ms": round(prefill_ms, 3),
+               "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               "tflops": round(flops / (prefill_ms * 1e-3) / 1e12, 1), "peak_tflops": pk["bf16_tflops"]}
+
+    points = {}
+    if not args.no_points:
+        pts_steps = max(16, args.steps // 2)
+        points["decode_b1"] = round(decode_device(1, pts_steps, 3, "a")[0], 1)
+        points["decode_b64"] = round(decode_device(64, pts_steps, 3, "b")[0], 1)
+
+    line = {
+        "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2048 tokens (Qwen2.5-7B bf16)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random token ids, random-init weights N(0, 0.02)",
+        "config": {"model": "Qwen2.5-7B shape", "global_batch": args.batch, "seq_len": args.prompt_len,
+                   "context_len": ctx_len, "parallelism": "single GPU", "layers": c.num_hidden_layers,
+                   "layers_of_model": SHAPE_7B["num_hidden_layers"], "hidden": c.hidden_size,
+                   "heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads, "head_dim": c.head_dim,
+                   "intermediate": c.intermediate_size, "vocab": c.vocab_size, "kv_block": page,
+                   "l2": "inputs larger than L2 (weights read every step)", "cuda_graphs": not args.no_graphs,
+                   "peaks": pk_kind},
+        "e2e": {"value": round(args.batch * 1000.0 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": launches,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clock_summary,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

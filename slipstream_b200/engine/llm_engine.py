@@ -121,6 +121,16 @@ class LLMEngine:
                 yield seq.output_token_ids[emitted]
                 emitted += 1
 
+    def add_request(self, request: Request) -> Sequence:
+        """Queue a request; ``step`` then advances everything queued by one engine step."""
+        seq = self._make_sequence(request)
+        self.scheduler.add_seq(seq)
+        return seq
+
+    def step(self) -> bool:
+        """One engine step: schedule, one step-function call, sample, finish.  False when idle."""
+        return self._step()
+
     def generate_batch(self, requests: list[Request]) -> list[list[int]]:
         """Continuous batching of several requests (slipstream/engine/llm_engine.py:107-119)."""
         seqs = [self._make_sequence(r) for r in requests]

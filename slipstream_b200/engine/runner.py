@@ -75,6 +75,7 @@ class ModelRunner:
         self.model.attach_store(self.store)
         self.has_state = any(self.model.entry_state)
         self.steps_run = 0
+        self.last_h2d_bytes = 0
         self.use_cuda_graphs = use_cuda_graphs
 
     # ------------------------------------------------------------------ requests
@@ -99,6 +100,7 @@ class ModelRunner:
             if e.request_id not in self.cache:
                 self.admit(e.request_id)
         ctx = build_context(entries, self.cache, self.config.vocab_size, self.device)
+        self.last_h2d_bytes = ctx.extras["host_buffer"].numel() * 4
         logits = self.run(ctx)
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))

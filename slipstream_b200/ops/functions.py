@@ -117,7 +117,21 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_launches = [0]
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far (each entry point below launches exactly one;
+    a replayed CUDA graph adds the kernels it holds, see ``count_launches``)."""
+    return _launches[0]
+
+
+def count_launches(n: int) -> None:
+    _launches[0] += n
+
+
 def _check(code: int, what: str) -> None:
+    _launches[0] += 1
     if code != 0:
         raise KernelError(f"{what}: CUDA error {code} at launch")
 
@@ -350,5 +364,5 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "require_cuda", "argmax", "sample", "mark_seen", "linear", "check_errors", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "require_cuda", "argmax", "sample", "mark_seen", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
            "attention_library"]
