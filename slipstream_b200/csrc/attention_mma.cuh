@@ -1,0 +1,402 @@
+// bfloat16 paged grouped-query attention on tensor cores (mma.sync m16n8k16, float32
+// accumulation, float32 online softmax), fed by cp.async from the pages.
+//
+// Two kernels share the tile code:
+//  * attn_prefill_mma: a block takes 64 "rows" of one (request, kv head), a row being a
+//    (query token, head of the group) pair in token-major order, so the heads of a group
+//    share every key/value tile that is fetched; it walks the keys in tiles of 64.
+//  * attn_decode_mma: requests that bring ONE token.  A block takes the (up to 16) heads of
+//    one (request, kv head) and one slice of the keys (split-KV); its four warps take
+//    different 16-key parts of each 64-key tile and merge at the end.  With more than one
+//    slice, partial results go to scratch memory and attn_merge_kernel combines them.
+//
+// Key tiles start at multiples of 64 counted from the request's first token.  Masking is
+// the packed-index causal rule of slipstream/models/layers/attention.py:46-51 plus an
+// optional window; softmax statistics are float32 (:64-88); probabilities are rounded to
+// bfloat16 for the second product as the reference's `.to(query.dtype)` does.
+// kv layout: [page][2][kv head][offset in page][D].
+#pragma once
+
+#include "common.cuh"
+
+#define MMA_BN 64          // keys per tile
+#define MMA_THREADS 128
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t r[4], const void* smem) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t r[4], const void* smem) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem)));
+}
+__device__ __forceinline__ void mma_bf16(float c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Stage keys [k0, k0 + 64) of one kv head: K rows to Ks, V rows to Vs (row stride D + 8).
+// Rows outside [lo, hi] or without a page are zero-filled.
+template <int D>
+__device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __restrict__ kv,
+                                             const int32_t* __restrict__ table, int k0, int lo, int hi,
+                                             int kvh, int n_kv, int page_size, int64_t num_pages, int* err) {
+    constexpr int CPR = D / 8;  // 16-byte chunks per row
+    constexpr int KSTR = D + 8;
+    const int64_t v_off = (int64_t)n_kv * page_size * D;
+    for (int c = threadIdx.x; c < MMA_BN * CPR; c += MMA_THREADS) {
+        const int row = c / CPR, col = (c - row * CPR) * 8;
+        const int key = k0 + row;
+        bool ok = key >= lo && key <= hi;
+        int64_t base = 0;
+        if (ok) {
+            const int64_t page = table[key / page_size];
+            if (page < 0 || page >= num_pages) {
+                if (page >= num_pages) atomicOr(err, SS_ERR_PAGE_RANGE);
+                ok = false;
+            } else {
+                base = ((page * 2 * n_kv + kvh) * page_size + key % page_size) * (int64_t)D + col;
+            }
+        }
+        cp_async16(Ks + row * KSTR + col, kv + base, ok);
+        cp_async16(Vs + row * KSTR + col, kv + base + v_off, ok);
+    }
+}
+
+// One warp: scores of its 16 rows against NK keys of a staged tile (keys key_off.. of the tile),
+// online-softmax update, and O += P V.  S/P registers: NK/8 n-tiles.
+template <int D, int NK>
+__device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const bf16* Ks, const bf16* Vs,
+                                          int key_off, int key0_abs, float scale_log2, int pos_lo, int pos_hi,
+                                          int window, float (&m)[2], float (&l)[2], float (&o)[D / 8][4]) {
+    constexpr int KSTR = D + 8;
+    constexpr int NT = NK / 8;
+    const int lane = threadIdx.x & 31;
+    float s[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+        for (int n = 0; n < NT; n += 2) {
+            uint32_t b[4];
+            const int row = key_off + n * 8 + (lane & 7) + ((lane >> 4) << 3);
+            const int col = ks * 16 + (((lane >> 3) & 1) << 3);
+            ldmatrix_x4(b, Ks + row * KSTR + col);
+            mma_bf16(s[n], qf[ks], b[0], b[1]);
+            mma_bf16(s[n + 1], qf[ks], b[2], b[3]);
+        }
+    }
+    // mask, scale, row maxima (rows lane/4 and lane/4 + 8)
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int key = key0_abs + key_off + n * 8 + ((lane & 3) << 1) + (e & 1);
+            const int pos = (e < 2) ? pos_lo : pos_hi;  // < 0: the row does not exist
+            const bool ok = key <= pos && (window <= 0 || key > pos - window);
+            const float v = ok ? s[n][e] * scale_log2 : -INFINITY;
+            s[n][e] = v;
+            mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+    }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m[r], mx[r]);
+        m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha[r] = exp2f(m[r] - m_use[r]);  // m = -inf gives 0
+        m[r] = m_new;
+        l[r] *= alpha[r];
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float p = exp2f(s[n][e] - m_use[e >> 1]);
+            s[n][e] = p;
+            l[e >> 1] += p;
+        }
+    }
+#pragma unroll
+    for (int d = 0; d < D / 8; ++d) {
+        o[d][0] *= alpha[0]; o[d][1] *= alpha[0];
+        o[d][2] *= alpha[1]; o[d][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < NK / 16; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int d = 0; d < D / 8; d += 2) {
+            uint32_t b[4];
+            const int row = key_off + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+            const int col = d * 8 + ((lane >> 4) << 3);
+            ldmatrix_x4_trans(b, Vs + row * KSTR + col);
+            mma_bf16(o[d], a, b[0], b[1]);
+            mma_bf16(o[d + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+template <int D>
+constexpr int mma_smem_bytes() {
+    return (64 * (D + 8) + 2 * 2 * MMA_BN * (D + 8)) * 2;  // Q tile + two stages of K and V
+}
+
+// ---------------------------------------------------------------- prompt portions (and mixed batches)
+
+template <int D>
+__global__ void __launch_bounds__(MMA_THREADS)
+attn_prefill_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__ out, int64_t out_stride,
+                 const bf16* __restrict__ kv, const int32_t* __restrict__ block_tables, int max_blocks,
+                 const int32_t* __restrict__ tile_req, const int32_t* __restrict__ tile_row0,
+                 const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens, int n_q, int n_kv,
+                 int page_size, int64_t num_pages, float scale, int window, int* err) {
+    constexpr int KSTR = D + 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
+    bf16* KV = Qs + 64 * KSTR;  // stage s: K at KV + s*2*64*KSTR, V after it
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = n_q / n_kv, kvh = blockIdx.y;
+    const int r = tile_req[blockIdx.x], row0 = tile_row0[blockIdx.x];
+    const int qs = q_start[r], q_len = q_start[r + 1] - qs, seq_len = seq_lens[r];
+    const int rows_total = q_len * G;
+    const int rows_here = min(64, rows_total - row0);
+    const int first_pos = seq_len - q_len + row0 / G;
+    const int last_pos = seq_len - q_len + (row0 + rows_here - 1) / G;
+    const int lo = window > 0 ? max(0, first_pos - window + 1) : 0;
+    const int32_t* table = block_tables + (int64_t)r * max_blocks;
+
+    // Q tile: row -> (token, head of the group)
+    for (int c = tid; c < 64 * (D / 8); c += MMA_THREADS) {
+        const int row = c / (D / 8), col = (c - row * (D / 8)) * 8;
+        const int gr = row0 + row;
+        const bool ok = row < rows_here;
+        const int tok = ok ? gr / G : 0, g = ok ? gr - tok * G : 0;
+        cp_async16(Qs + row * KSTR + col, q + (int64_t)(qs + tok) * q_stride + (int64_t)(kvh * G + g) * D + col, ok);
+    }
+    const int kt_lo = lo / MMA_BN, kt_hi = last_pos / MMA_BN;
+    load_kv_tile<D>(KV, KV + MMA_BN * KSTR, kv, table, kt_lo * MMA_BN, lo, last_pos, kvh, n_kv, page_size, num_pages, err);
+    cp_async_commit();
+
+    // this thread's two rows
+    int pos2[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = warp * 16 + (lane >> 2) + h * 8;
+        pos2[h] = row < rows_here ? seq_len - q_len + (row0 + row) / G : -1;
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int d = 0; d < D / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+    uint32_t qf[D / 16][4];
+    const float scale_log2 = scale * 1.4426950408889634f;
+
+    for (int kt = kt_lo; kt <= kt_hi; ++kt) {
+        const int stage = (kt - kt_lo) & 1;
+        bf16* Ks = KV + stage * 2 * MMA_BN * KSTR;
+        bf16* Vs = Ks + MMA_BN * KSTR;
+        if (kt < kt_hi) {
+            bf16* Kn = KV + (stage ^ 1) * 2 * MMA_BN * KSTR;
+            load_kv_tile<D>(Kn, Kn + MMA_BN * KSTR, kv, table, (kt + 1) * MMA_BN, lo, last_pos, kvh, n_kv, page_size, num_pages, err);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (kt == kt_lo) {
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks)
+                ldmatrix_x4(qf[ks], Qs + (warp * 16 + (lane & 15)) * KSTR + ks * 16 + ((lane >> 4) << 3));
+        }
+        // a warp whose rows all lie before this tile has nothing to add
+        const int warp_last = min(rows_here - 1, warp * 16 + 15);
+        const bool active = warp * 16 < rows_here && kt * MMA_BN <= seq_len - q_len + (row0 + warp_last) / G;
+        if (active)
+            warp_tile<D, MMA_BN>(qf, Ks, Vs, 0, kt * MMA_BN, scale_log2, pos2[0], pos2[1], window, m, l, o);
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+        const int row = warp * 16 + (lane >> 2) + h * 8;
+        if (row >= rows_here) continue;
+        const int gr = row0 + row, tok = gr / G, g = gr - tok * G;
+        const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+        bf16* dst = out + (int64_t)(qs + tok) * out_stride + (int64_t)(kvh * G + g) * D + ((lane & 3) << 1);
+#pragma unroll
+        for (int d = 0; d < D / 8; ++d)
+            *reinterpret_cast<__nv_bfloat162*>(dst + d * 8) = __floats2bfloat162_rn(o[d][2 * h] * inv, o[d][2 * h + 1] * inv);
+    }
+}
+
+// ---------------------------------------------------------------- single decoded tokens, split over the keys
+
+// grid: (request, kv head * head blocks, slice).  part_o: [request][q head][slice][D] float32 (normalised),
+// part_lse: [request][q head][slice] float32 (log2 of the sum of exponentials, -inf for an empty slice).
+template <int D>
+__global__ void __launch_bounds__(MMA_THREADS)
+attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__ out, int64_t out_stride,
+                const bf16* __restrict__ kv, const int32_t* __restrict__ block_tables, int max_blocks,
+                const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens, int n_q, int n_kv,
+                int page_size, int64_t num_pages, float scale, int window, int n_slices,
+                float* __restrict__ part_o, float* __restrict__ part_lse, int* err) {
+    constexpr int KSTR = D + 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
+    bf16* KV = Qs + 64 * KSTR;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = n_q / n_kv, hblocks = (G + 15) / 16;
+    const int r = blockIdx.x, kvh = blockIdx.y / hblocks, g0 = (blockIdx.y % hblocks) * 16;
+    const int heads_here = min(16, G - g0);
+    const int slice = blockIdx.z;
+    const int row_q = q_start[r], seq_len = seq_lens[r];
+    const int pos = seq_len - 1;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int32_t* table = block_tables + (int64_t)r * max_blocks;
+
+    const int kt_first = lo / MMA_BN, kt_last = pos / MMA_BN;
+    const int n_tiles = kt_last - kt_first + 1;
+    const int per = (n_tiles + n_slices - 1) / n_slices;
+    const int kt_lo = kt_first + slice * per, kt_hi = min(kt_last, kt_lo + per - 1);
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int d = 0; d < D / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+
+    if (seq_len > 0 && kt_lo <= kt_hi) {
+        for (int c = tid; c < 16 * (D / 8); c += MMA_THREADS) {
+            const int row = c / (D / 8), col = (c - row * (D / 8)) * 8;
+            const bool ok = row < heads_here;
+            cp_async16(Qs + row * KSTR + col, q + (int64_t)row_q * q_stride + (int64_t)(kvh * G + g0 + (ok ? row : 0)) * D + col, ok);
+        }
+        load_kv_tile<D>(KV, KV + MMA_BN * KSTR, kv, table, kt_lo * MMA_BN, lo, pos, kvh, n_kv, page_size, num_pages, err);
+        cp_async_commit();
+        uint32_t qf[D / 16][4];
+        const float scale_log2 = scale * 1.4426950408889634f;
+        const int p_lo = (lane >> 2) < heads_here ? pos : -1;
+        const int p_hi = (lane >> 2) + 8 < heads_here ? pos : -1;
+        for (int kt = kt_lo; kt <= kt_hi; ++kt) {
+            const int stage = (kt - kt_lo) & 1;
+            bf16* Ks = KV + stage * 2 * MMA_BN * KSTR;
+            bf16* Vs = Ks + MMA_BN * KSTR;
+            if (kt < kt_hi) {
+                bf16* Kn = KV + (stage ^ 1) * 2 * MMA_BN * KSTR;
+                load_kv_tile<D>(Kn, Kn + MMA_BN * KSTR, kv, table, (kt + 1) * MMA_BN, lo, pos, kvh, n_kv, page_size, num_pages, err);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncthreads();
+            if (kt == kt_lo) {
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks)
+                    ldmatrix_x4(qf[ks], Qs + (lane & 15) * KSTR + ks * 16 + ((lane >> 4) << 3));
+            }
+            if (kt * MMA_BN + warp * 16 <= pos)
+                warp_tile<D, 16>(qf, Ks, Vs, warp * 16, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
+            __syncthreads();
+        }
+    }
+
+    // merge the four warps: every warp publishes (m, l, O) for its 16 rows
+    float* Om = reinterpret_cast<float*>(smem_raw);          // [4][16][D]
+    float* Mm = Om + 4 * 16 * D;                             // [4][16]
+    float* Lm = Mm + 4 * 16;                                 // [4][16]
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+        const int row = (lane >> 2) + h * 8;
+        if ((lane & 3) == 0) {
+            Mm[warp * 16 + row] = m[h];
+            Lm[warp * 16 + row] = l[h];
+        }
+#pragma unroll
+        for (int d = 0; d < D / 8; ++d) {
+            float* dst = Om + ((warp * 16 + row) * D) + d * 8 + ((lane & 3) << 1);
+            dst[0] = o[d][2 * h];
+            dst[1] = o[d][2 * h + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < heads_here * D; idx += MMA_THREADS) {
+        const int row = idx / D, d = idx - row * D;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, Mm[w * 16 + row]);
+        float acc = 0.f, ll = 0.f;
+        if (mm != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = exp2f(Mm[w * 16 + row] - mm);
+                acc += Om[(w * 16 + row) * D + d] * f;
+                ll += Lm[w * 16 + row] * f;
+            }
+        }
+        const float val = ll > 0.f ? acc / ll : 0.f;
+        const int head = kvh * G + g0 + row;
+        if (n_slices == 1) {
+            out[(int64_t)row_q * out_stride + (int64_t)head * D + d] = __float2bfloat16_rn(val);
+        } else {
+            part_o[(((int64_t)r * n_q + head) * n_slices + slice) * D + d] = val;
+            if (d == 0) part_lse[((int64_t)r * n_q + head) * n_slices + slice] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
+        }
+    }
+}
+
+// out[r][head] = sum_s part_o[s] * 2^(lse_s - max) / sum_s 2^(lse_s - max);  grid (request, head)
+template <int D>
+__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                  bf16* __restrict__ out, int64_t out_stride, const int32_t* __restrict__ q_start,
+                                  int n_q, int n_slices) {
+    const int r = blockIdx.x, head = blockIdx.y;
+    const float* lse = part_lse + ((int64_t)r * n_q + head) * n_slices;
+    float mx = -INFINITY;
+    for (int s = 0; s < n_slices; ++s) mx = fmaxf(mx, lse[s]);
+    float den = 0.f;
+    if (mx != -INFINITY)
+        for (int s = 0; s < n_slices; ++s) den += exp2f(lse[s] - mx);
+    const float* po = part_o + ((int64_t)r * n_q + head) * n_slices * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.f;
+        if (mx != -INFINITY)
+            for (int s = 0; s < n_slices; ++s) {
+                const float w = exp2f(lse[s] - mx);
+                if (w > 0.f) acc += po[s * D + d] * w;
+            }
+        out[(int64_t)q_start[r] * out_stride + (int64_t)head * D + d] = __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+    }
+}

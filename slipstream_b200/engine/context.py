@@ -53,7 +53,7 @@ class StepContext:
     request_ids: list[object]
     device: torch.device
     num_logits: int = 0
-    _tiles: dict[int, tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
+    _tiles: dict[tuple[int, int], tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
     extras: dict[str, object] = field(default_factory=dict)
 
     @property
@@ -68,15 +68,17 @@ class StepContext:
     def is_decode_only(self) -> bool:
         return self.num_requests > 0 and self.max_q_len == 1
 
-    def query_tiles(self, rows: int = ATTN_TILE_ROWS) -> tuple[torch.Tensor, torch.Tensor]:
-        """(request index, first row within the request) of every tile of ``rows``
-        consecutive query tokens, as int32 device tensors."""
-        cached = self._tiles.get(rows)
+    def query_tiles(self, rows: int = ATTN_TILE_ROWS, group: int = 1) -> tuple[torch.Tensor, torch.Tensor]:
+        """(request index, first row within the request) of every tile of ``rows`` consecutive rows, as
+        int32 device tensors.  A request has ``q_len * group`` rows: with ``group`` 1 a row is a query
+        token; with the size of a kv group it is a (token, head of the group) pair."""
+        key = (rows, group)
+        cached = self._tiles.get(key)
         if cached is None:
-            req, q0 = query_tiles_host(self.q_lens_host, rows)
+            req, q0 = query_tiles_host(self.q_lens_host * group, rows)
             both = torch.from_numpy(np.concatenate([req, q0])).to(self.device, non_blocking=True)
             cached = (both[: req.size], both[req.size:])
-            self._tiles[rows] = cached
+            self._tiles[key] = cached
         return cached
 
 

@@ -53,6 +53,12 @@ _ATTN_SIGNATURES = {
     "ss_attn_simt": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                      c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float,
                      c_int, c_int, c_void_p, c_void_p],
+    "ss_attn_prefill_mma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
+                            c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float,
+                            c_int, c_void_p, c_void_p],
+    "ss_attn_decode_mma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
+                           c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
+                           c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
 _state: dict[str, object] = {}
@@ -285,16 +291,96 @@ def paged_attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: 
                             _code(q.dtype), error_word(q.device).data_ptr(), _stream()), "paged_attention_simt")
 
 
+def paged_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
+                            block_tables: torch.Tensor, tile_req: torch.Tensor, tile_row0: torch.Tensor,
+                            q_start: torch.Tensor, seq_lens: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
+                            scale: float, window: int = 0) -> None:
+    """bfloat16 tensor-core attention for prompt portions and mixed batches.  A tile is 64 consecutive
+    rows of one request, a row being a (query token, head of the kv group) pair in token-major order:
+    ``tile_req`` / ``tile_row0`` list (request index, first row)."""
+    _need(out, torch.bfloat16, "attention output")
+    _need(kv, torch.bfloat16, "kv pages")
+    if q.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core attention kernels take bfloat16")
+    for name, t in (("block_tables", block_tables), ("tile_req", tile_req), ("tile_row0", tile_row0),
+                    ("q_start", q_start), ("seq_lens", seq_lens)):
+        _need(t, torch.int32, name)
+    lib = attention_library(head_dim)
+    _check(lib.ss_attn_prefill_mma(q.data_ptr(), q_stride, out.data_ptr(), out.shape[1], kv.data_ptr(),
+                                   block_tables.data_ptr(), block_tables.shape[1], tile_req.data_ptr(),
+                                   tile_row0.data_ptr(), tile_req.numel(), q_start.data_ptr(), seq_lens.data_ptr(),
+                                   n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), int(window or 0),
+                                   error_word(q.device).data_ptr(), _stream()), "paged_attention_prefill")
+
+
+def decode_scratch(n_requests: int, n_q: int, n_slices: int, head_dim: int, device: torch.device):
+    """Scratch memory of the split decode kernel: partial outputs and their log-sum-exps."""
+    return (torch.empty((n_requests, n_q, n_slices, head_dim), dtype=torch.float32, device=device),
+            torch.empty((n_requests, n_q, n_slices), dtype=torch.float32, device=device))
+
+
+def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
+                           block_tables: torch.Tensor, q_start: torch.Tensor, seq_lens: torch.Tensor,
+                           n_requests: int, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
+                           n_slices: int = 1, scratch: tuple[torch.Tensor, torch.Tensor] | None = None) -> None:
+    """bfloat16 attention for requests that bring ONE token each, the keys of every request cut into
+    ``n_slices`` slices that run in parallel; with more than one slice the partial results pass through
+    ``scratch`` (see ``decode_scratch``) and a second kernel merges them."""
+    _need(out, torch.bfloat16, "attention output")
+    _need(kv, torch.bfloat16, "kv pages")
+    if q.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core attention kernels take bfloat16")
+    for name, t in (("block_tables", block_tables), ("q_start", q_start), ("seq_lens", seq_lens)):
+        _need(t, torch.int32, name)
+    part_o = part_lse = None
+    if n_slices > 1:
+        if scratch is None:
+            scratch = decode_scratch(n_requests, n_q, n_slices, head_dim, q.device)
+        part_o, part_lse = scratch
+        if part_o.numel() < n_requests * n_q * n_slices * head_dim or part_lse.numel() < n_requests * n_q * n_slices:
+            raise KernelError("decode scratch is too small")
+    lib = attention_library(head_dim)
+    _check(lib.ss_attn_decode_mma(q.data_ptr(), q_stride, out.data_ptr(), out.shape[1], kv.data_ptr(),
+                                  block_tables.data_ptr(), block_tables.shape[1], n_requests, q_start.data_ptr(),
+                                  seq_lens.data_ptr(), n_q, n_kv, kv.shape[3], kv.shape[0], float(scale),
+                                  int(window or 0), n_slices, _ptr(part_o), _ptr(part_lse),
+                                  error_word(q.device).data_ptr(), _stream()), "paged_attention_decode")
+    if n_slices > 1:
+        _launches[0] += 1  # the merge kernel
+
+
+def decode_slices(n_requests: int, n_kv: int, group: int, max_seq_len: int) -> int:
+    """How many slices to cut the keys into so that a decode step fills the 148 SMs about twice."""
+    blocks = n_requests * n_kv * ((group + 15) // 16)
+    tiles = max(1, (max_seq_len + 63) // 64)
+    return max(1, min((2 * 148 + blocks - 1) // blocks, tiles, 32))
+
+
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, block_tables: torch.Tensor,
                     ctx, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0) -> None:
     """Attention of the step's rows over the pages, choosing the kernel for the batch.
 
     ``qkv`` is the stacked projection output [N, (n_q + 2 n_kv) * D] whose first n_q heads are the
     rotated queries; ``ctx`` gives the rows of each request (``q_start``), the cached lengths after
-    this step (``seq_lens``) and the list of query tiles."""
-    tile_req, tile_q0 = ctx.query_tiles(16)
-    paged_attention_simt(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_q0, ctx.q_start,
-                         ctx.seq_lens, n_q, n_kv, head_dim, scale, window)
+    this step (``seq_lens``) and the lists of query tiles.  float32 runs the CUDA-core kernel;
+    bfloat16 the tensor-core kernels: the split decode kernel when every request brings one token,
+    else the tiled kernel."""
+    if qkv.dtype == torch.float32:
+        tile_req, tile_q0 = ctx.query_tiles(16)
+        paged_attention_simt(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_q0, ctx.q_start,
+                             ctx.seq_lens, n_q, n_kv, head_dim, scale, window)
+        return
+    group = n_q // n_kv
+    if ctx.is_decode_only:
+        slices = ctx.extras.get("decode_slices") or decode_slices(ctx.num_requests, n_kv, group,
+                                                                 min(ctx.max_seq_len, window or ctx.max_seq_len))
+        scratch = ctx.extras.get(("decode_scratch", n_q, head_dim))
+        paged_attention_decode(qkv, qkv.shape[1], out, kv, block_tables, ctx.q_start, ctx.seq_lens,
+                               ctx.num_requests, n_q, n_kv, head_dim, scale, window, slices, scratch)
+        return
+    tile_req, tile_row0 = ctx.query_tiles(64, group)
+    paged_attention_prefill(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_row0, ctx.q_start,
+                            ctx.seq_lens, n_q, n_kv, head_dim, scale, window)
 
 
 # --------------------------------------------------------------------------- sampling
@@ -364,5 +450,5 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "require_cuda", "argmax", "sample", "mark_seen", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "paged_attention_prefill", "paged_attention_decode", "decode_scratch", "decode_slices", "require_cuda", "argmax", "sample", "mark_seen", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
            "attention_library"]

@@ -1,0 +1,264 @@
+"""Each CUDA kernel alone against a plain float32/float64 PyTorch restatement of the same op, at sizes
+other than the engine's test models (widths and vocabularies that are no power of two, head sizes in
+steps of 16, odd group sizes, pages of odd size)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from slipstream_b200 import ops as o
+    return o
+
+
+def tol(dtype, f32=1e-5, bf16=1.6e-2):
+    return f32 if dtype == torch.float32 else bf16
+
+
+def rel_err(got, ref):
+    return ((got.double() - ref.double()).abs().max() / ref.double().abs().max().clamp_min(1e-30)).item()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden, vocab", [(72, 101), (3584, 1000)])
+def test_embedding(dtype, hidden, vocab):
+    table = torch.randn(vocab, hidden, device=DEV).to(dtype)
+    ids = torch.randint(0, vocab, (37,), device=DEV, dtype=torch.int32)
+    got = ops().embedding(ids, table)
+    assert got.dtype == torch.float32 and torch.equal(got, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [48, 1000, 3584, 5120])
+def test_add_rmsnorm(dtype, hidden):
+    torch.manual_seed(hidden)
+    n, eps = 19, 1e-5
+    residual = torch.randn(n, hidden, device=DEV) * 3
+    delta = torch.randn(n, hidden, device=DEV).to(dtype)
+    weight = (1 + 0.1 * torch.randn(hidden, device=DEV)).to(dtype)
+    summed = residual.double() + delta.double()
+    ref = summed * torch.rsqrt(summed.pow(2).mean(-1, keepdim=True) + eps) * weight.double()
+    res = residual.clone()
+    got = ops().add_rmsnorm(res, delta, weight, eps, dtype)
+    assert rel_err(got, ref) < tol(dtype, 2e-6, 1.2e-2)
+    assert torch.allclose(res.double(), summed, atol=1e-6)  # the stream is updated in float32
+    # without a delta; and selected rows only, which leaves the stream alone
+    got = ops().add_rmsnorm(res, None, weight, eps, dtype)
+    assert rel_err(got, ref) < tol(dtype, 2e-6, 1.2e-2)
+    rows = torch.tensor([5, 0, 18], device=DEV, dtype=torch.int32)
+    res2 = residual.clone()
+    got = ops().add_rmsnorm(res2, delta, weight, eps, dtype, rows=rows)
+    assert rel_err(got, ref[rows.long()]) < tol(dtype, 2e-6, 1.2e-2) and torch.equal(res2, residual)
+    # a float32 weight beside bfloat16 activations
+    if dtype == torch.bfloat16:
+        got = ops().add_rmsnorm(residual.clone(), delta, weight.float(), eps, dtype)
+        assert rel_err(got, ref) < 1.2e-2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q, n_kv, d, rot, page", [(6, 2, 16, 16, 4), (7, 1, 48, 48, 5), (8, 8, 128, 64, 16), (3, 3, 80, 0, 7)])
+def test_rope_and_cache(dtype, n_q, n_kv, d, rot, page):
+    torch.manual_seed(d)
+    n, pages, theta = 23, 9, 50000.0
+    qkv = torch.randn(n, (n_q + 2 * n_kv) * d, device=DEV).to(dtype)
+    pos = torch.randint(0, 5000, (n,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(pages * page, device=DEV)[:n].to(torch.int32)
+    slots[3] = -1  # this token is not written
+    kv = torch.zeros(pages, 2, n_kv, page, d, device=DEV, dtype=dtype)
+    inv_freq = None
+    x = qkv.double().view(n, n_q + 2 * n_kv, d).clone()
+    ref = x.clone()
+    if rot:
+        inv_freq = (1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(DEV)
+        # the angle is a float32 product, as in slipstream/models/layers/rope.py:100
+        ang = (pos.float()[:, None] * inv_freq[None, :]).double()
+        c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        x1, x2 = x[:, : n_q + n_kv, : rot // 2], x[:, : n_q + n_kv, rot // 2: rot]
+        ref[:, : n_q + n_kv, : rot // 2] = x1 * c - x2 * s
+        ref[:, : n_q + n_kv, rot // 2: rot] = x2 * c + x1 * s
+    work = qkv.clone()
+    ops().rope_and_cache(work, pos, slots, inv_freq, kv, n_q, n_kv, d, rot)
+    got = work.view(n, n_q + 2 * n_kv, d)
+    assert rel_err(got[:, :n_q], ref[:, :n_q]) < tol(dtype, 3e-6, 8e-3)
+    for t in range(n):
+        if slots[t] < 0:
+            continue
+        p, o = int(slots[t]) // page, int(slots[t]) % page
+        assert rel_err(kv[p, 0, :, o], ref[t, n_q: n_q + n_kv]) < tol(dtype, 3e-6, 8e-3)
+        assert torch.equal(kv[p, 1, :, o], qkv.view(n, -1, d)[t, n_q + n_kv:])
+    assert int((kv != 0).any(-1).any(-1).any(-1).sum()) <= n - 1  # no other page touched
+    ops().check_errors(torch.device(DEV))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    x = (torch.randn(13, 2 * 1234, device=DEV) * 3).to(dtype)
+    g, u = x[:, :1234].double(), x[:, 1234:].double()
+    assert rel_err(ops().swiglu(x), g * torch.sigmoid(g) * u) < tol(dtype, 2e-6, 8e-3)
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 130, 70), (37, 65, 1000), (200, 333, 96)])
+def test_float32_matrix_product_is_exact_to_rounding_and_independent_of_the_batch(m, n, k):
+    torch.manual_seed(m)
+    x, w, b = torch.randn(m, k, device=DEV), torch.randn(n, k, device=DEV), torch.randn(n, device=DEV)
+    got = ops().gemm_simt(x, w, b)
+    ref = x.double() @ w.double().T + b.double()
+    assert rel_err(got, ref) < 2e-6  # TF32 would be 1e-3
+    alone = ops().gemm_simt(x[:1].contiguous(), w, b)
+    assert torch.equal(alone, got[:1])
+
+
+def test_bfloat16_linear_gives_float32_logits():
+    x, w = torch.randn(5, 200, device=DEV).bfloat16(), torch.randn(1001, 200, device=DEV).bfloat16()
+    got = ops().linear(x, w, None, out_dtype=torch.float32)
+    assert got.dtype == torch.float32 and rel_err(got, x.double() @ w.double().T) < 1e-5
+    got = ops().gemm_simt(x, w, None, out_dtype=torch.float32)
+    assert rel_err(got, x.double() @ w.double().T) < 1e-5
+
+
+# --------------------------------------------------------------------------- attention
+
+def make_attention_case(dtype, lens, q_lens, n_q, n_kv, d, page, seed, sharp=None):
+    """Random pages in random order; returns tensors for the kernels and per-request dense K, V."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(lens)
+    blocks = [(l + page - 1) // page for l in lens]
+    pages = sum(blocks) + 3
+    perm = torch.randperm(pages, generator=g).tolist()
+    max_blocks = max(blocks)
+    table = torch.full((R, max_blocks), -1, dtype=torch.int32)
+    kv = torch.randn(pages, 2, n_kv, page, d, generator=g) * 0.5
+    k = 0
+    for r in range(R):
+        for b in range(blocks[r]):
+            table[r, b] = perm[k]
+            k += 1
+    if sharp is not None:  # one far key stands out for the last query of request 0
+        key_pos = sharp
+        kv[table[0, key_pos // page], 0, :, key_pos % page] *= 0
+    N = sum(q_lens)
+    q = torch.randn(N, n_q, d, generator=g)
+    q_start = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
+    if sharp is not None:
+        row = int(q_start[1]) - 1
+        direction = torch.randn(d, generator=g)
+        direction /= direction.norm()
+        q[row] = direction * 6
+        kv[table[0, sharp // page], 0, :, sharp % page] = direction * 6
+        kv[table[0, sharp // page], 1, :, sharp % page] = 5.0
+    return (q.to(dtype).to(DEV), kv.to(dtype).to(DEV), table.to(DEV), q_start.to(DEV),
+            torch.tensor(lens, dtype=torch.int32, device=DEV))
+
+
+def attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, scale, window):
+    N, n_q, d = q.shape
+    out = torch.zeros(N, n_q, d, dtype=torch.float64)
+    qd, kvd = q.double().cpu(), kv.double().cpu()
+    G = n_q // n_kv
+    for r in range(seq_lens.numel()):
+        a, b, S = int(q_start[r]), int(q_start[r + 1]), int(seq_lens[r])
+        T = b - a
+        nb = (S + page - 1) // page
+        pg = table[r, :nb].long().cpu()
+        K = kvd[pg, 0].permute(1, 0, 2, 3).reshape(n_kv, nb * page, d)[:, :S]
+        V = kvd[pg, 1].permute(1, 0, 2, 3).reshape(n_kv, nb * page, d)[:, :S]
+        for h in range(n_q):
+            s = (qd[a:b, h] @ K[h // G].T) * scale
+            pos = torch.arange(S - T, S)[:, None]
+            key = torch.arange(S)[None, :]
+            ok = key <= pos
+            if window:
+                ok &= key > pos - window
+            s = s.masked_fill(~ok, float("-inf"))
+            out[a:b, h] = torch.softmax(s, -1) @ V[h // G]
+    return out
+
+
+CASES = [  # lens, q_lens, n_q, n_kv, d, page, window
+    ([70, 5, 130], [70, 5, 17], 4, 2, 16, 4, 0),
+    ([300, 64, 65, 1], [3, 64, 1, 1], 7, 1, 48, 5, 0),
+    ([200, 129], [200, 100], 6, 3, 128, 16, 0),
+    ([500, 77, 300], [30, 77, 1], 8, 2, 64, 16, 37),
+    ([90], [90], 5, 5, 32, 8, 64),
+    ([257, 31], [2, 31], 40, 2, 16, 32, 0),  # a group of 20 heads
+]
+
+
+@pytest.mark.parametrize("case", range(len(CASES)))
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_tiled_kernels(dtype, case):
+    lens, q_lens, n_q, n_kv, d, page, window = CASES[case]
+    q, kv, table, q_start, seq_lens = make_attention_case(dtype, lens, q_lens, n_q, n_kv, d, page, seed=case)
+    scale = d ** -0.5
+    ref = attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, scale, window)
+    from slipstream_b200.engine.context import query_tiles_host
+    ql = np.asarray(q_lens, dtype=np.int32)
+    out = torch.full((q.shape[0], n_q * d), float("nan"), device=DEV, dtype=dtype)
+    req, q0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(ql, 16))
+    ops().paged_attention_simt(q.view(q.shape[0], -1), n_q * d, out, kv, table, req, q0, q_start, seq_lens,
+                               n_q, n_kv, d, scale, window)
+    assert rel_err(out.view_as(ref).cpu(), ref) < tol(dtype, 3e-6, 1e-2)
+    if dtype == torch.bfloat16:
+        out2 = torch.full_like(out, float("nan"))
+        req, r0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(ql * (n_q // n_kv), 64))
+        ops().paged_attention_prefill(q.view(q.shape[0], -1), n_q * d, out2, kv, table, req, r0, q_start, seq_lens,
+                                      n_q, n_kv, d, scale, window)
+        assert rel_err(out2.view_as(ref).cpu(), ref) < 1e-2
+    ops().check_errors(torch.device(DEV))
+
+
+@pytest.mark.parametrize("slices", [1, 2, 5, 32])
+@pytest.mark.parametrize("n_q, n_kv, d, page, window", [(28, 4, 128, 16, 0), (6, 6, 16, 4, 0), (40, 2, 64, 7, 0),
+                                                         (8, 2, 32, 16, 100), (3, 1, 256, 16, 0)])
+def test_split_decode_attention(slices, n_q, n_kv, d, page, window):
+    lens = [1, 63, 64, 65, 700, 129, 2000]
+    q, kv, table, q_start, seq_lens = make_attention_case(torch.bfloat16, lens, [1] * len(lens), n_q, n_kv, d, page, seed=d)
+    scale = d ** -0.5
+    ref = attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, scale, window)
+    out = torch.full((q.shape[0], n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops().paged_attention_decode(q.view(q.shape[0], -1), n_q * d, out, kv, table, q_start, seq_lens, len(lens),
+                                 n_q, n_kv, d, scale, window, n_slices=slices)
+    assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2
+    ops().check_errors(torch.device(DEV))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_far_key_among_hundreds_is_found(dtype):
+    """One key 700 tokens back matches the last query far better than all others: its value must
+    dominate the output, through every kernel."""
+    n_q, n_kv, d, page = 4, 2, 64, 16
+    for q_len in (1, 40):
+        q, kv, table, q_start, seq_lens = make_attention_case(dtype, [900, 50], [q_len, 3], n_q, n_kv, d, page, seed=1, sharp=197)
+        ref = attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, 1.0, 0)
+        row = q_len - 1
+        assert ref[row].min() > 4.9  # the oracle itself sees the far key
+        from slipstream_b200.engine.context import query_tiles_host
+        ql = np.asarray([q_len, 3], dtype=np.int32)
+        out = torch.zeros((q.shape[0], n_q * d), device=DEV, dtype=dtype)
+        req, q0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(ql, 16))
+        ops().paged_attention_simt(q.view(q.shape[0], -1), n_q * d, out, kv, table, req, q0, q_start, seq_lens, n_q, n_kv, d, 1.0, 0)
+        assert out[row].float().min() > 4.9 and rel_err(out.view_as(ref).cpu(), ref) < tol(dtype, 3e-6, 1e-2)
+        if dtype == torch.bfloat16:
+            out.zero_()
+            req, r0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(ql * 2, 64))
+            ops().paged_attention_prefill(q.view(q.shape[0], -1), n_q * d, out, kv, table, req, r0, q_start, seq_lens, n_q, n_kv, d, 1.0, 0)
+            assert out[row].float().min() > 4.9 and rel_err(out.view_as(ref).cpu(), ref) < 1e-2
+
+
+# --------------------------------------------------------------------------- sampling
+
+def test_argmax_lowest_index_wins_ties():
+    logits = torch.randn(9, 152064, device=DEV)
+    logits[2, 777] = logits[2, 70000] = 50.0
+    logits[5] = 0.0
+    got = ops().argmax(logits).cpu()
+    want = logits.argmax(-1).cpu()
+    assert got[2] == 777 and got[5] == 0
+    assert all(int(got[i]) == int(want[i]) for i in (0, 1, 3, 4, 6, 7, 8))
