@@ -94,8 +94,38 @@ class StepInputError(ValueError):
     """A step was asked for something it cannot run (checked on the host before any launch)."""
 
 
-def build_context(entries: list[StepEntry], cache: CacheManager, vocab_size: int, device: torch.device,
-                  reserve: bool = True) -> StepContext:
+@dataclass
+class HostPlan:
+    """The step's metadata as host arrays, before it goes to the device."""
+
+    entries: list[StepEntry]
+    q_lens: np.ndarray
+    token_ids: np.ndarray
+    positions: np.ndarray
+    q_start: np.ndarray
+    seq_lens: np.ndarray
+    slots: np.ndarray
+    first: np.ndarray
+    logit_rows: np.ndarray
+    tables: np.ndarray  # [groups, R, max_blocks]
+    slot_maps: np.ndarray  # [groups, N]
+    page_size: int
+
+    @property
+    def num_requests(self) -> int:
+        return self.q_lens.size
+
+    @property
+    def num_tokens(self) -> int:
+        return self.token_ids.size
+
+    @property
+    def is_decode_only(self) -> bool:
+        return bool((self.q_lens == 1).all())
+
+
+def plan_step(entries: list[StepEntry], cache: CacheManager, vocab_size: int, reserve: bool = True) -> HostPlan:
+    """Check the entries, reserve their pages and lay the step's metadata out in host arrays."""
     if not entries:
         raise StepInputError("a step needs at least one entry")
     seen: set[object] = set()
@@ -120,7 +150,7 @@ def build_context(entries: list[StepEntry], cache: CacheManager, vocab_size: int
             cache.reserve(e.request_id, len(e.tokens))
     reqs = [cache.get(e.request_id) for e in entries]
     before = np.fromiter((r.length for r in reqs), dtype=np.int32, count=R)
-    seq_lens = before + q_lens
+    seq_lens = (before + q_lens).astype(np.int32)
     q_start = np.zeros(R + 1, dtype=np.int32)
     np.cumsum(q_lens, out=q_start[1:])
     row_req = np.repeat(np.arange(R, dtype=np.int32), q_lens)
@@ -136,15 +166,22 @@ def build_context(entries: list[StepEntry], cache: CacheManager, vocab_size: int
     slot_maps = np.empty((n_groups, N), dtype=np.int32)
     for g in range(n_groups):
         for i, r in enumerate(reqs):
-            t = r.tables[g]
+            t = r.tables[g][:max_blocks]
             tables[g, i, : len(t)] = t
         pages = tables[g][row_req, positions // ps]
         if (pages < 0).any():
             raise StepInputError("a new token falls on a block without a page")
         slot_maps[g] = pages * ps + positions % ps
+    return HostPlan(entries, q_lens, token_ids.astype(np.int32), positions, q_start, seq_lens, slots, first,
+                    logit_rows, tables, slot_maps, ps)
 
-    parts = [token_ids.astype(np.int32), positions, q_start, seq_lens.astype(np.int32), slots, first,
-             logit_rows, tables.reshape(-1), slot_maps.reshape(-1)]
+
+def to_device(plan: HostPlan, device: torch.device) -> StepContext:
+    """One host buffer, one copy, then views of it."""
+    R, N = plan.num_requests, plan.num_tokens
+    n_groups, _, max_blocks = plan.tables.shape
+    parts = [plan.token_ids, plan.positions, plan.q_start, plan.seq_lens, plan.slots, plan.first,
+             plan.logit_rows, plan.tables.reshape(-1), plan.slot_maps.reshape(-1)]
     sizes = [p.size for p in parts]
     host = torch.empty(int(sum(sizes)), dtype=torch.int32, pin_memory=torch.cuda.is_available())
     np.concatenate(parts, out=host.numpy())
@@ -155,10 +192,16 @@ def build_context(entries: list[StepEntry], cache: CacheManager, vocab_size: int
     for g in range(n_groups):
         groups.append(GroupMeta(
             block_tables=cut[7][g * R * max_blocks: (g + 1) * R * max_blocks].view(R, max_blocks),
-            slot_mapping=cut[8][g * N: (g + 1) * N], page_size=ps, max_blocks=max_blocks))
+            slot_mapping=cut[8][g * N: (g + 1) * N], page_size=plan.page_size, max_blocks=max_blocks))
     ctx = StepContext(num_tokens=N, num_requests=R, token_ids=cut[0], positions=cut[1], q_start=cut[2],
                       seq_lens=cut[3], state_slots=cut[4], first_chunk=cut[5], logit_rows=cut[6],
-                      groups=groups, q_lens_host=q_lens, seq_lens_host=seq_lens.astype(np.int32),
-                      request_ids=[e.request_id for e in entries], device=device, num_logits=logit_rows.size)
+                      groups=groups, q_lens_host=plan.q_lens, seq_lens_host=plan.seq_lens,
+                      request_ids=[e.request_id for e in plan.entries], device=device,
+                      num_logits=plan.logit_rows.size)
     ctx.extras["host_buffer"] = host  # keep the pinned buffer alive until the copy has run
     return ctx
+
+
+def build_context(entries: list[StepEntry], cache: CacheManager, vocab_size: int, device: torch.device,
+                  reserve: bool = True) -> StepContext:
+    return to_device(plan_step(entries, cache, vocab_size, reserve), device)

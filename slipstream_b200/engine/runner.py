@@ -25,7 +25,8 @@ from slipstream_b200.registry import load_config
 from slipstream_b200.weights.loader import load_weights
 from slipstream_b200.weights.random_init import random_weights_on_device
 
-from .context import StepContext, StepEntry, StepInputError, build_context
+from .context import StepContext, StepEntry, StepInputError, build_context, plan_step, to_device
+from .graphs import DecodeGraph, bucket_for
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -76,7 +77,9 @@ class ModelRunner:
         self.has_state = any(self.model.entry_state)
         self.steps_run = 0
         self.last_h2d_bytes = 0
-        self.use_cuda_graphs = use_cuda_graphs
+        self.use_cuda_graphs = (use_cuda_graphs and self.device.type == "cuda"
+                                and all(getattr(p, "cuda_graph_safe", False) for p in self.model.parts()))
+        self._graphs: dict[int, DecodeGraph] = {}
 
     # ------------------------------------------------------------------ requests
     def admit(self, request_id: object) -> None:
@@ -99,9 +102,18 @@ class ModelRunner:
         for e in entries:
             if e.request_id not in self.cache:
                 self.admit(e.request_id)
-        ctx = build_context(entries, self.cache, self.config.vocab_size, self.device)
-        self.last_h2d_bytes = ctx.extras["host_buffer"].numel() * 4
-        logits = self.run(ctx)
+        plan = plan_step(entries, self.cache, self.config.vocab_size)
+        bucket = bucket_for(plan.num_requests) if self.use_cuda_graphs and plan.is_decode_only else None
+        if bucket is not None and bucket <= max(self.max_num_seqs, 1) * 2:
+            graph = self._graphs.get(bucket)
+            if graph is None:
+                graph = self._graphs[bucket] = DecodeGraph(self, bucket)
+            self.last_h2d_bytes = graph.h2d_bytes
+            logits = graph.run(plan)
+        else:
+            ctx = to_device(plan, self.device)
+            self.last_h2d_bytes = ctx.extras["host_buffer"].numel() * 4
+            logits = self.run(ctx)
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1

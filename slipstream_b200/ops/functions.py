@@ -372,8 +372,8 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
         return
     group = n_q // n_kv
     if ctx.is_decode_only:
-        slices = ctx.extras.get("decode_slices") or decode_slices(ctx.num_requests, n_kv, group,
-                                                                 min(ctx.max_seq_len, window or ctx.max_seq_len))
+        longest = ctx.extras.get("static_max_seq_len") or ctx.max_seq_len  # fixed when the step is captured
+        slices = decode_slices(ctx.num_requests, n_kv, group, min(longest, window or longest))
         scratch = ctx.extras.get(("decode_scratch", n_q, head_dim))
         paged_attention_decode(qkv, qkv.shape[1], out, kv, block_tables, ctx.q_start, ctx.seq_lens,
                                ctx.num_requests, n_q, n_kv, head_dim, scale, window, slices, scratch)

@@ -19,6 +19,8 @@ from .base import MIXERS, CacheSpec, LayerBinding, Mixer, PositionEncoding, Runt
 
 @MIXERS.register("paged_attention")
 class PagedAttention(Mixer):
+    cuda_graph_safe = True
+
     def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: PositionEncoding, qkv_bias: bool = True, out_bias: bool = False,
                  window: int | None = None, scale: float | None = None) -> None:

@@ -80,7 +80,13 @@ class Runtime:
 # --------------------------------------------------------------------------- parts
 
 class Part:
-    """Base of all parts.  ``bind`` receives the loaded tensors by full name."""
+    """Base of all parts.  ``bind`` receives the loaded tensors by full name.
+
+    ``cuda_graph_safe``: the part's forward launches the same kernels with the same grids for every
+    decode step of a given batch size and never synchronises with the host, so a decode step through
+    it may be captured in a CUDA graph.  Parts that do not say so run eagerly."""
+
+    cuda_graph_safe = False
 
     def weight_specs(self) -> list[WeightSpec]:
         return []

@@ -11,6 +11,8 @@ from .base import BLOCKS, Block, FeedForward, LayerBinding, Mixer, Norm, Part
 
 @BLOCKS.register("pre_norm")
 class PreNormBlock(Block):
+    cuda_graph_safe = True
+
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ffn_norm: Norm) -> None:
         self.mixer = mixer
         self.feed_forward = feed_forward

@@ -12,6 +12,8 @@ from .base import Part, Runtime, WeightSpec
 
 
 class TokenEmbedding(Part):
+    cuda_graph_safe = True
+
     def __init__(self, name: str, vocab_size: int, hidden_size: int) -> None:
         self.name = name
         self.vocab_size = vocab_size
@@ -29,6 +31,8 @@ class TokenEmbedding(Part):
 
 
 class LMHead(Part):
+    cuda_graph_safe = True
+
     def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: str | None) -> None:
         self.name = name
         self.vocab_size = vocab_size

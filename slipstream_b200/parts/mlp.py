@@ -13,6 +13,8 @@ from .base import FEED_FORWARDS, FeedForward, Runtime, WeightSpec
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLUFeedForward(FeedForward):
+    cuda_graph_safe = True
+
     def __init__(self, name: str, hidden_size: int, intermediate_size: int, bias: bool = False) -> None:
         self.name = name
         self.hidden_size = hidden_size

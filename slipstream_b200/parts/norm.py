@@ -16,6 +16,8 @@ from .base import NORMS, Norm, Runtime, WeightSpec
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
+    cuda_graph_safe = True
+
     def __init__(self, name: str, size: int, eps: float) -> None:
         self.name = name
         self.size = size

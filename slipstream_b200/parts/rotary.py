@@ -15,6 +15,8 @@ from .base import POSITION_ENCODINGS, PositionEncoding, Runtime
 
 @POSITION_ENCODINGS.register("rotary")
 class RotaryEncoding(PositionEncoding):
+    cuda_graph_safe = True
+
     def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None) -> None:
         self.head_dim = head_dim
         self.theta = float(theta)
@@ -38,3 +40,5 @@ class RotaryEncoding(PositionEncoding):
 @POSITION_ENCODINGS.register("none")
 class NoPositionEncoding(PositionEncoding):
     """Queries and keys are used as projected."""
+
+    cuda_graph_safe = True
