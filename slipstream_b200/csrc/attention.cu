@@ -76,3 +76,67 @@ extern "C" int ss_attn_decode_mma(const void* q, int64_t q_stride, void* out, in
                                                                          q_start, n_q, n_slices);
     return SS_LAUNCH_CHECK();
 }
+
+// ---------------------------------------------------------------- the entry point that allocates nothing
+#include "no_alloc.h"
+
+// Scratch of ss_attn_decode_noalloc.  In host code this name is only a handle for
+// cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float ss_noalloc_scratch[SS_NOALLOC_SCRATCH_FLOATS];
+
+#define SS_NOALLOC_MAX_DEVICES 64
+static float* ss_noalloc_ptr[SS_NOALLOC_MAX_DEVICES];  // device address of the array, per device
+
+extern "C" int64_t ss_attn_decode_noalloc_floats(int n_requests, int n_q, int n_slices) {
+    return (int64_t)n_requests * n_q * n_slices * (HEAD_DIM + 1);
+}
+
+extern "C" const char* ss_attn_decode_noalloc_message(int code) {
+    switch (code) {
+        case 0: return "ok";
+        case SS_NOALLOC_TOO_LARGE:
+            return "the call needs more than the 8 MiB of built-in scratch (n_requests * n_q * n_slices * "
+                   "(head size + 1) floats): use fewer slices or requests, or ss_attn_decode_mma with scratch of your own";
+        case SS_NOALLOC_BAD_ARGUMENT: return "a count is not positive or n_q is not a multiple of n_kv";
+        case SS_NOALLOC_SETUP_FAILED: return "could not look up the scratch array on the current device";
+        default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown code";
+    }
+}
+
+extern "C" int ss_attn_decode_noalloc(const void* q, int64_t q_stride, void* out, int64_t out_stride,
+                                      const void* kv, const int32_t* block_tables, int max_blocks,
+                                      int n_requests, const int32_t* q_start, const int32_t* seq_lens, int n_q,
+                                      int n_kv, int page_size, int64_t num_pages, float scale, int window,
+                                      int n_slices, int* err, cudaStream_t stream) {
+    if (n_requests <= 0 || n_q <= 0 || n_kv <= 0 || n_slices < 1 || n_q % n_kv != 0 || page_size <= 0)
+        return SS_NOALLOC_BAD_ARGUMENT;
+    const int64_t floats = ss_attn_decode_noalloc_floats(n_requests, n_q, n_slices);
+    if (floats > (int64_t)SS_NOALLOC_SCRATCH_FLOATS) return SS_NOALLOC_TOO_LARGE;
+
+    // set-up, once per device, with that device current
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= SS_NOALLOC_MAX_DEVICES)
+        return SS_NOALLOC_SETUP_FAILED;
+    float* scratch = ss_noalloc_ptr[device];
+    if (scratch == nullptr) {
+        if (cudaGetSymbolAddress((void**)&scratch, ss_noalloc_scratch) != cudaSuccess || scratch == nullptr)
+            return SS_NOALLOC_SETUP_FAILED;
+        ss_noalloc_ptr[device] = scratch;
+    }
+    float* part_o = scratch;
+    float* part_lse = scratch + (int64_t)n_requests * n_q * n_slices * HEAD_DIM;
+
+    constexpr int smem = mma_smem_bytes<HEAD_DIM>();
+    static int configured = set_smem(attn_decode_mma<HEAD_DIM>, smem);
+    if (configured != 0) return configured;
+    const int G = n_q / n_kv;
+    dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
+    attn_decode_mma<HEAD_DIM><<<grid, MMA_THREADS, smem, stream>>>(
+        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
+        seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, part_o, part_lse, err);
+    int rc = SS_LAUNCH_CHECK();
+    if (rc != 0 || n_slices == 1) return rc;
+    attn_merge_kernel<HEAD_DIM><<<dim3(n_requests, n_q), 128, 0, stream>>>(part_o, part_lse, (bf16*)out, out_stride,
+                                                                         q_start, n_q, n_slices);
+    return SS_LAUNCH_CHECK();
+}

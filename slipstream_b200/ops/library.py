@@ -68,7 +68,7 @@ def _build_dir() -> Path:
 
 def _digest(sources: list[Path], flags: list[str]) -> str:
     h = hashlib.sha256()
-    for path in sorted(set(list(CSRC.glob("*.cuh")) + sources)):
+    for path in sorted(set(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + sources)):
         h.update(path.name.encode())
         h.update(path.read_bytes())
     h.update(" ".join(flags).encode())
