@@ -109,6 +109,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run just this part and print a short line (for profiling)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU only (this engine uses a single device); got --gpus {args.gpus}")
@@ -175,6 +177,24 @@ def main() -> int:
     def decode_bytes(batch: int, steps: int, warmup: int) -> float:
         mean_ctx = args.prompt_len + warmup + (steps + 1) / 2
         return runner.weight_bytes_per_step() + batch * mean_ctx * runner.kv_bytes_per_token()
+
+    if args.only == "decode":
+        value, ms_step, launches = decode_device(args.batch, args.steps, args.warmup, "d")
+        print(json.dumps({"only": "decode", "batch": args.batch, "tokens_per_s": round(value, 1),
+                          "ms_per_step": round(ms_step, 4), "gpu_launches": launches}))
+        return 0
+    if args.only == "prefill":
+        T = 2048
+        for w in range(args.warmup + args.steps):
+            toks = rng.integers(0, vocab, T).tolist()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            runner.step([StepEntry(f"p{w}", toks, [T - 1])])
+            stop.record()
+            torch.cuda.synchronize()
+            runner.release(f"p{w}")
+        print(json.dumps({"only": "prefill", "tokens": T, "ms_last": round(start.elapsed_time(stop), 3)}))
+        return 0
 
     # ---- headline: decode at --batch, device-timed, with clocks sampled
     with ClockSampler() as clocks:

@@ -60,7 +60,7 @@ def sharpen(folder, factor=8.0):
     tensors = {}
     with safe_open(str(path), framework="pt") as handle:
         for key in handle.keys():
-            t = handle.get_tensor(key)
+            t = handle.get_tensor(key).clone()
             if ".q_proj." in key or ".k_proj." in key:
                 t = (t.float() * factor).to(t.dtype)
             if "mlp." in key or "embed_tokens" in key or "lm_head" in key:

@@ -1,0 +1,138 @@
+"""Each part of the model alone, built with sizes of its own and random tensors, against the plain
+functions of tests/plain_qwen2.py."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 1e-5, torch.bfloat16: 2e-2}
+
+
+def runtime(dtype):
+    from slipstream_b200.parts import Runtime
+    return Runtime(DEV, dtype)
+
+
+def rel(got, ref):
+    return ((got.double().cpu() - ref.double()).abs().max() / ref.double().abs().max()).item()
+
+
+def draw(part, dtype, seed=0, scale=1.0):
+    """Random tensors for a part's weight specs: (device tensors in the compute dtype, float64 copies of them)."""
+    g = torch.Generator().manual_seed(seed)
+    dev, ref = {}, {}
+    for spec in part.weight_specs():
+        t = torch.randn(spec.shape, generator=g) * (0.3 * scale if len(spec.shape) == 2 else 0.2)
+        if spec.init[0] == "one_plus_normal":
+            t = t + 1
+        dev[spec.name] = t.to(dtype).to(DEV)
+        ref[spec.name] = dev[spec.name].double().cpu()
+    return dev, ref
+
+
+def single_request_ctx(cache, request_id, tokens_or_n, vocab=10 ** 6):
+    from slipstream_b200.engine.context import StepEntry, build_context
+    n = tokens_or_n if isinstance(tokens_or_n, int) else len(tokens_or_n)
+    tokens = list(range(n)) if isinstance(tokens_or_n, int) else tokens_or_n
+    if request_id not in cache:
+        cache.admit(request_id)
+    ctx = build_context([StepEntry(request_id, tokens, [])], cache, vocab, DEV)
+    cache.commit(request_id, n)
+    return ctx
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm_part(dtype):
+    from slipstream_b200.parts import RMSNorm
+    part = RMSNorm("n", 200, 1e-4)
+    dev, ref = draw(part, dtype)
+    part.bind(dev, runtime(dtype))
+    x = torch.randn(7, 200)
+    got = part.forward(x.to(DEV))
+    assert got.dtype == dtype and rel(got, plain.rms_norm(x.double(), ref["n.weight"], 1e-4)) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu_feed_forward_part(dtype):
+    from slipstream_b200.parts import SwiGLUFeedForward
+    for bias in (False, True):
+        part = SwiGLUFeedForward("m", 72, 200, bias=bias)
+        dev, ref = draw(part, dtype, seed=3)
+        part.bind(dev, runtime(dtype))
+        x = torch.randn(11, 72).to(dtype)
+        got = part.forward(x.to(DEV), None)
+        assert rel(got, plain.swiglu_mlp(x.double(), ref, "m")) < TOL[dtype]
+        assert part.weight_bytes() == 3 * 72 * 200 * (4 if dtype == torch.float32 else 2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_lm_head_parts(dtype):
+    from slipstream_b200.parts import LMHead, TokenEmbedding
+    emb, head = TokenEmbedding("e", 301, 40), LMHead("h", 301, 40, tied_to="e.weight")
+    dev, ref = draw(emb, dtype)
+    dev["h.weight"] = dev["e.weight"]
+    emb.bind(dev, runtime(dtype)); head.bind(dev, runtime(dtype))
+    ids = torch.tensor([0, 300, 5, 5], dtype=torch.int32, device=DEV)
+    assert torch.equal(emb.forward(ids).cpu(), ref["e.weight"][ids.long().cpu()].float())
+    x = torch.randn(3, 40).to(dtype)
+    logits = head.forward(x.to(DEV))
+    assert logits.dtype == torch.float32 and rel(logits, x.double() @ ref["e.weight"].T) < TOL[dtype] / 2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv_heads, d, page, bias", [(6, 2, 32, 8, True), (5, 1, 16, 4, False), (4, 4, 64, 16, True)])
+def test_attention_part_in_two_portions_and_decoding(dtype, heads, kv_heads, d, page, bias):
+    """The mixer alone: a prompt portion, a second portion, then single tokens, against the plain
+    attention over the whole sequence."""
+    from slipstream_b200.cache import CacheManager, GroupLayout, PagedStore
+    from slipstream_b200.parts import LayerBinding, PagedAttention, RotaryEncoding
+    hidden, theta, n = 56, 30000.0, 45
+    part = PagedAttention("a", hidden, heads, kv_heads, d, RotaryEncoding(d, theta), qkv_bias=bias)
+    dev, ref = draw(part, dtype, seed=d, scale=0.5)  # scores of order one: keys matter, but no hard arg-max
+    part.bind(dev, runtime(dtype))
+    layouts = [GroupLayout(part.cache_spec(), 1)]
+    cache = CacheManager(layouts, 16, page, 2, 256)
+    store = PagedStore(layouts, 16, page, dtype, DEV, [[]], 2)
+    binding = LayerBinding(kv=store.kv[0][0], group=0)
+    x = torch.randn(n, hidden).to(dtype)
+    s = {"n_q": heads, "n_kv": kv_heads, "head_dim": d, "theta": theta}
+    want = plain.attention_block(x.double(), torch.arange(n), ref, "a", s)
+    outs, i = [], 0
+    for take in (20, 13, 1, 1, 2, 1, 7):
+        ctx = single_request_ctx(cache, "r", take)
+        outs.append(part.forward(x[i:i + take].to(DEV).contiguous(), ctx, binding))
+        i += take
+    assert i == n and rel(torch.cat(outs), want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_pre_norm_block(dtype):
+    from slipstream_b200.cache import CacheManager, GroupLayout, PagedStore
+    from slipstream_b200.parts import (LayerBinding, PagedAttention, PreNormBlock, RMSNorm, RotaryEncoding,
+                                       SwiGLUFeedForward)
+    hidden, heads, kv_heads, d, inter, eps, theta, n = 48, 3, 1, 16, 100, 1e-5, 1e4, 19
+    prefix = "model.layers.0"
+    block = PreNormBlock(PagedAttention(f"{prefix}.self_attn", hidden, heads, kv_heads, d, RotaryEncoding(d, theta)),
+                         SwiGLUFeedForward(f"{prefix}.mlp", hidden, inter),
+                         RMSNorm(f"{prefix}.input_layernorm", hidden, eps),
+                         RMSNorm(f"{prefix}.post_attention_layernorm", hidden, eps))
+    dev, ref = {}, {}
+    for k, child in enumerate(block.children()):
+        a, b = draw(child, dtype, seed=k)
+        dev.update(a); ref.update(b)
+    for child in block.children():
+        child.bind(dev, runtime(dtype))
+    layouts = [GroupLayout(block.mixer.cache_spec(), 1)]
+    cache = CacheManager(layouts, 8, 4, 2, 64)
+    store = PagedStore(layouts, 8, 4, dtype, DEV, [[]], 2)
+    x = torch.randn(n, hidden)
+    s = {"n_q": heads, "n_kv": kv_heads, "head_dim": d, "theta": theta, "eps": eps}
+    want = plain.decoder_layer(x.double(), torch.arange(n), ref, 0, s)
+    ctx = single_request_ctx(cache, "r", n)
+    residual, pending = block.forward(x.to(DEV).clone(), None, ctx, LayerBinding(kv=store.kv[0][0], group=0))
+    got = residual.double().cpu() + pending.double().cpu()  # the last add is left to the next norm
+    assert rel(got, want) < TOL[dtype]

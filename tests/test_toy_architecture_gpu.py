@@ -1,0 +1,228 @@
+"""A toy architecture defined HERE, registered, built and stepped without a change to the package:
+a mixer with fixed-size state of its own (a running mean), an attention layer with a window, a block
+that the execution order names twice, and an entry that reads another entry's cache.  It is checked
+against a plain whole-sequence restatement written in this file, under several ways of cutting."""
+import json
+from dataclasses import asdict, dataclass
+from typing import ClassVar
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+from conftest import random_tokens
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    architecture: ClassVar[str] = "ToyMixForCausalLM"
+    vocab_size: int = 97
+    hidden_size: int = 40
+    num_hidden_layers: int = 4
+    max_position_embeddings: int = 512
+    torch_dtype: str = "float32"
+    eos_token_id: int | None = None
+    heads: int = 5
+    kv_heads: int = 1
+    head_dim: int = 16
+    inter: int = 72
+    eps: float = 1e-5
+    theta: float = 2000.0
+    window: int = 9
+
+    @classmethod
+    def from_dict(cls, data, generation=None):
+        return cls(**{k: v for k, v in data.items() if k in cls.__dataclass_fields__})
+
+    def to_dict(self):
+        return dict(asdict(self), architectures=[self.architecture])
+
+
+def define_toy():
+    """Everything a user would write to add a mixer and an architecture."""
+    from slipstream_b200.models.decoder import DecoderLM, ExecEntry
+    from slipstream_b200.parts import (MIXERS, LMHead, Mixer, PagedAttention, PreNormBlock, RMSNorm, RotaryEncoding,
+                                       StateSpec, SwiGLUFeedForward, TokenEmbedding, WeightSpec)
+    from slipstream_b200.registry import register_architecture, unregister_architecture
+
+    MIXERS.unregister("running_mean")
+
+    @MIXERS.register("running_mean")
+    class RunningMean(Mixer):
+        """y_t = W * mean(x_0 .. x_t): needs the sum and the count of what it has seen, per request."""
+
+        def __init__(self, name, hidden):
+            self.name, self.hidden = name, hidden
+
+        def weight_specs(self):
+            return [WeightSpec(f"{self.name}.mix.weight", (self.hidden, self.hidden), init=("normal", 0.3))]
+
+        def state_specs(self):
+            return [StateSpec("sum", (self.hidden,), torch.float32), StateSpec("count", (1,), torch.float32)]
+
+        def bind(self, weights, runtime):
+            super().bind(weights, runtime)
+            self.weight = weights[f"{self.name}.mix.weight"]
+
+        def forward(self, x, ctx, layer):
+            out = torch.empty_like(x)
+            starts = ctx.q_start.tolist()
+            for r, slot in enumerate(ctx.state_slots.tolist()):
+                rows = x[starts[r]: starts[r + 1]].float()
+                total = layer.state["sum"][slot] + rows.cumsum(0)
+                count = layer.state["count"][slot] + torch.arange(1, rows.shape[0] + 1, device=x.device)[:, None]
+                out[starts[r]: starts[r + 1]] = ((total / count) @ self.weight.float().T).to(x.dtype)
+                layer.state["sum"][slot] = total[-1]
+                layer.state["count"][slot] = count[-1]
+            return out
+
+    def build(c: ToyConfig):
+        rotary = RotaryEncoding(c.head_dim, c.theta)
+
+        def block(i, mixer):
+            p = f"toy.layers.{i}"
+            return PreNormBlock(mixer, SwiGLUFeedForward(f"{p}.mlp", c.hidden_size, c.inter),
+                                RMSNorm(f"{p}.norm1", c.hidden_size, c.eps), RMSNorm(f"{p}.norm2", c.hidden_size, c.eps))
+
+        def attention(i, window):
+            return PagedAttention(f"toy.layers.{i}.attn", c.hidden_size, c.heads, c.kv_heads, c.head_dim, rotary,
+                                  qkv_bias=False, window=window)
+
+        blocks = [block(0, attention(0, None)), block(1, MIXERS.get("running_mean")("toy.layers.1", c.hidden_size)),
+                  block(2, attention(2, c.window)), block(3, attention(3, None))]
+        # block 0 runs twice (pages of its own each time); the last entry reads the pages entry 0 wrote
+        order = [ExecEntry(0), ExecEntry(1), ExecEntry(2), ExecEntry(0), ExecEntry(3, cache_of=0)]
+        return DecoderLM(c, TokenEmbedding("toy.embed", c.vocab_size, c.hidden_size), blocks,
+                         RMSNorm("toy.norm", c.hidden_size, c.eps), LMHead("toy.head", c.vocab_size, c.hidden_size, None),
+                         order=order)
+
+    unregister_architecture("ToyMixForCausalLM")
+    register_architecture("ToyMixForCausalLM", ToyConfig, build)
+    return build
+
+
+# --------------------------------------------------------------------------- plain restatement
+
+def plain_attention(x, w, prefix, c, window, kv_from=None):
+    T = x.shape[0]
+    q = (x @ w[f"{prefix}.q_proj.weight"].T).view(T, c.heads, c.head_dim)
+    k = (x @ w[f"{prefix}.k_proj.weight"].T).view(T, c.kv_heads, c.head_dim)
+    v = (x @ w[f"{prefix}.v_proj.weight"].T).view(T, c.kv_heads, c.head_dim)
+    cos, sin = plain.rotary_tables(torch.arange(T), c.head_dim, c.theta, x.dtype)
+    q, k = plain.apply_rotary(q, cos, sin), plain.apply_rotary(k, cos, sin)
+    made = (k, v)
+    if kv_from is not None:
+        k, v = kv_from
+    g = c.heads // c.kv_heads
+    s = torch.einsum("ihd,jhd->hij", q, k.repeat_interleave(g, 1)) * c.head_dim ** -0.5
+    i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+    ok = j <= i
+    if window:
+        ok &= j > i - window
+    s = s.masked_fill(~ok[None], float("-inf"))
+    out = torch.einsum("hij,jhd->ihd", torch.softmax(s, -1), v.repeat_interleave(g, 1)).reshape(T, -1)
+    return out @ w[f"{prefix}.o_proj.weight"].T, made
+
+
+def plain_toy(c, w, tokens):
+    x = w["toy.embed.weight"][torch.as_tensor(tokens)]
+    T = x.shape[0]
+    kv0 = None
+    for pos, (i, kind) in enumerate([(0, "full"), (1, "mean"), (2, "window"), (0, "full"), (3, "shared")]):
+        p = f"toy.layers.{i}"
+        h = plain.rms_norm(x, w[f"{p}.norm1.weight"], c.eps)
+        if kind == "mean":
+            mixed = (h.cumsum(0) / torch.arange(1, T + 1)[:, None]) @ w[f"{p}.mix.weight"].T
+        else:
+            mixed, made = plain_attention(h, w, f"{p}.attn", c, c.window if kind == "window" else None,
+                                          kv_from=kv0 if kind == "shared" else None)
+            if pos == 0:
+                kv0 = made
+        x = x + mixed
+        x = x + plain.swiglu_mlp(plain.rms_norm(x, w[f"{p}.norm2.weight"], c.eps), w, f"{p}.mlp")
+    return plain.rms_norm(x, w["toy.norm.weight"], c.eps) @ w["toy.head.weight"].T
+
+
+# --------------------------------------------------------------------------- the test
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_steps_like_its_plain_restatement(tmp_path, dtype):
+    from safetensors.torch import load_file, save_file
+    from slipstream_b200.engine.runner import ModelRunner, StepEntry
+    from slipstream_b200.registry import unregister_architecture
+    from slipstream_b200.weights.random_init import write_random_model
+
+    define_toy()
+    try:
+        c = ToyConfig()
+        write_random_model(c, tmp_path, seed=5)
+        tensors = {k: v.clone() for k, v in load_file(str(tmp_path / "model.safetensors")).items()}  # not views of the file
+        for k in tensors:  # far from uniform attention, visible feed-forward
+            if "q_proj" in k or "k_proj" in k:
+                tensors[k] = tensors[k] * 12
+            elif tensors[k].dim() == 2 and "mix" not in k:
+                tensors[k] = tensors[k] * 4
+        save_file(tensors, str(tmp_path / "model.safetensors"))
+        w = {k: (v.bfloat16() if dtype == "bfloat16" and v.dim() == 2 else v).double() for k, v in tensors.items()}
+
+        page = 4
+        runner = ModelRunner(str(tmp_path), dtype=dtype, page_size=page, num_pages=40, max_num_seqs=3)
+        model = runner.model
+        # two cache groups: all keys (three writers: entries 0 and 3; entry 4 shares 0's) and a window
+        specs = [(l.spec.window, l.num_entries) for l in model.group_layouts]
+        assert sorted(specs, key=str) == sorted([(None, 2), (c.window, 1)], key=str)
+        assert not runner.use_cuda_graphs  # the toy mixer did not declare itself safe to capture
+        assert [len(s) for s in model.entry_state] == [0, 2, 0, 0, 0]
+
+        reqs = {"a": random_tokens(c.vocab_size, 61, 1), "b": random_tokens(c.vocab_size, 30, 2), "c": random_tokens(c.vocab_size, 47, 3)}
+        want = {k: plain_toy(c, w, v).float() for k, v in reqs.items()}
+        tol = (3e-5 if dtype == "float32" else 4e-2)
+
+        def check(rows, what):
+            for k, ref in want.items():
+                err = (torch.cat(rows[k]) - ref).abs().max(dim=1).values
+                assert err.max() <= tol * ref.abs().max(), (what, k, int(err.argmax()), err.max().item())
+
+        # whole, each alone
+        rows = {}
+        for k, toks in reqs.items():
+            rows[k] = [runner.step([StepEntry(k, toks, list(range(len(toks))))]).cpu()]
+            runner.release(k)
+        check(rows, "whole")
+        # portions and single tokens, all three live at once; windowed pages are given back on the way
+        rows = {k: [] for k in reqs}
+        at = {k: 0 for k in reqs}
+        sizes = {"a": [7, 1, 1, 13, 2, 1, 30, 1, 5], "b": [2, 2, 1, 1, 1, 20, 3], "c": [40, 1, 1, 1, 1, 1, 1, 1]}
+        held_window_pages = []
+        for step in range(9):
+            entries = []
+            for k in reqs:
+                if step < len(sizes[k]):
+                    take = sizes[k][step]
+                    entries.append(StepEntry(k, reqs[k][at[k]: at[k] + take], list(range(take))))
+                    at[k] += take
+            out = runner.step(entries).cpu()
+            i = 0
+            for e in entries:
+                rows[e.request_id].append(out[i: i + len(e.tokens)])
+                i += len(e.tokens)
+            runner.cache.check_invariants()
+            g = [n for n, l in enumerate(model.group_layouts) if l.spec.window][0]
+            held_window_pages.append(max(sum(p >= 0 for p in runner.cache.get(k).tables[g]) for k in reqs))
+        assert all(at[k] == len(reqs[k]) for k in reqs)
+        check(rows, "portions")
+        assert held_window_pages[-1] <= (c.window + page - 1) // page + 1
+        for k in reqs:
+            runner.release(k)
+        assert all(p.num_free == 40 for p in runner.cache.pools)
+        # a released slot is zeroed for its next request: replay "a" in the slot "c" used last
+        rows = {"a": [runner.step([StepEntry("a2", reqs["a"], list(range(61)))]).cpu()]}
+        err = (rows["a"][0] - want["a"]).abs().max()
+        assert err <= tol * want["a"].abs().max()
+        runner.check()
+    finally:
+        unregister_architecture("ToyMixForCausalLM")
