@@ -42,7 +42,35 @@ extern "C" int ss_embedding(const int32_t* ids, const void* table, float* out, i
 
 // One block per output row.  residual (float32) += delta, y = weight * round(x_hat).
 // With `rows`, output row i reads input row rows[i] and the residual stays as it is.
-template <typename T>
+// VEC = 4: the row is read once with 16-byte loads and kept in registers (hidden % 4 == 0 and
+// hidden <= 8 * blockDim); VEC = 1: any width, the row is read twice.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[4]) {
+        const uint2 t = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+        v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[4]) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 t;
+        t.x = *reinterpret_cast<uint32_t*>(&a);
+        t.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = t;
+    }
+};
+
+template <typename T, int VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                    const void* __restrict__ weight, int w_f32, T* __restrict__ y,
                                    const int32_t* __restrict__ rows, int hidden, float eps) {
@@ -53,6 +81,41 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     T* out = y + (int64_t)blockIdx.x * hidden;
     const bool write_back = (rows == nullptr) && (del != nullptr);
 
+    if (VEC == 4) {
+        float v[2][4];
+        float ss = 0.f;
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int j = (threadIdx.x + it * blockDim.x) * 4;
+            if (j < hidden) {
+                Vec4<float>::load(res + j, v[it]);
+                if (del) {
+                    float d[4];
+                    Vec4<T>::load(del + j, d);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) v[it][e] = __fadd_rn(v[it][e], d[e]);
+                }
+                if (write_back) Vec4<float>::store(res + j, v[it]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) ss = fmaf(v[it][e], v[it][e], ss);
+            }
+        }
+        ss = block_sum(ss, scratch);
+        const float rstd = 1.0f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int j = (threadIdx.x + it * blockDim.x) * 4;
+            if (j < hidden) {
+                float w[4], o[4];
+                if (w_f32) Vec4<float>::load(reinterpret_cast<const float*>(weight) + j, w);
+                else Vec4<T>::load(reinterpret_cast<const T*>(weight) + j, w);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o[e] = w[e] * to_float(from_float<T>(v[it][e] * rstd));
+                Vec4<T>::store(out + j, o);
+            }
+        }
+        return;
+    }
     float ss = 0.f;
     for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
         float v = res[j];
@@ -70,15 +133,28 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     }
 }
 
+template <typename T>
+static void launch_add_rmsnorm(float* residual, const void* delta, const void* weight, int w_f32, void* y,
+                               const int32_t* rows, int n_rows, int hidden, float eps, cudaStream_t stream) {
+    if (hidden % 4 == 0 && hidden <= 8 * 1024) {
+        int threads = ((hidden / 4 + 1) / 2 + 31) / 32 * 32;  // two vectors per thread at most
+        if (hidden / 4 <= 1024) threads = (hidden / 4 + 31) / 32 * 32;  // one vector per thread when it fits
+        threads = threads < 32 ? 32 : threads;
+        add_rmsnorm_kernel<T, 4><<<n_rows, threads, 0, stream>>>(residual, (const T*)delta, weight, w_f32, (T*)y, rows, hidden, eps);
+    } else {
+        const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+        add_rmsnorm_kernel<T, 1><<<n_rows, threads, 0, stream>>>(residual, (const T*)delta, weight, w_f32, (T*)y, rows, hidden, eps);
+    }
+}
+
 extern "C" int ss_add_rmsnorm(float* residual, const void* delta, const void* weight, int w_f32,
                               void* y, const int32_t* rows, int n_rows, int hidden, float eps,
                               int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     if (dtype == SS_BF16)
-        add_rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(residual, (const bf16*)delta, weight, w_f32, (bf16*)y, rows, hidden, eps);
+        launch_add_rmsnorm<bf16>(residual, delta, weight, w_f32, y, rows, n_rows, hidden, eps, stream);
     else
-        add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(residual, (const float*)delta, weight, w_f32, (float*)y, rows, hidden, eps);
+        launch_add_rmsnorm<float>(residual, delta, weight, w_f32, y, rows, n_rows, hidden, eps, stream);
     return SS_LAUNCH_CHECK();
 }
 
@@ -105,24 +181,49 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int32_t* __restrict
     const int off = slot >= 0 ? (int)(slot % page_size) : 0;
     const int half = rot_dim / 2;
 
-    // rotated pairs of queries and keys
-    const int n_rot = (n_q + n_kv) * half;
-    for (int idx = threadIdx.x; idx < n_rot; idx += blockDim.x) {
-        const int h = idx / half, i = idx - h * half;
-        T* head = row + (int64_t)h * D;
-        const float x1 = to_float(head[i]), x2 = to_float(head[i + half]);
-        const float angle = __fmul_rn(pos, inv_freq[i]);
-        const float c = cosf(angle), s = sinf(angle);
-        // q*cos + rotate_half(q)*sin, each product and the sum rounded as written
-        const T o1 = from_float<T>(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(-x2, s)));
-        const T o2 = from_float<T>(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s)));
-        if (h < n_q || slot < 0) {
-            head[i] = o1;
-            head[i + half] = o2;
-        } else {
-            T* dst = kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
-            dst[i] = o1;
-            dst[i + half] = o2;
+    // rotated pairs of queries and keys: a thread owns pair i and walks over the heads, so the sine and
+    // cosine of its angle are formed once
+    const int lanes = half > 0 ? blockDim.x / half : 0;  // threads that share a pair index
+    if (lanes > 0) {
+        const int i = threadIdx.x % half, h0 = threadIdx.x / half;
+        if (h0 < lanes) {
+            const float angle = __fmul_rn(pos, inv_freq[i]);
+            float s, c;
+            sincosf(angle, &s, &c);
+            for (int h = h0; h < n_q + n_kv; h += lanes) {
+                T* head = row + (int64_t)h * D;
+                const float x1 = to_float(head[i]), x2 = to_float(head[i + half]);
+                // q*cos + rotate_half(q)*sin, each product and the sum rounded as written
+                const T o1 = from_float<T>(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(-x2, s)));
+                const T o2 = from_float<T>(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s)));
+                if (h < n_q || slot < 0) {
+                    head[i] = o1;
+                    head[i + half] = o2;
+                } else {
+                    T* dst = kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
+                    dst[i] = o1;
+                    dst[i + half] = o2;
+                }
+            }
+        }
+    } else if (half > 0) {  // more pairs than threads
+        for (int idx = threadIdx.x; idx < (n_q + n_kv) * half; idx += blockDim.x) {
+            const int h = idx / half, i = idx - h * half;
+            T* head = row + (int64_t)h * D;
+            const float x1 = to_float(head[i]), x2 = to_float(head[i + half]);
+            const float angle = __fmul_rn(pos, inv_freq[i]);
+            float s, c;
+            sincosf(angle, &s, &c);
+            const T o1 = from_float<T>(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(-x2, s)));
+            const T o2 = from_float<T>(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s)));
+            if (h < n_q || slot < 0) {
+                head[i] = o1;
+                head[i + half] = o2;
+            } else {
+                T* dst = kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
+                dst[i] = o1;
+                dst[i + half] = o2;
+            }
         }
     }
     if (slot < 0) return;
@@ -143,7 +244,7 @@ extern "C" int ss_rope_cache(void* qkv, const int32_t* positions, const int32_t*
                              int rot_dim, int page_size, int64_t num_pages, int write_cache, int dtype,
                              int* err, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    const int threads = 128;
+    const int threads = 256;
     const int64_t pool = num_pages * page_size;
     if (dtype == SS_BF16)
         rope_cache_kernel<bf16><<<n_tokens, threads, 0, stream>>>((bf16*)qkv, positions, slots, inv_freq, (bf16*)kv, n_q, n_kv, D, rot_dim, page_size, pool, write_cache, err);
@@ -155,29 +256,43 @@ extern "C" int ss_rope_cache(void* qkv, const int32_t* positions, const int32_t*
 // ---------------------------------------------------------------- SwiGLU
 
 // in: [n, 2*inter] = [gate | up];  out[n, inter] = silu(gate) * up, formed in float32.
-template <typename T>
+template <typename T, int VEC>
 __global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t n, int inter) {
-    const int64_t total = n * inter;
+    const int per_row = inter / VEC;
+    const int64_t total = n * per_row;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = idx / inter;
-        const int c = (int)(idx - r * inter);
-        const float g = to_float(in[r * 2 * inter + c]);
-        const float u = to_float(in[r * 2 * inter + inter + c]);
-        const float silu = g / (1.0f + expf(-g));
-        out[idx] = from_float<T>(silu * u);
+        const int64_t r = idx / per_row;
+        const int c = (int)(idx - r * per_row) * VEC;
+        const T* gp = in + r * 2 * inter + c;
+        if (VEC == 4) {
+            float g[4], u[4], o[4];
+            Vec4<T>::load(gp, g);
+            Vec4<T>::load(gp + inter, u);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
+            Vec4<T>::store(out + r * inter + c, o);
+        } else {
+            const float g = to_float(gp[0]), u = to_float(gp[inter]);
+            out[r * inter + c] = from_float<T>(g / (1.0f + expf(-g)) * u);
+        }
     }
+}
+
+template <typename T>
+static void launch_swiglu(const void* in, void* out, int64_t n, int inter, cudaStream_t stream) {
+    const int threads = 256;
+    const int vec = inter % 4 == 0 ? 4 : 1;
+    int64_t blocks = (n * (inter / vec) + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (vec == 4) swiglu_kernel<T, 4><<<(int)blocks, threads, 0, stream>>>((const T*)in, (T*)out, n, inter);
+    else swiglu_kernel<T, 1><<<(int)blocks, threads, 0, stream>>>((const T*)in, (T*)out, n, inter);
 }
 
 extern "C" int ss_swiglu(const void* in, void* out, int64_t n, int inter, int dtype, cudaStream_t stream) {
     if (n <= 0) return 0;
-    const int threads = 256;
-    int64_t blocks = (n * inter + threads - 1) / threads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    if (dtype == SS_BF16)
-        swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)in, (bf16*)out, n, inter);
-    else
-        swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)in, (float*)out, n, inter);
+    if (dtype == SS_BF16) launch_swiglu<bf16>(in, out, n, inter, stream);
+    else launch_swiglu<float>(in, out, n, inter, stream);
     return SS_LAUNCH_CHECK();
 }
 

@@ -56,20 +56,74 @@ __device__ __forceinline__ ArgMax block_argmax(ArgMax a, ArgMax* scratch /* >= 3
     return scratch[32];
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS)
-argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int vocab, int64_t stride) {
-    __shared__ ArgMax scratch[33];
-    const float* row = logits + (int64_t)blockIdx.x * stride;
-    ArgMax a{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) a = better(a, ArgMax{row[i], i});
-    a = block_argmax(a, scratch);
-    if (threadIdx.x == 0) out[blockIdx.x] = a.i == 0x7fffffff ? 0 : a.i;
+// Arg-max in two stages so that a handful of rows still fills the GPU: ARGMAX_CHUNKS blocks per row
+// each reduce a slice of the vocabulary to one packed (value, index) word; a second kernel reduces those.
+// Packed word: monotone key of the value in the high half, ~index in the low half, so that the largest
+// word is the largest value and, among equal values, the lowest index.  NaN never wins.
+#define ARGMAX_CHUNKS 32
+#define ARGMAX_THREADS 256
+
+__device__ __forceinline__ unsigned long long pack_arg(float v, int i) {
+    const uint32_t b = __float_as_uint(v);
+    const uint32_t key = (v != v) ? 0u : ((b & 0x80000000u) ? ~b : (b | 0x80000000u));
+    return ((unsigned long long)key << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)i);
 }
 
+__device__ __forceinline__ unsigned long long block_max_u64(unsigned long long v, unsigned long long* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+        v = other > v ? other : v;
+    }
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        unsigned long long t = lane < nwarps ? scratch[lane] : 0ull;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, t, o);
+            t = other > t ? other : t;
+        }
+        if (lane == 0) scratch[0] = t;
+    }
+    __syncthreads();
+    return scratch[0];
+}
+
+__global__ void __launch_bounds__(ARGMAX_THREADS)
+argmax_partial_kernel(const float* __restrict__ logits, unsigned long long* __restrict__ partial, int vocab,
+                      int64_t stride) {
+    __shared__ unsigned long long scratch[32];
+    const float* row = logits + (int64_t)blockIdx.x * stride;
+    const int per = (vocab + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+    const int begin = blockIdx.y * per, end = min(vocab, begin + per);
+    unsigned long long best = 0ull;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const unsigned long long w = pack_arg(row[i], i);
+        best = w > best ? w : best;
+    }
+    best = block_max_u64(best, scratch);
+    if (threadIdx.x == 0) partial[(int64_t)blockIdx.x * ARGMAX_CHUNKS + blockIdx.y] = best;
+}
+
+__global__ void argmax_final_kernel(const unsigned long long* __restrict__ partial, int32_t* __restrict__ out) {
+    unsigned long long v = partial[(int64_t)blockIdx.x * ARGMAX_CHUNKS + threadIdx.x];  // 32 threads
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+        v = other > v ? other : v;
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = v == 0ull ? 0 : (int32_t)(0xFFFFFFFFu - (uint32_t)(v & 0xFFFFFFFFull));
+}
+
+// scratch: rows * ARGMAX_CHUNKS 64-bit words of the caller
 extern "C" int ss_argmax(const float* logits, int32_t* out, int rows, int vocab, int64_t stride,
-                         cudaStream_t stream) {
+                         unsigned long long* scratch, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    argmax_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, out, vocab, stride);
+    static_assert(ARGMAX_CHUNKS == 32, "the final kernel reduces one warp of partial results");
+    argmax_partial_kernel<<<dim3(rows, ARGMAX_CHUNKS), ARGMAX_THREADS, 0, stream>>>(logits, scratch, vocab, stride);
+    argmax_final_kernel<<<rows, 32, 0, stream>>>(scratch, out);
     return SS_LAUNCH_CHECK();
 }
 

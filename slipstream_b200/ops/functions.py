@@ -43,7 +43,7 @@ _OPS_SIGNATURES = {
     "ss_swiglu": [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p],
     "ss_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64,
                      c_int64, c_int, c_int, c_void_p],
-    "ss_argmax": [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p],
+    "ss_argmax": [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p],
     "ss_sample": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                   c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
     "ss_mark_seen": [c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -390,7 +390,10 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     _need(logits, torch.float32, "logits")
     m, v = logits.shape
     out = torch.empty(m, dtype=torch.int32, device=logits.device)
-    _check(ops_library().ss_argmax(logits.data_ptr(), out.data_ptr(), m, v, logits.stride(0), _stream()), "argmax")
+    scratch = torch.empty(m * 32, dtype=torch.int64, device=logits.device)  # one packed word per (row, chunk)
+    _check(ops_library().ss_argmax(logits.data_ptr(), out.data_ptr(), m, v, logits.stride(0), scratch.data_ptr(),
+                                   _stream()), "argmax")
+    _launches[0] += 1  # two kernels
     return out
 
 
