@@ -1,0 +1,337 @@
+// bfloat16 matrix product on the 5th-generation tensor cores of sm_100a:
+//   C[M, N] = A[M, K] * B[N, K]^T (+ bias), A and B K-major, float32 accumulation in tensor memory.
+//
+// One block computes a 128 x BN tile.  Warp 0 (one lane) is the producer: it moves 128 x 64 tiles of A
+// and BN x 64 tiles of B into shared memory with TMA (cp.async.bulk.tensor, 128-byte swizzle) through a
+// ring of stages guarded by mbarriers.  Warp 1 (one lane) issues tcgen05.mma (cta_group::1, kind::f16,
+// M = 128, N = BN, K = 16) four times per stage, with the accumulator in tensor memory, and releases each
+// stage with tcgen05.commit.  Warps 2..5 are the epilogue: they read the accumulator with tcgen05.ld (one
+// quarter of the 128 lanes each), add the bias and store.
+//
+// Small batches (decode) run "swapped": the weight matrix is A, so that its rows fill the 128 lanes of the
+// MMA, and the few tokens are B (BN = 16..64).  The output is then written transposed.  When there are
+// fewer tiles than SMs the K range is cut into slices (grid.z); every slice writes its partial tile to
+// scratch memory and the block that finishes a tile last (an atomic counter, no waiting) adds the slices in
+// a fixed order and writes the result, so the sum does not depend on timing.
+//
+// Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the kernel sets SS_ERR_WAIT_LIMIT in the
+// error word, stops waiting everywhere, frees its tensor memory and returns.
+//
+// The reference has no counterpart: its projections are nn.Linear calls into a library
+// (slipstream/models/layers/attention.py:132-135, slipstream/models/layers/mlp.py:33-35).
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define WAIT_LIMIT (1u << 24)
+
+__device__ __forceinline__ uint32_t s_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s_addr(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait: false when the limit ran out (or another role already gave up).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* gave_up) {
+    for (uint32_t spins = 0; spins < WAIT_LIMIT; ++spins) {
+        uint32_t done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}"
+            : "=r"(done) : "r"(s_addr(bar)), "r"(parity) : "memory");
+        if (done) return true;
+        if ((spins & 1023u) == 1023u && *gave_up) return false;
+    }
+    *gave_up = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(s_addr(dst)), "l"(map), "r"(s_addr(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(const void* tile) {
+    uint64_t d = 0;
+    d |= (uint64_t)((s_addr(tile) & 0x3FFFF) >> 4);   // start address
+    d |= (uint64_t)(1024 >> 4) << 32;                 // stride between 8-row groups
+    d |= (uint64_t)1 << 46;                           // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                           // 128-byte swizzle
+    return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct GemmArgs {
+    void* C;            // output [M, N] (or [N, M] rows when swapped), bfloat16 or float32
+    const void* bias;   // per output feature, or null
+    float* partial;     // split-K scratch: [tiles][slices][BN][128] float32
+    int* counters;      // split-K: one per tile, zero between calls
+    int* err;
+    int M, N, K;        // MMA view: A is [M, K], B is [N, K]
+    int64_t ldc;
+    int slices;
+    int swapped;        // 1: C is written transposed, C[n * ldc + m], bias indexed by m
+    int out_f32;
+    int bias_f32;
+};
+
+template <int BN>
+__device__ __forceinline__ void store_out(const GemmArgs& g, int m, int n, float v) {
+    if (m >= g.M || n >= g.N) return;
+    if (g.bias) {
+        const int f = g.swapped ? m : n;
+        v += g.bias_f32 ? ((const float*)g.bias)[f] : to_float(((const bf16*)g.bias)[f]);
+    }
+    const int64_t at = g.swapped ? (int64_t)n * g.ldc + m : (int64_t)m * g.ldc + n;
+    if (g.out_f32) ((float*)g.C)[at] = v;
+    else ((bf16*)g.C)[at] = __float2bfloat16_rn(v);
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
+    constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
+    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * (A_BYTES + B_BYTES));
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_ready = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+    volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* last_flag = const_cast<int*>(gave_up) + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+    const int k_iters_total = (g.K + TC_BK - 1) / TC_BK;
+    const int per = (k_iters_total + g.slices - 1) / g.slices;
+    const int k_begin = blockIdx.z * per, k_end = min(k_iters_total, k_begin + per);
+    const int k_iters = max(0, k_end - k_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        *gave_up = 0;
+        *last_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // one warp allocates the accumulator columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_acc = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer
+        for (int it = 0; it < k_iters; ++it) {
+            const int s = it % STAGES;
+            if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, gave_up)) break;
+            mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+            unsigned char* a_tile = tiles + s * (A_BYTES + B_BYTES);
+            tma_load_2d(a_tile, &map_a, (k_begin + it) * TC_BK, m0, &full[s]);
+            tma_load_2d(a_tile + A_BYTES, &map_b, (k_begin + it) * TC_BK, n0, &full[s]);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer.  Instruction descriptor: D float32, A and B bfloat16, both K-major, N = BN, M = 128.
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+        bool ok = true;
+        for (int it = 0; it < k_iters && ok; ++it) {
+            const int s = it % STAGES;
+            ok = mbar_wait(&full[s], (it / STAGES) & 1, gave_up);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            unsigned char* a_tile = tiles + s * (A_BYTES + B_BYTES);
+            const uint64_t a_desc = smem_desc(a_tile), b_desc = smem_desc(a_tile + A_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < TC_BK / 16; ++kk)  // 16 K elements = 32 bytes further along the swizzled row
+                umma_f16(tmem_acc, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, (it | kk) != 0);
+            umma_commit(&empty[s]);
+        }
+        umma_commit(acc_ready);
+    } else if (warp >= 2) {
+        // ---- epilogue: warp w reads lanes 32 * (w % 4) .. + 31 of the accumulator
+        const int quarter = warp & 3;
+        const int m = m0 + quarter * 32 + lane;
+        if (k_iters > 0) mbar_wait(acc_ready, 0, gave_up);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // one thread decides for all four epilogue warps whether the tile is good, so that the barriers
+        // below are reached by all of them or by none
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) *last_flag = *gave_up ? -1 : 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*last_flag == 0) {
+            const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t r[16];
+                if (k_iters > 0) {
+                    tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + c, r);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = 0u;
+                }
+                if (g.slices == 1) {
+                    if (!g.swapped && !g.out_f32 && m < g.M && n0 + c + 16 <= g.N && (g.ldc % 8 == 0)) {
+                        // 16 consecutive bfloat16 of this thread's row: two 16-byte stores
+                        uint32_t packed[8];
+                        if (g.bias) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int f = n0 + c + j;
+                                const float b = g.bias_f32 ? ((const float*)g.bias)[f] : to_float(((const bf16*)g.bias)[f]);
+                                r[j] = __float_as_uint(__uint_as_float(r[j]) + b);
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                            packed[j] = *reinterpret_cast<uint32_t*>(&v);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>((bf16*)g.C + (int64_t)m * g.ldc + n0 + c);
+                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) store_out<BN>(g, m, n0 + c + j, __uint_as_float(r[j]));
+                    }
+                } else {
+                    float* dst = g.partial + (((int64_t)tile * g.slices + blockIdx.z) * BN + c) * TC_BM + quarter * 32 + lane;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) dst[(int64_t)j * TC_BM] = __uint_as_float(r[j]);
+                }
+            }
+            if (g.slices > 1) {
+                // the block that completes the tile last adds the slices, in slice order
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+                if (threadIdx.x == 64) {
+                    const int seen = atomicAdd(&g.counters[tile], 1);
+                    *last_flag = (seen == g.slices - 1);
+                    if (seen == g.slices - 1) g.counters[tile] = 0;  // ready for the next call
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*last_flag) {
+                    __threadfence();
+                    const int ml = quarter * 32 + lane;
+                    for (int c = 0; c < BN; ++c) {
+                        float acc = 0.f;
+                        const float* src = g.partial + (((int64_t)tile * g.slices) * BN + c) * TC_BM + ml;
+                        for (int s = 0; s < g.slices; ++s) acc += __ldcg(src + (int64_t)s * BN * TC_BM);
+                        store_out<BN>(g, m0 + ml, n0 + c, acc);
+                    }
+                }
+            }
+        }
+    }
+    if (*gave_up && threadIdx.x == 0) atomicOr(g.err, SS_ERR_WAIT_LIMIT);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TMEM_COLS));
+    }
+}
+
+// ---------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// K-major bfloat16 matrix [rows, K] with row stride ld (elements); box = 64 x box_rows, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows) {
+    EncodeTiled enc = encode_tiled();
+    if (!enc) return -2001;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -2002;
+}
+
+template <int BN, int STAGES>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, dim3 grid, cudaStream_t stream) {
+    constexpr int smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 256;
+    static int configured = (int)cudaFuncSetAttribute(gemm_tc5_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (configured != 0) return configured;
+    gemm_tc5_kernel<BN, STAGES><<<grid, TC_THREADS, smem, stream>>>(ma, mb, g);
+    return SS_LAUNCH_CHECK();
+}
+
+// How many float32 the split-K scratch must hold, and how many counters, for a problem.
+extern "C" int64_t ss_gemm_tc5_scratch_floats(int tiles, int slices, int bn) { return (int64_t)tiles * slices * bn * TC_BM; }
+
+// C = A * B^T (+ bias) in the MMA view: A [M, K] with row stride lda, B [N, K] with row stride ldb, both
+// bfloat16 and K-major, K a multiple of 8 and both bases 16-byte aligned.  bn: tile width (16, 32, 64, 128
+// or 256).  swapped: write C transposed (C[n * ldc + m]).  slices > 1 needs `partial` (see
+// ss_gemm_tc5_scratch_floats) and `counters` (one int per tile, zero; left zero).
+extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
+                           int64_t lda, int64_t ldb, int64_t ldc, int bn, int swapped, int out_f32, int slices,
+                           float* partial, int* counters, int* err, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return -2003;
+    if (((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2004;
+    if (slices < 1 || (slices > 1 && (!partial || !counters))) return -2005;
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, A, M, K, lda, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mb, B, N, K, ldb, bn);
+    if (rc) return rc;
+    GemmArgs g;
+    g.C = C; g.bias = bias; g.partial = partial; g.counters = counters; g.err = err;
+    g.M = M; g.N = N; g.K = K; g.ldc = ldc; g.slices = slices; g.swapped = swapped; g.out_f32 = out_f32;
+    g.bias_f32 = bias_f32;
+    dim3 grid((N + bn - 1) / bn, (M + TC_BM - 1) / TC_BM, slices);
+    switch (bn) {
+        case 16: return launch<16, 8>(ma, mb, g, grid, stream);
+        case 32: return launch<32, 8>(ma, mb, g, grid, stream);
+        case 64: return launch<64, 8>(ma, mb, g, grid, stream);
+        case 128: return launch<128, 6>(ma, mb, g, grid, stream);
+        case 256: return launch<256, 4>(ma, mb, g, grid, stream);
+        default: return -2006;
+    }
+}

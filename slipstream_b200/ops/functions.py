@@ -61,6 +61,11 @@ _ATTN_SIGNATURES = {
                            c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
+_GEMM_SIGNATURES = {
+    "ss_gemm_tc5": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
+                    c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+}
+
 _state: dict[str, object] = {}
 
 
@@ -80,6 +85,16 @@ def ops_library() -> ctypes.CDLL:
         lib = load_library("slipstream_ops", ["ops.cu", "sampling.cu"])
         _declare(lib, _OPS_SIGNATURES)
         _state["ops"] = lib
+    return lib  # type: ignore[return-value]
+
+
+def gemm_library() -> ctypes.CDLL:
+    lib = _state.get("gemm")
+    if lib is None:
+        require_cuda()
+        lib = load_library("slipstream_gemm", ["gemm_tc5.cu"])
+        _declare(lib, _GEMM_SIGNATURES)
+        _state["gemm"] = lib
     return lib  # type: ignore[return-value]
 
 
@@ -435,6 +450,74 @@ def mark_seen(seen_row: torch.Tensor, token_ids: torch.Tensor, vocab: int) -> No
                                       _stream()), "mark_seen")
 
 
+# --------------------------------------------------------------------------- tensor-core matrix product
+
+_GEMM_COUNTERS = 8192
+_GEMM_SCRATCH_FLOATS = 8 * 1024 * 1024
+
+
+def _gemm_workspace(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Split-K scratch (partial tiles) and per-tile counters; the counters are zero between calls."""
+    key = f"gemm_ws{device}"
+    ws = _state.get(key)
+    if ws is None:
+        ws = (torch.empty(_GEMM_SCRATCH_FLOATS, dtype=torch.float32, device=device),
+              torch.zeros(_GEMM_COUNTERS, dtype=torch.int32, device=device))
+        _state[key] = ws
+    return ws  # type: ignore[return-value]
+
+
+def gemm_plan(tokens: int, features: int, k: int) -> tuple[bool, int, int]:
+    """(swapped, tile width, K slices) for ``x[tokens, k] @ w[features, k].T`` on 148 SMs."""
+    k_iters = (k + 63) // 64
+    if tokens <= 64:
+        bn = 16 if tokens <= 16 else (32 if tokens <= 32 else 64)
+        tiles = (features + 127) // 128
+        slices = max(1, min(k_iters, (2 * 148 + tiles - 1) // tiles if tiles < 148 else 1, 16))
+        while slices > 1 and tiles * slices * bn * 128 > _GEMM_SCRATCH_FLOATS:
+            slices -= 1
+        return True, bn, slices
+    bn = 256 if features >= 256 else (128 if features >= 128 else (64 if features >= 64 else (32 if features >= 32 else 16)))
+    return False, bn, 1
+
+
+def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+                 out_dtype: torch.dtype | None = None, plan: tuple[bool, int, int] | None = None) -> torch.Tensor:
+    """``x @ weight.T + bias`` for bfloat16 ``x`` [tokens, K] and ``weight`` [features, K] on the tcgen05 tensor
+    cores (TMA-fed, accumulator in tensor memory); output bfloat16 or float32.  K must be a multiple of 8."""
+    _need(x, torch.bfloat16, "x")
+    _need(weight, torch.bfloat16, "weight")
+    tokens, k = x.shape
+    features = weight.shape[0]
+    if weight.shape[1] != k:
+        raise KernelError(f"weight {tuple(weight.shape)} does not match x {tuple(x.shape)}")
+    if k % 8 != 0:
+        raise KernelError(f"the tensor-core matrix product needs K to be a multiple of 8, got {k}")
+    out_dtype = out_dtype or torch.bfloat16
+    out = torch.empty((tokens, features), dtype=out_dtype, device=x.device)
+    if tokens == 0:
+        return out
+    bias_f32 = 0
+    if bias is not None:
+        _need(bias, None, "bias")
+        bias_f32 = int(bias.dtype == torch.float32)
+        if bias.numel() != features or bias.dtype not in (torch.float32, torch.bfloat16):
+            raise KernelError("bias has the wrong size or dtype")
+    swapped, bn, slices = plan or gemm_plan(tokens, features, k)
+    partial = counters = None
+    if slices > 1:
+        partial, counters = _gemm_workspace(x.device)
+        tiles = ((features if swapped else tokens) + 127) // 128 * (((tokens if swapped else features) + bn - 1) // bn)
+        if tiles > _GEMM_COUNTERS or tiles * slices * bn * 128 > _GEMM_SCRATCH_FLOATS:
+            raise KernelError("split-K workspace too small for this problem")
+    a, b = (weight, x) if swapped else (x, weight)
+    rc = gemm_library().ss_gemm_tc5(a.data_ptr(), b.data_ptr(), _ptr(bias), bias_f32, out.data_ptr(), a.shape[0],
+                                    b.shape[0], k, k, k, features, bn, int(swapped), int(out_dtype == torch.float32),
+                                    slices, _ptr(partial), _ptr(counters), error_word(x.device).data_ptr(), _stream())
+    _check(rc, "gemm_tcgen05")
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
            out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """A projection ``x @ weight.T + bias``.  float32 runs the SIMT kernel (no reduced-precision
@@ -453,5 +536,5 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "paged_attention_prefill", "paged_attention_decode", "decode_scratch", "decode_slices", "require_cuda", "argmax", "sample", "mark_seen", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "paged_attention_prefill", "paged_attention_decode", "decode_scratch", "decode_slices", "require_cuda", "argmax", "sample", "mark_seen", "gemm_tcgen05", "gemm_plan", "gemm_library", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
            "attention_library"]

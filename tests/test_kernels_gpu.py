@@ -262,3 +262,36 @@ def test_argmax_lowest_index_wins_ties():
     want = logits.argmax(-1).cpu()
     assert got[2] == 777 and got[5] == 0
     assert all(int(got[i]) == int(want[i]) for i in (0, 1, 3, 4, 6, 7, 8))
+
+
+# --------------------------------------------------------------------------- tcgen05 matrix product
+
+@pytest.mark.parametrize("tokens, features, k", [(1, 128, 64), (8, 3584, 3584), (8, 200, 136), (13, 4608, 3584), (33, 1000, 512),
+                                                 (64, 263, 80), (8, 3584, 18944), (65, 256, 64), (300, 520, 200), (2048, 4608, 3584),
+                                                 (129, 100, 72)])
+def test_tcgen05_matrix_product(tokens, features, k):
+    torch.manual_seed(tokens + features)
+    x = torch.randn(tokens, k, device=DEV).bfloat16()
+    w = (torch.randn(features, k, device=DEV) * 0.05).bfloat16()
+    b = torch.randn(features, device=DEV).bfloat16()
+    ref = x.double() @ w.double().T
+    got = ops().gemm_tcgen05(x, w, None, torch.float32)
+    assert rel_err(got, ref) < 2e-5, "float32 output of bfloat16 inputs is exact up to the order of additions"
+    got = ops().gemm_tcgen05(x, w, b)
+    assert got.dtype == torch.bfloat16 and rel_err(got, ref + b.double()) < 6e-3
+    got = ops().gemm_tcgen05(x, w, b.float(), torch.float32)
+    assert rel_err(got, ref + b.double()) < 2e-5
+    ops().check_errors(torch.device(DEV))
+
+
+def test_tcgen05_split_k_is_deterministic_and_leaves_its_counters_clean():
+    x = torch.randn(8, 18944, device=DEV).bfloat16()
+    w = (torch.randn(3584, 18944, device=DEV) * 0.02).bfloat16()
+    assert ops().gemm_plan(8, 3584, 18944)[2] > 1
+    a = ops().gemm_tcgen05(x, w, None, torch.float32)
+    for _ in range(3):
+        assert torch.equal(ops().gemm_tcgen05(x, w, None, torch.float32), a)
+    for slices in (1, 2, 7):
+        got = ops().gemm_tcgen05(x, w, None, torch.float32, plan=(True, 16, slices))
+        assert rel_err(got, a) < 1e-4  # 18,944 float32 additions in another order
+    ops().check_errors(torch.device(DEV))
