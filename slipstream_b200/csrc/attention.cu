@@ -46,34 +46,31 @@ extern "C" int ss_attn_prefill_mma(const void* q, int64_t q_stride, void* out, i
     static int configured = set_smem(attn_prefill_mma<HEAD_DIM>, smem);
     if (configured != 0) return configured;
     dim3 grid(n_tiles, n_kv);
-    attn_prefill_mma<HEAD_DIM><<<grid, MMA_THREADS, smem, stream>>>(
+    ss_launch(attn_prefill_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, tile_req,
         tile_row0, q_start, seq_lens, n_q, n_kv, page_size, num_pages, scale, window, err);
     return SS_LAUNCH_CHECK();
 }
 
 // Requests that bring one token each, bfloat16, split over the keys into n_slices.  part_o
-// ([requests][n_q][n_slices][D] float32) and part_lse ([requests][n_q][n_slices] float32) are scratch
-// memory of the caller; they are not touched when n_slices is 1.
+// ([requests][n_q][n_slices][D] float32), part_lse ([requests][n_q][n_slices] float32) and counters (one int
+// per request and block of 16 heads of a kv group; zero before the first call, left zero by every call) are
+// scratch memory of the caller; they are not touched when n_slices is 1.
 extern "C" int ss_attn_decode_mma(const void* q, int64_t q_stride, void* out, int64_t out_stride,
                                   const void* kv, const int32_t* block_tables, int max_blocks, int n_requests,
                                   const int32_t* q_start, const int32_t* seq_lens, int n_q, int n_kv,
                                   int page_size, int64_t num_pages, float scale, int window, int n_slices,
-                                  float* part_o, float* part_lse, int* err, cudaStream_t stream) {
+                                  float* part_o, float* part_lse, int* counters, int* err, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
-    if (n_slices < 1 || (n_slices > 1 && (!part_o || !part_lse))) return (int)cudaErrorInvalidValue;
-    constexpr int smem = mma_smem_bytes<HEAD_DIM>();
+    if (n_slices < 1 || (n_slices > 1 && (!part_o || !part_lse || !counters))) return (int)cudaErrorInvalidValue;
+    constexpr int smem = mma_smem_bytes<HEAD_DIM>(16);
     static int configured = set_smem(attn_decode_mma<HEAD_DIM>, smem);
     if (configured != 0) return configured;
     const int G = n_q / n_kv;
     dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
-    attn_decode_mma<HEAD_DIM><<<grid, MMA_THREADS, smem, stream>>>(
+    ss_launch(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
-        seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, part_o, part_lse, err);
-    int rc = SS_LAUNCH_CHECK();
-    if (rc != 0 || n_slices == 1) return rc;
-    attn_merge_kernel<HEAD_DIM><<<dim3(n_requests, n_q), 128, 0, stream>>>(part_o, part_lse, (bf16*)out, out_stride,
-                                                                         q_start, n_q, n_slices);
+        seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, part_o, part_lse, counters, err);
     return SS_LAUNCH_CHECK();
 }
 
@@ -86,6 +83,11 @@ static __device__ __align__(256) float ss_noalloc_scratch[SS_NOALLOC_SCRATCH_FLO
 
 #define SS_NOALLOC_MAX_DEVICES 64
 static float* ss_noalloc_ptr[SS_NOALLOC_MAX_DEVICES];  // device address of the array, per device
+
+// One counter per (request, block of 16 heads of a kv group): the slice that finishes last combines the
+// others.  Zero when the library is loaded; every call leaves them zero.
+static __device__ __align__(256) int ss_noalloc_counters[SS_NOALLOC_COUNTERS];
+static int* ss_noalloc_counter_ptr[SS_NOALLOC_MAX_DEVICES];
 
 extern "C" int64_t ss_attn_decode_noalloc_floats(int n_requests, int n_q, int n_slices) {
     return (int64_t)n_requests * n_q * n_slices * (HEAD_DIM + 1);
@@ -112,6 +114,7 @@ extern "C" int ss_attn_decode_noalloc(const void* q, int64_t q_stride, void* out
         return SS_NOALLOC_BAD_ARGUMENT;
     const int64_t floats = ss_attn_decode_noalloc_floats(n_requests, n_q, n_slices);
     if (floats > (int64_t)SS_NOALLOC_SCRATCH_FLOATS) return SS_NOALLOC_TOO_LARGE;
+    if ((int64_t)n_requests * n_kv * ((n_q / n_kv + 15) / 16) > (int64_t)SS_NOALLOC_COUNTERS) return SS_NOALLOC_TOO_LARGE;
 
     // set-up, once per device, with that device current
     int device = -1;
@@ -123,20 +126,24 @@ extern "C" int ss_attn_decode_noalloc(const void* q, int64_t q_stride, void* out
             return SS_NOALLOC_SETUP_FAILED;
         ss_noalloc_ptr[device] = scratch;
     }
+    int* counters = ss_noalloc_counter_ptr[device];
+    if (counters == nullptr) {
+        if (cudaGetSymbolAddress((void**)&counters, ss_noalloc_counters) != cudaSuccess || counters == nullptr)
+            return SS_NOALLOC_SETUP_FAILED;
+        ss_noalloc_counter_ptr[device] = counters;
+    }
     float* part_o = scratch;
     float* part_lse = scratch + (int64_t)n_requests * n_q * n_slices * HEAD_DIM;
 
-    constexpr int smem = mma_smem_bytes<HEAD_DIM>();
+    constexpr int smem = mma_smem_bytes<HEAD_DIM>(16);
     static int configured = set_smem(attn_decode_mma<HEAD_DIM>, smem);
     if (configured != 0) return configured;
     const int G = n_q / n_kv;
     dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
-    attn_decode_mma<HEAD_DIM><<<grid, MMA_THREADS, smem, stream>>>(
+    ss_launch(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
-        seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, part_o, part_lse, err);
-    int rc = SS_LAUNCH_CHECK();
-    if (rc != 0 || n_slices == 1) return rc;
-    attn_merge_kernel<HEAD_DIM><<<dim3(n_requests, n_q), 128, 0, stream>>>(part_o, part_lse, (bf16*)out, out_stride,
-                                                                         q_start, n_q, n_slices);
+        seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, part_o, part_lse, counters, err);
     return SS_LAUNCH_CHECK();
 }
+
+extern "C" void ss_set_pdl(int on) { ss_pdl_flag() = on; }

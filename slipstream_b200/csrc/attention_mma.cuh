@@ -8,7 +8,8 @@
 //  * attn_decode_mma: requests that bring ONE token.  A block takes the (up to 16) heads of
 //    one (request, kv head) and one slice of the keys (split-KV); its four warps take
 //    different 16-key parts of each 64-key tile and merge at the end.  With more than one
-//    slice, partial results go to scratch memory and attn_merge_kernel combines them.
+//    slice, partial results go to scratch memory and the block that finishes a (request, head
+//    block) last combines them (an atomic counter; no block waits for another).
 //
 // Key tiles start at multiples of 64 counted from the request's first token.  Masking is
 // the packed-index causal rule of slipstream/models/layers/attention.py:46-51 plus an
@@ -162,8 +163,8 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const
 }
 
 template <int D>
-constexpr int mma_smem_bytes() {
-    return (64 * (D + 8) + 2 * 2 * MMA_BN * (D + 8)) * 2;  // Q tile + two stages of K and V
+constexpr int mma_smem_bytes(int q_rows = 64) {
+    return (q_rows * (D + 8) + 2 * 2 * MMA_BN * (D + 8)) * 2;  // Q tile + two stages of K and V
 }
 
 // ---------------------------------------------------------------- prompt portions (and mixed batches)
@@ -175,6 +176,8 @@ attn_prefill_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict_
                  const int32_t* __restrict__ tile_req, const int32_t* __restrict__ tile_row0,
                  const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens, int n_q, int n_kv,
                  int page_size, int64_t num_pages, float scale, int window, int* err) {
+    pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
+    pdl_wait();               // nothing below runs before the kernels before this one are complete
     constexpr int KSTR = D + 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
@@ -268,11 +271,13 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
                 const bf16* __restrict__ kv, const int32_t* __restrict__ block_tables, int max_blocks,
                 const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens, int n_q, int n_kv,
                 int page_size, int64_t num_pages, float scale, int window, int n_slices,
-                float* __restrict__ part_o, float* __restrict__ part_lse, int* err) {
+                float* __restrict__ part_o, float* __restrict__ part_lse, int* __restrict__ counters, int* err) {
+    pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
+    pdl_wait();               // nothing below runs before the kernels before this one are complete
     constexpr int KSTR = D + 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
-    bf16* KV = Qs + 64 * KSTR;
+    bf16* KV = Qs + 16 * KSTR;  // the decode tile has 16 query rows
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = n_q / n_kv, hblocks = (G + 15) / 16;
@@ -375,28 +380,50 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
             if (d == 0) part_lse[((int64_t)r * n_q + head) * n_slices + slice] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
         }
     }
-}
+    if (n_slices == 1) return;
 
-// out[r][head] = sum_s part_o[s] * 2^(lse_s - max) / sum_s 2^(lse_s - max);  grid (request, head)
-template <int D>
-__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
-                                  bf16* __restrict__ out, int64_t out_stride, const int32_t* __restrict__ q_start,
-                                  int n_q, int n_slices) {
-    const int r = blockIdx.x, head = blockIdx.y;
-    const float* lse = part_lse + ((int64_t)r * n_q + head) * n_slices;
-    float mx = -INFINITY;
-    for (int s = 0; s < n_slices; ++s) mx = fmaxf(mx, lse[s]);
-    float den = 0.f;
-    if (mx != -INFINITY)
-        for (int s = 0; s < n_slices; ++s) den += exp2f(lse[s] - mx);
-    const float* po = part_o + ((int64_t)r * n_q + head) * n_slices * D;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    // The block that finishes a (request, head block) last combines the slices, in slice order: no block
+    // waits for another.  counters: one int per (request, head block), zero between launches.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int* counter = counters + (int64_t)r * gridDim.y + blockIdx.y;
+        const int seen = atomicAdd(counter, 1);
+        is_last = (seen == n_slices - 1);
+        if (is_last) *counter = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // weights of the slices, once per head: w[row][s] = 2^(lse_s - max) / sum (shared memory is free now)
+    float* W = reinterpret_cast<float*>(smem_raw);  // [16][n_slices]
+    for (int idx = tid; idx < heads_here * n_slices; idx += MMA_THREADS) {
+        const int row = idx / n_slices, sl = idx - row * n_slices;
+        W[row * n_slices + sl] = __ldcg(part_lse + ((int64_t)r * n_q + kvh * G + g0 + row) * n_slices + sl);
+    }
+    __syncthreads();
+    if (tid < heads_here) {
+        float* w = W + tid * n_slices;
+        float mx = -INFINITY, den = 0.f;
+        for (int sl = 0; sl < n_slices; ++sl) mx = fmaxf(mx, w[sl]);
+        for (int sl = 0; sl < n_slices; ++sl) {
+            const float e = mx == -INFINITY ? 0.f : exp2f(w[sl] - mx);
+            w[sl] = e;
+            den += e;
+        }
+        const float inv = den > 0.f ? 1.f / den : 0.f;
+        for (int sl = 0; sl < n_slices; ++sl) w[sl] *= inv;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < heads_here * D; idx += MMA_THREADS) {
+        const int row = idx / D, d = idx - row * D;
+        const int head = kvh * G + g0 + row;
+        const float* po = part_o + ((int64_t)r * n_q + head) * n_slices * D + d;
+        const float* w = W + row * n_slices;
         float acc = 0.f;
-        if (mx != -INFINITY)
-            for (int s = 0; s < n_slices; ++s) {
-                const float w = exp2f(lse[s] - mx);
-                if (w > 0.f) acc += po[s * D + d] * w;
-            }
-        out[(int64_t)q_start[r] * out_stride + (int64_t)head * D + d] = __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+#pragma unroll 8
+        for (int sl = 0; sl < n_slices; ++sl) acc += __ldcg(po + (int64_t)sl * D) * w[sl];  // slices in order
+        out[(int64_t)row_q * out_stride + (int64_t)head * D + d] = __float2bfloat16_rn(acc);
     }
 }

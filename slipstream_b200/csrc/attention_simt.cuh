@@ -36,6 +36,8 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, T* __restrict__ out,
                  const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens,
                  int n_q, int n_kv, int page_size, int64_t num_pages, float scale, int window,
                  int* err) {
+    pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
+    pdl_wait();               // nothing below runs before the kernels before this one are complete
     constexpr int DPL = (D + 31) / 32;
     constexpr int KS = D + 4;
     extern __shared__ float smem[];
@@ -182,7 +184,7 @@ int launch_attn_simt(const void* q, int64_t q_stride, void* out, int64_t out_str
         configured = true;
     }
     dim3 grid(n_tiles, n_q);
-    attn_simt_kernel<T, D><<<grid, ATT_WARPS * 32, smem, stream>>>(
+    ss_launch(attn_simt_kernel<T, D>, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, 
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)kv, block_tables, max_blocks, tile_req,
         tile_q0, q_start, seq_lens, n_q, n_kv, page_size, num_pages, scale, window, err);
     return SS_LAUNCH_CHECK();

@@ -63,3 +63,33 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 }
 
 #define SS_LAUNCH_CHECK() (int)cudaGetLastError()
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// Kernels are launched so that the next kernel in the stream may start while this one is still running
+// (cudaLaunchAttributeProgrammaticStreamSerialization).  A kernel calls pdl_launch_dependents() as early
+// as it likes and must call pdl_wait() before it reads anything an earlier kernel wrote and before it
+// writes anything an earlier kernel may still read; until then it may only touch constants (weights).
+// In a decode step this lets a matrix product stream its weights while the small kernel before it runs.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline int& ss_pdl_flag() {
+    static int enabled = 1;
+    return enabled;
+}
+
+template <typename... KArgs, typename... Args>
+static inline void ss_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ss_pdl_flag() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -99,7 +99,23 @@ struct GemmArgs {
     int swapped;        // 1: C is written transposed, C[n * ldc + m], bias indexed by m
     int out_f32;
     int bias_f32;
+    int swiglu;         // 1 (swapped only): rows 0..63 of a tile are gate features, rows 64..127 the matching up
+                        // features; the output has M / 2 features: out[n][tile * 64 + r] = silu(gate) * up
 };
+
+__device__ __forceinline__ float bias_at(const GemmArgs& g, int f) {
+    return g.bias_f32 ? ((const float*)g.bias)[f] : to_float(((const bf16*)g.bias)[f]);
+}
+
+// Output of the fused SwiGLU: gate and up are rows m and m + 64 of the swapped product (token n).
+__device__ __forceinline__ void store_swiglu(const GemmArgs& g, int m, int n, float gate, float up) {
+    if (m + 64 >= g.M || n >= g.N) return;
+    if (g.bias) { gate += bias_at(g, m); up += bias_at(g, m + 64); }
+    const float v = gate / (1.0f + expf(-gate)) * up;
+    const int64_t at = (int64_t)n * g.ldc + (m / TC_BM) * 64 + (m % TC_BM);
+    if (g.out_f32) ((float*)g.C)[at] = v;
+    else ((bf16*)g.C)[at] = __float2bfloat16_rn(v);
+}
 
 template <int BN>
 __device__ __forceinline__ void store_out(const GemmArgs& g, int m, int n, float v) {
@@ -114,7 +130,7 @@ __device__ __forceinline__ void store_out(const GemmArgs& g, int m, int n, float
 }
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS)
 gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
     constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
     constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
@@ -127,6 +143,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = const_cast<int*>(gave_up) + 1;
 
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
     const int k_iters_total = (g.K + TC_BK - 1) / TC_BK;
@@ -135,6 +152,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int k_iters = max(0, k_end - k_begin);
 
     if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_ready, 1);
         *gave_up = 0;
@@ -151,8 +170,17 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t tmem_acc = *tmem_slot;
 
     if (warp == 0 && lane == 0) {
-        // ---- producer
-        for (int it = 0; it < k_iters; ++it) {
+        // ---- producer.  When the block runs swapped, A is the weight matrix: a constant, so its first
+        // tiles are fetched before the kernels before this one have finished; B (activations) only after.
+        const int ahead = g.swapped ? min(STAGES, k_iters) : 0;
+        for (int it = 0; it < ahead; ++it) {
+            mbar_expect_tx(&full[it], A_BYTES + B_BYTES);
+            tma_load_2d(tiles + it * (A_BYTES + B_BYTES), &map_a, (k_begin + it) * TC_BK, m0, &full[it]);
+        }
+        pdl_wait();
+        for (int it = 0; it < ahead; ++it)
+            tma_load_2d(tiles + it * (A_BYTES + B_BYTES) + A_BYTES, &map_b, (k_begin + it) * TC_BK, n0, &full[it]);
+        for (int it = ahead; it < k_iters; ++it) {
             const int s = it % STAGES;
             if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, gave_up)) break;
             mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
@@ -181,6 +209,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // ---- epilogue: warp w reads lanes 32 * (w % 4) .. + 31 of the accumulator
         const int quarter = warp & 3;
         const int m = m0 + quarter * 32 + lane;
+        pdl_wait();  // the output, the scratch and the counters may still be in use by earlier kernels
         if (k_iters > 0) mbar_wait(acc_ready, 0, gave_up);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         // one thread decides for all four epilogue warps whether the tile is good, so that the barriers
@@ -199,7 +228,12 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < 16; ++j) r[j] = 0u;
                 }
-                if (g.slices == 1) {
+                if (g.slices == 1 && g.swiglu) {
+                    // all stages have been consumed: the ring's memory is free to carry the tile across warps
+                    float* xbuf = reinterpret_cast<float*>(tiles);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) xbuf[(c + j) * TC_BM + quarter * 32 + lane] = __uint_as_float(r[j]);
+                } else if (g.slices == 1) {
                     if (!g.swapped && !g.out_f32 && m < g.M && n0 + c + 16 <= g.N && (g.ldc % 8 == 0)) {
                         // 16 consecutive bfloat16 of this thread's row: two 16-byte stores
                         uint32_t packed[8];
@@ -229,6 +263,14 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     for (int j = 0; j < 16; ++j) dst[(int64_t)j * TC_BM] = __uint_as_float(r[j]);
                 }
             }
+            if (g.slices == 1 && g.swiglu) {
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const float* xbuf = reinterpret_cast<const float*>(tiles);
+                const int ml = quarter * 32 + lane;
+                if (ml < 64)
+                    for (int c = 0; c < BN; ++c)
+                        store_swiglu(g, m0 + ml, n0 + c, xbuf[c * TC_BM + ml], xbuf[c * TC_BM + ml + 64]);
+            }
             if (g.slices > 1) {
                 // the block that completes the tile last adds the slices, in slice order
                 __threadfence();
@@ -242,11 +284,28 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (*last_flag) {
                     __threadfence();
                     const int ml = quarter * 32 + lane;
-                    for (int c = 0; c < BN; ++c) {
-                        float acc = 0.f;
-                        const float* src = g.partial + (((int64_t)tile * g.slices) * BN + c) * TC_BM + ml;
-                        for (int s = 0; s < g.slices; ++s) acc += __ldcg(src + (int64_t)s * BN * TC_BM);
-                        store_out<BN>(g, m0 + ml, n0 + c, acc);
+                    const int n_live = min(BN, g.N - n0);  // columns that hold tokens
+                    for (int c0 = 0; c0 < n_live; c0 += 4) {
+                        // four columns at a time so that many loads are in flight; slices are added in order
+                        float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
+                        const float* src = g.partial + (((int64_t)tile * g.slices) * BN + c0) * TC_BM + ml;
+#pragma unroll 4
+                        for (int s = 0; s < g.slices; ++s) {
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) acc[u] += __ldcg(src + ((int64_t)s * BN + u) * TC_BM);
+                        }
+                        if (g.swiglu && ml < 64) {
+#pragma unroll 4
+                            for (int s = 0; s < g.slices; ++s) {
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) acc2[u] += __ldcg(src + 64 + ((int64_t)s * BN + u) * TC_BM);
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            if (!g.swiglu) store_out<BN>(g, m0 + ml, n0 + c0 + u, acc[u]);
+                            else if (ml < 64) store_swiglu(g, m0 + ml, n0 + c0 + u, acc[u], acc2[u]);
+                        }
                     }
                 }
             }
@@ -298,7 +357,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& 
     constexpr int smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 256;
     static int configured = (int)cudaFuncSetAttribute(gemm_tc5_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (configured != 0) return configured;
-    gemm_tc5_kernel<BN, STAGES><<<grid, TC_THREADS, smem, stream>>>(ma, mb, g);
+    ss_launch(gemm_tc5_kernel<BN, STAGES>, dim3(grid), dim3(TC_THREADS), smem, stream, ma, mb, g);
     return SS_LAUNCH_CHECK();
 }
 
@@ -307,12 +366,16 @@ extern "C" int64_t ss_gemm_tc5_scratch_floats(int tiles, int slices, int bn) { r
 
 // C = A * B^T (+ bias) in the MMA view: A [M, K] with row stride lda, B [N, K] with row stride ldb, both
 // bfloat16 and K-major, K a multiple of 8 and both bases 16-byte aligned.  bn: tile width (16, 32, 64, 128
-// or 256).  swapped: write C transposed (C[n * ldc + m]).  slices > 1 needs `partial` (see
+// or 256).  swapped: write C transposed (C[n * ldc + m]).  swiglu (swapped, M a multiple of 128): A's rows
+// alternate 64 gate and 64 up features; C gets M / 2 features, silu(gate) * up.  slices > 1 needs `partial` (see
 // ss_gemm_tc5_scratch_floats) and `counters` (one int per tile, zero; left zero).
+extern "C" void ss_set_pdl(int on) { ss_pdl_flag() = on; }
+
 extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
                            int64_t lda, int64_t ldb, int64_t ldc, int bn, int swapped, int out_f32, int slices,
-                           float* partial, int* counters, int* err, cudaStream_t stream) {
+                           int swiglu, float* partial, int* counters, int* err, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
+    if (swiglu && (!swapped || M % TC_BM != 0)) return -2007;
     if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return -2003;
     if (((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2004;
     if (slices < 1 || (slices > 1 && (!partial || !counters))) return -2005;
@@ -324,12 +387,12 @@ extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int b
     GemmArgs g;
     g.C = C; g.bias = bias; g.partial = partial; g.counters = counters; g.err = err;
     g.M = M; g.N = N; g.K = K; g.ldc = ldc; g.slices = slices; g.swapped = swapped; g.out_f32 = out_f32;
-    g.bias_f32 = bias_f32;
+    g.bias_f32 = bias_f32; g.swiglu = swiglu;
     dim3 grid((N + bn - 1) / bn, (M + TC_BM - 1) / TC_BM, slices);
     switch (bn) {
-        case 16: return launch<16, 8>(ma, mb, g, grid, stream);
-        case 32: return launch<32, 8>(ma, mb, g, grid, stream);
-        case 64: return launch<64, 8>(ma, mb, g, grid, stream);
+        case 16: return launch<16, 4>(ma, mb, g, grid, stream);  // three blocks fit on an SM
+        case 32: return launch<32, 4>(ma, mb, g, grid, stream);
+        case 64: return launch<64, 4>(ma, mb, g, grid, stream);  // two blocks fit on an SM
         case 128: return launch<128, 6>(ma, mb, g, grid, stream);
         case 256: return launch<256, 4>(ma, mb, g, grid, stream);
         default: return -2006;

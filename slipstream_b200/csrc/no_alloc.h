@@ -23,9 +23,12 @@
 //    more is refused with SS_NOALLOC_TOO_LARGE and launches nothing.
 //  * The first call on each device looks up the array's device address (with that
 //    device current).  Make that first call during set-up, before any stream capture.
+//  * Beside the floats there are SS_NOALLOC_COUNTERS small counters (one per request and
+//    block of 16 heads of a kv group); a call with more of those is refused the same way.
 //  * All calls share the one array, and it keeps what the last call left in it.
-//    Nothing in it has to start at zero: every slice of every head writes its whole
-//    partial result before the merge reads it.  Two calls that overlap on the GPU
+//    Nothing in the float part has to start at zero: every slice of every head writes its
+//    whole partial result before the merge reads it.  The counters must be zero between
+//    calls; the kernel itself puts them back to zero (the last slice to finish does it).  Two calls that overlap on the GPU
 //    (different streams) would race on the array: run them in one stream or order
 //    them with events.
 #pragma once
@@ -34,6 +37,7 @@
 #include <stdint.h>
 
 #define SS_NOALLOC_SCRATCH_FLOATS (2u * 1024u * 1024u)
+#define SS_NOALLOC_COUNTERS 16384u
 #define SS_NOALLOC_TOO_LARGE (-1001)   // the call needs more scratch than the array holds
 #define SS_NOALLOC_BAD_ARGUMENT (-1002)
 #define SS_NOALLOC_SETUP_FAILED (-1003)  // cudaGetDevice / cudaGetSymbolAddress failed

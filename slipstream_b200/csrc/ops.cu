@@ -16,6 +16,8 @@
 template <typename T>
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab, int* err) {
+    pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
+    pdl_wait();               // nothing below runs before the kernels before this one are complete
     const int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= vocab) {
@@ -32,9 +34,9 @@ extern "C" int ss_embedding(const int32_t* ids, const void* table, float* out, i
     if (n_tokens <= 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (dtype == SS_BF16)
-        embedding_kernel<bf16><<<n_tokens, threads, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab, err);
+        ss_launch(embedding_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, ids, (const bf16*)table, out, hidden, vocab, err);
     else
-        embedding_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, err);
+        ss_launch(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, ids, (const float*)table, out, hidden, vocab, err);
     return SS_LAUNCH_CHECK();
 }
 
@@ -74,6 +76,8 @@ template <typename T, int VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                    const void* __restrict__ weight, int w_f32, T* __restrict__ y,
                                    const int32_t* __restrict__ rows, int hidden, float eps) {
+    pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
+    pdl_wait();               // nothing below runs before the kernels before this one are complete
     __shared__ float scratch[33];
     const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
     float* res = residual + src * hidden;
@@ -140,10 +144,10 @@ static void launch_add_rmsnorm(float* residual, const void* delta, const void* w
         int threads = ((hidden / 4 + 1) / 2 + 31) / 32 * 32;  // two vectors per thread at most
         if (hidden / 4 <= 1024) threads = (hidden / 4 + 31) / 32 * 32;  // one vector per thread when it fits
         threads = threads < 32 ? 32 : threads;
-        add_rmsnorm_kernel<T, 4><<<n_rows, threads, 0, stream>>>(residual, (const T*)delta, weight, w_f32, (T*)y, rows, hidden, eps);
+        ss_launch(add_rmsnorm_kernel<T, 4>, dim3(n_rows), dim3(threads), 0, stream, residual, (const T*)delta, weight, w_f32, (T*)y, rows, hidden, eps);
     } else {
         const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-        add_rmsnorm_kernel<T, 1><<<n_rows, threads, 0, stream>>>(residual, (const T*)delta, weight, w_f32, (T*)y, rows, hidden, eps);
+        ss_launch(add_rmsnorm_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, stream, residual, (const T*)delta, weight, w_f32, (T*)y, rows, hidden, eps);
     }
 }
 
@@ -160,81 +164,53 @@ extern "C" int ss_add_rmsnorm(float* residual, const void* delta, const void* we
 
 // ---------------------------------------------------------------- rotary + page write
 
-// One block per token.  qkv row = [n_q heads | n_kv key heads | n_kv value heads] x D.
-// Queries are rotated in place; keys are rotated and written to their page, values
-// are copied to theirs.  kv layout: [page][2][kv head][offset in page][D].
-// A slot of -1 (or write_cache == 0) skips the write; keys are then rotated in place.
+// qkv row = [n_q heads | n_kv key heads | n_kv value heads] x D.  Queries are rotated in place; keys are
+// rotated and written to their page, values are copied to theirs.  kv layout:
+// [page][2][kv head][offset in page][D].  A slot of -1 (or write_cache == 0) skips the write; keys are then
+// rotated in place.  Grid: (token, chunk of the token's work); a thread owns one rotated pair, or one key
+// element beyond the rotary part, or one value element, so that nothing in the kernel is a serial chain.
 template <typename T>
 __global__ void rope_cache_kernel(T* __restrict__ qkv, const int32_t* __restrict__ positions,
                                   const int32_t* __restrict__ slots, const float* __restrict__ inv_freq,
                                   T* __restrict__ kv, int n_q, int n_kv, int D, int rot_dim,
                                   int page_size, int64_t pool_slots, int write_cache, int* err) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     T* row = qkv + (int64_t)t * (n_q + 2 * n_kv) * D;
-    const float pos = (float)positions[t];
     int64_t slot = (write_cache && slots) ? (int64_t)slots[t] : -1;
     if (slot >= pool_slots) {
-        if (threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
+        if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
         slot = -1;
     }
     const int64_t page = slot >= 0 ? slot / page_size : 0;
     const int off = slot >= 0 ? (int)(slot % page_size) : 0;
-    const int half = rot_dim / 2;
-
-    // rotated pairs of queries and keys: a thread owns pair i and walks over the heads, so the sine and
-    // cosine of its angle are formed once
-    const int lanes = half > 0 ? blockDim.x / half : 0;  // threads that share a pair index
-    if (lanes > 0) {
-        const int i = threadIdx.x % half, h0 = threadIdx.x / half;
-        if (h0 < lanes) {
-            const float angle = __fmul_rn(pos, inv_freq[i]);
-            float s, c;
-            sincosf(angle, &s, &c);
-            for (int h = h0; h < n_q + n_kv; h += lanes) {
-                T* head = row + (int64_t)h * D;
-                const float x1 = to_float(head[i]), x2 = to_float(head[i + half]);
-                // q*cos + rotate_half(q)*sin, each product and the sum rounded as written
-                const T o1 = from_float<T>(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(-x2, s)));
-                const T o2 = from_float<T>(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s)));
-                if (h < n_q || slot < 0) {
-                    head[i] = o1;
-                    head[i + half] = o2;
-                } else {
-                    T* dst = kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
-                    dst[i] = o1;
-                    dst[i + half] = o2;
-                }
-            }
+    const int half = rot_dim / 2, tail = D - rot_dim;
+    const int n_rot = (n_q + n_kv) * half, n_tail = n_kv * tail, n_val = n_kv * D;
+    const int idx = blockIdx.y * blockDim.x + threadIdx.x;
+    if (idx < n_rot) {
+        const int h = idx / half, i = idx - h * half;
+        T* head = row + (int64_t)h * D;
+        const float x1 = to_float(head[i]), x2 = to_float(head[i + half]);
+        const float angle = __fmul_rn((float)positions[t], inv_freq[i]);
+        float s, c;
+        sincosf(angle, &s, &c);
+        // q*cos + rotate_half(q)*sin, each product and the sum rounded as written
+        const T o1 = from_float<T>(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(-x2, s)));
+        const T o2 = from_float<T>(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s)));
+        if (h < n_q || slot < 0) {
+            head[i] = o1;
+            head[i + half] = o2;
+        } else {
+            T* dst = kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
+            dst[i] = o1;
+            dst[i + half] = o2;
         }
-    } else if (half > 0) {  // more pairs than threads
-        for (int idx = threadIdx.x; idx < (n_q + n_kv) * half; idx += blockDim.x) {
-            const int h = idx / half, i = idx - h * half;
-            T* head = row + (int64_t)h * D;
-            const float x1 = to_float(head[i]), x2 = to_float(head[i + half]);
-            const float angle = __fmul_rn(pos, inv_freq[i]);
-            float s, c;
-            sincosf(angle, &s, &c);
-            const T o1 = from_float<T>(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(-x2, s)));
-            const T o2 = from_float<T>(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s)));
-            if (h < n_q || slot < 0) {
-                head[i] = o1;
-                head[i + half] = o2;
-            } else {
-                T* dst = kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
-                dst[i] = o1;
-                dst[i + half] = o2;
-            }
-        }
-    }
-    if (slot < 0) return;
-    // key dims beyond the rotary part, and the values
-    const int tail = D - rot_dim;
-    for (int idx = threadIdx.x; idx < n_kv * tail; idx += blockDim.x) {
-        const int h = idx / tail, d = rot_dim + (idx - h * tail);
+    } else if (slot >= 0 && idx < n_rot + n_tail) {
+        const int j = idx - n_rot, h = j / tail, d = rot_dim + (j - h * tail);
         kv[(((page * 2 + 0) * n_kv + h) * page_size + off) * (int64_t)D + d] = row[(int64_t)(n_q + h) * D + d];
-    }
-    for (int idx = threadIdx.x; idx < n_kv * D; idx += blockDim.x) {
-        const int h = idx / D, d = idx - h * D;
+    } else if (slot >= 0 && idx < n_rot + n_tail + n_val) {
+        const int j = idx - n_rot - n_tail, h = j / D, d = j - h * D;
         kv[(((page * 2 + 1) * n_kv + h) * page_size + off) * (int64_t)D + d] = row[(int64_t)(n_q + n_kv + h) * D + d];
     }
 }
@@ -245,54 +221,60 @@ extern "C" int ss_rope_cache(void* qkv, const int32_t* positions, const int32_t*
                              int* err, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const int threads = 256;
+    const int work = (n_q + n_kv) * (rot_dim / 2) + n_kv * (D - rot_dim) + n_kv * D;
+    const dim3 grid(n_tokens, (work + threads - 1) / threads);
     const int64_t pool = num_pages * page_size;
     if (dtype == SS_BF16)
-        rope_cache_kernel<bf16><<<n_tokens, threads, 0, stream>>>((bf16*)qkv, positions, slots, inv_freq, (bf16*)kv, n_q, n_kv, D, rot_dim, page_size, pool, write_cache, err);
+        ss_launch(rope_cache_kernel<bf16>, grid, dim3(threads), 0, stream, (bf16*)qkv, positions, slots, inv_freq, (bf16*)kv, n_q, n_kv, D, rot_dim, page_size, pool, write_cache, err);
     else
-        rope_cache_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, positions, slots, inv_freq, (float*)kv, n_q, n_kv, D, rot_dim, page_size, pool, write_cache, err);
+        ss_launch(rope_cache_kernel<float>, grid, dim3(threads), 0, stream, (float*)qkv, positions, slots, inv_freq, (float*)kv, n_q, n_kv, D, rot_dim, page_size, pool, write_cache, err);
     return SS_LAUNCH_CHECK();
 }
 
 // ---------------------------------------------------------------- SwiGLU
 
-// in: [n, 2*inter] = [gate | up];  out[n, inter] = silu(gate) * up, formed in float32.
+// in: [n, 2*inter]: gate and up features alternate in runs of `block` ([gate run | up run | gate run | ...];
+// block = inter is the plain [gate | up]);  out[n, inter] = silu(gate) * up, formed in float32.
 template <typename T, int VEC>
-__global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t n, int inter) {
+__global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t n, int inter, int block) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int per_row = inter / VEC;
     const int64_t total = n * per_row;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = idx / per_row;
         const int c = (int)(idx - r * per_row) * VEC;
-        const T* gp = in + r * 2 * inter + c;
+        const T* gp = in + r * 2 * inter + (int64_t)(c / block) * 2 * block + (c % block);
         if (VEC == 4) {
             float g[4], u[4], o[4];
             Vec4<T>::load(gp, g);
-            Vec4<T>::load(gp + inter, u);
+            Vec4<T>::load(gp + block, u);
 #pragma unroll
             for (int e = 0; e < 4; ++e) o[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
             Vec4<T>::store(out + r * inter + c, o);
         } else {
-            const float g = to_float(gp[0]), u = to_float(gp[inter]);
+            const float g = to_float(gp[0]), u = to_float(gp[block]);
             out[r * inter + c] = from_float<T>(g / (1.0f + expf(-g)) * u);
         }
     }
 }
 
 template <typename T>
-static void launch_swiglu(const void* in, void* out, int64_t n, int inter, cudaStream_t stream) {
+static void launch_swiglu(const void* in, void* out, int64_t n, int inter, int block, cudaStream_t stream) {
     const int threads = 256;
-    const int vec = inter % 4 == 0 ? 4 : 1;
+    const int vec = (inter % 4 == 0 && block % 4 == 0) ? 4 : 1;
     int64_t blocks = (n * (inter / vec) + threads - 1) / threads;
     if (blocks > 148 * 32) blocks = 148 * 32;
-    if (vec == 4) swiglu_kernel<T, 4><<<(int)blocks, threads, 0, stream>>>((const T*)in, (T*)out, n, inter);
-    else swiglu_kernel<T, 1><<<(int)blocks, threads, 0, stream>>>((const T*)in, (T*)out, n, inter);
+    if (vec == 4) ss_launch(swiglu_kernel<T, 4>, dim3((int)blocks), dim3(threads), 0, stream, (const T*)in, (T*)out, n, inter, block);
+    else ss_launch(swiglu_kernel<T, 1>, dim3((int)blocks), dim3(threads), 0, stream, (const T*)in, (T*)out, n, inter, block);
 }
 
-extern "C" int ss_swiglu(const void* in, void* out, int64_t n, int inter, int dtype, cudaStream_t stream) {
+extern "C" int ss_swiglu(const void* in, void* out, int64_t n, int inter, int block, int dtype, cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (dtype == SS_BF16) launch_swiglu<bf16>(in, out, n, inter, stream);
-    else launch_swiglu<float>(in, out, n, inter, stream);
+    if (block <= 0 || inter % block != 0) return (int)cudaErrorInvalidValue;
+    if (dtype == SS_BF16) launch_swiglu<bf16>(in, out, n, inter, block, stream);
+    else launch_swiglu<float>(in, out, n, inter, block, stream);
     return SS_LAUNCH_CHECK();
 }
 
@@ -311,6 +293,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TA* __restrict__ A
                                                         const void* __restrict__ bias, int bias_f32,
                                                         TC* __restrict__ C, int M, int N, int K,
                                                         int64_t lda, int64_t ldc) {
+    pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
+    pdl_wait();               // nothing below runs before the kernels before this one are complete
     __shared__ float As[GB_K][GB_M + 4];
     __shared__ float Ws[GB_K][GB_N + 4];
     const int tid = threadIdx.x;
@@ -369,12 +353,14 @@ extern "C" int ss_gemm_simt(const void* A, const void* W, const void* bias, int 
     if (M <= 0 || N <= 0) return 0;
     dim3 grid((N + GB_N - 1) / GB_N, (M + GB_M - 1) / GB_M);
     if (dtype_in == SS_F32 && dtype_out == SS_F32)
-        gemm_simt_kernel<float, float, float><<<grid, 256, 0, stream>>>((const float*)A, (const float*)W, bias, bias_f32, (float*)C, M, N, K, lda, ldc);
+        ss_launch(gemm_simt_kernel<float, float, float>, dim3(grid), dim3(256), 0, stream, (const float*)A, (const float*)W, bias, bias_f32, (float*)C, M, N, K, lda, ldc);
     else if (dtype_in == SS_BF16 && dtype_out == SS_F32)
-        gemm_simt_kernel<bf16, bf16, float><<<grid, 256, 0, stream>>>((const bf16*)A, (const bf16*)W, bias, bias_f32, (float*)C, M, N, K, lda, ldc);
+        ss_launch(gemm_simt_kernel<bf16, bf16, float>, dim3(grid), dim3(256), 0, stream, (const bf16*)A, (const bf16*)W, bias, bias_f32, (float*)C, M, N, K, lda, ldc);
     else if (dtype_in == SS_BF16 && dtype_out == SS_BF16)
-        gemm_simt_kernel<bf16, bf16, bf16><<<grid, 256, 0, stream>>>((const bf16*)A, (const bf16*)W, bias, bias_f32, (bf16*)C, M, N, K, lda, ldc);
+        ss_launch(gemm_simt_kernel<bf16, bf16, bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)A, (const bf16*)W, bias, bias_f32, (bf16*)C, M, N, K, lda, ldc);
     else
         return (int)cudaErrorInvalidValue;
     return SS_LAUNCH_CHECK();
 }
+
+extern "C" void ss_set_pdl(int on) { ss_pdl_flag() = on; }

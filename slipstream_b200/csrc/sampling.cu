@@ -94,6 +94,8 @@ __device__ __forceinline__ unsigned long long block_max_u64(unsigned long long v
 __global__ void __launch_bounds__(ARGMAX_THREADS)
 argmax_partial_kernel(const float* __restrict__ logits, unsigned long long* __restrict__ partial, int vocab,
                       int64_t stride) {
+    pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
+    pdl_wait();               // nothing below runs before the kernels before this one are complete
     __shared__ unsigned long long scratch[32];
     const float* row = logits + (int64_t)blockIdx.x * stride;
     const int per = (vocab + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
@@ -108,6 +110,8 @@ argmax_partial_kernel(const float* __restrict__ logits, unsigned long long* __re
 }
 
 __global__ void argmax_final_kernel(const unsigned long long* __restrict__ partial, int32_t* __restrict__ out) {
+    pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
+    pdl_wait();               // nothing below runs before the kernels before this one are complete
     unsigned long long v = partial[(int64_t)blockIdx.x * ARGMAX_CHUNKS + threadIdx.x];  // 32 threads
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -122,8 +126,8 @@ extern "C" int ss_argmax(const float* logits, int32_t* out, int rows, int vocab,
                          unsigned long long* scratch, cudaStream_t stream) {
     if (rows <= 0) return 0;
     static_assert(ARGMAX_CHUNKS == 32, "the final kernel reduces one warp of partial results");
-    argmax_partial_kernel<<<dim3(rows, ARGMAX_CHUNKS), ARGMAX_THREADS, 0, stream>>>(logits, scratch, vocab, stride);
-    argmax_final_kernel<<<rows, 32, 0, stream>>>(scratch, out);
+    ss_launch(argmax_partial_kernel, dim3(dim3(rows, ARGMAX_CHUNKS)), dim3(ARGMAX_THREADS), 0, stream, logits, scratch, vocab, stride);
+    ss_launch(argmax_final_kernel, dim3(rows), dim3(32), 0, stream, scratch, out);
     return SS_LAUNCH_CHECK();
 }
 
@@ -178,6 +182,8 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, int32_t* __restr
               const float* __restrict__ penalty, const int64_t* __restrict__ seeds,
               const int64_t* __restrict__ draws, uint32_t* __restrict__ seen_all,
               int seen_words, const int32_t* __restrict__ slots, int vocab) {
+    pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
+    pdl_wait();               // nothing below runs before the kernels before this one are complete
     __shared__ SampleShared sh;
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (int64_t)r * stride;
@@ -318,7 +324,7 @@ extern "C" int ss_sample(const float* logits, int64_t stride, int32_t* out, cons
                          uint32_t* seen, int seen_words, const int32_t* slots, int rows, int vocab,
                          cudaStream_t stream) {
     if (rows <= 0) return 0;
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, stride, out, temperature, top_k, top_p,
+    ss_launch(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, stride, out, temperature, top_k, top_p,
                                                        min_p, penalty, seeds, draws, seen, seen_words,
                                                        slots, vocab);
     return SS_LAUNCH_CHECK();
@@ -327,6 +333,8 @@ extern "C" int ss_sample(const float* logits, int64_t stride, int32_t* out, cons
 // Set the history bits of `n` token ids in one request's row of the seen-token table.
 __global__ void mark_seen_kernel(uint32_t* __restrict__ seen_row, const int32_t* __restrict__ ids, int n,
                                  int vocab) {
+    pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
+    pdl_wait();               // nothing below runs before the kernels before this one are complete
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const int t = ids[i];
         if (t >= 0 && t < vocab) atomicOr(&seen_row[t >> 5], 1u << (t & 31));
@@ -335,6 +343,6 @@ __global__ void mark_seen_kernel(uint32_t* __restrict__ seen_row, const int32_t*
 
 extern "C" int ss_mark_seen(uint32_t* seen_row, const int32_t* ids, int n, int vocab, cudaStream_t stream) {
     if (n <= 0) return 0;
-    mark_seen_kernel<<<(n + 255) / 256 > 64 ? 64 : (n + 255) / 256, 256, 0, stream>>>(seen_row, ids, n, vocab);
+    ss_launch(mark_seen_kernel, dim3((n + 255) / 256 > 64 ? 64 : (n + 255) / 256), dim3(256), 0, stream, seen_row, ids, n, vocab);
     return SS_LAUNCH_CHECK();
 }

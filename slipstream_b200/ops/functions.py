@@ -40,7 +40,7 @@ _OPS_SIGNATURES = {
                        c_float, c_int, c_void_p],
     "ss_rope_cache": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                       c_int, c_int, c_int64, c_int, c_int, c_void_p, c_void_p],
-    "ss_swiglu": [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p],
+    "ss_swiglu": [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p],
     "ss_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64,
                      c_int64, c_int, c_int, c_void_p],
     "ss_argmax": [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p],
@@ -58,12 +58,12 @@ _ATTN_SIGNATURES = {
                             c_int, c_void_p, c_void_p],
     "ss_attn_decode_mma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
-                           c_void_p, c_void_p, c_void_p, c_void_p],
+                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
 _GEMM_SIGNATURES = {
     "ss_gemm_tc5": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
-                    c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+                    c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
 _state: dict[str, object] = {}
@@ -246,15 +246,19 @@ def rope_and_cache(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tens
                                        error_word(qkv.device).data_ptr(), _stream()), "rope_and_cache")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``silu(gate) * up`` for ``gate_up`` = [N, 2 * I] holding [gate | up]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, block: int | None = None) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gate_up`` = [N, 2 * I].  Gate and up features alternate in runs of ``block``
+    columns (gate run, up run, gate run, ...); the default, ``block`` = I, is the plain [gate | up]."""
     _need(gate_up, None, "gate_up")
     n, two_i = gate_up.shape
     inter = two_i // 2
+    block = inter if block is None else block
+    if block < 1 or inter % block:
+        raise KernelError(f"block {block} does not divide the {inter} features")
     if out is None:
         out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
     _need(out, gate_up.dtype, "swiglu output")
-    _check(ops_library().ss_swiglu(gate_up.data_ptr(), out.data_ptr(), n, inter, _code(gate_up.dtype),
+    _check(ops_library().ss_swiglu(gate_up.data_ptr(), out.data_ptr(), n, inter, block, _code(gate_up.dtype),
                                    _stream()), "swiglu")
     return out
 
@@ -328,6 +332,20 @@ def paged_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
                                    error_word(q.device).data_ptr(), _stream()), "paged_attention_prefill")
 
 
+_DECODE_COUNTERS = 65536
+
+
+def decode_counters(device: torch.device) -> torch.Tensor:
+    """Counters of the split decode kernel (one per request and head block): zero between launches, which
+    the kernel itself restores, so one tensor per device serves every call."""
+    key = f"decode_counters{device}"
+    counters = _state.get(key)
+    if counters is None:
+        counters = torch.zeros(_DECODE_COUNTERS, dtype=torch.int32, device=device)
+        _state[key] = counters
+    return counters  # type: ignore[return-value]
+
+
 def decode_scratch(n_requests: int, n_q: int, n_slices: int, head_dim: int, device: torch.device):
     """Scratch memory of the split decode kernel: partial outputs and their log-sum-exps."""
     return (torch.empty((n_requests, n_q, n_slices, head_dim), dtype=torch.float32, device=device),
@@ -340,15 +358,18 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
                            n_slices: int = 1, scratch: tuple[torch.Tensor, torch.Tensor] | None = None) -> None:
     """bfloat16 attention for requests that bring ONE token each, the keys of every request cut into
     ``n_slices`` slices that run in parallel; with more than one slice the partial results pass through
-    ``scratch`` (see ``decode_scratch``) and a second kernel merges them."""
+    ``scratch`` (see ``decode_scratch``) and the block that finishes a head block last combines them."""
     _need(out, torch.bfloat16, "attention output")
     _need(kv, torch.bfloat16, "kv pages")
     if q.dtype != torch.bfloat16:
         raise KernelError("the tensor-core attention kernels take bfloat16")
     for name, t in (("block_tables", block_tables), ("q_start", q_start), ("seq_lens", seq_lens)):
         _need(t, torch.int32, name)
-    part_o = part_lse = None
+    part_o = part_lse = counters = None
     if n_slices > 1:
+        counters = decode_counters(q.device)
+        if n_requests * n_kv * ((n_q // n_kv + 15) // 16) > _DECODE_COUNTERS:
+            raise KernelError("too many (request, head block) pairs for the decode counters")
         if scratch is None:
             scratch = decode_scratch(n_requests, n_q, n_slices, head_dim, q.device)
         part_o, part_lse = scratch
@@ -358,17 +379,16 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
     _check(lib.ss_attn_decode_mma(q.data_ptr(), q_stride, out.data_ptr(), out.shape[1], kv.data_ptr(),
                                   block_tables.data_ptr(), block_tables.shape[1], n_requests, q_start.data_ptr(),
                                   seq_lens.data_ptr(), n_q, n_kv, kv.shape[3], kv.shape[0], float(scale),
-                                  int(window or 0), n_slices, _ptr(part_o), _ptr(part_lse),
+                                  int(window or 0), n_slices, _ptr(part_o), _ptr(part_lse), _ptr(counters),
                                   error_word(q.device).data_ptr(), _stream()), "paged_attention_decode")
-    if n_slices > 1:
-        _launches[0] += 1  # the merge kernel
 
 
 def decode_slices(n_requests: int, n_kv: int, group: int, max_seq_len: int) -> int:
-    """How many slices to cut the keys into so that a decode step fills the 148 SMs about twice."""
+    """How many slices to cut the keys into: as many as keep all blocks resident at once (two per SM on
+    148 SMs), so that the step is one wave of blocks."""
     blocks = n_requests * n_kv * ((group + 15) // 16)
     tiles = max(1, (max_seq_len + 63) // 64)
-    return max(1, min((2 * 148 + blocks - 1) // blocks, tiles, 32))
+    return max(1, min((2 * 148) // blocks, tiles, 32))
 
 
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, block_tables: torch.Tensor,
@@ -482,9 +502,13 @@ def gemm_plan(tokens: int, features: int, k: int) -> tuple[bool, int, int]:
 
 
 def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
-                 out_dtype: torch.dtype | None = None, plan: tuple[bool, int, int] | None = None) -> torch.Tensor:
+                 out_dtype: torch.dtype | None = None, plan: tuple[bool, int, int] | None = None,
+                 swiglu: bool = False) -> torch.Tensor:
     """``x @ weight.T + bias`` for bfloat16 ``x`` [tokens, K] and ``weight`` [features, K] on the tcgen05 tensor
-    cores (TMA-fed, accumulator in tensor memory); output bfloat16 or float32.  K must be a multiple of 8."""
+    cores (TMA-fed, accumulator in tensor memory); output bfloat16 or float32.  K must be a multiple of 8.
+
+    ``swiglu`` (at most 64 tokens, features a multiple of 128): the weight's rows alternate 64 gate and 64 up
+    features; the result is ``silu(gate) * up`` with features / 2 columns, formed in the product's epilogue."""
     _need(x, torch.bfloat16, "x")
     _need(weight, torch.bfloat16, "weight")
     tokens, k = x.shape
@@ -494,7 +518,9 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
     if k % 8 != 0:
         raise KernelError(f"the tensor-core matrix product needs K to be a multiple of 8, got {k}")
     out_dtype = out_dtype or torch.bfloat16
-    out = torch.empty((tokens, features), dtype=out_dtype, device=x.device)
+    if swiglu and (tokens > 64 or features % 128):
+        raise KernelError("the fused SwiGLU epilogue takes at most 64 tokens and a multiple of 128 weight rows")
+    out = torch.empty((tokens, features // 2 if swiglu else features), dtype=out_dtype, device=x.device)
     if tokens == 0:
         return out
     bias_f32 = 0
@@ -512,19 +538,36 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
             raise KernelError("split-K workspace too small for this problem")
     a, b = (weight, x) if swapped else (x, weight)
     rc = gemm_library().ss_gemm_tc5(a.data_ptr(), b.data_ptr(), _ptr(bias), bias_f32, out.data_ptr(), a.shape[0],
-                                    b.shape[0], k, k, k, features, bn, int(swapped), int(out_dtype == torch.float32),
-                                    slices, _ptr(partial), _ptr(counters), error_word(x.device).data_ptr(), _stream())
+                                    b.shape[0], k, k, k, out.shape[1], bn, int(swapped), int(out_dtype == torch.float32),
+                                    slices, int(swiglu), _ptr(partial), _ptr(counters),
+                                    error_word(x.device).data_ptr(), _stream())
     _check(rc, "gemm_tcgen05")
     return out
 
 
+SMALL_BATCH = 64  # up to this many tokens a projection may stream its weights through the tcgen05 kernel
+STREAM_TILES = 148  # ... when its 128-row weight tiles are at least as many as the SMs (no K slices needed)
+
+
+def streams_weights(tokens: int, features: int, k: int) -> bool:
+    """True where the hand-written tcgen05 kernel is the faster way to run a bfloat16 projection: few tokens
+    and enough weight tiles to give every SM one (measured: 43 us against the library's 46.5 us for the
+    gate/up product of the 7B shape at 8 tokens; smaller products, which need K slices, are slower)."""
+    return tokens <= SMALL_BATCH and k % 8 == 0 and (features + 127) // 128 >= STREAM_TILES
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
            out_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """A projection ``x @ weight.T + bias``.  float32 runs the SIMT kernel (no reduced-precision
-    matrix mode); bfloat16 runs the library matrix product, as the reference's nn.Linear does
-    (slipstream/models/layers/attention.py:132-135)."""
+    """A projection ``x @ weight.T + bias``.
+
+    float32 runs the CUDA-core kernel (no reduced-precision matrix mode).  bfloat16 with few tokens (decode
+    steps) and a large weight runs the hand-written tcgen05 kernel, which streams the weights once and
+    overlaps its first fetches with the kernel before it; other bfloat16 products run the library matrix
+    product, as the reference's nn.Linear does (slipstream/models/layers/attention.py:132-135)."""
     if x.dtype == torch.float32:
         return gemm_simt(x, weight, bias, out_dtype)
+    if streams_weights(x.shape[0], weight.shape[0], x.shape[1]):
+        return gemm_tcgen05(x, weight, bias, out_dtype)
     if out_dtype is None or out_dtype == x.dtype:
         if bias is not None:
             return torch.addmm(bias, x, weight.t())
@@ -535,6 +578,25 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     return out
 
 
+def gate_up_swiglu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, block: int) -> torch.Tensor:
+    """``silu(x @ Wg.T + bg) * (x @ Wu.T + bu)`` where ``weight`` [2 I, K] holds gate and up rows alternating in
+    runs of ``block``.  Small bfloat16 batches with runs of 64 do it in one kernel."""
+    if (x.dtype == torch.bfloat16 and block == 64 and weight.shape[0] % 128 == 0
+            and streams_weights(x.shape[0], weight.shape[0], x.shape[1])):
+        return gemm_tcgen05(x, weight, bias, swiglu=True)
+    return swiglu(linear(x, weight, bias), block=block)
+
+
+def set_programmatic_launch(enabled: bool) -> None:
+    """Turn programmatic dependent launch of this package's kernels on or off (on by default)."""
+    libs = [ops_library(), gemm_library()] + [lib for key, lib in _state.items() if key.startswith("attn")]
+    for lib in libs:
+        lib.ss_set_pdl.argtypes = [c_int]
+        lib.ss_set_pdl.restype = None
+        lib.ss_set_pdl(int(enabled))
+    _state["pdl"] = bool(enabled)
+
+
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "paged_attention_prefill", "paged_attention_decode", "decode_scratch", "decode_slices", "require_cuda", "argmax", "sample", "mark_seen", "gemm_tcgen05", "gemm_plan", "gemm_library", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "paged_attention_prefill", "paged_attention_decode", "decode_scratch", "decode_slices", "require_cuda", "argmax", "sample", "mark_seen", "gemm_tcgen05", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
            "attention_library"]

@@ -35,16 +35,26 @@ class SwiGLUFeedForward(FeedForward):
     def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(weights, runtime)
         n = self.name
-        self.gate_up = torch.cat([weights[f"{n}.gate_proj.weight"], weights[f"{n}.up_proj.weight"]], dim=0).contiguous()
+        # gate and up rows alternate in runs of `block`, so that one 128-row tile of the stacked product holds
+        # 64 gate features and the 64 matching up features (the fused epilogue needs both in one block)
+        i = self.intermediate_size
+        self.block = 64 if i % 64 == 0 else i
+
+        def interleave(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+            g = gate.reshape(i // self.block, self.block, *gate.shape[1:])
+            u = up.reshape(i // self.block, self.block, *up.shape[1:])
+            return torch.stack([g, u], dim=1).reshape(2 * i, *gate.shape[1:]).contiguous()
+
+        self.gate_up = interleave(weights[f"{n}.gate_proj.weight"], weights[f"{n}.up_proj.weight"])
         self.down = weights[f"{n}.down_proj.weight"]
         self.gate_up_bias = self.down_bias = None
         if self.bias:
-            self.gate_up_bias = torch.cat([weights[f"{n}.gate_proj.bias"], weights[f"{n}.up_proj.bias"]]).to(runtime.dtype)
+            self.gate_up_bias = interleave(weights[f"{n}.gate_proj.bias"], weights[f"{n}.up_proj.bias"]).to(runtime.dtype)
             self.down_bias = weights[f"{n}.down_proj.bias"].to(runtime.dtype)
 
     def weight_bytes(self) -> int:
         return (self.gate_up.numel() + self.down.numel()) * self.down.element_size()
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        gate_up = ops.linear(x, self.gate_up, self.gate_up_bias)
-        return ops.linear(ops.swiglu(gate_up), self.down, self.down_bias)
+        hidden = ops.gate_up_swiglu(x, self.gate_up, self.gate_up_bias, self.block)
+        return ops.linear(hidden, self.down, self.down_bias)

@@ -102,6 +102,11 @@ def test_swiglu(dtype):
     x = (torch.randn(13, 2 * 1234, device=DEV) * 3).to(dtype)
     g, u = x[:, :1234].double(), x[:, 1234:].double()
     assert rel_err(ops().swiglu(x), g * torch.sigmoid(g) * u) < tol(dtype, 2e-6, 8e-3)
+    # gate and up alternating in runs of 2 and of 617 columns
+    for block in (2, 617):
+        v = x.double().view(13, 1234 // block, 2, block)
+        g, u = v[:, :, 0].reshape(13, 1234), v[:, :, 1].reshape(13, 1234)
+        assert rel_err(ops().swiglu(x, block=block), g * torch.sigmoid(g) * u) < tol(dtype, 2e-6, 8e-3)
 
 
 @pytest.mark.parametrize("m, n, k", [(1, 130, 70), (37, 65, 1000), (200, 333, 96)])
@@ -294,4 +299,23 @@ def test_tcgen05_split_k_is_deterministic_and_leaves_its_counters_clean():
     for slices in (1, 2, 7):
         got = ops().gemm_tcgen05(x, w, None, torch.float32, plan=(True, 16, slices))
         assert rel_err(got, a) < 1e-4  # 18,944 float32 additions in another order
+    ops().check_errors(torch.device(DEV))
+
+
+@pytest.mark.parametrize("tokens, inter, k, bias", [(1, 64, 64, False), (8, 18944, 3584, False), (33, 192, 136, True), (64, 640, 200, True)])
+def test_tcgen05_fused_swiglu(tokens, inter, k, bias):
+    """Weight rows alternate 64 gate and 64 up features; the epilogue gives silu(gate) * up."""
+    torch.manual_seed(inter)
+    x = torch.randn(tokens, k, device=DEV).bfloat16()
+    gate, up = ((torch.randn(inter, k, device=DEV) * 0.05).bfloat16() for _ in range(2))
+    bg, bu = ((torch.randn(inter, device=DEV) * 0.5).bfloat16() for _ in range(2))
+    mix = lambda a, b: torch.stack([a.reshape(inter // 64, 64, *a.shape[1:]), b.reshape(inter // 64, 64, *b.shape[1:])], 1).reshape(2 * inter, *a.shape[1:]).contiguous()
+    g = x.double() @ gate.double().T + (bg.double() if bias else 0)
+    u = x.double() @ up.double().T + (bu.double() if bias else 0)
+    ref = g * torch.sigmoid(g) * u
+    for plan in (None, (True, 16 if tokens <= 16 else 64, 1), (True, 64, 3)):
+        got = ops().gemm_tcgen05(x, mix(gate, up), mix(bg, bu) if bias else None, swiglu=True, plan=plan)
+        assert got.shape == (tokens, inter) and rel_err(got, ref) < 8e-3, plan
+    got = ops().gate_up_swiglu(x, mix(gate, up), mix(bg, bu) if bias else None, 64)
+    assert rel_err(got, ref) < 8e-3
     ops().check_errors(torch.device(DEV))

@@ -59,14 +59,15 @@ def test_rmsnorm_part(dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu_feed_forward_part(dtype):
     from slipstream_b200.parts import SwiGLUFeedForward
-    for bias in (False, True):
-        part = SwiGLUFeedForward("m", 72, 200, bias=bias)
+    for bias, inter, tokens in ((False, 200, 11), (True, 200, 11), (True, 192, 5), (False, 320, 100)):
+        part = SwiGLUFeedForward("m", 72, inter, bias=bias)
         dev, ref = draw(part, dtype, seed=3)
         part.bind(dev, runtime(dtype))
-        x = torch.randn(11, 72).to(dtype)
+        assert part.block == (64 if inter % 64 == 0 else inter)
+        x = torch.randn(tokens, 72).to(dtype)
         got = part.forward(x.to(DEV), None)
         assert rel(got, plain.swiglu_mlp(x.double(), ref, "m")) < TOL[dtype]
-        assert part.weight_bytes() == 3 * 72 * 200 * (4 if dtype == torch.float32 else 2)
+        assert part.weight_bytes() == 3 * 72 * inter * (4 if dtype == torch.float32 else 2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
