@@ -63,7 +63,7 @@ extern "C" int ss_attn_decode_mma(const void* q, int64_t q_stride, void* out, in
                                   float* part_o, float* part_lse, int* counters, int* err, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (n_slices < 1 || (n_slices > 1 && (!part_o || !part_lse || !counters))) return (int)cudaErrorInvalidValue;
-    constexpr int smem = mma_smem_bytes<HEAD_DIM>(16);
+    constexpr int smem = mma_smem_bytes<HEAD_DIM>(16, DECODE_STAGES);
     static int configured = set_smem(attn_decode_mma<HEAD_DIM>, smem);
     if (configured != 0) return configured;
     const int G = n_q / n_kv;
@@ -135,7 +135,7 @@ extern "C" int ss_attn_decode_noalloc(const void* q, int64_t q_stride, void* out
     float* part_o = scratch;
     float* part_lse = scratch + (int64_t)n_requests * n_q * n_slices * HEAD_DIM;
 
-    constexpr int smem = mma_smem_bytes<HEAD_DIM>(16);
+    constexpr int smem = mma_smem_bytes<HEAD_DIM>(16, DECODE_STAGES);
     static int configured = set_smem(attn_decode_mma<HEAD_DIM>, smem);
     if (configured != 0) return configured;
     const int G = n_q / n_kv;

@@ -52,11 +52,43 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+#define MMA_TABLE_MAX 1024  // block-table entries a block keeps in shared memory
+
+// The part of a request's block table a block needs: entry of block b is p[b - base].  p points at a copy
+// in shared memory when the range fits, else at the table in global memory (base 0).
+struct TableRef {
+    const int32_t* p;
+    int base;
+    int shift;  // log2(page_size) when it is a power of two, else -1
+};
+
+__device__ __forceinline__ TableRef stage_table(int32_t* smem_table, const int32_t* __restrict__ table, int first_key,
+                                                int last_key, int page_size) {
+    TableRef t;
+    t.shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
+    const int b0 = first_key / page_size, b1 = last_key / page_size;
+    if (last_key >= first_key && b1 - b0 + 1 <= MMA_TABLE_MAX) {
+        for (int i = threadIdx.x; i <= b1 - b0; i += blockDim.x) smem_table[i] = table[b0 + i];
+        t.p = smem_table;
+        t.base = b0;
+    } else {
+        t.p = table;
+        t.base = 0;
+    }
+    return t;  // the caller synchronises the block before the first use
+}
+
 // Stage keys [k0, k0 + 64) of one kv head: K rows to Ks, V rows to Vs (row stride D + 8).
 // Rows outside [lo, hi] or without a page are zero-filled.
 template <int D>
 __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __restrict__ kv,
-                                             const int32_t* __restrict__ table, int k0, int lo, int hi,
+                                             const TableRef table, int k0, int lo, int hi,
                                              int kvh, int n_kv, int page_size, int64_t num_pages, int* err) {
     constexpr int CPR = D / 8;  // 16-byte chunks per row
     constexpr int KSTR = D + 8;
@@ -67,12 +99,14 @@ __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __r
         bool ok = key >= lo && key <= hi;
         int64_t base = 0;
         if (ok) {
-            const int64_t page = table[key / page_size];
+            const int blk = table.shift >= 0 ? key >> table.shift : key / page_size;
+            const int in_page = table.shift >= 0 ? key & (page_size - 1) : key - blk * page_size;
+            const int64_t page = table.p[blk - table.base];
             if (page < 0 || page >= num_pages) {
                 if (page >= num_pages) atomicOr(err, SS_ERR_PAGE_RANGE);
                 ok = false;
             } else {
-                base = ((page * 2 * n_kv + kvh) * page_size + key % page_size) * (int64_t)D + col;
+                base = ((page * 2 * n_kv + kvh) * page_size + in_page) * (int64_t)D + col;
             }
         }
         cp_async16(Ks + row * KSTR + col, kv + base, ok);
@@ -82,7 +116,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __r
 
 // One warp: scores of its 16 rows against NK keys of a staged tile (keys key_off.. of the tile),
 // online-softmax update, and O += P V.  S/P registers: NK/8 n-tiles.
-template <int D, int NK>
+template <int D, int NK, bool MASK>
 __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const bf16* Ks, const bf16* Vs,
                                           int key_off, int key0_abs, float scale_log2, int pos_lo, int pos_hi,
                                           int window, float (&m)[2], float (&l)[2], float (&o)[D / 8][4]) {
@@ -110,9 +144,12 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const
     for (int n = 0; n < NT; ++n) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const int key = key0_abs + key_off + n * 8 + ((lane & 3) << 1) + (e & 1);
-            const int pos = (e < 2) ? pos_lo : pos_hi;  // < 0: the row does not exist
-            const bool ok = key <= pos && (window <= 0 || key > pos - window);
+            bool ok = true;
+            if (MASK) {  // tiles that every row of the warp sees whole skip this
+                const int key = key0_abs + key_off + n * 8 + ((lane & 3) << 1) + (e & 1);
+                const int pos = (e < 2) ? pos_lo : pos_hi;  // < 0: the row does not exist
+                ok = key <= pos && (window <= 0 || key > pos - window);
+            }
             const float v = ok ? s[n][e] * scale_log2 : -INFINITY;
             s[n][e] = v;
             mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -125,7 +162,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
         const float m_new = fmaxf(m[r], mx[r]);
         m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
-        alpha[r] = exp2f(m[r] - m_use[r]);  // m = -inf gives 0
+        alpha[r] = fast_exp2(m[r] - m_use[r]);  // m = -inf gives 0
         m[r] = m_new;
         l[r] *= alpha[r];
     }
@@ -133,7 +170,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const
     for (int n = 0; n < NT; ++n) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const float p = exp2f(s[n][e] - m_use[e >> 1]);
+            const float p = fast_exp2(s[n][e] - m_use[e >> 1]);
             s[n][e] = p;
             l[e >> 1] += p;
         }
@@ -162,9 +199,13 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const
     }
 }
 
+#ifndef DECODE_STAGES
+#define DECODE_STAGES (HEAD_DIM <= 128 ? 3 : 2)  // key/value tiles in flight in the decode kernel
+#endif
+
 template <int D>
-constexpr int mma_smem_bytes(int q_rows = 64) {
-    return (q_rows * (D + 8) + 2 * 2 * MMA_BN * (D + 8)) * 2;  // Q tile + two stages of K and V
+constexpr int mma_smem_bytes(int q_rows = 64, int stages = 2) {
+    return (q_rows * (D + 8) + stages * 2 * MMA_BN * (D + 8)) * 2;  // Q tile + stages of K and V
 }
 
 // ---------------------------------------------------------------- prompt portions (and mixed batches)
@@ -192,7 +233,9 @@ attn_prefill_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict_
     const int first_pos = seq_len - q_len + row0 / G;
     const int last_pos = seq_len - q_len + (row0 + rows_here - 1) / G;
     const int lo = window > 0 ? max(0, first_pos - window + 1) : 0;
-    const int32_t* table = block_tables + (int64_t)r * max_blocks;
+    __shared__ int32_t table_s[MMA_TABLE_MAX];
+    const TableRef table = stage_table(table_s, block_tables + (int64_t)r * max_blocks, lo, last_pos, page_size);
+    __syncthreads();
 
     // Q tile: row -> (token, head of the group)
     for (int c = tid; c < 64 * (D / 8); c += MMA_THREADS) {
@@ -238,11 +281,18 @@ attn_prefill_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict_
             for (int ks = 0; ks < D / 16; ++ks)
                 ldmatrix_x4(qf[ks], Qs + (warp * 16 + (lane & 15)) * KSTR + ks * 16 + ((lane >> 4) << 3));
         }
-        // a warp whose rows all lie before this tile has nothing to add
+        // a warp whose rows all lie before this tile has nothing to add; a tile that every row of the warp
+        // sees whole (all its keys at or before the warp's first position, and inside every window) needs no mask
         const int warp_last = min(rows_here - 1, warp * 16 + 15);
-        const bool active = warp * 16 < rows_here && kt * MMA_BN <= seq_len - q_len + (row0 + warp_last) / G;
-        if (active)
-            warp_tile<D, MMA_BN>(qf, Ks, Vs, 0, kt * MMA_BN, scale_log2, pos2[0], pos2[1], window, m, l, o);
+        const int warp_first_pos = seq_len - q_len + (row0 + warp * 16) / G;
+        const int warp_last_pos = seq_len - q_len + (row0 + warp_last) / G;
+        const bool active = warp * 16 < rows_here && kt * MMA_BN <= warp_last_pos;
+        const bool whole = warp * 16 + 15 < rows_here && kt * MMA_BN + MMA_BN - 1 <= warp_first_pos &&
+                           (window <= 0 || kt * MMA_BN > warp_last_pos - window);
+        if (active) {
+            if (whole) warp_tile<D, MMA_BN, false>(qf, Ks, Vs, 0, kt * MMA_BN, scale_log2, pos2[0], pos2[1], window, m, l, o);
+            else warp_tile<D, MMA_BN, true>(qf, Ks, Vs, 0, kt * MMA_BN, scale_log2, pos2[0], pos2[1], window, m, l, o);
+        }
         __syncthreads();
     }
 
@@ -287,7 +337,6 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
     const int row_q = q_start[r], seq_len = seq_lens[r];
     const int pos = seq_len - 1;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int32_t* table = block_tables + (int64_t)r * max_blocks;
 
     const int kt_first = lo / MMA_BN, kt_last = pos / MMA_BN;
     const int n_tiles = kt_last - kt_first + 1;
@@ -300,39 +349,55 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
     for (int d = 0; d < D / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
     if (seq_len > 0 && kt_lo <= kt_hi) {
+        __shared__ int32_t table_s[MMA_TABLE_MAX];
+        const TableRef table = stage_table(table_s, block_tables + (int64_t)r * max_blocks, max(lo, kt_lo * MMA_BN),
+                                           min(pos, kt_hi * MMA_BN + MMA_BN - 1), page_size);
         for (int c = tid; c < 16 * (D / 8); c += MMA_THREADS) {
             const int row = c / (D / 8), col = (c - row * (D / 8)) * 8;
             const bool ok = row < heads_here;
             cp_async16(Qs + row * KSTR + col, q + (int64_t)row_q * q_stride + (int64_t)(kvh * G + g0 + (ok ? row : 0)) * D + col, ok);
         }
-        load_kv_tile<D>(KV, KV + MMA_BN * KSTR, kv, table, kt_lo * MMA_BN, lo, pos, kvh, n_kv, page_size, num_pages, err);
-        cp_async_commit();
+        __syncthreads();  // the staged table is complete
+        // NS stages: tiles kt .. kt + NS - 2 are in flight while tile kt is used, so the latency of a tile
+        // (table entry, then the page) is paid once per NS - 1 tiles
+        constexpr int NS = DECODE_STAGES;
+#pragma unroll
+        for (int st = 0; st < NS - 1; ++st) {
+            if (kt_lo + st <= kt_hi) {
+                bf16* Kn = KV + st * 2 * MMA_BN * KSTR;
+                load_kv_tile<D>(Kn, Kn + MMA_BN * KSTR, kv, table, (kt_lo + st) * MMA_BN, lo, pos, kvh, n_kv, page_size, num_pages, err);
+            }
+            cp_async_commit();
+        }
         uint32_t qf[D / 16][4];
         const float scale_log2 = scale * 1.4426950408889634f;
         const int p_lo = (lane >> 2) < heads_here ? pos : -1;
         const int p_hi = (lane >> 2) + 8 < heads_here ? pos : -1;
         for (int kt = kt_lo; kt <= kt_hi; ++kt) {
-            const int stage = (kt - kt_lo) & 1;
+            const int stage = (kt - kt_lo) % NS;
             bf16* Ks = KV + stage * 2 * MMA_BN * KSTR;
             bf16* Vs = Ks + MMA_BN * KSTR;
-            if (kt < kt_hi) {
-                bf16* Kn = KV + (stage ^ 1) * 2 * MMA_BN * KSTR;
-                load_kv_tile<D>(Kn, Kn + MMA_BN * KSTR, kv, table, (kt + 1) * MMA_BN, lo, pos, kvh, n_kv, page_size, num_pages, err);
-                cp_async_commit();
-                cp_async_wait<1>();
-            } else {
-                cp_async_wait<0>();
+            if (kt + NS - 1 <= kt_hi) {
+                bf16* Kn = KV + ((kt - kt_lo + NS - 1) % NS) * 2 * MMA_BN * KSTR;
+                load_kv_tile<D>(Kn, Kn + MMA_BN * KSTR, kv, table, (kt + NS - 1) * MMA_BN, lo, pos, kvh, n_kv, page_size, num_pages, err);
             }
+            cp_async_commit();
+            cp_async_wait<NS - 1>();  // everything but the NS - 1 newest groups: tile kt has landed
             __syncthreads();
             if (kt == kt_lo) {
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
                     ldmatrix_x4(qf[ks], Qs + (lane & 15) * KSTR + ks * 16 + ((lane >> 4) << 3));
             }
-            if (kt * MMA_BN + warp * 16 <= pos)
-                warp_tile<D, 16>(qf, Ks, Vs, warp * 16, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
-            __syncthreads();
+            if (kt * MMA_BN + warp * 16 <= pos) {
+                const bool whole = heads_here == 16 && kt * MMA_BN + warp * 16 + 15 <= pos &&
+                                   (window <= 0 || kt * MMA_BN + warp * 16 > pos - window);
+                if (whole) warp_tile<D, 16, false>(qf, Ks, Vs, warp * 16, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
+                else warp_tile<D, 16, true>(qf, Ks, Vs, warp * 16, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
+            }
+            __syncthreads();  // the stage may be refilled by the next iteration's prefetch
         }
+        cp_async_wait<0>();
     }
 
     // merge the four warps: every warp publishes (m, l, O) for its 16 rows
