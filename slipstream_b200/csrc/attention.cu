@@ -74,6 +74,45 @@ extern "C" int ss_attn_decode_mma(const void* q, int64_t q_stride, void* out, in
     return SS_LAUNCH_CHECK();
 }
 
+// ---------------------------------------------------------------- tcgen05 prefill attention (head size 64 or 128)
+#if HEAD_DIM == 64 || HEAD_DIM == 128
+#include "attention_tc5.cuh"
+
+extern "C" int ss_attn_prefill_tc5_supported() { return 1; }
+
+// q: first query head of row 0 of the stacked [N, q_stride] projection output (n_q heads of HEAD_DIM);
+// kv: this layer's pages [num_pages][2][n_kv][page_size][HEAD_DIM].  Tiles: (request, first token) of
+// 128 / (n_q / n_kv) consecutive query tokens of one request.  page_size must be a multiple of 8 that divides 64.
+extern "C" int ss_attn_prefill_tc5(const void* q, int64_t q_stride, int n_tokens, void* out, int64_t out_stride,
+                                   const void* kv, const int32_t* block_tables, int max_blocks,
+                                   const int32_t* tile_req, const int32_t* tile_tok0, int n_tiles,
+                                   const int32_t* q_start, const int32_t* seq_lens, int n_q, int n_kv, int page_size,
+                                   int64_t num_pages, float scale, int* err, cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    const int G = n_q / n_kv;
+    if (G < 1 || G > 128 || page_size % 8 != 0 || 64 % page_size != 0 || q_stride % 8 != 0) return -3003;
+    const int TOK = 128 / G;
+    CUtensorMap map_q, map_kv;
+    int rc = fa::make_map3(&map_q, q, HEAD_DIM, (uint64_t)n_q, (uint64_t)n_tokens, (uint64_t)HEAD_DIM * 2,
+                           (uint64_t)q_stride * 2, 64, (uint32_t)G, (uint32_t)TOK);
+    if (rc) return rc;
+    rc = fa::make_map3(&map_kv, kv, HEAD_DIM, (uint64_t)page_size, (uint64_t)num_pages * 2 * n_kv, (uint64_t)HEAD_DIM * 2,
+                       (uint64_t)page_size * HEAD_DIM * 2, 64, (uint32_t)page_size, 1);
+    if (rc) return rc;
+    fa::Args a;
+    a.out = (bf16*)out; a.out_stride = out_stride; a.block_tables = block_tables; a.max_blocks = max_blocks;
+    a.tile_req = tile_req; a.tile_tok0 = tile_tok0; a.q_start = q_start; a.seq_lens = seq_lens;
+    a.n_q = n_q; a.n_kv = n_kv; a.page_size = page_size; a.num_pages = num_pages; a.scale = scale; a.err = err;
+    constexpr int smem = fa::smem_bytes<HEAD_DIM>();
+    static int configured = set_smem(fa::attn_prefill_tc5<HEAD_DIM>, smem);
+    if (configured != 0) return configured;
+    ss_launch(fa::attn_prefill_tc5<HEAD_DIM>, dim3(n_tiles, n_kv), dim3(FA_THREADS), smem, stream, map_q, map_kv, a);
+    return SS_LAUNCH_CHECK();
+}
+#else
+extern "C" int ss_attn_prefill_tc5_supported() { return 0; }
+#endif
+
 // ---------------------------------------------------------------- the entry point that allocates nothing
 #include "no_alloc.h"
 

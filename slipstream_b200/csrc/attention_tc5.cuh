@@ -1,0 +1,394 @@
+// Paged causal grouped-query attention for prompt portions on the 5th-generation tensor cores
+// (tcgen05.mma with accumulators in tensor memory, operands staged by TMA), bfloat16, head size 64 or 128.
+//
+// A block takes up to 128 "rows" of one (request, kv head): TOK = 128 / G consecutive query tokens times the
+// G heads of the kv group, token-major, so the group shares every key/value tile.  Roles:
+//   warp 0 (one lane)  producer: TMA loads of the Q tile and, per 64-key tile, of the K and V pages
+//                      (one box per page and 64-column half; 128-byte swizzle) into two-stage rings;
+//   warp 1 (one lane)  MMA issuer: S = Q K^T (M 128, N 64) into one of two S buffers in tensor memory,
+//                      then O += P V (M 128, N = head size, V read MN-major) into the O columns;
+//   warps 2..5         softmax: one thread per row reads its S row with tcgen05.ld, scales, masks the
+//                      diagonal tile, keeps a running maximum and sum in float32, writes P (bfloat16) into
+//                      shared memory in the swizzled K-major layout, and rescales O in tensor memory only
+//                      when the maximum has grown by more than 2^8 (the sum carries the same reference).
+// Masking is the packed-index causal rule of slipstream/models/layers/attention.py:46-51; softmax is float32
+// (:64-88).  No window here: windowed layers, other head sizes and page sizes that do not divide 64 run the
+// mma.sync kernel of attention_mma.cuh.  Every mbarrier wait is bounded (see gemm_tc5.cu).
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define FA_THREADS 192
+#define FA_BN 64
+#define FA_WAIT_LIMIT (1u << 20)
+
+namespace fa {
+
+__device__ __forceinline__ uint32_t s_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_addr(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* gave_up) {
+    for (uint32_t spins = 0; spins < FA_WAIT_LIMIT; ++spins) {
+        uint32_t done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}"
+            : "=r"(done) : "r"(s_addr(bar)), "r"(parity) : "memory");
+        if (done) return true;
+        if ((spins & 1023u) == 1023u && *gave_up) return false;
+    }
+    *gave_up = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(s_addr(dst)), "l"(map), "r"(s_addr(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+// K-major operand: rows of 128 bytes, 128-byte swizzle, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(const void* tile) {
+    return (uint64_t)((s_addr(tile) & 0x3FFFF) >> 4) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand (V: keys are rows of 128 bytes = 64 head dims): 8-key groups 1024 bytes apart (stride
+// offset), the next 64 head dims `lbo` bytes further (leading offset).
+__device__ __forceinline__ uint64_t desc_mn_major(const void* tile, uint32_t lbo) {
+    return (uint64_t)((s_addr(tile) & 0x3FFFF) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+struct Args {
+    bf16* out;
+    int64_t out_stride;
+    const int32_t* block_tables;
+    int max_blocks;
+    const int32_t* tile_req;
+    const int32_t* tile_tok0;
+    const int32_t* q_start;
+    const int32_t* seq_lens;
+    int n_q, n_kv, page_size;
+    int64_t num_pages;
+    float scale;
+    int* err;
+};
+
+template <int D>
+constexpr int smem_bytes() {
+    // Q (128 rows) + two stages each of K and V (64 keys) + two P buffers (128 x 64), + barriers, + alignment
+    return 128 * D * 2 + 2 * 2 * FA_BN * D * 2 + 2 * 128 * FA_BN * 2 + 512 + 1024;
+}
+
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Args a) {
+    constexpr int HALVES = D / 64;
+    constexpr int Q_BYTES = 128 * D * 2, KV_BYTES = FA_BN * D * 2, P_BYTES = 128 * FA_BN * 2;
+    constexpr int HALF_Q = 128 * 128, HALF_KV = FA_BN * 128;  // bytes of one 64-column half
+    constexpr int TMEM_COLS = 256;  // S0 [0,64), S1 [64,128), O [128, 128 + D)
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* Qs = base;
+    unsigned char* Ks = Qs + Q_BYTES;            // [2][KV_BYTES]
+    unsigned char* Vs = Ks + 2 * KV_BYTES;       // [2][KV_BYTES]
+    unsigned char* Ps = Vs + 2 * KV_BYTES;       // [2][P_BYTES]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + 2 * P_BYTES);
+    uint64_t* q_full = bars;          // 1
+    uint64_t* k_full = bars + 1;      // 2
+    uint64_t* v_full = bars + 3;      // 2
+    uint64_t* k_empty = bars + 5;     // 2
+    uint64_t* v_empty = bars + 7;     // 2
+    uint64_t* s_ready = bars + 9;     // 2
+    uint64_t* p_ready = bars + 11;    // 2 (128 arrivals each)
+    uint64_t* pv_done = bars + 13;    // 2
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = a.n_q / a.n_kv, kvh = blockIdx.y;
+    const int TOK = 128 / G;
+    pdl_wait();  // q, the pages and the tables come from the kernels before this one
+    const int r = a.tile_req[blockIdx.x], tok0 = a.tile_tok0[blockIdx.x];
+    const int qs = a.q_start[r], q_len = a.q_start[r + 1] - qs, seq_len = a.seq_lens[r];
+    const int toks_here = min(TOK, q_len - tok0);
+    const int rows_valid = toks_here * G;
+    const int pos0 = seq_len - q_len + tok0;           // position of the tile's first token
+    const int last_pos = pos0 + toks_here - 1;
+    const int n_tiles = last_pos / FA_BN + 1;          // key tiles 0 .. n_tiles - 1
+    const int32_t* table = a.block_tables + (int64_t)r * a.max_blocks;
+
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kv) : "memory");
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
+            mbar_init(&s_ready[s], 1); mbar_init(&p_ready[s], 128); mbar_init(&pv_done[s], 1);
+        }
+        *gave_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- producer
+        mbar_expect_tx(q_full, (uint32_t)(TOK * G * 128 * HALVES));
+        for (int h = 0; h < HALVES; ++h)
+            tma_load_3d(Qs + h * HALF_Q, &map_q, h * 64, kvh * G, qs + tok0, q_full);
+        const int ps = a.page_size, pages_per_tile = FA_BN / ps;
+        const int live_blocks = (seq_len + ps - 1) / ps;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int st = j & 1;
+            const uint32_t par = ((j >> 1) & 1) ^ 1;
+            // keys
+            if (!mbar_wait(&k_empty[st], par, gave_up)) break;
+            mbar_expect_tx(&k_full[st], KV_BYTES);
+            int64_t pg[8];
+            for (int p = 0; p < pages_per_tile; ++p) {
+                const int blk = j * pages_per_tile + p;
+                int64_t page = blk < live_blocks ? (int64_t)table[blk] : -1;
+                if (page >= a.num_pages) { atomicOr(a.err, SS_ERR_PAGE_RANGE); page = -1; }
+                if (page < 0) page = table[0];  // keys past the request's end are masked; any finite page will do
+                pg[p] = page;
+                for (int h = 0; h < HALVES; ++h)
+                    tma_load_3d(Ks + st * KV_BYTES + h * HALF_KV + p * ps * 128, &map_kv, h * 64, 0,
+                                (int)((page * 2 + 0) * a.n_kv + kvh), &k_full[st]);
+            }
+            // values
+            if (!mbar_wait(&v_empty[st], par, gave_up)) break;
+            mbar_expect_tx(&v_full[st], KV_BYTES);
+            for (int p = 0; p < pages_per_tile; ++p)
+                for (int h = 0; h < HALVES; ++h)
+                    tma_load_3d(Vs + st * KV_BYTES + h * HALF_KV + p * ps * 128, &map_kv, h * 64, 0,
+                                (int)((pg[p] * 2 + 1) * a.n_kv + kvh), &v_full[st]);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer
+        // instruction descriptors: D float32, A and B bfloat16, M = 128; S: N = 64, both K-major; PV: N = D, B MN-major
+        constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FA_BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        bool ok = mbar_wait(q_full, 0, gave_up);
+        auto issue_s = [&](int j) {
+            const int st = j & 1;
+            if (!mbar_wait(&k_full[st], (j >> 1) & 1, gave_up)) return false;
+            // the S and P buffers of this parity are free once the PV product two tiles back is complete
+            if (j >= 2 && !mbar_wait(&pv_done[st], ((j - 2) >> 1) & 1, gave_up)) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const uint64_t ad = desc_k_major(Qs + (kk / 4) * HALF_Q) + (uint64_t)((kk % 4) * 2);
+                const uint64_t bd = desc_k_major(Ks + st * KV_BYTES + (kk / 4) * HALF_KV) + (uint64_t)((kk % 4) * 2);
+                umma(tmem + st * FA_BN, ad, bd, idesc_s, kk != 0);
+            }
+            umma_commit(&s_ready[st]);
+            umma_commit(&k_empty[st]);
+            return true;
+        };
+        if (ok) ok = issue_s(0);
+        if (ok && n_tiles > 1) ok = issue_s(1);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int st = j & 1;
+            ok = mbar_wait(&p_ready[st], (j >> 1) & 1, gave_up) && mbar_wait(&v_full[st], (j >> 1) & 1, gave_up);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int kk = 0; kk < FA_BN / 16; ++kk) {  // 16 keys per instruction
+                const uint64_t ad = desc_k_major(Ps + st * P_BYTES) + (uint64_t)(kk * 2);
+                const uint64_t bd = desc_mn_major(Vs + st * KV_BYTES + kk * 16 * 128, HALF_KV);
+                umma(tmem + 128, ad, bd, idesc_pv, (j | kk) != 0);
+            }
+            umma_commit(&pv_done[st]);
+            umma_commit(&v_empty[st]);
+            if (j + 2 < n_tiles) ok = issue_s(j + 2);
+        }
+    } else if (warp >= 2) {
+        // ---------------- softmax: one thread per row
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const bool valid = row < rows_valid;
+        const int tok = valid ? row / G : 0, g = valid ? row - tok * G : 0;
+        const int pos = pos0 + tok;
+        const float scale_log2 = a.scale * 1.4426950408889634f;
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int st = j & 1;
+            // tcgen05.ld / st are warp-wide instructions: every decision around them is made for the whole warp
+            ok = __all_sync(0xffffffffu, mbar_wait(&s_ready[st], (j >> 1) & 1, gave_up));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t sr[2][32];
+            tmem_ld32(tmem + lane_base + st * FA_BN, sr[0]);
+            tmem_ld32(tmem + lane_base + st * FA_BN + 32, sr[1]);
+            const bool diagonal = j * FA_BN + FA_BN - 1 > pos;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+                float v = __uint_as_float(sr[c >> 5][c & 31]) * scale_log2;
+                if (diagonal && j * FA_BN + c > pos) v = -INFINITY;
+                sr[c >> 5][c & 31] = __float_as_uint(v);
+                mx = fmaxf(mx, v);
+            }
+            if (!valid) mx = 0.f;  // rows without a query: keep the numbers finite
+            if (__any_sync(0xffffffffu, mx > m_ref + 8.0f)) {
+                // some row's maximum moved far: bring O and the sum to the new reference (rows whose maximum
+                // did not move keep theirs: alpha = 1).  O is ours while the PV product of the previous tile
+                // is complete and the next one has not been released.
+                const float m_new = mx > m_ref + 8.0f ? mx : m_ref;
+                if (j > 0) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, gave_up));
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const float alpha = ex2(m_ref - m_new);
+                    l *= alpha;
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(tmem + lane_base + 128 + c, o);
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                        tmem_st32(tmem + lane_base + 128 + c, o);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+                m_ref = m_new;
+            }
+            // P row, bfloat16, into the swizzled K-major layout (8 chunks of 16 bytes, chunk ^ (row % 8))
+            unsigned char* prow = Ps + st * P_BYTES + row * 128;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int c = ch * 8 + e * 2;
+                    const float p0 = ex2(__uint_as_float(sr[c >> 5][c & 31]) - m_ref);
+                    const float p1 = ex2(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]) - m_ref);
+                    l += p0 + p1;
+                    __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+                    packed[e] = *reinterpret_cast<uint32_t*>(&v);
+                }
+                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads P through the async proxy
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&p_ready[st]);
+        }
+        // ---------------- epilogue: O / l for the rows that hold a query
+        if (ok) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, gave_up);
+        ok = __all_sync(0xffffffffu, ok);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* dst = a.out + (int64_t)(qs + tok0 + tok) * a.out_stride + (int64_t)(kvh * G + g) * D;
+#pragma unroll 1
+            for (int c = 0; c < D; c += 32) {
+                uint32_t o[32];
+                tmem_ld32(tmem + lane_base + 128 + c, o);
+                if (valid) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(o[e + 2 * k]) * inv, __uint_as_float(o[e + 2 * k + 1]) * inv);
+                            packed[k] = *reinterpret_cast<uint32_t*>(&v);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c + e) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    }
+                }
+            }
+        }
+    }
+    if (*gave_up && threadIdx.x == 0) atomicOr(a.err, SS_ERR_WAIT_LIMIT);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+    }
+}
+
+// ---------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// 3-D bfloat16 map: dims (inner to outer) d0 x d1 x d2 with byte strides s1, s2; box b0 x b1 x b2; 128-byte swizzle.
+static int make_map3(CUtensorMap* map, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1, uint64_t s2,
+                     uint32_t b0, uint32_t b1, uint32_t b2) {
+    EncodeTiled enc = encode_tiled();
+    if (!enc) return -3001;
+    cuuint64_t dims[3] = {d0, d1, d2};
+    cuuint64_t strides[2] = {s1, s2};
+    cuuint32_t box[3] = {b0, b1, b2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -3002;
+}
+
+}  // namespace fa

@@ -27,7 +27,7 @@
 #define TC_BM 128
 #define TC_BK 64
 #define TC_THREADS 192
-#define WAIT_LIMIT (1u << 24)
+#define WAIT_LIMIT (1u << 20)
 
 __device__ __forceinline__ uint32_t s_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

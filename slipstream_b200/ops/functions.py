@@ -56,6 +56,9 @@ _ATTN_SIGNATURES = {
     "ss_attn_prefill_mma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                             c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float,
                             c_int, c_void_p, c_void_p],
+    "ss_attn_prefill_tc5": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
+                            c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_void_p,
+                            c_void_p],
     "ss_attn_decode_mma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
                            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -116,7 +119,8 @@ def error_word(device: torch.device) -> torch.Tensor:
     key = f"err{device}"
     word = _state.get(key)
     if word is None:
-        word = torch.zeros(1, dtype=torch.int32, device=device)
+        with torch.inference_mode(False):  # the word is cleared in place later, from any mode
+            word = torch.zeros(1, dtype=torch.int32, device=device)
         _state[key] = word
     return word  # type: ignore[return-value]
 
@@ -332,6 +336,36 @@ def paged_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
                                    error_word(q.device).data_ptr(), _stream()), "paged_attention_prefill")
 
 
+def tcgen05_attention_fits(head_dim: int, n_q: int, n_kv: int, page_size: int, window: int) -> bool:
+    """Whether the tcgen05 prefill attention kernel takes this layer: head size 64 or 128, no window, pages of
+    8, 16, 32 or 64 tokens, at most 128 query heads per kv head."""
+    return (head_dim in (64, 128) and not window and page_size in (8, 16, 32, 64) and n_q // n_kv <= 128)
+
+
+def paged_attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
+                                    block_tables: torch.Tensor, tile_req: torch.Tensor, tile_tok0: torch.Tensor,
+                                    q_start: torch.Tensor, seq_lens: torch.Tensor, n_q: int, n_kv: int,
+                                    head_dim: int, scale: float) -> None:
+    """bfloat16 causal attention for prompt portions and mixed batches on the tcgen05 tensor cores (Q, K, V
+    tiles by TMA, S and O in tensor memory).  A tile is ``128 // (n_q // n_kv)`` consecutive query tokens of
+    one request: ``tile_req`` / ``tile_tok0`` list (request index, first token within the request's rows)."""
+    _need(out, torch.bfloat16, "attention output")
+    _need(kv, torch.bfloat16, "kv pages")
+    if q.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core attention kernels take bfloat16")
+    if not tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], 0):
+        raise KernelError("the tcgen05 attention kernel does not take this head size or page size")
+    for name, t in (("block_tables", block_tables), ("tile_req", tile_req), ("tile_tok0", tile_tok0),
+                    ("q_start", q_start), ("seq_lens", seq_lens)):
+        _need(t, torch.int32, name)
+    lib = attention_library(head_dim)
+    _check(lib.ss_attn_prefill_tc5(q.data_ptr(), q_stride, q.shape[0], out.data_ptr(), out.shape[1], kv.data_ptr(),
+                                   block_tables.data_ptr(), block_tables.shape[1], tile_req.data_ptr(),
+                                   tile_tok0.data_ptr(), tile_req.numel(), q_start.data_ptr(), seq_lens.data_ptr(),
+                                   n_q, n_kv, kv.shape[3], kv.shape[0], float(scale),
+                                   error_word(q.device).data_ptr(), _stream()), "paged_attention_prefill_tcgen05")
+
+
 _DECODE_COUNTERS = 65536
 
 
@@ -398,8 +432,8 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
     ``qkv`` is the stacked projection output [N, (n_q + 2 n_kv) * D] whose first n_q heads are the
     rotated queries; ``ctx`` gives the rows of each request (``q_start``), the cached lengths after
     this step (``seq_lens``) and the lists of query tiles.  float32 runs the CUDA-core kernel;
-    bfloat16 the tensor-core kernels: the split decode kernel when every request brings one token,
-    else the tiled kernel."""
+    bfloat16 the tensor-core kernels: the split decode kernel when every request brings one token, else
+    the tcgen05 kernel (head size 64 or 128, no window) or the mma.sync tiled kernel."""
     if qkv.dtype == torch.float32:
         tile_req, tile_q0 = ctx.query_tiles(16)
         paged_attention_simt(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_q0, ctx.q_start,
@@ -412,6 +446,11 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
         scratch = ctx.extras.get(("decode_scratch", n_q, head_dim))
         paged_attention_decode(qkv, qkv.shape[1], out, kv, block_tables, ctx.q_start, ctx.seq_lens,
                                ctx.num_requests, n_q, n_kv, head_dim, scale, window, slices, scratch)
+        return
+    if tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], window):
+        tile_req, tile_tok0 = ctx.query_tiles(128 // group, 1)
+        paged_attention_prefill_tcgen05(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_tok0, ctx.q_start,
+                                        ctx.seq_lens, n_q, n_kv, head_dim, scale)
         return
     tile_req, tile_row0 = ctx.query_tiles(64, group)
     paged_attention_prefill(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_row0, ctx.q_start,
@@ -598,5 +637,5 @@ def set_programmatic_launch(enabled: bool) -> None:
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "paged_attention_prefill", "paged_attention_decode", "decode_scratch", "decode_slices", "require_cuda", "argmax", "sample", "mark_seen", "gemm_tcgen05", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "require_cuda", "argmax", "sample", "mark_seen", "gemm_tcgen05", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
            "attention_library"]

@@ -319,3 +319,47 @@ def test_tcgen05_fused_swiglu(tokens, inter, k, bias):
     got = ops().gate_up_swiglu(x, mix(gate, up), mix(bg, bu) if bias else None, 64)
     assert rel_err(got, ref) < 8e-3
     ops().check_errors(torch.device(DEV))
+
+
+TC5_CASES = [  # lens, q_lens, n_q, n_kv, d, page
+    ([200, 129], [200, 100], 6, 3, 128, 16),
+    ([300, 64, 65, 1, 130], [3, 64, 1, 1, 130], 28, 4, 128, 16),   # groups of 7: 18 tokens per tile
+    ([500, 77], [400, 77], 4, 4, 64, 8),                           # one head per group: 128 tokens per tile
+    ([257, 31, 700], [2, 31, 300], 40, 2, 64, 32),                 # groups of 20
+    ([1000], [1000], 8, 1, 128, 64),
+]
+
+
+@pytest.mark.parametrize("case", range(len(TC5_CASES)))
+def test_tcgen05_prefill_attention(case):
+    lens, q_lens, n_q, n_kv, d, page = TC5_CASES[case]
+    q, kv, table, q_start, seq_lens = make_attention_case(torch.bfloat16, lens, q_lens, n_q, n_kv, d, page, seed=50 + case)
+    scale = d ** -0.5
+    ref = attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, scale, 0)
+    from slipstream_b200.engine.context import query_tiles_host
+    tok = 128 // (n_q // n_kv)
+    req, t0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(np.asarray(q_lens, dtype=np.int32), tok))
+    out = torch.full((q.shape[0], n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops().paged_attention_prefill_tcgen05(q.view(q.shape[0], -1), n_q * d, out, kv, table, req, t0, q_start, seq_lens,
+                                          n_q, n_kv, d, scale)
+    assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2
+    ops().check_errors(torch.device(DEV))
+
+
+def test_tcgen05_prefill_attention_with_growing_maxima():
+    """Keys grow with their position, so every row's running maximum moves by far more than the
+    threshold of the lazy rescaling, in different tiles for different rows of a warp."""
+    n_q, n_kv, d, page, n = 28, 4, 128, 16, 700
+    q, kv, table, q_start, seq_lens = make_attention_case(torch.bfloat16, [n], [n], n_q, n_kv, d, page, seed=77)
+    kvf = kv.float()
+    for p in range(n):
+        kvf[table[0, p // page].long(), 0, :, p % page] *= 1.0 + 0.02 * p * ((p * 7919) % 5 == 0)
+    kv = kvf.bfloat16()
+    scale = 1.0
+    ref = attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, scale, 0)
+    from slipstream_b200.engine.context import query_tiles_host
+    req, t0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(np.asarray([n], dtype=np.int32), 128 // 7))
+    out = torch.full((n, n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops().paged_attention_prefill_tcgen05(q.view(n, -1), n_q * d, out, kv, table, req, t0, q_start, seq_lens, n_q, n_kv, d, scale)
+    assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2
+    ops().check_errors(torch.device(DEV))
