@@ -82,8 +82,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
@@ -116,24 +116,27 @@ struct Args {
 
 template <int D>
 constexpr int smem_bytes() {
-    // Q (128 rows) + two stages each of K and V (64 keys) + two P buffers (128 x 64), + barriers, + alignment
-    return 128 * D * 2 + 2 * 2 * FA_BN * D * 2 + 2 * 128 * FA_BN * 2 + 512 + 1024;
+    // Q (128 rows) + two stages each of K and V (64 keys) + one P buffer (128 x 64), + barriers, + alignment:
+    // 112 KB for head size 128, so that two blocks share an SM (one's softmax overlaps the other's products)
+    return 128 * D * 2 + 2 * 2 * FA_BN * D * 2 + 128 * FA_BN * 2 + 512;
 }
 
 template <int D>
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(FA_THREADS, 2)
 attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Args a) {
     constexpr int HALVES = D / 64;
     constexpr int Q_BYTES = 128 * D * 2, KV_BYTES = FA_BN * D * 2, P_BYTES = 128 * FA_BN * 2;
     constexpr int HALF_Q = 128 * 128, HALF_KV = FA_BN * 128;  // bytes of one 64-column half
     constexpr int TMEM_COLS = 256;  // S0 [0,64), S1 [64,128), O [128, 128 + D)
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    // The swizzled tiles need 1024-byte alignment.  The block has no static shared memory in front of this
+    // array, so it starts at the block's shared window, which is aligned; checked below, not assumed.
+    unsigned char* base = smem_raw;
     unsigned char* Qs = base;
     unsigned char* Ks = Qs + Q_BYTES;            // [2][KV_BYTES]
     unsigned char* Vs = Ks + 2 * KV_BYTES;       // [2][KV_BYTES]
-    unsigned char* Ps = Vs + 2 * KV_BYTES;       // [2][P_BYTES]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + 2 * P_BYTES);
+    unsigned char* Ps = Vs + 2 * KV_BYTES;       // [P_BYTES]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + P_BYTES);
     uint64_t* q_full = bars;          // 1
     uint64_t* k_full = bars + 1;      // 2
     uint64_t* v_full = bars + 3;      // 2
@@ -146,11 +149,17 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     pdl_launch_dependents();
+    if ((s_addr(smem_raw) & 1023u) != 0) {  // uniform over the block: nothing has been set up yet
+        if (threadIdx.x == 0) atomicOr(a.err, SS_ERR_WAIT_LIMIT);
+        return;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = a.n_q / a.n_kv, kvh = blockIdx.y;
     const int TOK = 128 / G;
     pdl_wait();  // q, the pages and the tables come from the kernels before this one
-    const int r = a.tile_req[blockIdx.x], tok0 = a.tile_tok0[blockIdx.x];
+    // the host lists tiles in token order; later tokens see more keys, so the list is walked from its end
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int r = a.tile_req[tile], tok0 = a.tile_tok0[tile];
     const int qs = a.q_start[r], q_len = a.q_start[r + 1] - qs, seq_len = a.seq_lens[r];
     const int toks_here = min(TOK, q_len - tok0);
     const int rows_valid = toks_here * G;
@@ -219,9 +228,8 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         bool ok = mbar_wait(q_full, 0, gave_up);
         auto issue_s = [&](int j) {
             const int st = j & 1;
+            // the S buffer of this parity is free: the softmax of two tiles back has read it (p_ready was seen)
             if (!mbar_wait(&k_full[st], (j >> 1) & 1, gave_up)) return false;
-            // the S and P buffers of this parity are free once the PV product two tiles back is complete
-            if (j >= 2 && !mbar_wait(&pv_done[st], ((j - 2) >> 1) & 1, gave_up)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
@@ -242,7 +250,7 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int kk = 0; kk < FA_BN / 16; ++kk) {  // 16 keys per instruction
-                const uint64_t ad = desc_k_major(Ps + st * P_BYTES) + (uint64_t)(kk * 2);
+                const uint64_t ad = desc_k_major(Ps) + (uint64_t)(kk * 2);
                 const uint64_t bd = desc_mn_major(Vs + st * KV_BYTES + kk * 16 * 128, HALF_KV);
                 umma(tmem + 128, ad, bd, idesc_pv, (j | kk) != 0);
             }
@@ -270,15 +278,17 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             uint32_t sr[2][32];
             tmem_ld32(tmem + lane_base + st * FA_BN, sr[0]);
             tmem_ld32(tmem + lane_base + st * FA_BN + 32, sr[1]);
-            const bool diagonal = j * FA_BN + FA_BN - 1 > pos;
-            float mx = -INFINITY;
+            tmem_ld_wait();
+            // raw scores; the scale is folded into the exponent below.  Four running maxima keep the chain short.
+            if (j * FA_BN + FA_BN - 1 > pos) {  // the diagonal tile: keys after the row's own position are masked
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                float v = __uint_as_float(sr[c >> 5][c & 31]) * scale_log2;
-                if (diagonal && j * FA_BN + c > pos) v = -INFINITY;
-                sr[c >> 5][c & 31] = __float_as_uint(v);
-                mx = fmaxf(mx, v);
+                for (int c = 0; c < 64; ++c)
+                    if (j * FA_BN + c > pos) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c >> 5][c & 31]));
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
             if (!valid) mx = 0.f;  // rows without a query: keep the numbers finite
             if (__any_sync(0xffffffffu, mx > m_ref + 8.0f)) {
                 // some row's maximum moved far: bring O and the sum to the new reference (rows whose maximum
@@ -295,6 +305,7 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     for (int c = 0; c < D; c += 32) {
                         uint32_t o[32];
                         tmem_ld32(tmem + lane_base + 128 + c, o);
+                        tmem_ld_wait();
 #pragma unroll
                         for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
                         tmem_st32(tmem + lane_base + 128 + c, o);
@@ -303,22 +314,29 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 }
                 m_ref = m_new;
             }
-            // P row, bfloat16, into the swizzled K-major layout (8 chunks of 16 bytes, chunk ^ (row % 8))
-            unsigned char* prow = Ps + st * P_BYTES + row * 128;
+            // P row, bfloat16, into the swizzled K-major layout (8 chunks of 16 bytes, chunk ^ (row % 8)).  The one
+            // P buffer is free once the PV product of the previous tile is complete.
+            if (j > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, gave_up));
+                if (!ok) break;
+            }
+            unsigned char* prow = Ps + row * 128;
+            float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch) {
                 uint32_t packed[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int c = ch * 8 + e * 2;
-                    const float p0 = ex2(__uint_as_float(sr[c >> 5][c & 31]) - m_ref);
-                    const float p1 = ex2(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]) - m_ref);
-                    l += p0 + p1;
+                    const float p0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), scale_log2, -m_ref));
+                    const float p1 = ex2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), scale_log2, -m_ref));
+                    l4[e] += p0 + p1;
                     __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
                     packed[e] = *reinterpret_cast<uint32_t*>(&v);
                 }
                 *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
+            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads P through the async proxy
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(&p_ready[st]);
@@ -334,6 +352,7 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             for (int c = 0; c < D; c += 32) {
                 uint32_t o[32];
                 tmem_ld32(tmem + lane_base + 128 + c, o);
+                tmem_ld_wait();
                 if (valid) {
 #pragma unroll
                     for (int e = 0; e < 32; e += 8) {
