@@ -167,8 +167,8 @@ extern "C" int ss_add_rmsnorm(float* residual, const void* delta, const void* we
 // qkv row = [n_q heads | n_kv key heads | n_kv value heads] x D.  Queries are rotated in place; keys are
 // rotated and written to their page, values are copied to theirs.  kv layout:
 // [page][2][kv head][offset in page][D].  A slot of -1 (or write_cache == 0) skips the write; keys are then
-// rotated in place.  Grid: (token, chunk of the token's work); a thread owns one rotated pair, or one key
-// element beyond the rotary part, or one value element, so that nothing in the kernel is a serial chain.
+// rotated in place.  Grid: (token, chunk of the token's work); a thread owns one rotary pair of four heads, or
+// one key element beyond the rotary part, or one value element.
 template <typename T>
 __global__ void rope_cache_kernel(T* __restrict__ qkv, const int32_t* __restrict__ positions,
                                   const int32_t* __restrict__ slots, const float* __restrict__ inv_freq,
@@ -186,23 +186,33 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int32_t* __restrict
     const int64_t page = slot >= 0 ? slot / page_size : 0;
     const int off = slot >= 0 ? (int)(slot % page_size) : 0;
     const int half = rot_dim / 2, tail = D - rot_dim;
-    const int n_rot = (n_q + n_kv) * half, n_tail = n_kv * tail, n_val = n_kv * D;
+    constexpr int HPT = 4;  // heads per thread: one sine and cosine serve four heads, and their loads overlap
+    const int head_groups = (n_q + n_kv + HPT - 1) / HPT;
+    const int n_rot = head_groups * half, n_tail = n_kv * tail, n_val = n_kv * D;
     const int idx = blockIdx.y * blockDim.x + threadIdx.x;
     if (idx < n_rot) {
-        const int h = idx / half, i = idx - h * half;
-        T* head = row + (int64_t)h * D;
-        const float x1 = to_float(head[i]), x2 = to_float(head[i + half]);
+        const int hg = idx / half, i = idx - hg * half;
         const float angle = __fmul_rn((float)positions[t], inv_freq[i]);
         float s, c;
         sincosf(angle, &s, &c);
-        // q*cos + rotate_half(q)*sin, each product and the sum rounded as written
-        const T o1 = from_float<T>(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(-x2, s)));
-        const T o2 = from_float<T>(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s)));
-        if (h < n_q || slot < 0) {
-            head[i] = o1;
-            head[i + half] = o2;
-        } else {
-            T* dst = kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
+        float x1[HPT], x2[HPT];
+#pragma unroll
+        for (int u = 0; u < HPT; ++u) {
+            const int h = hg * HPT + u;
+            if (h < n_q + n_kv) {
+                x1[u] = to_float(row[(int64_t)h * D + i]);
+                x2[u] = to_float(row[(int64_t)h * D + i + half]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < HPT; ++u) {
+            const int h = hg * HPT + u;
+            if (h >= n_q + n_kv) break;
+            // q*cos + rotate_half(q)*sin, each product and the sum rounded as written
+            const T o1 = from_float<T>(__fadd_rn(__fmul_rn(x1[u], c), __fmul_rn(-x2[u], s)));
+            const T o2 = from_float<T>(__fadd_rn(__fmul_rn(x2[u], c), __fmul_rn(x1[u], s)));
+            T* dst = (h < n_q || slot < 0) ? row + (int64_t)h * D
+                                           : kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
             dst[i] = o1;
             dst[i + half] = o2;
         }
@@ -221,7 +231,7 @@ extern "C" int ss_rope_cache(void* qkv, const int32_t* positions, const int32_t*
                              int* err, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const int threads = 256;
-    const int work = (n_q + n_kv) * (rot_dim / 2) + n_kv * (D - rot_dim) + n_kv * D;
+    const int work = ((n_q + n_kv + 3) / 4) * (rot_dim / 2) + n_kv * (D - rot_dim) + n_kv * D;
     const dim3 grid(n_tokens, (work + threads - 1) / threads);
     const int64_t pool = num_pages * page_size;
     if (dtype == SS_BF16)
