@@ -32,6 +32,65 @@ SHAPE_7B = dict(vocab_size=152064, hidden_size=3584, num_hidden_layers=28, inter
                 torch_dtype="bfloat16")
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
+# The other measured workloads of BASELINE.json (configs[3] and configs[4]): end to end through the scheduler.
+WORKLOADS = {
+    "0.5b-mixed": dict(
+        shape=dict(vocab_size=151936, hidden_size=896, num_hidden_layers=24, intermediate_size=4864,
+                   num_attention_heads=14, num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-6,
+                   rope_theta=1000000.0, tie_word_embeddings=True, max_position_embeddings=8192, torch_dtype="bfloat16"),
+        requests=64, prompt=(16, 2048), new_tokens=128, chunk=512),
+    "14b": dict(
+        shape=dict(vocab_size=152064, hidden_size=5120, num_hidden_layers=48, intermediate_size=13824,
+                   num_attention_heads=40, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-5,
+                   rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=8192, torch_dtype="bfloat16"),
+        requests=32, prompt=(2048, 2048), new_tokens=256, chunk=2048),
+}
+
+
+def run_workload(name: str, args) -> int:
+    """Generate through ``LLMEngine.generate_batch`` (scheduler, chunked prefill, continuous batching) and print
+    one JSON line with the end-to-end token rates."""
+    import numpy as np
+    import torch
+
+    from slipstream_b200 import CacheConfig, EngineConfig, SamplingParams, SchedulerConfig
+    from slipstream_b200.engine.llm_engine import LLMEngine, Request
+
+    w = WORKLOADS[name]
+    folder = tempfile.mkdtemp(prefix=f"bench_{name}_")
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(dict(w["shape"], architectures=["Qwen2ForCausalLM"], model_type="qwen2"), f)
+    rng = np.random.default_rng(0)
+    lo, hi = w["prompt"]
+    lengths = rng.integers(lo, hi + 1, w["requests"]).tolist()
+    pages = sum((n + w["new_tokens"] + 15) // 16 + 1 for n in lengths) + 64
+    engine = LLMEngine(EngineConfig.for_model(
+        folder, dtype="bfloat16", load_format="random", max_model_len=8192,
+        cache=CacheConfig(block_size=16, num_gpu_blocks=pages),
+        scheduler=SchedulerConfig(max_num_seqs=w["requests"], max_num_batched_tokens=8192, prefill_chunk_size=w["chunk"])))
+    vocab = w["shape"]["vocab_size"]
+
+    def requests(tag: str, new_tokens: int):
+        return [Request(f"{tag}{i}", None, rng.integers(0, vocab, n).tolist(),
+                        SamplingParams(max_tokens=new_tokens, temperature=0.0, ignore_eos=True), float(i) * 1e-6)
+                for i, n in enumerate(lengths)]
+
+    engine.generate_batch(requests("w", 4))  # warm-up: kernels compiled, graphs captured for the first buckets
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = engine.generate_batch(requests("r", w["new_tokens"]))
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    assert all(len(o) == w["new_tokens"] for o in outs)
+    generated, prompt_tokens = w["requests"] * w["new_tokens"], int(sum(lengths))
+    print(json.dumps({"workload": name, "requests": w["requests"], "prompt_tokens": prompt_tokens,
+                      "generated_tokens": generated, "seconds": round(seconds, 3),
+                      "generated_tokens_per_s": round(generated / seconds, 1),
+                      "total_tokens_per_s": round((generated + prompt_tokens) / seconds, 1),
+                      "steps": engine.stats.step, "preemptions": engine.scheduler.preemptions,
+                      "layers": w["shape"]["num_hidden_layers"], "dtype": "bf16", "data": "synthetic"}))
+    return 0
+
 
 def peaks() -> tuple[dict, str]:
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -90,7 +149,7 @@ def reference_arm(args) -> int:
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "slipstream")):
         print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is not installed under baseline/_ref (see DESIGN.md)"}))
+                          "the reference is not installed under baseline/_ref (pip install --no-deps --target baseline/_ref <reference>)"}))
         return 0
     from baseline.reference_bench import run_reference  # noqa: E402
 
@@ -105,7 +164,7 @@ def reference_arm(args) -> int:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=1024)
@@ -113,6 +172,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
+                    help="run another measured workload end to end through the scheduler instead")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run just this part and print a short line (for profiling)")
     args = ap.parse_args()
@@ -121,6 +182,8 @@ def main() -> int:
         return 2
     if args.impl == "reference":
         return reference_arm(args)
+    if args.workload:
+        return run_workload(args.workload, args)
     if args.warmup < 3:
         args.warmup = 3
 

@@ -47,15 +47,16 @@ def main(argv: list[str] | None = None) -> int:
     import numpy as np
 
     from slipstream_b200.engine.runner import ModelRunner, StepEntry
+    from slipstream_b200.registry import load_config
 
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
     num_pages = (args.max_tokens + args.block_size - 1) // args.block_size
+    # a trace may run a request past the checkpoint's max_position_embeddings, as far as the pool allows
+    _, config = load_config(args.model)
     runner = ModelRunner(args.model, dtype=args.dtype, page_size=args.block_size, num_pages=num_pages,
                          max_num_seqs=args.max_num_seqs,
-                         max_model_len=None)
-    # a trace may run a request past the checkpoint's max_position_embeddings only as far as the pool allows
-    runner.cache.max_model_len = max(runner.cache.max_model_len, args.max_tokens)
+                         max_model_len=max(config.max_position_embeddings, num_pages * args.block_size))
 
     for line in sys.stdin:
         line = line.strip()

@@ -363,3 +363,65 @@ def test_tcgen05_prefill_attention_with_growing_maxima():
     ops().paged_attention_prefill_tcgen05(q.view(n, -1), n_q * d, out, kv, table, req, t0, q_start, seq_lens, n_q, n_kv, d, scale)
     assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2
     ops().check_errors(torch.device(DEV))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("sharp", [15, 16, 63, 64, 127, 128, 191, 899])
+def test_a_standout_key_at_a_page_or_tile_edge(dtype, sharp):
+    """The one key that matters sits on the last slot of a page, the first slot of the next, the edge of a
+    64-key tile, or is the newest key: every kernel must find it there."""
+    n_q, n_kv, d, page = 4, 2, 64, 16
+    from slipstream_b200.engine.context import query_tiles_host
+    for q_len in (1, 5):
+        q, kv, table, q_start, seq_lens = make_attention_case(dtype, [900, 50], [q_len, 3], n_q, n_kv, d, page, seed=sharp, sharp=sharp)
+        ref = attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, 1.0, 0)
+        row = q_len - 1
+        assert ref[row].min() > 4.9
+        ql = np.asarray([q_len, 3], dtype=np.int32)
+        outs = {}
+        out = torch.zeros((q.shape[0], n_q * d), device=DEV, dtype=dtype)
+        req, q0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(ql, 16))
+        ops().paged_attention_simt(q.view(q.shape[0], -1), n_q * d, out, kv, table, req, q0, q_start, seq_lens, n_q, n_kv, d, 1.0, 0)
+        outs["simt"] = out
+        if dtype == torch.bfloat16:
+            out = torch.zeros_like(out)
+            req, r0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(ql * 2, 64))
+            ops().paged_attention_prefill(q.view(q.shape[0], -1), n_q * d, out, kv, table, req, r0, q_start, seq_lens, n_q, n_kv, d, 1.0, 0)
+            outs["mma"] = out
+            out = torch.zeros_like(out)
+            req, t0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(ql, 64))
+            ops().paged_attention_prefill_tcgen05(q.view(q.shape[0], -1), n_q * d, out, kv, table, req, t0, q_start, seq_lens, n_q, n_kv, d, 1.0)
+            outs["tcgen05"] = out
+        for name, o in outs.items():
+            assert o[row].float().min() > 4.9, (name, q_len)
+            assert rel_err(o.view_as(ref).cpu(), ref) < tol(dtype, 3e-6, 1e-2), (name, q_len)
+    if dtype == torch.bfloat16:  # and through the split decode kernel
+        q, kv, table, q_start, seq_lens = make_attention_case(dtype, [900, 50], [1, 1], n_q, n_kv, d, page, seed=sharp, sharp=sharp)
+        ref = attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, 1.0, 0)
+        for slices in (1, 4):
+            out = torch.zeros((2, n_q * d), device=DEV, dtype=dtype)
+            ops().paged_attention_decode(q.view(2, -1), n_q * d, out, kv, table, q_start, seq_lens, 2, n_q, n_kv, d, 1.0, 0, n_slices=slices)
+            assert out[0].float().min() > 4.9 and rel_err(out.view_as(ref).cpu(), ref) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_the_edge_of_a_window(dtype):
+    """With a window of W keys, the key W back is invisible and the key W - 1 back is visible: put the
+    standout key on either side of the edge."""
+    n_q, n_kv, d, page, window, n = 2, 1, 32, 8, 40, 300
+    from slipstream_b200.engine.context import query_tiles_host
+    for back, seen in ((window - 1, True), (window, False)):
+        sharp = n - 1 - back
+        q, kv, table, q_start, seq_lens = make_attention_case(dtype, [n, 20], [1, 2], n_q, n_kv, d, page, seed=3, sharp=sharp)
+        ref = attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, 1.0, window)
+        assert (ref[0].min() > 4.9) == seen
+        ql = np.asarray([1, 2], dtype=np.int32)
+        out = torch.zeros((3, n_q * d), device=DEV, dtype=dtype)
+        req, q0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(ql, 16))
+        ops().paged_attention_simt(q.view(3, -1), n_q * d, out, kv, table, req, q0, q_start, seq_lens, n_q, n_kv, d, 1.0, window)
+        assert (out[0].float().min() > 4.9) == seen and rel_err(out.view_as(ref).cpu(), ref) < tol(dtype, 3e-6, 1e-2)
+        if dtype == torch.bfloat16:
+            out.zero_()
+            req, r0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(ql * 2, 64))
+            ops().paged_attention_prefill(q.view(3, -1), n_q * d, out, kv, table, req, r0, q_start, seq_lens, n_q, n_kv, d, 1.0, window)
+            assert (out[0].float().min() > 4.9) == seen and rel_err(out.view_as(ref).cpu(), ref) < 1e-2
