@@ -40,6 +40,22 @@ extern "C" int ss_embedding(const int32_t* ids, const void* table, float* out, i
     return SS_LAUNCH_CHECK();
 }
 
+// Token ids that are still on the device: ids[r] = pending[src[r]] where src[r] >= 0 (rows whose next token
+// was sampled by the step before and has not been read by the host yet); other rows keep the id the host wrote.
+__global__ void gather_tokens_kernel(int32_t* __restrict__ ids, const int32_t* __restrict__ src,
+                                     const int32_t* __restrict__ pending, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < n && src[r] >= 0) ids[r] = pending[src[r]];
+}
+
+extern "C" int ss_gather_tokens(int32_t* ids, const int32_t* src, const int32_t* pending, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    ss_launch(gather_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids, src, pending, n);
+    return SS_LAUNCH_CHECK();
+}
+
 // ---------------------------------------------------------------- add + RMSNorm
 
 // One block per output row.  residual (float32) += delta, y = weight * round(x_hat).

@@ -41,9 +41,9 @@ class DecodeGraph:
         self.n_groups = len(cache.groups)
         self.max_blocks = max(1, (runner.max_model_len + cache.page_size - 1) // cache.page_size)
         B, G, MB = bucket, self.n_groups, self.max_blocks
-        names = ["token_ids", "positions", "q_start", "seq_lens", "slots", "first", "logit_rows", "tables",
-                 "slot_maps"]
-        sizes = [B, B, B + 1, B, B, B, B, G * B * MB, G * B]
+        names = ["token_ids", "positions", "q_start", "seq_lens", "slots", "first", "logit_rows", "src_rows",
+                 "tables", "slot_maps"]
+        sizes = [B, B, B + 1, B, B, B, B, B, G * B * MB, G * B]
         self.offsets = dict(zip(names, np.concatenate([[0], np.cumsum(sizes)])[:-1].tolist()))
         self.sizes = dict(zip(names, sizes))
         total = int(sum(sizes))
@@ -94,6 +94,7 @@ class DecodeGraph:
         host[o["logit_rows"]: o["logit_rows"] + B] = np.arange(B, dtype=np.int32)
         host[o["tables"]: o["tables"] + G * B * MB] = -1
         host[o["slot_maps"]: o["slot_maps"] + G * B] = -1
+        host[o["src_rows"]: o["src_rows"] + B] = -1
         if plan is None:
             return
         R = plan.num_requests
@@ -105,19 +106,35 @@ class DecodeGraph:
         tables[:, :R, :mb] = plan.tables
         host[o["slot_maps"]: o["slot_maps"] + G * B].reshape(G, B)[:, :R] = plan.slot_maps
 
-    def run(self, plan: HostPlan) -> torch.Tensor:
+    def run(self, plan: HostPlan, pending: torch.Tensor | None = None, src_rows: np.ndarray | None = None,
+            keep: bool = True) -> torch.Tensor:
+        """Refill the static metadata, replay the step, return the logits of the wanted rows.
+
+        ``pending`` / ``src_rows``: token ids that are still on the device (sampled by the step before): row r
+        takes ``pending[src_rows[r]]`` where ``src_rows[r] >= 0``.  ``keep`` False returns a view of the static
+        logits buffer, valid until the next replay."""
         i = self.turn
         self.turn = (i + 1) % HOST_RING
         if self.events[i] is not None:
             self.events[i].synchronize()  # the copy that last used this host buffer has run
-        self._fill(self.hosts[i].numpy(), plan)
+        host = self.hosts[i].numpy()
+        self._fill(host, plan)
+        if src_rows is not None:
+            o = self.offsets["src_rows"]
+            host[o: o + src_rows.size] = src_rows
         self.static.copy_(self.hosts[i], non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         self.events[i] = event
+        if pending is not None:
+            o = self.offsets
+            ops.gather_tokens(self.static[o["token_ids"]: o["token_ids"] + self.bucket],
+                              self.static[o["src_rows"]: o["src_rows"] + self.bucket], pending)
         self.graph.replay()
         ops.count_launches(self.kernels)
         R = plan.num_requests
+        if not keep and plan.logit_rows.size == R and bool((plan.logit_rows == np.arange(R)).all()):
+            return self.logits[:R]
         if plan.logit_rows.size == R and bool((plan.logit_rows == np.arange(R)).all()):
             return self.logits[:R].clone()
         if plan.logit_rows.size == 0:

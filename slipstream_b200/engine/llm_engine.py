@@ -21,6 +21,7 @@ from collections.abc import Iterator
 from dataclasses import dataclass, field
 from pathlib import Path
 
+import numpy as np
 import torch
 
 from slipstream_b200.config.engine_config import CacheConfig, EngineConfig, SchedulerConfig
@@ -71,6 +72,20 @@ class StepStats:
     step_time_ms: float = 0.0
 
 
+PENDING = -1  # placeholder in a sequence's output for a token that was sampled but not yet read by the host
+
+
+@dataclass
+class InFlight:
+    """A decode step whose sampled tokens are still on their way to the host."""
+
+    seqs: list[Sequence]
+    where: list[int]  # index into each sequence's output of the placeholder this step fills
+    tokens_dev: torch.Tensor  # int32 [len(seqs)] on the device
+    tokens_host: torch.Tensor  # pinned copy, valid once ``ready`` has happened
+    ready: torch.cuda.Event
+
+
 def capped_new_tokens(prompt_len: int, max_tokens: int, max_model_len: int) -> int:
     """New tokens that fit under the context window (slipstream/engine/llm_engine.py:56-63)."""
     if max_tokens < 1:
@@ -103,6 +118,9 @@ class LLMEngine:
             self.tokenizer = Tokenizer.from_file(str(folder / "tokenizer.json"))
         self.stats = StepStats()
         self._requests_seen = 0
+        self._inflight: InFlight | None = None
+        self._zombies: list[Sequence] = []  # stopped while their next token was already being computed
+        self.run_ahead = True  # decode steps are launched before the tokens of the step before reach the host
 
     # ------------------------------------------------------------------ public calls
     def generate(self, request: Request) -> list[int]:
@@ -117,9 +135,13 @@ class LLMEngine:
         while self.scheduler.has_work():
             if not self._step():
                 break
-            while emitted < seq.num_output_tokens:
+            while emitted < seq.num_output_tokens and seq.output_token_ids[emitted] != PENDING:
                 yield seq.output_token_ids[emitted]
                 emitted += 1
+        self.drain()
+        while emitted < seq.num_output_tokens:
+            yield seq.output_token_ids[emitted]
+            emitted += 1
 
     def add_request(self, request: Request) -> Sequence:
         """Queue a request; ``step`` then advances everything queued by one engine step."""
@@ -147,6 +169,7 @@ class LLMEngine:
             steps += 1
             if not self._step():
                 break
+        self.drain()
         for seq in seqs:
             if not seq.is_finished:
                 seq.status = SequenceStatus.FINISHED_ABORTED
@@ -192,8 +215,105 @@ class LLMEngine:
             return any(stop and stop in text for stop in params.stop_strings)
         return False
 
+    # ------------------------------------------------------------------ decode steps that run ahead of the host
+    def _collect(self, flight: InFlight) -> None:
+        """Read the tokens of a launched step, put them in place of their placeholders, finish what is done."""
+        flight.ready.synchronize()
+        tokens = flight.tokens_host.tolist()
+        for seq, at, token in zip(flight.seqs, flight.where, tokens):
+            if seq in self._zombies:  # stopped one token earlier; this token was computed for nothing
+                self._zombies.remove(seq)
+                self.scheduler.finish(seq)
+                continue
+            seq.output_token_ids[at] = int(token)
+            ahead = at + 1 < len(seq.output_token_ids)  # its next token is already being computed
+            if self._is_stop(seq, int(token)):
+                seq.status = SequenceStatus.FINISHED_STOPPED
+                if ahead:
+                    del seq.output_token_ids[at + 1:]
+                    self._zombies.append(seq)  # keeps its pages until that step has run
+                else:
+                    self.scheduler.finish(seq)
+            elif not ahead and (seq.num_output_tokens >= seq.max_new_tokens or seq.num_tokens >= self.max_model_len):
+                seq.status = SequenceStatus.FINISHED_LENGTH
+                self.scheduler.finish(seq)
+
+    def drain(self) -> None:
+        """Wait for the tokens of the decode step that is still running, if one is, and put them in place."""
+        if self._inflight is not None:
+            flight, self._inflight = self._inflight, None
+            self._collect(flight)
+
+    def _run_ahead_candidates(self) -> list[Sequence] | None:
+        """The sequences of a steady decode step, or None when the next step is not one: somebody waits to be
+        admitted, or still has prompt to run, or needs its text (stop strings), or pages are short."""
+        sched = self.scheduler
+        if not self.run_ahead or sched.waiting or not sched.running:
+            return None
+        live = [s for s in sched.running if not s.is_finished]
+        if not live or len(live) > sched.config.max_num_batched_tokens:
+            return None
+        for seq in live:
+            if not seq.is_decoding or seq.sampling_params.stop_strings:
+                return None
+        # a sequence whose last allowed token is already being computed takes no further step
+        todo = [s for s in live if s.num_output_tokens < s.max_new_tokens and s.num_tokens < self.max_model_len]
+        if not todo or not self.runner.can_run_ahead(len(todo)):
+            return None
+        if not all(self.runner.cache.can_reserve(s.seq_id, 1) for s in todo):
+            return None
+        need = [n for s in todo for n in self.runner.cache.pages_needed(s.seq_id, 1)]
+        if sum(need) > self.runner.cache.min_free_pages():
+            return None  # growing needs a preemption: the ordinary path decides that
+        return todo
+
+    def _step_run_ahead(self, todo: list[Sequence]) -> bool:
+        """Launch the next decode step with token ids taken on the device from the step before, then read the
+        tokens of the step before while the new one runs."""
+        started = time.perf_counter()
+        prev = self._inflight
+        index = {id(s): i for i, s in enumerate(prev.seqs)} if prev is not None else {}
+        entries, src_rows, rows, where = [], [], [], []
+        for seq in todo:
+            last = seq.output_token_ids[-1]
+            src_rows.append(index[id(seq)] if last == PENDING else -1)
+            entries.append(StepEntry(seq.seq_id, [0 if last == PENDING else last], [0]))
+            rows.append(SampleRow(seq.sampling_params, seq.seed, seq.num_output_tokens,
+                                  self.runner.cache.get(seq.seq_id).slot))
+        for seq in todo:
+            self.runner.cache.reserve(seq.seq_id, 1)
+        logits = self.runner.step_decode(entries, prev.tokens_dev if prev is not None else None,
+                                         np.asarray(src_rows, dtype=np.int32))
+        tokens_dev = self.sampler.sample(logits, rows)
+        tokens_host = torch.empty(len(todo), dtype=torch.int32, pin_memory=True)
+        tokens_host.copy_(tokens_dev, non_blocking=True)
+        ready = torch.cuda.Event()
+        ready.record()
+        for seq in todo:  # the host's view moves on at once; the token's value follows
+            seq.num_computed_tokens += 1
+            where.append(len(seq.output_token_ids))
+            seq.output_token_ids.append(PENDING)
+        self._inflight = InFlight(todo, where, tokens_dev, tokens_host, ready)
+        if prev is not None:
+            self._collect(prev)
+        st = self.stats
+        st.step += 1
+        st.num_running, st.num_waiting = len(self.scheduler.running), len(self.scheduler.waiting)
+        st.num_batched_tokens = st.decode_tokens = len(todo)
+        st.prefill_tokens = 0
+        st.free_pages = self.runner.cache.min_free_pages()
+        st.preemptions = self.scheduler.preemptions
+        st.step_time_ms = (time.perf_counter() - started) * 1e3
+        return True
+
     def _step(self) -> bool:
         """Schedule, run one step-function call, sample, finish.  False when nothing can run."""
+        todo = self._run_ahead_candidates()
+        if todo is not None:
+            return self._step_run_ahead(todo)
+        self.drain()
+        if not self.scheduler.has_work():
+            return False
         started = time.perf_counter()
         plan = self.scheduler.schedule()
         if not plan.scheduled:

@@ -16,6 +16,7 @@ from __future__ import annotations
 
 from pathlib import Path
 
+import numpy as np
 import torch
 
 from slipstream_b200 import ops
@@ -103,8 +104,8 @@ class ModelRunner:
             if e.request_id not in self.cache:
                 self.admit(e.request_id)
         plan = plan_step(entries, self.cache, self.config.vocab_size)
-        bucket = bucket_for(plan.num_requests) if self.use_cuda_graphs and plan.is_decode_only else None
-        if bucket is not None and bucket <= max(self.max_num_seqs, 1) * 2:
+        bucket = self._graph_bucket(plan.num_requests) if plan.is_decode_only else None
+        if bucket is not None:
             graph = self._graphs.get(bucket)
             if graph is None:
                 graph = self._graphs[bucket] = DecodeGraph(self, bucket)
@@ -114,6 +115,35 @@ class ModelRunner:
             ctx = to_device(plan, self.device)
             self.last_h2d_bytes = ctx.extras["host_buffer"].numel() * 4
             logits = self.run(ctx)
+        for e in entries:
+            self.cache.commit(e.request_id, len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    def _graph_bucket(self, n_requests: int) -> int | None:
+        bucket = bucket_for(n_requests) if self.use_cuda_graphs else None
+        return bucket if bucket is not None and bucket <= max(self.max_num_seqs, 1) * 2 else None
+
+    def can_run_ahead(self, n_requests: int) -> bool:
+        """Whether a decode-only step of this many requests goes through a captured graph (the only kind of
+        step that can take token ids straight from the device)."""
+        return self._graph_bucket(n_requests) is not None
+
+    @torch.inference_mode()
+    def step_decode(self, entries: list[StepEntry], pending: torch.Tensor | None,
+                    src_rows: "np.ndarray | None") -> torch.Tensor:
+        """A decode-only step whose token ids may still be on the device: row r takes
+        ``pending[src_rows[r]]`` where ``src_rows[r] >= 0`` (its entry's token is then a placeholder).
+        Returns logits of every row as a view that is valid until the next step."""
+        plan = plan_step(entries, self.cache, self.config.vocab_size)
+        if not plan.is_decode_only or not self.can_run_ahead(plan.num_requests):
+            raise StepInputError("step_decode takes decode-only steps that fit a captured graph")
+        bucket = self._graph_bucket(plan.num_requests)
+        graph = self._graphs.get(bucket)
+        if graph is None:
+            graph = self._graphs[bucket] = DecodeGraph(self, bucket)
+        self.last_h2d_bytes = graph.h2d_bytes
+        logits = graph.run(plan, pending=pending, src_rows=src_rows, keep=False)
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1

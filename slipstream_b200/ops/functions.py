@@ -36,6 +36,7 @@ def _code(dtype: torch.dtype) -> int:
 
 _OPS_SIGNATURES = {
     "ss_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "ss_gather_tokens": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "ss_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                        c_float, c_int, c_void_p],
     "ss_rope_cache": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -188,6 +189,15 @@ def embedding(token_ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | 
                                       vocab, _code(table.dtype), error_word(table.device).data_ptr(),
                                       _stream()), "embedding")
     return out
+
+
+def gather_tokens(token_ids: torch.Tensor, src_rows: torch.Tensor, pending: torch.Tensor) -> None:
+    """``token_ids[r] = pending[src_rows[r]]`` where ``src_rows[r] >= 0`` (int32 tensors on the device): token ids
+    sampled by the step before that the host has not read yet."""
+    for name, t in (("token_ids", token_ids), ("src_rows", src_rows), ("pending", pending)):
+        _need(t, torch.int32, name)
+    _check(ops_library().ss_gather_tokens(token_ids.data_ptr(), src_rows.data_ptr(), pending.data_ptr(),
+                                          src_rows.numel(), _stream()), "gather_tokens")
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
@@ -637,5 +647,5 @@ def set_programmatic_launch(enabled: bool) -> None:
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "require_cuda", "argmax", "sample", "mark_seen", "gemm_tcgen05", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "gemm_tcgen05", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
            "attention_library"]

@@ -254,3 +254,45 @@ def test_command_line(model_folders, tmp_path):
     proc = subprocess.run([sys.executable, "-m", "slipstream_b200.entrypoints.cli", "--model", str(out),
                            "--write-random-model", str(src), "--seed", "5"], capture_output=True, text=True, cwd=str(ROOT))
     assert proc.returncode == 0 and (out / "model.safetensors").is_file() and (out / "config.json").is_file()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_that_run_ahead_of_the_host_give_the_same_tokens(model_folders, dtype):
+    """Decode steps are launched before the tokens of the step before reach the host.  With requests of
+    different lengths, a stop token that arrives while the next step already runs, sampling with a penalty
+    and a request that joins late, the tokens are those of the engine that waits for every token."""
+    from slipstream_b200 import SamplingParams
+    from slipstream_b200.engine.llm_engine import Request
+    folder, config, page = model_folders["B"]
+    prompts = [random_tokens(config.vocab_size, n, 90 + n) for n in (3, 21, 38, 9)]
+    probe = make_engine(folder, page, dtype=dtype)
+    probe.run_ahead = False
+    free = probe.generate(Request("p", None, prompts[1], SamplingParams(max_tokens=20, temperature=0.0, ignore_eos=True), 0.0))
+    stop = free[7]  # request 1 stops at the first place where this token appears
+    params = [SamplingParams(max_tokens=25, temperature=0.0, ignore_eos=True),
+              SamplingParams(max_tokens=20, temperature=0.0, ignore_eos=True, stop_token_ids=[stop]),
+              SamplingParams(max_tokens=9, temperature=0.9, top_k=12, top_p=0.9, repetition_penalty=1.3, seed=5, ignore_eos=True),
+              SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)]
+
+    def run(ahead):
+        engine = make_engine(folder, page, dtype=dtype)
+        engine.run_ahead = ahead
+        seqs = [engine.add_request(Request(f"r{i}", None, p, s, float(i))) for i, (p, s) in enumerate(zip(prompts[:3], params[:3]))]
+        steps = 0
+        while engine.scheduler.has_work() and steps < 500:
+            if steps == 6:  # joins while the others decode
+                seqs.append(engine.add_request(Request("late", None, prompts[3], params[3], 9.0)))
+                seqs.append(engine.add_request(Request("late2", None, prompts[0], params[2], 9.5)))
+            engine.step()
+            steps += 1
+        engine.drain()
+        assert engine.runner.cache.min_free_pages() == 64 and not engine.scheduler.has_work()
+        engine.runner.cache.check_invariants()
+        engine.runner.check()
+        return [list(s.output_token_ids) for s in seqs], [s.status for s in seqs]
+
+    want, want_status = run(False)
+    got, got_status = run(True)
+    assert got == want and got_status == want_status
+    assert want[1][-1] == stop and len(want[1]) <= 8 and all(t >= 0 for out in got for t in out)
+    assert list(map(len, want)) == [25, len(want[1]), 9, 1, 9]
