@@ -12,7 +12,10 @@
 // MMA, and the few tokens are B (BN = 16..64).  The output is then written transposed.  When there are
 // fewer tiles than SMs the K range is cut into slices (grid.z); every slice writes its partial tile to
 // scratch memory and the block that finishes a tile last (an atomic counter, no waiting) adds the slices in
-// a fixed order and writes the result, so the sum does not depend on timing.
+// a fixed order and writes the result, so the sum does not depend on timing.  With 2..8 slices in swapped mode
+// the slices of a tile form a thread-block cluster instead: every block leaves its partial tile in its own
+// shared memory, and after a cluster barrier block r adds, in slice order, the token columns r, r + slices, ...
+// out of the shared memory of all blocks of the cluster.  No scratch, no counters, no trip through global memory.
 //
 // Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the kernel sets SS_ERR_WAIT_LIMIT in the
 // error word, stops waiting everywhere, frees its tensor memory and returns.
@@ -99,6 +102,7 @@ struct GemmArgs {
     int swapped;        // 1: C is written transposed, C[n * ldc + m], bias indexed by m
     int out_f32;
     int bias_f32;
+    int cluster;        // 1: the slices of a tile are one thread-block cluster and are added through shared memory
     int swiglu;         // 1 (swapped only): rows 0..63 of a tile are gate features, rows 64..127 the matching up
                         // features; the output has M / 2 features: out[n][tile * 64 + r] = silu(gate) * up
 };
@@ -228,7 +232,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < 16; ++j) r[j] = 0u;
                 }
-                if (g.slices == 1 && g.swiglu) {
+                if (g.cluster || (g.slices == 1 && g.swiglu)) {
                     // all stages have been consumed: the ring's memory is free to carry the tile across warps
                     float* xbuf = reinterpret_cast<float*>(tiles);
 #pragma unroll
@@ -271,7 +275,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     for (int c = 0; c < BN; ++c)
                         store_swiglu(g, m0 + ml, n0 + c, xbuf[c * TC_BM + ml], xbuf[c * TC_BM + ml + 64]);
             }
-            if (g.slices > 1) {
+            if (g.slices > 1 && !g.cluster) {
                 // the block that completes the tile last adds the slices, in slice order
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
@@ -310,6 +314,27 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 }
             }
         }
+    }
+    if (g.cluster) {
+        cluster_sync_all();  // every block's partial tile lies in its shared memory
+        if (warp >= 2) {
+            const float* xbuf = reinterpret_cast<const float*>(tiles);
+            const int ml = (warp & 3) * 32 + lane;
+            const int n_live = min(BN, g.N - n0);
+            for (int c = (int)cluster_rank(); c < n_live; c += g.slices) {
+                float acc = 0.f, acc2 = 0.f;
+#pragma unroll 8
+                for (int s = 0; s < g.slices; ++s) acc += ld_cluster_f32(xbuf + c * TC_BM + ml, (uint32_t)s);
+                if (!g.swiglu) {
+                    store_out<BN>(g, m0 + ml, n0 + c, acc);
+                } else if (ml < 64) {
+#pragma unroll 8
+                    for (int s = 0; s < g.slices; ++s) acc2 += ld_cluster_f32(xbuf + c * TC_BM + ml + 64, (uint32_t)s);
+                    store_swiglu(g, m0 + ml, n0 + c, acc, acc2);
+                }
+            }
+        }
+        cluster_sync_all();  // nobody leaves while its shared memory is still being read
     }
     if (*gave_up && threadIdx.x == 0) atomicOr(g.err, SS_ERR_WAIT_LIMIT);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -357,7 +382,10 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& 
     constexpr int smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 256;
     static int configured = (int)cudaFuncSetAttribute(gemm_tc5_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (configured != 0) return configured;
-    ss_launch(gemm_tc5_kernel<BN, STAGES>, dim3(grid), dim3(TC_THREADS), smem, stream, ma, mb, g);
+    if (g.cluster)
+        ss_launch_cluster(gemm_tc5_kernel<BN, STAGES>, dim3(grid), dim3(TC_THREADS), smem, stream, g.slices, ma, mb, g);
+    else
+        ss_launch(gemm_tc5_kernel<BN, STAGES>, dim3(grid), dim3(TC_THREADS), smem, stream, ma, mb, g);
     return SS_LAUNCH_CHECK();
 }
 
@@ -368,7 +396,8 @@ extern "C" int64_t ss_gemm_tc5_scratch_floats(int tiles, int slices, int bn) { r
 // bfloat16 and K-major, K a multiple of 8 and both bases 16-byte aligned.  bn: tile width (16, 32, 64, 128
 // or 256).  swapped: write C transposed (C[n * ldc + m]).  swiglu (swapped, M a multiple of 128): A's rows
 // alternate 64 gate and 64 up features; C gets M / 2 features, silu(gate) * up.  slices > 1 needs `partial` (see
-// ss_gemm_tc5_scratch_floats) and `counters` (one int per tile, zero; left zero).
+// ss_gemm_tc5_scratch_floats) and `counters` (one int per tile, zero; left zero), except in swapped mode with
+// 2..8 slices and N <= bn, where the slices are added through the shared memory of a thread-block cluster.
 extern "C" void ss_set_pdl(int on) { ss_pdl_flag() = on; }
 
 extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
@@ -378,7 +407,8 @@ extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int b
     if (swiglu && (!swapped || M % TC_BM != 0)) return -2007;
     if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return -2003;
     if (((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2004;
-    if (slices < 1 || (slices > 1 && (!partial || !counters))) return -2005;
+    const int cluster = swapped && slices >= 2 && slices <= 8 && N <= bn;
+    if (slices < 1 || (slices > 1 && !cluster && (!partial || !counters))) return -2005;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, M, K, lda, TC_BM);
     if (rc) return rc;
@@ -387,7 +417,7 @@ extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int b
     GemmArgs g;
     g.C = C; g.bias = bias; g.partial = partial; g.counters = counters; g.err = err;
     g.M = M; g.N = N; g.K = K; g.ldc = ldc; g.slices = slices; g.swapped = swapped; g.out_f32 = out_f32;
-    g.bias_f32 = bias_f32; g.swiglu = swiglu;
+    g.bias_f32 = bias_f32; g.swiglu = swiglu; g.cluster = cluster;
     dim3 grid((N + bn - 1) / bn, (M + TC_BM - 1) / TC_BM, slices);
     switch (bn) {
         case 16: return launch<16, 4>(ma, mb, g, grid, stream);  // three blocks fit on an SM

@@ -542,9 +542,8 @@ def gemm_plan(tokens: int, features: int, k: int) -> tuple[bool, int, int]:
     if tokens <= 64:
         bn = 16 if tokens <= 16 else (32 if tokens <= 32 else 64)
         tiles = (features + 127) // 128
-        slices = max(1, min(k_iters, (2 * 148 + tiles - 1) // tiles if tiles < 148 else 1, 16))
-        while slices > 1 and tiles * slices * bn * 128 > _GEMM_SCRATCH_FLOATS:
-            slices -= 1
+        # at most 8 slices: they then form one thread-block cluster and are added through shared memory
+        slices = max(1, min(k_iters, (2 * 148 + tiles - 1) // tiles if tiles < 148 else 1, 8))
         return True, bn, slices
     bn = 256 if features >= 256 else (128 if features >= 128 else (64 if features >= 64 else (32 if features >= 32 else 16)))
     return False, bn, 1
@@ -580,7 +579,7 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
             raise KernelError("bias has the wrong size or dtype")
     swapped, bn, slices = plan or gemm_plan(tokens, features, k)
     partial = counters = None
-    if slices > 1:
+    if slices > 1 and not (swapped and slices <= 8 and tokens <= bn):
         partial, counters = _gemm_workspace(x.device)
         tiles = ((features if swapped else tokens) + 127) // 128 * (((tokens if swapped else features) + bn - 1) // bn)
         if tiles > _GEMM_COUNTERS or tiles * slices * bn * 128 > _GEMM_SCRATCH_FLOATS:
@@ -596,13 +595,18 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
 
 SMALL_BATCH = 64  # up to this many tokens a projection may stream its weights through the tcgen05 kernel
 STREAM_TILES = 148  # ... when its 128-row weight tiles are at least as many as the SMs (no K slices needed)
+CLUSTER_BATCH = 16  # ... or, up to this many tokens, whatever its size (K slices added inside a cluster)
 
 
 def streams_weights(tokens: int, features: int, k: int) -> bool:
-    """True where the hand-written tcgen05 kernel is the faster way to run a bfloat16 projection: few tokens
-    and enough weight tiles to give every SM one (measured: 43 us against the library's 46.5 us for the
-    gate/up product of the 7B shape at 8 tokens; smaller products, which need K slices, are slower)."""
-    return tokens <= SMALL_BATCH and k % 8 == 0 and (features + 127) // 128 >= STREAM_TILES
+    """True where the hand-written tcgen05 kernel is the faster way to run a bfloat16 projection.  Measured
+    on the 7B shape inside a decode step: with enough weight tiles to give every SM one (gate/up, LM head) it
+    wins up to 64 tokens (43 us against the library's 46.5 us at 8 tokens); the smaller products (q/k/v, o,
+    down), whose K range is cut into slices that a thread-block cluster adds, win up to 16 tokens (a step of
+    8 requests: 3.18 ms against 3.41 ms with the library's split-K kernels) and lose at 64."""
+    if k % 8 != 0:
+        return False
+    return tokens <= CLUSTER_BATCH or (tokens <= SMALL_BATCH and (features + 127) // 128 >= STREAM_TILES)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
