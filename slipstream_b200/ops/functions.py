@@ -13,6 +13,7 @@ synchronising copy) and raises.
 from __future__ import annotations
 
 import ctypes
+import functools
 from ctypes import c_float, c_int, c_int64, c_void_p
 
 import torch
@@ -536,6 +537,7 @@ def _gemm_workspace(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
     return ws  # type: ignore[return-value]
 
 
+@functools.lru_cache(maxsize=None)
 def gemm_plan(tokens: int, features: int, k: int) -> tuple[bool, int, int]:
     """(swapped, tile width, K slices) for ``x[tokens, k] @ w[features, k].T`` on 148 SMs."""
     k_iters = (k + 63) // 64
@@ -596,6 +598,7 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
 SMALL_BATCH = 64  # up to this many tokens a projection may stream its weights through the tcgen05 kernel
 STREAM_TILES = 148  # ... when its 128-row weight tiles are at least as many as the SMs (no K slices needed)
 CLUSTER_BATCH = 16  # ... or, up to this many tokens, whatever its size (K slices added inside a cluster)
+DEEP_K = 8192  # ... or when K is at least this deep: every block then streams enough to pay for its set-up
 
 
 def streams_weights(tokens: int, features: int, k: int) -> bool:
@@ -603,10 +606,11 @@ def streams_weights(tokens: int, features: int, k: int) -> bool:
     on the 7B shape inside a decode step: with enough weight tiles to give every SM one (gate/up, LM head) it
     wins up to 64 tokens (43 us against the library's 46.5 us at 8 tokens); the smaller products (q/k/v, o,
     down), whose K range is cut into slices that a thread-block cluster adds, win up to 16 tokens (a step of
-    8 requests: 3.18 ms against 3.41 ms with the library's split-K kernels) and lose at 64."""
-    if k % 8 != 0:
+    8 requests: 3.18 ms against 3.41 ms with the library's split-K kernels); at 32 and 64 tokens only the
+    down product still wins (25.6 and 28.0 us against 29.1 and 30.8), q/k/v and o lose by 1 to 9 us."""
+    if k % 8 != 0 or tokens > SMALL_BATCH:
         return False
-    return tokens <= CLUSTER_BATCH or (tokens <= SMALL_BATCH and (features + 127) // 128 >= STREAM_TILES)
+    return tokens <= CLUSTER_BATCH or (features + 127) // 128 >= STREAM_TILES or k >= DEEP_K
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
