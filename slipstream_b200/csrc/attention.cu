@@ -62,15 +62,21 @@ extern "C" int ss_attn_decode_mma(const void* q, int64_t q_stride, void* out, in
                                   int page_size, int64_t num_pages, float scale, int window, int n_slices,
                                   float* part_o, float* part_lse, int* counters, int* err, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
-    if (n_slices < 1 || (n_slices > 1 && (!part_o || !part_lse || !counters))) return (int)cudaErrorInvalidValue;
+    const int cluster = n_slices >= 2 && n_slices <= 8;  // the slices are combined through shared memory
+    if (n_slices < 1 || (n_slices > 1 && !cluster && (!part_o || !part_lse || !counters))) return (int)cudaErrorInvalidValue;
     constexpr int smem = mma_smem_bytes<HEAD_DIM>(16, DECODE_STAGES);
     static int configured = set_smem(attn_decode_mma<HEAD_DIM>, smem);
     if (configured != 0) return configured;
     const int G = n_q / n_kv;
     dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
-    ss_launch(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, 
-        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
-        seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, part_o, part_lse, counters, err);
+    if (cluster)
+        ss_launch_cluster(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, n_slices,
+            (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
+            seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 1, part_o, part_lse, counters, err);
+    else
+        ss_launch(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream,
+            (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
+            seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 0, part_o, part_lse, counters, err);
     return SS_LAUNCH_CHECK();
 }
 
@@ -181,7 +187,7 @@ extern "C" int ss_attn_decode_noalloc(const void* q, int64_t q_stride, void* out
     dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
     ss_launch(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
-        seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, part_o, part_lse, counters, err);
+        seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 0, part_o, part_lse, counters, err);
     return SS_LAUNCH_CHECK();
 }
 

@@ -205,7 +205,9 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const
 
 template <int D>
 constexpr int mma_smem_bytes(int q_rows = 64, int stages = 2) {
-    return (q_rows * (D + 8) + stages * 2 * MMA_BN * (D + 8)) * 2;  // Q tile + stages of K and V
+    const int tiles = (q_rows * (D + 8) + stages * 2 * MMA_BN * (D + 8)) * 2;  // Q tile + stages of K and V
+    const int merge = (4 * 16 * (D + 8) + 2 * 4 * 16 + 16 * D + 16) * 4;       // the decode kernel's merge buffers
+    return tiles > merge ? tiles : merge;
 }
 
 // ---------------------------------------------------------------- prompt portions (and mixed batches)
@@ -320,10 +322,12 @@ __global__ void __launch_bounds__(MMA_THREADS)
 attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__ out, int64_t out_stride,
                 const bf16* __restrict__ kv, const int32_t* __restrict__ block_tables, int max_blocks,
                 const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens, int n_q, int n_kv,
-                int page_size, int64_t num_pages, float scale, int window, int n_slices,
+                int page_size, int64_t num_pages, float scale, int window, int n_slices, int cluster,
                 float* __restrict__ part_o, float* __restrict__ part_lse, int* __restrict__ counters, int* err) {
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
-    pdl_wait();               // nothing below runs before the kernels before this one are complete
+    // Until pdl_wait() below, only what no kernel of this step writes is touched: the lengths, the block
+    // table, and keys and values at positions before the newest token (earlier steps wrote those).  The
+    // fetch of the cached keys so overlaps the projection that is still producing this step's query.
     constexpr int KSTR = D + 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
@@ -352,18 +356,27 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
         __shared__ int32_t table_s[MMA_TABLE_MAX];
         const TableRef table = stage_table(table_s, block_tables + (int64_t)r * max_blocks, max(lo, kt_lo * MMA_BN),
                                            min(pos, kt_hi * MMA_BN + MMA_BN - 1), page_size);
+        __syncthreads();  // the staged table is complete
+        // NS stages: tiles kt .. kt + NS - 2 are in flight while tile kt is used, so the latency of a tile
+        // (table entry, then the page) is paid once per NS - 1 tiles.  Tiles before the one that holds the
+        // newest token are fetched at once; that one and the query only after the kernels before this one.
+        constexpr int NS = DECODE_STAGES;
+#pragma unroll
+        for (int st = 0; st < NS - 1; ++st) {
+            if (kt_lo + st <= kt_hi && kt_lo + st < kt_last) {
+                bf16* Kn = KV + st * 2 * MMA_BN * KSTR;
+                load_kv_tile<D>(Kn, Kn + MMA_BN * KSTR, kv, table, (kt_lo + st) * MMA_BN, lo, pos, kvh, n_kv, page_size, num_pages, err);
+            }
+        }
+        pdl_wait();
         for (int c = tid; c < 16 * (D / 8); c += MMA_THREADS) {
             const int row = c / (D / 8), col = (c - row * (D / 8)) * 8;
             const bool ok = row < heads_here;
             cp_async16(Qs + row * KSTR + col, q + (int64_t)row_q * q_stride + (int64_t)(kvh * G + g0 + (ok ? row : 0)) * D + col, ok);
         }
-        __syncthreads();  // the staged table is complete
-        // NS stages: tiles kt .. kt + NS - 2 are in flight while tile kt is used, so the latency of a tile
-        // (table entry, then the page) is paid once per NS - 1 tiles
-        constexpr int NS = DECODE_STAGES;
 #pragma unroll
         for (int st = 0; st < NS - 1; ++st) {
-            if (kt_lo + st <= kt_hi) {
+            if (kt_lo + st <= kt_hi && kt_lo + st == kt_last) {
                 bf16* Kn = KV + st * 2 * MMA_BN * KSTR;
                 load_kv_tile<D>(Kn, Kn + MMA_BN * KSTR, kv, table, (kt_lo + st) * MMA_BN, lo, pos, kvh, n_kv, page_size, num_pages, err);
             }
@@ -398,12 +411,17 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
             __syncthreads();  // the stage may be refilled by the next iteration's prefetch
         }
         cp_async_wait<0>();
+    } else {
+        pdl_wait();
     }
 
     // merge the four warps: every warp publishes (m, l, O) for its 16 rows
-    float* Om = reinterpret_cast<float*>(smem_raw);          // [4][16][D]
-    float* Mm = Om + 4 * 16 * D;                             // [4][16]
+    constexpr int OSTR = D + 8;  // row stride that spreads a warp's two-float stores over all banks
+    float* Om = reinterpret_cast<float*>(smem_raw);          // [4][16][OSTR]
+    float* Mm = Om + 4 * 16 * OSTR;                          // [4][16]
     float* Lm = Mm + 4 * 16;                                 // [4][16]
+    float* Pc = Lm + 4 * 16;                                 // [16][D]: this slice's result, read by the cluster
+    float* Lc = Pc + 16 * D;                                 // [16]: its log2 sum of exponentials
     __syncthreads();
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -416,9 +434,8 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
         }
 #pragma unroll
         for (int d = 0; d < D / 8; ++d) {
-            float* dst = Om + ((warp * 16 + row) * D) + d * 8 + ((lane & 3) << 1);
-            dst[0] = o[d][2 * h];
-            dst[1] = o[d][2 * h + 1];
+            float* dst = Om + ((warp * 16 + row) * OSTR) + d * 8 + ((lane & 3) << 1);
+            *reinterpret_cast<float2*>(dst) = make_float2(o[d][2 * h], o[d][2 * h + 1]);
         }
     }
     __syncthreads();
@@ -432,7 +449,7 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
                 const float f = exp2f(Mm[w * 16 + row] - mm);
-                acc += Om[(w * 16 + row) * D + d] * f;
+                acc += Om[(w * 16 + row) * OSTR + d] * f;
                 ll += Lm[w * 16 + row] * f;
             }
         }
@@ -440,12 +457,46 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
         const int head = kvh * G + g0 + row;
         if (n_slices == 1) {
             out[(int64_t)row_q * out_stride + (int64_t)head * D + d] = __float2bfloat16_rn(val);
+        } else if (cluster) {
+            Pc[row * D + d] = val;
+            if (d == 0) Lc[row] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
         } else {
             part_o[(((int64_t)r * n_q + head) * n_slices + slice) * D + d] = val;
             if (d == 0) part_lse[((int64_t)r * n_q + head) * n_slices + slice] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
         }
     }
     if (n_slices == 1) return;
+
+    if (cluster) {
+        // The slices of a (request, head block) are one thread-block cluster (2..8 blocks): block c combines,
+        // in slice order, heads c, c + n_slices, ... out of the shared memory of all blocks.
+        cluster_sync_all();
+        const int mine = heads_here > (int)cluster_rank() ? (heads_here - 1 - (int)cluster_rank()) / n_slices + 1 : 0;
+        for (int idx = tid; idx < mine * D; idx += MMA_THREADS) {
+            const int row = (int)cluster_rank() + (idx / D) * n_slices, d = idx % D;
+            float lse[8], p[8];
+#pragma unroll
+            for (int sl = 0; sl < 8; ++sl) {
+                lse[sl] = sl < n_slices ? ld_cluster_f32(Lc + row, (uint32_t)sl) : -INFINITY;
+                p[sl] = sl < n_slices ? ld_cluster_f32(Pc + row * D + d, (uint32_t)sl) : 0.f;
+            }
+            float mx = -INFINITY, den = 0.f;
+#pragma unroll
+            for (int sl = 0; sl < 8; ++sl) mx = fmaxf(mx, lse[sl]);
+#pragma unroll
+            for (int sl = 0; sl < 8; ++sl) {
+                lse[sl] = mx == -INFINITY ? 0.f : exp2f(lse[sl] - mx);
+                den += lse[sl];
+            }
+            const float inv = den > 0.f ? 1.f / den : 0.f;
+            float acc = 0.f;
+#pragma unroll
+            for (int sl = 0; sl < 8; ++sl) acc += p[sl] * (lse[sl] * inv);
+            out[(int64_t)row_q * out_stride + (int64_t)(kvh * G + g0 + row) * D + d] = __float2bfloat16_rn(acc);
+        }
+        cluster_sync_all();  // nobody leaves while its shared memory is still being read
+        return;
+    }
 
     // The block that finishes a (request, head block) last combines the slices, in slice order: no block
     // waits for another.  counters: one int per (request, head block), zero between launches.

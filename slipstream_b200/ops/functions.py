@@ -402,8 +402,9 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
                            n_requests: int, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
                            n_slices: int = 1, scratch: tuple[torch.Tensor, torch.Tensor] | None = None) -> None:
     """bfloat16 attention for requests that bring ONE token each, the keys of every request cut into
-    ``n_slices`` slices that run in parallel; with more than one slice the partial results pass through
-    ``scratch`` (see ``decode_scratch``) and the block that finishes a head block last combines them."""
+    ``n_slices`` slices that run in parallel.  Up to 8 slices form a thread-block cluster and are combined
+    through shared memory; with more, the partial results pass through ``scratch`` (see ``decode_scratch``)
+    and the block that finishes a head block last combines them."""
     _need(out, torch.bfloat16, "attention output")
     _need(kv, torch.bfloat16, "kv pages")
     if q.dtype != torch.bfloat16:
@@ -411,7 +412,7 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
     for name, t in (("block_tables", block_tables), ("q_start", q_start), ("seq_lens", seq_lens)):
         _need(t, torch.int32, name)
     part_o = part_lse = counters = None
-    if n_slices > 1:
+    if n_slices > 8:
         counters = decode_counters(q.device)
         if n_requests * n_kv * ((n_q // n_kv + 15) // 16) > _DECODE_COUNTERS:
             raise KernelError("too many (request, head block) pairs for the decode counters")
@@ -430,10 +431,10 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
 
 def decode_slices(n_requests: int, n_kv: int, group: int, max_seq_len: int) -> int:
     """How many slices to cut the keys into: as many as keep all blocks resident at once (two per SM on
-    148 SMs), so that the step is one wave of blocks."""
+    148 SMs), so that the step is one wave of blocks; at most 8, the size of a thread-block cluster."""
     blocks = n_requests * n_kv * ((group + 15) // 16)
     tiles = max(1, (max_seq_len + 63) // 64)
-    return max(1, min((2 * 148) // blocks, tiles, 32))
+    return max(1, min((2 * 148) // blocks, tiles, 8))
 
 
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, block_tables: torch.Tensor,
