@@ -55,14 +55,17 @@ extern "C" int ss_attn_prefill_mma(const void* q, int64_t q_stride, void* out, i
 // Requests that bring one token each, bfloat16, split over the keys into n_slices.  part_o
 // ([requests][n_q][n_slices][D] float32), part_lse ([requests][n_q][n_slices] float32) and counters (one int
 // per request and block of 16 heads of a kv group; zero before the first call, left zero by every call) are
-// scratch memory of the caller; they are not touched when n_slices is 1.
+// scratch memory of the caller; they are not touched when n_slices is at most 8.  fused: q points at rows
+// [q heads | k heads | v heads] as projected; the kernel rotates queries and the newest key by the request's
+// last position (inv_freq: float32 [rot_dim / 2]) and writes the newest key and value to their page.
 extern "C" int ss_attn_decode_mma(const void* q, int64_t q_stride, void* out, int64_t out_stride,
                                   const void* kv, const int32_t* block_tables, int max_blocks, int n_requests,
                                   const int32_t* q_start, const int32_t* seq_lens, int n_q, int n_kv,
                                   int page_size, int64_t num_pages, float scale, int window, int n_slices,
-                                  float* part_o, float* part_lse, int* counters, int* err, cudaStream_t stream) {
+                                  const float* inv_freq, int rot_dim, int fused, float* part_o, float* part_lse, int* counters, int* err, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     const int cluster = n_slices >= 2 && n_slices <= 8;  // the slices are combined through shared memory
+    if (fused && (rot_dim < 0 || rot_dim > HEAD_DIM || rot_dim % 2 || (rot_dim > 0 && !inv_freq))) return (int)cudaErrorInvalidValue;
     if (n_slices < 1 || (n_slices > 1 && !cluster && (!part_o || !part_lse || !counters))) return (int)cudaErrorInvalidValue;
     constexpr int smem = mma_smem_bytes<HEAD_DIM>(16, DECODE_STAGES);
     static int configured = set_smem(attn_decode_mma<HEAD_DIM>, smem);
@@ -72,11 +75,11 @@ extern "C" int ss_attn_decode_mma(const void* q, int64_t q_stride, void* out, in
     if (cluster)
         ss_launch_cluster(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, n_slices,
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
-            seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 1, part_o, part_lse, counters, err);
+            seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 1, inv_freq, rot_dim, fused, part_o, part_lse, counters, err);
     else
         ss_launch(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream,
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
-            seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 0, part_o, part_lse, counters, err);
+            seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 0, inv_freq, rot_dim, fused, part_o, part_lse, counters, err);
     return SS_LAUNCH_CHECK();
 }
 
@@ -187,7 +190,7 @@ extern "C" int ss_attn_decode_noalloc(const void* q, int64_t q_stride, void* out
     dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
     ss_launch(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, q_start,
-        seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 0, part_o, part_lse, counters, err);
+        seq_lens, n_q, n_kv, page_size, num_pages, scale, window, n_slices, 0, (const float*)nullptr, 0, 0, part_o, part_lse, counters, err);
     return SS_LAUNCH_CHECK();
 }
 

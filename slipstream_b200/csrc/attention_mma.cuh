@@ -85,17 +85,19 @@ __device__ __forceinline__ TableRef stage_table(int32_t* smem_table, const int32
 }
 
 // Stage keys [k0, k0 + 64) of one kv head: K rows to Ks, V rows to Vs (row stride D + 8).
-// Rows outside [lo, hi] or without a page are zero-filled.
+// Rows outside [lo, hi] or without a page are zero-filled; the row of key `skip` is left alone.
 template <int D>
 __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __restrict__ kv,
                                              const TableRef table, int k0, int lo, int hi,
-                                             int kvh, int n_kv, int page_size, int64_t num_pages, int* err) {
+                                             int kvh, int n_kv, int page_size, int64_t num_pages, int* err,
+                                             int skip = -1) {
     constexpr int CPR = D / 8;  // 16-byte chunks per row
     constexpr int KSTR = D + 8;
     const int64_t v_off = (int64_t)n_kv * page_size * D;
     for (int c = threadIdx.x; c < MMA_BN * CPR; c += MMA_THREADS) {
         const int row = c / CPR, col = (c - row * CPR) * 8;
         const int key = k0 + row;
+        if (key == skip) continue;
         bool ok = key >= lo && key <= hi;
         int64_t base = 0;
         if (ok) {
@@ -323,6 +325,7 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
                 const bf16* __restrict__ kv, const int32_t* __restrict__ block_tables, int max_blocks,
                 const int32_t* __restrict__ q_start, const int32_t* __restrict__ seq_lens, int n_q, int n_kv,
                 int page_size, int64_t num_pages, float scale, int window, int n_slices, int cluster,
+                const float* __restrict__ inv_freq, int rot_dim, int fused,
                 float* __restrict__ part_o, float* __restrict__ part_lse, int* __restrict__ counters, int* err) {
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
     // Until pdl_wait() below, only what no kernel of this step writes is touched: the lengths, the block
@@ -356,6 +359,65 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
         __shared__ int32_t table_s[MMA_TABLE_MAX];
         const TableRef table = stage_table(table_s, block_tables + (int64_t)r * max_blocks, max(lo, kt_lo * MMA_BN),
                                            min(pos, kt_hi * MMA_BN + MMA_BN - 1), page_size);
+        // fused: q is the projection output [q heads | k heads | v heads] before rotation.  This kernel rotates
+        // its query heads in shared memory, and the block whose slice ends at the newest token rotates that
+        // token's key, puts key and value into its tile and (first head block only) into their page.
+        __shared__ float cos_s[128], sin_s[128];
+        const int half = rot_dim / 2;
+        const int skip = fused ? pos : -1;
+        if (fused) {
+            for (int i = tid; i < half; i += MMA_THREADS) {
+                const float angle = __fmul_rn((float)pos, inv_freq[i]);
+                sincosf(angle, &sin_s[i], &cos_s[i]);
+            }
+        }
+        __shared__ __align__(16) bf16 newest_k[256], newest_v[256];
+        const bool has_newest = fused && kt_hi == kt_last;
+        // after the wait: rotate the newest key, keep it and the value for the tile, write both to their page
+        auto make_newest = [&]() {
+            const bf16* kn = q + (int64_t)row_q * q_stride + (int64_t)(n_q + kvh) * D;
+            const bf16* vn = kn + (int64_t)n_kv * D;
+            const int blk = pos / page_size, off = pos - blk * page_size;
+            const int64_t page = table.p[blk - table.base];
+            bool wr = g0 == 0;
+            if (page < 0 || page >= num_pages) {
+                if (tid == 0) atomicOr(err, SS_ERR_PAGE_RANGE);
+                wr = false;
+            }
+            bf16* kc = const_cast<bf16*>(kv) + (((wr ? page : 0) * 2 * n_kv + kvh) * page_size + off) * (int64_t)D;
+            bf16* vc = kc + (int64_t)n_kv * page_size * D;
+            const int tail = D - rot_dim;
+            for (int idx = tid; idx < half + tail + D; idx += MMA_THREADS) {
+                if (idx < half) {
+                    const float x1 = to_float(kn[idx]), x2 = to_float(kn[idx + half]);
+                    const float c = cos_s[idx], sn = sin_s[idx];
+                    const bf16 o1 = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(-x2, sn)));
+                    const bf16 o2 = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)));
+                    newest_k[idx] = o1;
+                    newest_k[idx + half] = o2;
+                    if (wr) { kc[idx] = o1; kc[idx + half] = o2; }
+                } else if (idx < half + tail) {
+                    const int d = rot_dim + idx - half;
+                    const bf16 v = kn[d];
+                    newest_k[d] = v;
+                    if (wr) kc[d] = v;
+                } else {
+                    const int d = idx - half - tail;
+                    const bf16 v = vn[d];
+                    newest_v[d] = v;
+                    if (wr) vc[d] = v;
+                }
+            }
+        };
+        // its row of the tile that holds it (the tile's fetch leaves that row alone)
+        auto put_newest = [&](bf16* Ks, bf16* Vs) {
+            const int prow = pos - kt_last * MMA_BN;
+            for (int c = tid; c < 2 * (D / 8); c += MMA_THREADS) {
+                const int col = (c % (D / 8)) * 8;
+                if (c < D / 8) *reinterpret_cast<uint4*>(Ks + prow * KSTR + col) = *reinterpret_cast<const uint4*>(newest_k + col);
+                else *reinterpret_cast<uint4*>(Vs + prow * KSTR + col) = *reinterpret_cast<const uint4*>(newest_v + col);
+            }
+        };
         __syncthreads();  // the staged table is complete
         // NS stages: tiles kt .. kt + NS - 2 are in flight while tile kt is used, so the latency of a tile
         // (table entry, then the page) is paid once per NS - 1 tiles.  Tiles before the one that holds the
@@ -374,11 +436,16 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
             const bool ok = row < heads_here;
             cp_async16(Qs + row * KSTR + col, q + (int64_t)row_q * q_stride + (int64_t)(kvh * G + g0 + (ok ? row : 0)) * D + col, ok);
         }
+        if (has_newest) {
+            make_newest();
+            __syncthreads();
+        }
 #pragma unroll
         for (int st = 0; st < NS - 1; ++st) {
             if (kt_lo + st <= kt_hi && kt_lo + st == kt_last) {
                 bf16* Kn = KV + st * 2 * MMA_BN * KSTR;
-                load_kv_tile<D>(Kn, Kn + MMA_BN * KSTR, kv, table, (kt_lo + st) * MMA_BN, lo, pos, kvh, n_kv, page_size, num_pages, err);
+                load_kv_tile<D>(Kn, Kn + MMA_BN * KSTR, kv, table, (kt_lo + st) * MMA_BN, lo, pos, kvh, n_kv, page_size, num_pages, err, skip);
+                if (fused) put_newest(Kn, Kn + MMA_BN * KSTR);
             }
             cp_async_commit();
         }
@@ -392,12 +459,24 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
             bf16* Vs = Ks + MMA_BN * KSTR;
             if (kt + NS - 1 <= kt_hi) {
                 bf16* Kn = KV + ((kt - kt_lo + NS - 1) % NS) * 2 * MMA_BN * KSTR;
-                load_kv_tile<D>(Kn, Kn + MMA_BN * KSTR, kv, table, (kt + NS - 1) * MMA_BN, lo, pos, kvh, n_kv, page_size, num_pages, err);
+                load_kv_tile<D>(Kn, Kn + MMA_BN * KSTR, kv, table, (kt + NS - 1) * MMA_BN, lo, pos, kvh, n_kv, page_size, num_pages, err, skip);
+                if (fused && kt + NS - 1 == kt_last) put_newest(Kn, Kn + MMA_BN * KSTR);
             }
             cp_async_commit();
             cp_async_wait<NS - 1>();  // everything but the NS - 1 newest groups: tile kt has landed
             __syncthreads();
             if (kt == kt_lo) {
+                if (fused && half > 0) {
+                    for (int idx = tid; idx < 16 * half; idx += MMA_THREADS) {
+                        const int row = idx / half, i = idx - row * half;
+                        bf16* qr = Qs + row * KSTR;
+                        const float x1 = to_float(qr[i]), x2 = to_float(qr[i + half]);
+                        const float c = cos_s[i], sn = sin_s[i];
+                        qr[i] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(-x2, sn)));
+                        qr[i + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)));
+                    }
+                    __syncthreads();
+                }
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
                     ldmatrix_x4(qf[ks], Qs + (lane & 15) * KSTR + ks * 16 + ((lane >> 4) << 3));

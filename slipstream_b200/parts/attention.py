@@ -77,9 +77,13 @@ class PagedAttention(Mixer):
         meta = ctx.groups[layer.group]
         qkv = ops.linear(x, self.qkv_weight, self.qkv_b)
         inv_freq, rotary_dim = self.position_encoding.rotary_table()
-        ops.rope_and_cache(qkv, ctx.positions, meta.slot_mapping, inv_freq, layer.kv, self.num_heads,
-                           self.num_kv_heads, self.head_dim, rotary_dim, write_cache=layer.writes_cache)
+        # a decode step's attention kernel rotates and writes the newest key and value itself
+        fused = layer.writes_cache and ops.fuses_rope(qkv, ctx)
+        if not fused:
+            ops.rope_and_cache(qkv, ctx.positions, meta.slot_mapping, inv_freq, layer.kv, self.num_heads,
+                               self.num_kv_heads, self.head_dim, rotary_dim, write_cache=layer.writes_cache)
         out = torch.empty((x.shape[0], self.num_heads * self.head_dim), dtype=x.dtype, device=x.device)
         ops.paged_attention(qkv, out, layer.kv, meta.block_tables, ctx, self.num_heads, self.num_kv_heads,
-                            self.head_dim, self.scale, self.window or 0)
+                            self.head_dim, self.scale, self.window or 0,
+                            rope=(inv_freq, rotary_dim) if fused else None)
         return ops.linear(out, self.o_weight, self.o_b)

@@ -234,6 +234,39 @@ def test_split_decode_attention(slices, n_q, n_kv, d, page, window):
     ops().check_errors(torch.device(DEV))
 
 
+@pytest.mark.parametrize("slices", [1, 3, 8, 11])
+@pytest.mark.parametrize("n_q, n_kv, d, rot, page, window", [(28, 4, 128, 128, 16, 0), (6, 6, 16, 8, 4, 0),
+                                                              (40, 2, 64, 64, 7, 0), (8, 2, 32, 0, 16, 100)])
+def test_decode_attention_that_rotates_and_writes_the_newest_token_itself(slices, n_q, n_kv, d, rot, page, window):
+    """The decode kernel given the projection output as it is (rope=...) must leave the same pages and the
+    same output, bit for bit, as the rotary kernel followed by the decode kernel."""
+    lens = [1, 63, 64, 65, 700, 129, 2000, 16, 17]
+    R = len(lens)
+    _, kv, table, q_start, seq_lens = make_attention_case(torch.bfloat16, lens, [1] * R, n_q, n_kv, d, page, seed=d + 1)
+    g = torch.Generator().manual_seed(5)
+    qkv = (torch.randn(R, (n_q + 2 * n_kv) * d, generator=g) * 0.7).bfloat16().to(DEV)
+    inv_freq = (1.0 / 10000.0 ** (torch.arange(0, rot, 2, dtype=torch.float32) / max(rot, 1))).to(DEV) if rot else None
+    positions = (seq_lens - 1).int()
+    pages_of = table.long()[torch.arange(R, device=DEV), (positions // page).long()]
+    slots = (pages_of * page + positions % page).int()
+    scale = d ** -0.5
+    # two steps
+    qkv_a, kv_a = qkv.clone(), kv.clone()
+    ops().rope_and_cache(qkv_a, positions, slots, inv_freq, kv_a, n_q, n_kv, d, rot)
+    out_a = torch.full((R, n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops().paged_attention_decode(qkv_a, qkv_a.shape[1], out_a, kv_a, table, q_start, seq_lens, R, n_q, n_kv, d, scale,
+                                 window, n_slices=slices)
+    # one step
+    qkv_b, kv_b = qkv.clone(), kv.clone()
+    out_b = torch.full_like(out_a, float("nan"))
+    ops().paged_attention_decode(qkv_b, qkv_b.shape[1], out_b, kv_b, table, q_start, seq_lens, R, n_q, n_kv, d, scale,
+                                 window, n_slices=slices, rope=(inv_freq, rot))
+    assert torch.equal(kv_a, kv_b), "the pages differ"
+    assert not torch.equal(kv_b, kv) and torch.equal(qkv_b, qkv)
+    assert torch.equal(out_a, out_b)
+    ops().check_errors(torch.device(DEV))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_a_far_key_among_hundreds_is_found(dtype):
     """One key 700 tokens back matches the last query far better than all others: its value must
