@@ -118,6 +118,40 @@ extern "C" int ss_attn_prefill_tc5(const void* q, int64_t q_stride, int n_tokens
     ss_launch(fa::attn_prefill_tc5<HEAD_DIM>, dim3(n_tiles, n_kv), dim3(FA_THREADS), smem, stream, map_q, map_kv, a);
     return SS_LAUNCH_CHECK();
 }
+
+#include "attention_decode_tma.cuh"
+
+// The decode kernel with TMA-fed tiles: arguments as ss_attn_decode_mma; page_size 8, 16, 32 or 64.
+extern "C" int ss_attn_decode_tma(const void* q, int64_t q_stride, void* out, int64_t out_stride,
+                                  void* kv, const int32_t* block_tables, int max_blocks, int n_requests,
+                                  const int32_t* q_start, const int32_t* seq_lens, int n_q, int n_kv,
+                                  int page_size, int64_t num_pages, float scale, int window, int n_slices,
+                                  const float* inv_freq, int rot_dim, int fused, float* part_o,
+                                  float* part_lse, int* counters, int* err, cudaStream_t stream) {
+    if (n_requests <= 0) return 0;
+    if (page_size % 8 != 0 || 64 % page_size != 0) return -3003;
+    const int cluster = n_slices >= 2 && n_slices <= 8;
+    if (n_slices < 1 || (n_slices > 1 && !cluster && (!part_o || !part_lse || !counters))) return (int)cudaErrorInvalidValue;
+    if (fused && (rot_dim < 0 || rot_dim > HEAD_DIM || rot_dim % 2 || (rot_dim > 0 && !inv_freq))) return (int)cudaErrorInvalidValue;
+    CUtensorMap map_kv;
+    int rc = fa::make_map3(&map_kv, kv, HEAD_DIM, (uint64_t)page_size, (uint64_t)num_pages * 2 * n_kv, (uint64_t)HEAD_DIM * 2,
+                           (uint64_t)page_size * HEAD_DIM * 2, 64, (uint32_t)page_size, 1);
+    if (rc) return rc;
+    DecodeTmaArgs a;
+    a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride; a.kv = (bf16*)kv;
+    a.block_tables = block_tables; a.max_blocks = max_blocks; a.q_start = q_start; a.seq_lens = seq_lens;
+    a.n_q = n_q; a.n_kv = n_kv; a.page_size = page_size; a.num_pages = num_pages; a.scale = scale; a.window = window;
+    a.n_slices = n_slices; a.cluster = cluster; a.inv_freq = inv_freq; a.rot_dim = rot_dim; a.fused = fused;
+    a.part_o = part_o; a.part_lse = part_lse; a.counters = counters; a.err = err;
+    constexpr int smem = decode_tma_smem_bytes<HEAD_DIM>();
+    static int configured = set_smem(attn_decode_tma<HEAD_DIM>, smem);
+    if (configured != 0) return configured;
+    const int G = n_q / n_kv;
+    dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
+    if (cluster) ss_launch_cluster(attn_decode_tma<HEAD_DIM>, dim3(grid), dim3(DT_THREADS), smem, stream, n_slices, map_kv, a);
+    else ss_launch(attn_decode_tma<HEAD_DIM>, dim3(grid), dim3(DT_THREADS), smem, stream, map_kv, a);
+    return SS_LAUNCH_CHECK();
+}
 #else
 extern "C" int ss_attn_prefill_tc5_supported() { return 0; }
 #endif

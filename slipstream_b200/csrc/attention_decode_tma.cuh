@@ -1,0 +1,385 @@
+// Split-KV paged decode attention with the keys and values moved by TMA: requests that bring ONE token,
+// bfloat16, head size 64 or 128, page sizes 8, 16, 32 and 64.
+//
+// The arithmetic is that of attn_decode_mma (attention_mma.cuh): a block takes the (up to 16) heads of one
+// (request, kv head) and one slice of the keys; its four consumer warps take different 16-key parts of each
+// 64-key tile (mma.sync m16n8k16, float32 online softmax) and merge at the end; the slices of a head block
+// are a thread-block cluster and merge through shared memory (or, beyond 8 slices, through scratch memory).
+// What differs is how a tile gets into shared memory.  There every thread issued sixteen 16-byte cp.async per
+// tile, and issuing them took three times as long as the arithmetic on the tile (1.5 us against 0.5 us per
+// tile and block, measured), whatever the memory did.  Here a fifth warp's first lane issues one
+// cp.async.bulk.tensor per page and 64-element half of the head (128-byte swizzle, so that ldmatrix reads
+// without bank conflicts), completion is counted by an mbarrier per stage, and the consumer warps hand a
+// stage back through a second mbarrier: no block-wide barrier in the loop, no address arithmetic in the
+// consumers.
+//
+// Keys past the request's end, before its window, or on a block without a page are masked; so that masked
+// values are finite, a block without a page is fetched from the slice's first page instead.
+// With `fused` the kernel rotates its queries and the newest key itself and writes the newest key and value to
+// their page (see attn_decode_mma); all tiles can then be fetched before the kernels before this one have
+// finished, since the one row that is not in its page yet is put into the tile from the projection output.
+//
+// Every mbarrier wait is bounded (fa::mbar_wait); a wait that gives up sets SS_ERR_WAIT_LIMIT.
+#pragma once
+
+#include "attention_mma.cuh"
+#include "attention_tc5.cuh"
+
+#define DT_THREADS 160  // four consumer warps and the producer warp
+#define DT_STAGES 3
+
+struct DecodeTmaArgs {
+    const bf16* q;
+    int64_t q_stride;
+    bf16* out;
+    int64_t out_stride;
+    bf16* kv;
+    const int32_t* block_tables;
+    int max_blocks;
+    const int32_t* q_start;
+    const int32_t* seq_lens;
+    int n_q, n_kv, page_size;
+    int64_t num_pages;
+    float scale;
+    int window, n_slices, cluster;
+    const float* inv_freq;
+    int rot_dim, fused;
+    float* part_o;
+    float* part_lse;
+    int* counters;
+    int* err;
+};
+
+template <int D>
+constexpr int decode_tma_tile_bytes() {
+    const int tiles = DT_STAGES * 2 * MMA_BN * D * 2;                          // stages of K and V
+    const int merge = (4 * 16 * (D + 8) + 2 * 4 * 16 + 16 * D + 16) * 4;       // the merge buffers, which reuse them
+    return tiles > merge ? tiles : merge;
+}
+template <int D>
+constexpr int decode_tma_smem_bytes() {
+    return 1024 + decode_tma_tile_bytes<D>() + 16 * (D + 8) * 2 + 128;  // alignment slack, tiles, Q, mbarriers
+}
+
+template <int D>
+__global__ void __launch_bounds__(DT_THREADS)
+attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs a) {
+    pdl_launch_dependents();
+    constexpr int KSTR = D + 8, NS = DT_STAGES, HALVES = D / 64;
+    constexpr int STAGE = 2 * MMA_BN * D;  // elements: K tile then V tile
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    bf16* KV = reinterpret_cast<bf16*>(base);
+    bf16* Qs = reinterpret_cast<bf16*>(base + decode_tma_tile_bytes<D>());
+    uint64_t* full = reinterpret_cast<uint64_t*>(Qs + 16 * KSTR);
+    uint64_t* empty = full + NS;
+    volatile int* gave_up = reinterpret_cast<volatile int*>(empty + NS);
+    __shared__ int32_t table_s[MMA_TABLE_MAX];
+    __shared__ float cos_s[128], sin_s[128];
+    __shared__ __align__(16) bf16 newest_k[256], newest_v[256];
+    __shared__ int is_last;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n_q = a.n_q, n_kv = a.n_kv, page_size = a.page_size, n_slices = a.n_slices, window = a.window;
+    const int G = n_q / n_kv, hblocks = (G + 15) / 16;
+    const int r = blockIdx.x, kvh = blockIdx.y / hblocks, g0 = (blockIdx.y % hblocks) * 16;
+    const int heads_here = min(16, G - g0);
+    const int slice = blockIdx.z;
+    const int row_q = a.q_start[r], seq_len = a.seq_lens[r];
+    const int pos = seq_len - 1;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int kt_first = lo / MMA_BN, kt_last = pos / MMA_BN;
+    const int n_tiles = kt_last - kt_first + 1;
+    const int per = (n_tiles + n_slices - 1) / n_slices;
+    const int kt_lo = kt_first + slice * per, kt_hi = min(kt_last, kt_lo + per - 1);
+    const bool work = seq_len > 0 && kt_lo <= kt_hi;
+    const int half = a.rot_dim / 2;
+    const bool has_newest = a.fused && work && kt_hi == kt_last;
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) { fa::mbar_init(&full[s], 1); fa::mbar_init(&empty[s], 4); }
+        *gave_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    TableRef table;
+    table.p = a.block_tables; table.base = 0; table.shift = -1;
+    if (work) {
+        table = stage_table(table_s, a.block_tables + (int64_t)r * a.max_blocks, max(lo, kt_lo * MMA_BN),
+                            min(pos, kt_hi * MMA_BN + MMA_BN - 1), page_size);
+        if (a.fused) {
+            for (int i = tid; i < half; i += DT_THREADS) {
+                const float angle = __fmul_rn((float)pos, a.inv_freq[i]);
+                sincosf(angle, &sin_s[i], &cos_s[i]);
+            }
+        }
+    }
+    __syncthreads();  // barriers, table, sines and cosines
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int d = 0; d < D / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+
+    if (warp == 4) {
+        // ---------------- producer: one bulk tensor copy per page and half of the head, keys then values
+        if (lane == 0 && work) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kv) : "memory");
+            const int ppt = MMA_BN / page_size;
+            const int b_first = max(lo, kt_lo * MMA_BN) / page_size, b_last = min(pos, kt_hi * MMA_BN + MMA_BN - 1) / page_size;
+            int64_t spare = table.p[b_first - table.base];  // a page of this request, for blocks that have none
+            if (spare < 0 || spare >= a.num_pages) {
+                atomicOr(a.err, SS_ERR_PAGE_RANGE);
+                spare = 0;
+            }
+            bool waited = false;
+            for (int kt = kt_lo; kt <= kt_hi; ++kt) {
+                const int i = kt - kt_lo, st = i % NS;
+                if (i >= NS && !fa::mbar_wait(&empty[st], ((i / NS) - 1) & 1, gave_up)) break;
+                if (!a.fused && kt == kt_last && !waited) {
+                    pdl_wait();  // the newest key and value are written by the kernel before this one
+                    waited = true;
+                }
+                fa::mbar_expect_tx(&full[st], STAGE * 2);
+                bf16* Ks = KV + st * STAGE;
+                bf16* Vs = Ks + MMA_BN * D;
+                for (int p = 0; p < ppt; ++p) {
+                    const int blk = kt * ppt + p;
+                    int64_t page = (blk >= b_first && blk <= b_last) ? (int64_t)table.p[blk - table.base] : -1;
+                    if (page >= a.num_pages) {
+                        atomicOr(a.err, SS_ERR_PAGE_RANGE);
+                        page = -1;
+                    }
+                    if (page < 0) page = spare;
+                    for (int h = 0; h < HALVES; ++h) {
+                        fa::tma_load_3d(Ks + h * (MMA_BN * 64) + p * page_size * 64, &map_kv, h * 64, 0,
+                                        (int)((page * 2 + 0) * n_kv + kvh), &full[st]);
+                        fa::tma_load_3d(Vs + h * (MMA_BN * 64) + p * page_size * 64, &map_kv, h * 64, 0,
+                                        (int)((page * 2 + 1) * n_kv + kvh), &full[st]);
+                    }
+                }
+            }
+        }
+        pdl_wait();
+    } else {
+        // ---------------- consumers
+        pdl_wait();
+        if (work) {
+            for (int c = tid; c < 16 * (D / 8); c += MMA_THREADS) {
+                const int row = c / (D / 8), col = (c - row * (D / 8)) * 8;
+                const bool ok = row < heads_here;
+                cp_async16(Qs + row * KSTR + col, a.q + (int64_t)row_q * a.q_stride + (int64_t)(kvh * G + g0 + (ok ? row : 0)) * D + col, ok);
+            }
+            cp_async_commit();
+            if (has_newest) {
+                // rotate the newest key; keep it and the value for their tile; write both to their page
+                const bf16* kn = a.q + (int64_t)row_q * a.q_stride + (int64_t)(n_q + kvh) * D;
+                const bf16* vn = kn + (int64_t)n_kv * D;
+                const int blk = pos / page_size, off = pos - blk * page_size;
+                const int64_t page = table.p[blk - table.base];
+                bool wr = g0 == 0;
+                if (page < 0 || page >= a.num_pages) {
+                    if (tid == 0) atomicOr(a.err, SS_ERR_PAGE_RANGE);
+                    wr = false;
+                }
+                bf16* kc = a.kv + (((wr ? page : 0) * 2 * n_kv + kvh) * page_size + off) * (int64_t)D;
+                bf16* vc = kc + (int64_t)n_kv * page_size * D;
+                const int tail = D - a.rot_dim;
+                for (int idx = tid; idx < half + tail + D; idx += MMA_THREADS) {
+                    if (idx < half) {
+                        const float x1 = to_float(kn[idx]), x2 = to_float(kn[idx + half]);
+                        const float c = cos_s[idx], sn = sin_s[idx];
+                        const bf16 o1 = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(-x2, sn)));
+                        const bf16 o2 = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)));
+                        newest_k[idx] = o1;
+                        newest_k[idx + half] = o2;
+                        if (wr) { kc[idx] = o1; kc[idx + half] = o2; }
+                    } else if (idx < half + tail) {
+                        const int d = a.rot_dim + idx - half;
+                        const bf16 v = kn[d];
+                        newest_k[d] = v;
+                        if (wr) kc[d] = v;
+                    } else {
+                        const int d = idx - half - tail;
+                        const bf16 v = vn[d];
+                        newest_v[d] = v;
+                        if (wr) vc[d] = v;
+                    }
+                }
+            }
+            cp_async_wait<0>();
+            asm volatile("bar.sync 1, 128;" ::: "memory");  // the four consumer warps: Q and the newest row are in place
+            if (a.fused && half > 0) {
+                for (int idx = tid; idx < 16 * half; idx += MMA_THREADS) {
+                    const int row = idx / half, i = idx - row * half;
+                    bf16* qr = Qs + row * KSTR;
+                    const float x1 = to_float(qr[i]), x2 = to_float(qr[i + half]);
+                    const float c = cos_s[i], sn = sin_s[i];
+                    qr[i] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(-x2, sn)));
+                    qr[i + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)));
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+            uint32_t qf[D / 16][4];
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks)
+                ldmatrix_x4(qf[ks], Qs + (lane & 15) * KSTR + ks * 16 + ((lane >> 4) << 3));
+            const float scale_log2 = a.scale * 1.4426950408889634f;
+            const int p_lo = (lane >> 2) < heads_here ? pos : -1;
+            const int p_hi = (lane >> 2) + 8 < heads_here ? pos : -1;
+            for (int kt = kt_lo; kt <= kt_hi; ++kt) {
+                const int i = kt - kt_lo, st = i % NS;
+                bf16* Ks = KV + st * STAGE;
+                bf16* Vs = Ks + MMA_BN * D;
+                // a wait that gives up makes every later wait give up at once; the loop still runs to its end
+                // so that the barrier below is reached by all four warps or by none
+                const bool ok = fa::mbar_wait(&full[st], (i / NS) & 1, gave_up);
+                if (a.fused && kt == kt_last) {
+                    // the newest token's row of this tile comes from the projection output, not from the page
+                    const int prow = pos - kt_last * MMA_BN;
+                    for (int c = tid; c < 2 * (D / 8); c += MMA_THREADS) {
+                        const int col = (c % (D / 8)) * 8;
+                        if (c < D / 8) *reinterpret_cast<uint4*>(const_cast<bf16*>(tile_at<D, true>(Ks, prow, col))) = *reinterpret_cast<const uint4*>(newest_k + col);
+                        else *reinterpret_cast<uint4*>(const_cast<bf16*>(tile_at<D, true>(Vs, prow, col))) = *reinterpret_cast<const uint4*>(newest_v + col);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                }
+                if (ok && kt * MMA_BN + warp * 16 <= pos) {
+                    const bool whole = heads_here == 16 && kt * MMA_BN + warp * 16 + 15 <= pos && kt * MMA_BN + warp * 16 >= lo;
+                    if (whole) warp_tile<D, 16, false, true>(qf, Ks, Vs, warp * 16, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
+                    else warp_tile<D, 16, true, true>(qf, Ks, Vs, warp * 16, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // before the next copy into this stage
+                    fa::mbar_arrive(&empty[st]);
+                }
+            }
+        }
+    }
+
+    // merge the four consumer warps: every warp publishes (m, l, O) for its 16 rows (the tiles are done with)
+    constexpr int OSTR = D + 8;
+    float* Om = reinterpret_cast<float*>(base);              // [4][16][OSTR]
+    float* Mm = Om + 4 * 16 * OSTR;                          // [4][16]
+    float* Lm = Mm + 4 * 16;                                 // [4][16]
+    float* Pc = Lm + 4 * 16;                                 // [16][D]: this slice's result, read by the cluster
+    float* Lc = Pc + 16 * D;                                 // [16]
+    __syncthreads();
+    if (warp < 4) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+            l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+            const int row = (lane >> 2) + h * 8;
+            if ((lane & 3) == 0) {
+                Mm[warp * 16 + row] = m[h];
+                Lm[warp * 16 + row] = l[h];
+            }
+#pragma unroll
+            for (int d = 0; d < D / 8; ++d) {
+                float* dst = Om + ((warp * 16 + row) * OSTR) + d * 8 + ((lane & 3) << 1);
+                *reinterpret_cast<float2*>(dst) = make_float2(o[d][2 * h], o[d][2 * h + 1]);
+            }
+        }
+    }
+    __syncthreads();
+    const int64_t head0 = (int64_t)kvh * G + g0;
+    for (int idx = tid; idx < heads_here * D; idx += DT_THREADS) {
+        const int row = idx / D, d = idx - row * D;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, Mm[w * 16 + row]);
+        float acc = 0.f, ll = 0.f;
+        if (mm != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = exp2f(Mm[w * 16 + row] - mm);
+                acc += Om[(w * 16 + row) * OSTR + d] * f;
+                ll += Lm[w * 16 + row] * f;
+            }
+        }
+        const float val = ll > 0.f ? acc / ll : 0.f;
+        if (n_slices == 1) {
+            a.out[(int64_t)row_q * a.out_stride + (head0 + row) * D + d] = __float2bfloat16_rn(val);
+        } else if (a.cluster) {
+            Pc[row * D + d] = val;
+            if (d == 0) Lc[row] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
+        } else {
+            a.part_o[(((int64_t)r * n_q + head0 + row) * n_slices + slice) * D + d] = val;
+            if (d == 0) a.part_lse[((int64_t)r * n_q + head0 + row) * n_slices + slice] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
+        }
+    }
+    if (*gave_up && tid == 0) atomicOr(a.err, SS_ERR_WAIT_LIMIT);
+    if (n_slices == 1) return;
+
+    if (a.cluster) {
+        cluster_sync_all();
+        const int rank = (int)cluster_rank();
+        const int mine = heads_here > rank ? (heads_here - 1 - rank) / n_slices + 1 : 0;
+        for (int idx = tid; idx < mine * D; idx += DT_THREADS) {
+            const int row = rank + (idx / D) * n_slices, d = idx % D;
+            float lse[8], p[8];
+#pragma unroll
+            for (int sl = 0; sl < 8; ++sl) {
+                lse[sl] = sl < n_slices ? ld_cluster_f32(Lc + row, (uint32_t)sl) : -INFINITY;
+                p[sl] = sl < n_slices ? ld_cluster_f32(Pc + row * D + d, (uint32_t)sl) : 0.f;
+            }
+            float mx = -INFINITY, den = 0.f;
+#pragma unroll
+            for (int sl = 0; sl < 8; ++sl) mx = fmaxf(mx, lse[sl]);
+#pragma unroll
+            for (int sl = 0; sl < 8; ++sl) {
+                lse[sl] = mx == -INFINITY ? 0.f : exp2f(lse[sl] - mx);
+                den += lse[sl];
+            }
+            const float inv = den > 0.f ? 1.f / den : 0.f;
+            float acc = 0.f;
+#pragma unroll
+            for (int sl = 0; sl < 8; ++sl) acc += p[sl] * (lse[sl] * inv);
+            a.out[(int64_t)row_q * a.out_stride + (head0 + row) * D + d] = __float2bfloat16_rn(acc);
+        }
+        cluster_sync_all();  // nobody leaves while its shared memory is still being read
+        return;
+    }
+
+    // more than 8 slices: through scratch memory; the block that finishes a head block last combines them
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int* counter = a.counters + (int64_t)r * gridDim.y + blockIdx.y;
+        const int seen = atomicAdd(counter, 1);
+        is_last = (seen == n_slices - 1);
+        if (is_last) *counter = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    float* W = reinterpret_cast<float*>(base);  // [16][n_slices]
+    for (int idx = tid; idx < heads_here * n_slices; idx += DT_THREADS) {
+        const int row = idx / n_slices, sl = idx - row * n_slices;
+        W[row * n_slices + sl] = __ldcg(a.part_lse + ((int64_t)r * n_q + head0 + row) * n_slices + sl);
+    }
+    __syncthreads();
+    if (tid < heads_here) {
+        float* w = W + tid * n_slices;
+        float mx = -INFINITY, den = 0.f;
+        for (int sl = 0; sl < n_slices; ++sl) mx = fmaxf(mx, w[sl]);
+        for (int sl = 0; sl < n_slices; ++sl) {
+            const float e = mx == -INFINITY ? 0.f : exp2f(w[sl] - mx);
+            w[sl] = e;
+            den += e;
+        }
+        const float inv = den > 0.f ? 1.f / den : 0.f;
+        for (int sl = 0; sl < n_slices; ++sl) w[sl] *= inv;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < heads_here * D; idx += DT_THREADS) {
+        const int row = idx / D, d = idx - row * D;
+        const float* po = a.part_o + ((int64_t)r * n_q + head0 + row) * n_slices * D + d;
+        const float* w = W + row * n_slices;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int sl = 0; sl < n_slices; ++sl) acc += __ldcg(po + (int64_t)sl * D) * w[sl];
+        a.out[(int64_t)row_q * a.out_stride + (head0 + row) * D + d] = __float2bfloat16_rn(acc);
+    }
+}

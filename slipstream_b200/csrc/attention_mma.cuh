@@ -116,9 +116,18 @@ __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __r
     }
 }
 
+// Address of 8 consecutive elements (col a multiple of 8) of row `row` of a staged 64-key tile.  Plain: rows
+// of D + 8 elements.  SWZ: the layout TMA writes with its 128-byte swizzle, [D / 64 halves][64 rows][64
+// elements], the 16-byte chunks of a row permuted by the row's low three bits.
+template <int D, bool SWZ>
+__device__ __forceinline__ const bf16* tile_at(const bf16* base, int row, int col) {
+    if (SWZ) return base + (col >> 6) * (MMA_BN * 64) + row * 64 + ((((col >> 3) & 7) ^ (row & 7)) << 3);
+    return base + row * (D + 8) + col;
+}
+
 // One warp: scores of its 16 rows against NK keys of a staged tile (keys key_off.. of the tile),
 // online-softmax update, and O += P V.  S/P registers: NK/8 n-tiles.
-template <int D, int NK, bool MASK>
+template <int D, int NK, bool MASK, bool SWZ = false>
 __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const bf16* Ks, const bf16* Vs,
                                           int key_off, int key0_abs, float scale_log2, int pos_lo, int pos_hi,
                                           int window, float (&m)[2], float (&l)[2], float (&o)[D / 8][4]) {
@@ -135,7 +144,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const
             uint32_t b[4];
             const int row = key_off + n * 8 + (lane & 7) + ((lane >> 4) << 3);
             const int col = ks * 16 + (((lane >> 3) & 1) << 3);
-            ldmatrix_x4(b, Ks + row * KSTR + col);
+            ldmatrix_x4(b, tile_at<D, SWZ>(Ks, row, col));
             mma_bf16(s[n], qf[ks], b[0], b[1]);
             mma_bf16(s[n + 1], qf[ks], b[2], b[3]);
         }
@@ -194,7 +203,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const
             uint32_t b[4];
             const int row = key_off + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
             const int col = d * 8 + ((lane >> 4) << 3);
-            ldmatrix_x4_trans(b, Vs + row * KSTR + col);
+            ldmatrix_x4_trans(b, tile_at<D, SWZ>(Vs, row, col));
             mma_bf16(o[d], a, b[0], b[1]);
             mma_bf16(o[d + 1], a, b[2], b[3]);
         }

@@ -61,6 +61,9 @@ _ATTN_SIGNATURES = {
     "ss_attn_prefill_tc5": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                             c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_void_p,
                             c_void_p],
+    "ss_attn_decode_tma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
+                           c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
+                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "ss_attn_decode_mma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
                            c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -401,7 +404,7 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
                            block_tables: torch.Tensor, q_start: torch.Tensor, seq_lens: torch.Tensor,
                            n_requests: int, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
                            n_slices: int = 1, scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
-                           rope: tuple[torch.Tensor | None, int] | None = None) -> None:
+                           rope: tuple[torch.Tensor | None, int] | None = None, tma: bool | None = None) -> None:
     """bfloat16 attention for requests that bring ONE token each, the keys of every request cut into
     ``n_slices`` slices that run in parallel.  Up to 8 slices form a thread-block cluster and are combined
     through shared memory; with more, the partial results pass through ``scratch`` (see ``decode_scratch``)
@@ -410,7 +413,15 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
     ``rope`` = (inverse frequencies, rotary_dim): ``q`` is then the stacked projection output
     [N, (n_q + 2 n_kv) * D] as projected, and the kernel itself rotates queries and the newest key by each
     request's last position and writes the newest key and value to their page (what ``rope_and_cache`` does
-    for other steps)."""
+    for other steps).
+
+    ``tma``: the kernel whose tiles are moved by TMA (head size 64 or 128, pages of 8, 16, 32 or 64 tokens;
+    the default where it fits), or the one that moves them with cp.async (every head and page size)."""
+    fits = tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], 0)
+    if tma is None:
+        tma = fits
+    elif tma and not fits:
+        raise KernelError("the TMA decode kernel takes head size 64 or 128 and pages of 8, 16, 32 or 64 tokens")
     _need(out, torch.bfloat16, "attention output")
     _need(kv, torch.bfloat16, "kv pages")
     if q.dtype != torch.bfloat16:
@@ -438,7 +449,8 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
             if inv_freq.numel() != rotary_dim // 2:
                 raise KernelError("inv_freq must hold rotary_dim / 2 values")
     lib = attention_library(head_dim)
-    _check(lib.ss_attn_decode_mma(q.data_ptr(), q_stride, out.data_ptr(), out.shape[1], kv.data_ptr(),
+    entry = lib.ss_attn_decode_tma if tma else lib.ss_attn_decode_mma
+    _check(entry(q.data_ptr(), q_stride, out.data_ptr(), out.shape[1], kv.data_ptr(),
                                   block_tables.data_ptr(), block_tables.shape[1], n_requests, q_start.data_ptr(),
                                   seq_lens.data_ptr(), n_q, n_kv, kv.shape[3], kv.shape[0], float(scale),
                                   int(window or 0), n_slices, _ptr(inv_freq) if rotary_dim else None, rotary_dim,

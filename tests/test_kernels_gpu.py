@@ -221,22 +221,26 @@ def test_paged_attention_tiled_kernels(dtype, case):
 
 @pytest.mark.parametrize("slices", [1, 2, 5, 32])
 @pytest.mark.parametrize("n_q, n_kv, d, page, window", [(28, 4, 128, 16, 0), (6, 6, 16, 4, 0), (40, 2, 64, 7, 0),
-                                                         (8, 2, 32, 16, 100), (3, 1, 256, 16, 0)])
+                                                         (8, 2, 32, 16, 100), (3, 1, 256, 16, 0), (40, 2, 64, 8, 0),
+                                                         (9, 3, 128, 64, 150), (4, 4, 64, 32, 33)])
 def test_split_decode_attention(slices, n_q, n_kv, d, page, window):
     lens = [1, 63, 64, 65, 700, 129, 2000]
     q, kv, table, q_start, seq_lens = make_attention_case(torch.bfloat16, lens, [1] * len(lens), n_q, n_kv, d, page, seed=d)
     scale = d ** -0.5
     ref = attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, scale, window)
-    out = torch.full((q.shape[0], n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
-    ops().paged_attention_decode(q.view(q.shape[0], -1), n_q * d, out, kv, table, q_start, seq_lens, len(lens),
-                                 n_q, n_kv, d, scale, window, n_slices=slices)
-    assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2
+    kernels = [False] + ([True] if ops().tcgen05_attention_fits(d, n_q, n_kv, page, 0) else [])
+    for tma in kernels:  # tiles moved by cp.async, and by TMA where the sizes allow it
+        out = torch.full((q.shape[0], n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+        ops().paged_attention_decode(q.view(q.shape[0], -1), n_q * d, out, kv, table, q_start, seq_lens, len(lens),
+                                     n_q, n_kv, d, scale, window, n_slices=slices, tma=tma)
+        assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2, tma
     ops().check_errors(torch.device(DEV))
 
 
 @pytest.mark.parametrize("slices", [1, 3, 8, 11])
 @pytest.mark.parametrize("n_q, n_kv, d, rot, page, window", [(28, 4, 128, 128, 16, 0), (6, 6, 16, 8, 4, 0),
-                                                              (40, 2, 64, 64, 7, 0), (8, 2, 32, 0, 16, 100)])
+                                                              (40, 2, 64, 64, 7, 0), (8, 2, 32, 0, 16, 100),
+                                                              (40, 2, 64, 32, 8, 0), (9, 3, 128, 128, 64, 150)])
 def test_decode_attention_that_rotates_and_writes_the_newest_token_itself(slices, n_q, n_kv, d, rot, page, window):
     """The decode kernel given the projection output as it is (rope=...) must leave the same pages and the
     same output, bit for bit, as the rotary kernel followed by the decode kernel."""
@@ -256,14 +260,17 @@ def test_decode_attention_that_rotates_and_writes_the_newest_token_itself(slices
     out_a = torch.full((R, n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
     ops().paged_attention_decode(qkv_a, qkv_a.shape[1], out_a, kv_a, table, q_start, seq_lens, R, n_q, n_kv, d, scale,
                                  window, n_slices=slices)
-    # one step
-    qkv_b, kv_b = qkv.clone(), kv.clone()
-    out_b = torch.full_like(out_a, float("nan"))
-    ops().paged_attention_decode(qkv_b, qkv_b.shape[1], out_b, kv_b, table, q_start, seq_lens, R, n_q, n_kv, d, scale,
-                                 window, n_slices=slices, rope=(inv_freq, rot))
-    assert torch.equal(kv_a, kv_b), "the pages differ"
-    assert not torch.equal(kv_b, kv) and torch.equal(qkv_b, qkv)
-    assert torch.equal(out_a, out_b)
+    ops().paged_attention_decode(qkv_a, qkv_a.shape[1], out_a, kv_a, table, q_start, seq_lens, R, n_q, n_kv, d, scale,
+                                 window, n_slices=slices, tma=False)
+    # one step, with either way of moving the tiles
+    for tma in [False] + ([True] if ops().tcgen05_attention_fits(d, n_q, n_kv, page, 0) else []):
+        qkv_b, kv_b = qkv.clone(), kv.clone()
+        out_b = torch.full_like(out_a, float("nan"))
+        ops().paged_attention_decode(qkv_b, qkv_b.shape[1], out_b, kv_b, table, q_start, seq_lens, R, n_q, n_kv, d,
+                                     scale, window, n_slices=slices, rope=(inv_freq, rot), tma=tma)
+        assert torch.equal(kv_a, kv_b), "the pages differ"
+        assert not torch.equal(kv_b, kv) and torch.equal(qkv_b, qkv)
+        assert torch.equal(out_a, out_b), tma
     ops().check_errors(torch.device(DEV))
 
 
