@@ -466,13 +466,15 @@ def decode_slices(n_requests: int, n_kv: int, group: int, max_seq_len: int) -> i
     return max(1, min((2 * 148) // blocks, tiles, 8))
 
 
-def fuses_rope(qkv: torch.Tensor, ctx) -> bool:
+def fuses_rope(qkv: torch.Tensor, ctx, head_dim: int, n_q: int, n_kv: int, page_size: int) -> bool:
     """Whether ``paged_attention`` should do the rotation and the page write of this step itself (``rope=``):
-    bfloat16 steps in which every request brings one token, up to the batch at which the projection before
-    it is the tcgen05 kernel (which lets the attention kernel fetch cached keys while it still runs; behind
-    the library product the separate rotary kernel is what gives that overlap: 4.18 against 4.28 ms a step
-    at 64 requests, 3.01 against 3.08 ms at 8)."""
-    return qkv.dtype == torch.bfloat16 and ctx.is_decode_only and qkv.shape[0] <= CLUSTER_BATCH
+    bfloat16 steps in which every request brings one token.  With the TMA-fed decode kernel always (3.90
+    against 3.94 ms a step at 64 requests, 3.01 against 3.08 at 8); with the cp.async one only up to the batch
+    at which the projection before it is the tcgen05 kernel, since behind the library product the separate
+    rotary kernel is what lets the attention kernel fetch cached keys early (4.18 against 4.28 ms at 64)."""
+    if qkv.dtype != torch.bfloat16 or not ctx.is_decode_only:
+        return False
+    return tcgen05_attention_fits(head_dim, n_q, n_kv, page_size, 0) or qkv.shape[0] <= CLUSTER_BATCH
 
 
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, block_tables: torch.Tensor,
@@ -488,7 +490,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
 
     ``rope`` (only where ``fuses_rope``): queries and keys of ``qkv`` are not rotated yet and the newest keys
     and values not yet in their pages; the decode kernel does both."""
-    if rope is not None and not fuses_rope(qkv, ctx):
+    if rope is not None and not (qkv.dtype == torch.bfloat16 and ctx.is_decode_only):
         raise KernelError("only bfloat16 decode steps rotate inside the attention kernel")
     if qkv.dtype == torch.float32:
         tile_req, tile_q0 = ctx.query_tiles(16)

@@ -78,7 +78,8 @@ class PagedAttention(Mixer):
         qkv = ops.linear(x, self.qkv_weight, self.qkv_b)
         inv_freq, rotary_dim = self.position_encoding.rotary_table()
         # a decode step's attention kernel rotates and writes the newest key and value itself
-        fused = layer.writes_cache and ops.fuses_rope(qkv, ctx)
+        fused = layer.writes_cache and ops.fuses_rope(qkv, ctx, self.head_dim, self.num_heads, self.num_kv_heads,
+                                                        layer.kv.shape[3])
         if not fused:
             ops.rope_and_cache(qkv, ctx.positions, meta.slot_mapping, inv_freq, layer.kv, self.num_heads,
                                self.num_kv_heads, self.head_dim, rotary_dim, write_cache=layer.writes_cache)
