@@ -26,7 +26,10 @@
 #include "attention_tc5.cuh"
 
 #define DT_THREADS 160  // four consumer warps and the producer warp
-#define DT_STAGES 3
+#ifndef DT_STAGES
+#define DT_STAGES 2
+#endif
+#define DT_TABLE_MAX 512  // block-table entries of a slice kept in shared memory
 
 struct DecodeTmaArgs {
     const bf16* q;
@@ -74,9 +77,9 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
     uint64_t* full = reinterpret_cast<uint64_t*>(Qs + 16 * KSTR);
     uint64_t* empty = full + NS;
     volatile int* gave_up = reinterpret_cast<volatile int*>(empty + NS);
-    __shared__ int32_t table_s[MMA_TABLE_MAX];
-    __shared__ float cos_s[128], sin_s[128];
-    __shared__ __align__(16) bf16 newest_k[256], newest_v[256];
+    __shared__ int32_t table_s[DT_TABLE_MAX];
+    __shared__ float cos_s[64], sin_s[64];
+    __shared__ __align__(16) bf16 newest_k[128], newest_v[128];
     __shared__ int is_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -105,7 +108,7 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
     table.p = a.block_tables; table.base = 0; table.shift = -1;
     if (work) {
         table = stage_table(table_s, a.block_tables + (int64_t)r * a.max_blocks, max(lo, kt_lo * MMA_BN),
-                            min(pos, kt_hi * MMA_BN + MMA_BN - 1), page_size);
+                            min(pos, kt_hi * MMA_BN + MMA_BN - 1), page_size, DT_TABLE_MAX);
         if (a.fused) {
             for (int i = tid; i < half; i += DT_THREADS) {
                 const float angle = __fmul_rn((float)pos, a.inv_freq[i]);

@@ -69,11 +69,11 @@ struct TableRef {
 };
 
 __device__ __forceinline__ TableRef stage_table(int32_t* smem_table, const int32_t* __restrict__ table, int first_key,
-                                                int last_key, int page_size) {
+                                                int last_key, int page_size, int capacity = MMA_TABLE_MAX) {
     TableRef t;
     t.shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
     const int b0 = first_key / page_size, b1 = last_key / page_size;
-    if (last_key >= first_key && b1 - b0 + 1 <= MMA_TABLE_MAX) {
+    if (last_key >= first_key && b1 - b0 + 1 <= capacity) {
         for (int i = threadIdx.x; i <= b1 - b0; i += blockDim.x) smem_table[i] = table[b0 + i];
         t.p = smem_table;
         t.base = b0;
