@@ -241,6 +241,75 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const int32_t* __restrict
     }
 }
 
+// The same for bfloat16 with 16-byte accesses (rot_dim a multiple of 16, D a multiple of 8): one block per
+// token computes the token's sines and cosines once, then every thread takes 8 rotary pairs of one head (two
+// 16-byte loads and stores), or 8 elements of a key's unrotated tail or of a value.
+__global__ void __launch_bounds__(256)
+rope_cache_bf16x8_kernel(bf16* __restrict__ qkv, const int32_t* __restrict__ positions,
+                         const int32_t* __restrict__ slots, const float* __restrict__ inv_freq,
+                         bf16* __restrict__ kv, int n_q, int n_kv, int D, int rot_dim,
+                         int page_size, int64_t pool_slots, int write_cache, int* err) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float cos_s[128], sin_s[128];
+    const int t = blockIdx.x, half = rot_dim / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float angle = __fmul_rn((float)positions[t], inv_freq[i]);
+        sincosf(angle, &sin_s[i], &cos_s[i]);
+    }
+    bf16* row = qkv + (int64_t)t * (n_q + 2 * n_kv) * D;
+    int64_t slot = (write_cache && slots) ? (int64_t)slots[t] : -1;
+    if (slot >= pool_slots) {
+        if (threadIdx.x == 0) atomicOr(err, SS_ERR_SLOT_RANGE);
+        slot = -1;
+    }
+    const int64_t page = slot >= 0 ? slot / page_size : 0;
+    const int off = slot >= 0 ? (int)(slot % page_size) : 0;
+    __syncthreads();
+    const int cpr = half / 8;                 // 16-byte chunks in half a rotary span
+    const int n_rot = (n_q + n_kv) * cpr;
+    const int tail8 = (D - rot_dim) / 8;      // chunks of a key's unrotated tail
+    const int n_tail = slot >= 0 ? n_kv * tail8 : 0, n_val = slot >= 0 ? n_kv * (D / 8) : 0;
+    for (int idx = threadIdx.x; idx < n_rot + n_tail + n_val; idx += blockDim.x) {
+        if (idx < n_rot) {
+            const int h = idx / cpr, i0 = (idx - h * cpr) * 8;
+            const bf16* src = row + (int64_t)h * D;
+            bf16* dst = (h < n_q || slot < 0) ? row + (int64_t)h * D
+                                              : kv + ((((page * 2 + 0) * n_kv + (h - n_q)) * page_size + off) * (int64_t)D);
+            const uint4 lo = *reinterpret_cast<const uint4*>(src + i0);
+            const uint4 hi = *reinterpret_cast<const uint4*>(src + i0 + half);
+            const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w}, hw[4] = {hi.x, hi.y, hi.z, hi.w};
+            uint32_t o1[4], o2[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&lw[e]);
+                const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&hw[e]);
+                const float x1[2] = {__low2float(a), __high2float(a)}, x2[2] = {__low2float(b), __high2float(b)};
+                float r1[2], r2[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const float c = cos_s[i0 + 2 * e + u], sn = sin_s[i0 + 2 * e + u];
+                    r1[u] = __fadd_rn(__fmul_rn(x1[u], c), __fmul_rn(-x2[u], sn));
+                    r2[u] = __fadd_rn(__fmul_rn(x2[u], c), __fmul_rn(x1[u], sn));
+                }
+                const __nv_bfloat162 p1 = __floats2bfloat162_rn(r1[0], r1[1]), p2 = __floats2bfloat162_rn(r2[0], r2[1]);
+                o1[e] = *reinterpret_cast<const uint32_t*>(&p1);
+                o2[e] = *reinterpret_cast<const uint32_t*>(&p2);
+            }
+            *reinterpret_cast<uint4*>(dst + i0) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+            *reinterpret_cast<uint4*>(dst + i0 + half) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+        } else if (idx < n_rot + n_tail) {
+            const int j = idx - n_rot, h = j / tail8, d = rot_dim + (j - h * tail8) * 8;
+            *reinterpret_cast<uint4*>(kv + (((page * 2 + 0) * n_kv + h) * page_size + off) * (int64_t)D + d) =
+                *reinterpret_cast<const uint4*>(row + (int64_t)(n_q + h) * D + d);
+        } else {
+            const int j = idx - n_rot - n_tail, h = j / (D / 8), d = (j - h * (D / 8)) * 8;
+            *reinterpret_cast<uint4*>(kv + (((page * 2 + 1) * n_kv + h) * page_size + off) * (int64_t)D + d) =
+                *reinterpret_cast<const uint4*>(row + (int64_t)(n_q + n_kv + h) * D + d);
+        }
+    }
+}
+
 extern "C" int ss_rope_cache(void* qkv, const int32_t* positions, const int32_t* slots,
                              const float* inv_freq, void* kv, int n_tokens, int n_q, int n_kv, int D,
                              int rot_dim, int page_size, int64_t num_pages, int write_cache, int dtype,
@@ -250,6 +319,12 @@ extern "C" int ss_rope_cache(void* qkv, const int32_t* positions, const int32_t*
     const int work = ((n_q + n_kv + 3) / 4) * (rot_dim / 2) + n_kv * (D - rot_dim) + n_kv * D;
     const dim3 grid(n_tokens, (work + threads - 1) / threads);
     const int64_t pool = num_pages * page_size;
+    if (dtype == SS_BF16 && rot_dim % 16 == 0 && D % 8 == 0 && rot_dim <= 256 && ((uintptr_t)qkv & 15) == 0 &&
+        (kv == nullptr || ((uintptr_t)kv & 15) == 0)) {
+        ss_launch(rope_cache_bf16x8_kernel, dim3(n_tokens), dim3(256), 0, stream, (bf16*)qkv, positions, slots, inv_freq,
+                  (bf16*)kv, n_q, n_kv, D, rot_dim, page_size, pool, write_cache, err);
+        return SS_LAUNCH_CHECK();
+    }
     if (dtype == SS_BF16)
         ss_launch(rope_cache_kernel<bf16>, grid, dim3(threads), 0, stream, (bf16*)qkv, positions, slots, inv_freq, (bf16*)kv, n_q, n_kv, D, rot_dim, page_size, pool, write_cache, err);
     else
@@ -286,9 +361,43 @@ __global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int
     }
 }
 
+// bfloat16 with 16-byte loads: a thread takes 8 gate and the 8 matching up features (block % 8 == 0).
+__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int64_t n, int inter, int block) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int per_row = inter / 8;
+    const int64_t total = n * per_row;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / per_row;
+        const int c = (int)(idx - r * per_row) * 8;
+        const bf16* gp = in + r * 2 * inter + (int64_t)(c / block) * 2 * block + (c % block);
+        const uint4 gv = *reinterpret_cast<const uint4*>(gp);
+        const uint4 uv = *reinterpret_cast<const uint4*>(gp + block);
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(&gw[e]);
+            const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(&uw[e]);
+            const float g0 = __low2float(g2), g1 = __high2float(g2);
+            const __nv_bfloat162 o2 = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * __low2float(u2),
+                                                            g1 / (1.0f + expf(-g1)) * __high2float(u2));
+            ow[e] = *reinterpret_cast<const uint32_t*>(&o2);
+        }
+        *reinterpret_cast<uint4*>(out + r * inter + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
 template <typename T>
 static void launch_swiglu(const void* in, void* out, int64_t n, int inter, int block, cudaStream_t stream) {
     const int threads = 256;
+    if (sizeof(T) == 2 && inter % 8 == 0 && block % 8 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        int64_t blocks = (n * (inter / 8) + threads - 1) / threads;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        ss_launch(swiglu_bf16x8_kernel, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)in, (bf16*)out, n, inter, block);
+        return;
+    }
     const int vec = (inter % 4 == 0 && block % 4 == 0) ? 4 : 1;
     int64_t blocks = (n * (inter / vec) + threads - 1) / threads;
     if (blocks > 148 * 32) blocks = 148 * 32;

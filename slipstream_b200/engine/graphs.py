@@ -15,6 +15,8 @@ into its serving loop (slipstream/engine/cuda_graph.py:1-93).
 
 from __future__ import annotations
 
+import gc
+
 import numpy as np
 import torch
 
@@ -82,8 +84,17 @@ class DecodeGraph:
         torch.cuda.synchronize(device)
         self.graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
-        with torch.cuda.graph(self.graph):
-            self.logits = runner.model.forward(self.ctx)
+        # Python's collector must not run inside the capture: if it frees a dead object that owns pinned memory
+        # or another graph (an engine that is no longer used), the calls that frees make invalidate the capture
+        gc.collect()
+        collector_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.logits = runner.model.forward(self.ctx)
+        finally:
+            if collector_was_on:
+                gc.enable()
         self.kernels = ops.launch_count() - before
 
     def _fill(self, host: np.ndarray, plan: HostPlan | None) -> None:

@@ -63,7 +63,7 @@ def test_add_rmsnorm(dtype, hidden):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n_q, n_kv, d, rot, page", [(6, 2, 16, 16, 4), (7, 1, 48, 48, 5), (8, 8, 128, 64, 16), (3, 3, 80, 0, 7)])
+@pytest.mark.parametrize("n_q, n_kv, d, rot, page", [(6, 2, 16, 16, 4), (7, 1, 48, 48, 5), (8, 8, 128, 64, 16), (3, 3, 80, 0, 7), (28, 4, 128, 128, 16), (5, 1, 32, 8, 8)])
 def test_rope_and_cache(dtype, n_q, n_kv, d, rot, page):
     torch.manual_seed(d)
     n, pages, theta = 23, 9, 50000.0
@@ -106,6 +106,12 @@ def test_swiglu(dtype):
     for block in (2, 617):
         v = x.double().view(13, 1234 // block, 2, block)
         g, u = v[:, :, 0].reshape(13, 1234), v[:, :, 1].reshape(13, 1234)
+        assert rel_err(ops().swiglu(x, block=block), g * torch.sigmoid(g) * u) < tol(dtype, 2e-6, 8e-3)
+    # widths that take the 16-byte path in bfloat16: runs of 64, of 8, and the plain [gate | up]
+    x = (torch.randn(70, 2 * 1280, device=DEV) * 3).to(dtype)
+    for block in (64, 8, 1280):
+        v = x.double().view(70, 1280 // block, 2, block)
+        g, u = v[:, :, 0].reshape(70, 1280), v[:, :, 1].reshape(70, 1280)
         assert rel_err(ops().swiglu(x, block=block), g * torch.sigmoid(g) * u) < tol(dtype, 2e-6, 8e-3)
 
 
