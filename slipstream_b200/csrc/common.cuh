@@ -32,6 +32,14 @@ __device__ __forceinline__ float load_vec(const void* base, int64_t i, int is_f3
                   : to_float(reinterpret_cast<const T*>(base)[i]);
 }
 
+// silu(gate) * up, formed in float32.  FAST (the bfloat16 kernels): the approximate exponential and division,
+// whose error (about 2^-21) is far below the rounding of the result to bfloat16; every bfloat16 kernel that forms
+// this product uses the same expression, so a value does not depend on which of them ran.
+template <bool FAST>
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    return FAST ? __fdividef(g, 1.0f + __expf(-g)) * u : g / (1.0f + expf(-g)) * u;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

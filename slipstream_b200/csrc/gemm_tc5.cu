@@ -115,7 +115,7 @@ __device__ __forceinline__ float bias_at(const GemmArgs& g, int f) {
 __device__ __forceinline__ void store_swiglu(const GemmArgs& g, int m, int n, float gate, float up) {
     if (m + 64 >= g.M || n >= g.N) return;
     if (g.bias) { gate += bias_at(g, m); up += bias_at(g, m + 64); }
-    const float v = gate / (1.0f + expf(-gate)) * up;
+    const float v = silu_mul<true>(gate, up);
     const int64_t at = (int64_t)n * g.ldc + (m / TC_BM) * 64 + (m % TC_BM);
     if (g.out_f32) ((float*)g.C)[at] = v;
     else ((bf16*)g.C)[at] = __float2bfloat16_rn(v);

@@ -352,11 +352,11 @@ __global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int
             Vec4<T>::load(gp, g);
             Vec4<T>::load(gp + block, u);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) o[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
+            for (int e = 0; e < 4; ++e) o[e] = silu_mul<sizeof(T) == 2>(g[e], u[e]);
             Vec4<T>::store(out + r * inter + c, o);
         } else {
             const float g = to_float(gp[0]), u = to_float(gp[block]);
-            out[r * inter + c] = from_float<T>(g / (1.0f + expf(-g)) * u);
+            out[r * inter + c] = from_float<T>(silu_mul<sizeof(T) == 2>(g, u));
         }
     }
 }
@@ -381,8 +381,8 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restri
             const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(&gw[e]);
             const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(&uw[e]);
             const float g0 = __low2float(g2), g1 = __high2float(g2);
-            const __nv_bfloat162 o2 = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * __low2float(u2),
-                                                            g1 / (1.0f + expf(-g1)) * __high2float(u2));
+            const __nv_bfloat162 o2 = __floats2bfloat162_rn(silu_mul<true>(g0, __low2float(u2)),
+                                                            silu_mul<true>(g1, __high2float(u2)));
             ow[e] = *reinterpret_cast<const uint32_t*>(&o2);
         }
         *reinterpret_cast<uint4*>(out + r * inter + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
