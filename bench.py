@@ -75,7 +75,9 @@ def run_workload(name: str, args) -> int:
                         SamplingParams(max_tokens=new_tokens, temperature=0.0, ignore_eos=True), float(i) * 1e-6)
                 for i, n in enumerate(lengths)]
 
-    engine.generate_batch(requests("w", 4))  # warm-up: kernels compiled, graphs captured for the first buckets
+    # warm-up: the same workload once, so that kernels are compiled and a graph is captured for every batch
+    # bucket the run passes through while its requests finish (a capture inside the timed run costs tens of ms)
+    engine.generate_batch(requests("w", w["new_tokens"]))
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     outs = engine.generate_batch(requests("r", w["new_tokens"]))

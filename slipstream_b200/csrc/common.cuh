@@ -134,6 +134,14 @@ __device__ __forceinline__ uint32_t cluster_rank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
+// four floats (16-byte aligned) at the same shared-memory offset in block `rank` of this cluster
+__device__ __forceinline__ float4 ld_cluster_f32x4(const float* local, uint32_t rank) {
+    uint32_t addr = (uint32_t)__cvta_generic_to_shared(local), remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
 // float at the same shared-memory offset in block `rank` of this cluster
 __device__ __forceinline__ float ld_cluster_f32(const float* local, uint32_t rank) {
     uint32_t addr = (uint32_t)__cvta_generic_to_shared(local), remote;

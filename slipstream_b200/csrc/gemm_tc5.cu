@@ -318,19 +318,45 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (g.cluster) {
         cluster_sync_all();  // every block's partial tile lies in its shared memory
         if (warp >= 2) {
+            // a warp takes one token column at a time, a lane four consecutive features of it: 16-byte reads of
+            // the other blocks' shared memory, slices added in slice order
             const float* xbuf = reinterpret_cast<const float*>(tiles);
-            const int ml = (warp & 3) * 32 + lane;
             const int n_live = min(BN, g.N - n0);
-            for (int c = (int)cluster_rank(); c < n_live; c += g.slices) {
-                float acc = 0.f, acc2 = 0.f;
-#pragma unroll 8
-                for (int s = 0; s < g.slices; ++s) acc += ld_cluster_f32(xbuf + c * TC_BM + ml, (uint32_t)s);
+            const int rank = (int)cluster_rank(), q = warp & 3;
+            const int mine = n_live > rank ? (n_live - 1 - rank) / g.slices + 1 : 0;  // columns rank, rank + slices, ...
+            for (int i = q; i < mine; i += 4) {
+                const int c = rank + i * g.slices;
                 if (!g.swiglu) {
-                    store_out<BN>(g, m0 + ml, n0 + c, acc);
-                } else if (ml < 64) {
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
-                    for (int s = 0; s < g.slices; ++s) acc2 += ld_cluster_f32(xbuf + c * TC_BM + ml + 64, (uint32_t)s);
-                    store_swiglu(g, m0 + ml, n0 + c, acc, acc2);
+                    for (int s = 0; s < g.slices; ++s) {
+                        const float4 v = ld_cluster_f32x4(xbuf + c * TC_BM + lane * 4, (uint32_t)s);
+                        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                    }
+                    const int m = m0 + lane * 4, n = n0 + c;
+                    if (g.swapped && !g.out_f32 && m + 3 < g.M && (g.ldc & 3) == 0) {
+                        if (g.bias) { acc.x += bias_at(g, m); acc.y += bias_at(g, m + 1); acc.z += bias_at(g, m + 2); acc.w += bias_at(g, m + 3); }
+                        const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+                        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+                        *reinterpret_cast<uint2*>((bf16*)g.C + (int64_t)n * g.ldc + m) = packed;
+                    } else {
+                        store_out<BN>(g, m, n, acc.x); store_out<BN>(g, m + 1, n, acc.y);
+                        store_out<BN>(g, m + 2, n, acc.z); store_out<BN>(g, m + 3, n, acc.w);
+                    }
+                } else if (lane < 16) {
+                    float4 ga = make_float4(0.f, 0.f, 0.f, 0.f), ua = ga;
+#pragma unroll 8
+                    for (int s = 0; s < g.slices; ++s) {
+                        const float4 v = ld_cluster_f32x4(xbuf + c * TC_BM + lane * 4, (uint32_t)s);
+                        const float4 w = ld_cluster_f32x4(xbuf + c * TC_BM + 64 + lane * 4, (uint32_t)s);
+                        ga.x += v.x; ga.y += v.y; ga.z += v.z; ga.w += v.w;
+                        ua.x += w.x; ua.y += w.y; ua.z += w.z; ua.w += w.w;
+                    }
+                    const int m = m0 + lane * 4, n = n0 + c;
+                    store_swiglu(g, m, n, ga.x, ua.x); store_swiglu(g, m + 1, n, ga.y, ua.y);
+                    store_swiglu(g, m + 2, n, ga.z, ua.z); store_swiglu(g, m + 3, n, ga.w, ua.w);
                 }
             }
         }
