@@ -124,28 +124,34 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
     for (int d = 0; d < D / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
     if (warp == 4) {
-        // ---------------- producer: one bulk tensor copy per page and half of the head, keys then values
-        if (lane == 0 && work) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kv) : "memory");
+        // ---------------- producer: one bulk tensor copy per page and 64-element half of the head, for keys and for
+        // values.  Issuing a copy costs the issuing thread about a hundred cycles, so the copies of a tile are
+        // spread over the lanes of the warp: lane p * HALVES + h takes page p, half h.
+        if (work) {
+            if (lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kv) : "memory");
             const int ppt = MMA_BN / page_size;
             const int b_first = max(lo, kt_lo * MMA_BN) / page_size, b_last = min(pos, kt_hi * MMA_BN + MMA_BN - 1) / page_size;
             int64_t spare = table.p[b_first - table.base];  // a page of this request, for blocks that have none
             if (spare < 0 || spare >= a.num_pages) {
-                atomicOr(a.err, SS_ERR_PAGE_RANGE);
+                if (lane == 0) atomicOr(a.err, SS_ERR_PAGE_RANGE);
                 spare = 0;
             }
-            bool waited = false;
-            for (int kt = kt_lo; kt <= kt_hi; ++kt) {
+            const int p = lane / HALVES, h = lane % HALVES;
+            const bool mine = p < ppt;
+            bool waited = false, ok = true;
+            for (int kt = kt_lo; kt <= kt_hi && ok; ++kt) {
                 const int i = kt - kt_lo, st = i % NS;
-                if (i >= NS && !fa::mbar_wait(&empty[st], ((i / NS) - 1) & 1, gave_up)) break;
+                if (i >= NS) ok = __all_sync(0xffffffffu, fa::mbar_wait(&empty[st], ((i / NS) - 1) & 1, gave_up));
+                if (!ok) break;
                 if (!a.fused && kt == kt_last && !waited) {
                     pdl_wait();  // the newest key and value are written by the kernel before this one
                     waited = true;
                 }
-                fa::mbar_expect_tx(&full[st], STAGE * 2);
-                bf16* Ks = KV + st * STAGE;
-                bf16* Vs = Ks + MMA_BN * D;
-                for (int p = 0; p < ppt; ++p) {
+                if (lane == 0) fa::mbar_expect_tx(&full[st], STAGE * 2);
+                __syncwarp();
+                if (mine) {
+                    bf16* Ks = KV + st * STAGE;
+                    bf16* Vs = Ks + MMA_BN * D;
                     const int blk = kt * ppt + p;
                     int64_t page = (blk >= b_first && blk <= b_last) ? (int64_t)table.p[blk - table.base] : -1;
                     if (page >= a.num_pages) {
@@ -153,12 +159,10 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
                         page = -1;
                     }
                     if (page < 0) page = spare;
-                    for (int h = 0; h < HALVES; ++h) {
-                        fa::tma_load_3d(Ks + h * (MMA_BN * 64) + p * page_size * 64, &map_kv, h * 64, 0,
-                                        (int)((page * 2 + 0) * n_kv + kvh), &full[st]);
-                        fa::tma_load_3d(Vs + h * (MMA_BN * 64) + p * page_size * 64, &map_kv, h * 64, 0,
-                                        (int)((page * 2 + 1) * n_kv + kvh), &full[st]);
-                    }
+                    fa::tma_load_3d(Ks + h * (MMA_BN * 64) + p * page_size * 64, &map_kv, h * 64, 0,
+                                    (int)((page * 2 + 0) * n_kv + kvh), &full[st]);
+                    fa::tma_load_3d(Vs + h * (MMA_BN * 64) + p * page_size * 64, &map_kv, h * 64, 0,
+                                    (int)((page * 2 + 1) * n_kv + kvh), &full[st]);
                 }
             }
         }

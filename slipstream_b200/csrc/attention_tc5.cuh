@@ -71,6 +71,13 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t 
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
         ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with the A operand in tensor memory (row = lane, two bfloat16 per 32-bit column).
+__device__ __forceinline__ void umma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_addr(bar)) : "memory");
 }
@@ -116,16 +123,16 @@ struct Args {
 
 template <int D>
 constexpr int smem_bytes() {
-    // Q (128 rows) + two stages each of K and V (64 keys) + one P buffer (128 x 64), + barriers, + alignment:
-    // 112 KB for head size 128, so that two blocks share an SM (one's softmax overlaps the other's products)
-    return 128 * D * 2 + 2 * 2 * FA_BN * D * 2 + 128 * FA_BN * 2 + 512;
+    // Q (128 rows) + two stages each of K and V (64 keys) + barriers: 96.5 KB for head size 128, so that two
+    // blocks share an SM (one's softmax overlaps the other's products).  P lives in tensor memory.
+    return 128 * D * 2 + 2 * 2 * FA_BN * D * 2 + 512;
 }
 
 template <int D>
 __global__ void __launch_bounds__(FA_THREADS, 2)
 attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Args a) {
     constexpr int HALVES = D / 64;
-    constexpr int Q_BYTES = 128 * D * 2, KV_BYTES = FA_BN * D * 2, P_BYTES = 128 * FA_BN * 2;
+    constexpr int Q_BYTES = 128 * D * 2, KV_BYTES = FA_BN * D * 2;
     constexpr int HALF_Q = 128 * 128, HALF_KV = FA_BN * 128;  // bytes of one 64-column half
     constexpr int TMEM_COLS = 256;  // S0 [0,64), S1 [64,128), O [128, 128 + D)
     extern __shared__ unsigned char smem_raw[];
@@ -135,15 +142,14 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     unsigned char* Qs = base;
     unsigned char* Ks = Qs + Q_BYTES;            // [2][KV_BYTES]
     unsigned char* Vs = Ks + 2 * KV_BYTES;       // [2][KV_BYTES]
-    unsigned char* Ps = Vs + 2 * KV_BYTES;       // [P_BYTES]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + P_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + 2 * KV_BYTES);
     uint64_t* q_full = bars;          // 1
     uint64_t* k_full = bars + 1;      // 2
     uint64_t* v_full = bars + 3;      // 2
     uint64_t* k_empty = bars + 5;     // 2
     uint64_t* v_empty = bars + 7;     // 2
     uint64_t* s_ready = bars + 9;     // 2
-    uint64_t* p_ready = bars + 11;    // 2 (128 arrivals each)
+    uint64_t* p_ready = bars + 11;    // 2 (one arrival per softmax warp)
     uint64_t* pv_done = bars + 13;    // 2
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
     volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -174,7 +180,7 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
-            mbar_init(&s_ready[s], 1); mbar_init(&p_ready[s], 128); mbar_init(&pv_done[s], 1);
+            mbar_init(&s_ready[s], 1); mbar_init(&p_ready[s], 4); mbar_init(&pv_done[s], 1);
         }
         *gave_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -188,37 +194,51 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 0 && lane == 0) {
-        // ---------------- producer
-        mbar_expect_tx(q_full, (uint32_t)(TOK * G * 128 * HALVES));
-        for (int h = 0; h < HALVES; ++h)
-            tma_load_3d(Qs + h * HALF_Q, &map_q, h * 64, kvh * G, qs + tok0, q_full);
+    if (warp == 0) {
+        // ---------------- producer: the whole warp.  Issuing a bulk tensor copy costs the issuing thread about a
+        // hundred cycles, and a tile is 16 of them (a page and a 64-element half of the head each, keys and
+        // values): from one thread they took 1,800 cycles a tile and bounded the kernel.  Here lane
+        // p * HALVES + h issues the copies of page p, half h, and reads that page's block-table entry itself.
+        if (lane == 0) {
+            mbar_expect_tx(q_full, (uint32_t)(TOK * G * 128 * HALVES));
+            for (int h = 0; h < HALVES; ++h)
+                tma_load_3d(Qs + h * HALF_Q, &map_q, h * 64, kvh * G, qs + tok0, q_full);
+        }
         const int ps = a.page_size, pages_per_tile = FA_BN / ps;
         const int live_blocks = (seq_len + ps - 1) / ps;
+        const int p = lane / HALVES, h = lane % HALVES;
+        const bool mine = p < pages_per_tile;
+        int64_t spare = __ldg(table);  // keys past the request's end are masked; any finite page will do
+        if (spare < 0 || spare >= a.num_pages) spare = 0;
+        auto entry = [&](int j) -> int64_t {
+            const int blk = j * pages_per_tile + p;
+            int64_t page = (mine && blk < live_blocks) ? (int64_t)__ldg(table + blk) : -1;
+            if (page >= a.num_pages) { atomicOr(a.err, SS_ERR_PAGE_RANGE); page = -1; }
+            return page < 0 ? spare : page;
+        };
+        int64_t next_page = entry(0);
+        bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int st = j & 1;
             const uint32_t par = ((j >> 1) & 1) ^ 1;
+            const int64_t page = next_page;
+            if (j + 1 < n_tiles) next_page = entry(j + 1);  // in flight while this tile is issued
             // keys
-            if (!mbar_wait(&k_empty[st], par, gave_up)) break;
-            mbar_expect_tx(&k_full[st], KV_BYTES);
-            int64_t pg[8];
-            for (int p = 0; p < pages_per_tile; ++p) {
-                const int blk = j * pages_per_tile + p;
-                int64_t page = blk < live_blocks ? (int64_t)table[blk] : -1;
-                if (page >= a.num_pages) { atomicOr(a.err, SS_ERR_PAGE_RANGE); page = -1; }
-                if (page < 0) page = table[0];  // keys past the request's end are masked; any finite page will do
-                pg[p] = page;
-                for (int h = 0; h < HALVES; ++h)
-                    tma_load_3d(Ks + st * KV_BYTES + h * HALF_KV + p * ps * 128, &map_kv, h * 64, 0,
-                                (int)((page * 2 + 0) * a.n_kv + kvh), &k_full[st]);
-            }
+            ok = __all_sync(0xffffffffu, mbar_wait(&k_empty[st], par, gave_up));
+            if (!ok) break;
+            if (lane == 0) mbar_expect_tx(&k_full[st], KV_BYTES);
+            __syncwarp();
+            if (mine)
+                tma_load_3d(Ks + st * KV_BYTES + h * HALF_KV + p * ps * 128, &map_kv, h * 64, 0,
+                            (int)((page * 2 + 0) * a.n_kv + kvh), &k_full[st]);
             // values
-            if (!mbar_wait(&v_empty[st], par, gave_up)) break;
-            mbar_expect_tx(&v_full[st], KV_BYTES);
-            for (int p = 0; p < pages_per_tile; ++p)
-                for (int h = 0; h < HALVES; ++h)
-                    tma_load_3d(Vs + st * KV_BYTES + h * HALF_KV + p * ps * 128, &map_kv, h * 64, 0,
-                                (int)((pg[p] * 2 + 1) * a.n_kv + kvh), &v_full[st]);
+            ok = __all_sync(0xffffffffu, mbar_wait(&v_empty[st], par, gave_up));
+            if (!ok) break;
+            if (lane == 0) mbar_expect_tx(&v_full[st], KV_BYTES);
+            __syncwarp();
+            if (mine)
+                tma_load_3d(Vs + st * KV_BYTES + h * HALF_KV + p * ps * 128, &map_kv, h * 64, 0,
+                            (int)((page * 2 + 1) * a.n_kv + kvh), &v_full[st]);
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer
@@ -249,10 +269,9 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int kk = 0; kk < FA_BN / 16; ++kk) {  // 16 keys per instruction
-                const uint64_t ad = desc_k_major(Ps) + (uint64_t)(kk * 2);
+            for (int kk = 0; kk < FA_BN / 16; ++kk) {  // 16 keys per instruction: 8 columns of P
                 const uint64_t bd = desc_mn_major(Vs + st * KV_BYTES + kk * 16 * 128, HALF_KV);
-                umma(tmem + 128, ad, bd, idesc_pv, (j | kk) != 0);
+                umma_a_tmem(tmem + 128, tmem + st * FA_BN + kk * 8, bd, idesc_pv, (j | kk) != 0);
             }
             umma_commit(&pv_done[st]);
             umma_commit(&v_empty[st]);
@@ -314,32 +333,25 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 }
                 m_ref = m_new;
             }
-            // P row, bfloat16, into the swizzled K-major layout (8 chunks of 16 bytes, chunk ^ (row % 8)).  The one
-            // P buffer is free once the PV product of the previous tile is complete.
-            if (j > 0) {
-                ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, gave_up));
-                if (!ok) break;
-            }
-            unsigned char* prow = Ps + row * 128;
+            // P row, bfloat16, two per column, over the first 32 columns of this tile's S buffer (the row's scores
+            // are in registers by now); the PV product reads it from there, and the S product of the tile after
+            // next, which reuses the buffer, is issued behind that PV product.
+            uint32_t packed[32];
             float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-                uint32_t packed[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int c = ch * 8 + e * 2;
-                    const float p0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), scale_log2, -m_ref));
-                    const float p1 = ex2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), scale_log2, -m_ref));
-                    l4[e] += p0 + p1;
-                    __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
-                    packed[e] = *reinterpret_cast<uint32_t*>(&v);
-                }
-                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            for (int c = 0; c < 64; c += 2) {
+                const float p0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), scale_log2, -m_ref));
+                const float p1 = ex2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), scale_log2, -m_ref));
+                l4[(c >> 1) & 3] += p0 + p1;
+                __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+                packed[c >> 1] = *reinterpret_cast<uint32_t*>(&v);
             }
             l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads P through the async proxy
+            tmem_st32(tmem + lane_base + st * FA_BN, packed);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(&p_ready[st]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready[st]);  // one arrival per softmax warp
         }
         // ---------------- epilogue: O / l for the rows that hold a query
         if (ok) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, gave_up);
