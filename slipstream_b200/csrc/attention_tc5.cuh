@@ -3,14 +3,17 @@
 //
 // A block takes up to 128 "rows" of one (request, kv head): TOK = 128 / G consecutive query tokens times the
 // G heads of the kv group, token-major, so the group shares every key/value tile.  Roles:
-//   warp 0 (one lane)  producer: TMA loads of the Q tile and, per 64-key tile, of the K and V pages
-//                      (one box per page and 64-column half; 128-byte swizzle) into two-stage rings;
+//   warp 0             producer: TMA loads of the Q tile and, per 64-key tile, of the K and V pages (one box
+//                      per page and 64-column half, 128-byte swizzle; each box issued by a lane of its own)
+//                      into a three-stage ring of K tiles and a two-stage ring of V tiles;
 //   warp 1 (one lane)  MMA issuer: S = Q K^T (M 128, N 64) into one of two S buffers in tensor memory,
-//                      then O += P V (M 128, N = head size, V read MN-major) into the O columns;
+//                      then O += P V (M 128, N = head size, P read from tensor memory, V MN-major from
+//                      shared memory) into the O columns;
 //   warps 2..5         softmax: one thread per row reads its S row with tcgen05.ld, scales, masks the
-//                      diagonal tile, keeps a running maximum and sum in float32, writes P (bfloat16) into
-//                      shared memory in the swizzled K-major layout, and rescales O in tensor memory only
-//                      when the maximum has grown by more than 2^8 (the sum carries the same reference).
+//                      diagonal tile, keeps a running maximum and sum in float32, writes P (bfloat16, two
+//                      per column) with tcgen05.st over the first half of the S buffer it came from, and
+//                      rescales O in tensor memory only when the maximum has grown by more than 2^8 (the
+//                      sum carries the same reference).
 // Masking is the packed-index causal rule of slipstream/models/layers/attention.py:46-51; softmax is float32
 // (:64-88).  No window here: windowed layers, other head sizes and page sizes that do not divide 64 run the
 // mma.sync kernel of attention_mma.cuh.  Every mbarrier wait is bounded (see gemm_tc5.cu).
@@ -22,6 +25,7 @@
 
 #define FA_THREADS 192
 #define FA_BN 64
+#define FA_KS 3  // stages of K: a K tile is asked for two S products ahead, so that the MMA lane never waits for it
 #define FA_WAIT_LIMIT (1u << 20)
 
 namespace fa {
@@ -123,9 +127,9 @@ struct Args {
 
 template <int D>
 constexpr int smem_bytes() {
-    // Q (128 rows) + two stages each of K and V (64 keys) + barriers: 96.5 KB for head size 128, so that two
-    // blocks share an SM (one's softmax overlaps the other's products).  P lives in tensor memory.
-    return 128 * D * 2 + 2 * 2 * FA_BN * D * 2 + 512;
+    // Q (128 rows) + three stages of K and two of V (64 keys each) + barriers: 112.5 KB for head size 128, so
+    // that two blocks share an SM (one's softmax overlaps the other's products).  P lives in tensor memory.
+    return 128 * D * 2 + (FA_KS + 2) * FA_BN * D * 2 + 512;
 }
 
 template <int D>
@@ -140,18 +144,18 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     // array, so it starts at the block's shared window, which is aligned; checked below, not assumed.
     unsigned char* base = smem_raw;
     unsigned char* Qs = base;
-    unsigned char* Ks = Qs + Q_BYTES;            // [2][KV_BYTES]
-    unsigned char* Vs = Ks + 2 * KV_BYTES;       // [2][KV_BYTES]
+    unsigned char* Ks = Qs + Q_BYTES;            // [FA_KS][KV_BYTES]
+    unsigned char* Vs = Ks + FA_KS * KV_BYTES;   // [2][KV_BYTES]
     uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + 2 * KV_BYTES);
     uint64_t* q_full = bars;          // 1
-    uint64_t* k_full = bars + 1;      // 2
-    uint64_t* v_full = bars + 3;      // 2
-    uint64_t* k_empty = bars + 5;     // 2
-    uint64_t* v_empty = bars + 7;     // 2
-    uint64_t* s_ready = bars + 9;     // 2
-    uint64_t* p_ready = bars + 11;    // 2 (one arrival per softmax warp)
-    uint64_t* pv_done = bars + 13;    // 2
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    uint64_t* v_full = bars + 1;      // 2
+    uint64_t* v_empty = bars + 3;     // 2
+    uint64_t* s_ready = bars + 5;     // 2
+    uint64_t* p_ready = bars + 7;     // 2 (one arrival per softmax warp)
+    uint64_t* pv_done = bars + 9;     // 2
+    uint64_t* k_full = bars + 11;     // FA_KS
+    uint64_t* k_empty = k_full + FA_KS;  // FA_KS
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(k_empty + FA_KS);
     volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     pdl_launch_dependents();
@@ -179,9 +183,10 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kv) : "memory");
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
+            mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
             mbar_init(&s_ready[s], 1); mbar_init(&p_ready[s], 4); mbar_init(&pv_done[s], 1);
         }
+        for (int s = 0; s < FA_KS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
         *gave_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -210,27 +215,27 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const bool mine = p < pages_per_tile;
         int64_t spare = __ldg(table);  // keys past the request's end are masked; any finite page will do
         if (spare < 0 || spare >= a.num_pages) spare = 0;
-        auto entry = [&](int j) -> int64_t {
+        auto entry = [&](int j) -> int32_t {  // the raw entry: it is looked at one tile later, when it has arrived
             const int blk = j * pages_per_tile + p;
-            int64_t page = (mine && blk < live_blocks) ? (int64_t)__ldg(table + blk) : -1;
-            if (page >= a.num_pages) { atomicOr(a.err, SS_ERR_PAGE_RANGE); page = -1; }
-            return page < 0 ? spare : page;
+            return (mine && blk < live_blocks) ? __ldg(table + blk) : -1;
         };
-        int64_t next_page = entry(0);
+        int32_t next_entry = entry(0);
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
-            const int st = j & 1;
-            const uint32_t par = ((j >> 1) & 1) ^ 1;
-            const int64_t page = next_page;
-            if (j + 1 < n_tiles) next_page = entry(j + 1);  // in flight while this tile is issued
+            const int st = j & 1, kst = j % FA_KS;
+            const uint32_t par = ((j >> 1) & 1) ^ 1, kpar = ((j / FA_KS) & 1) ^ 1;
+            int64_t page = next_entry;
+            if (j + 1 < n_tiles) next_entry = entry(j + 1);  // in flight while this tile is issued
+            if (page >= a.num_pages) { atomicOr(a.err, SS_ERR_PAGE_RANGE); page = -1; }
+            if (page < 0) page = spare;
             // keys
-            ok = __all_sync(0xffffffffu, mbar_wait(&k_empty[st], par, gave_up));
+            ok = __all_sync(0xffffffffu, mbar_wait(&k_empty[kst], kpar, gave_up));
             if (!ok) break;
-            if (lane == 0) mbar_expect_tx(&k_full[st], KV_BYTES);
+            if (lane == 0) mbar_expect_tx(&k_full[kst], KV_BYTES);
             __syncwarp();
             if (mine)
-                tma_load_3d(Ks + st * KV_BYTES + h * HALF_KV + p * ps * 128, &map_kv, h * 64, 0,
-                            (int)((page * 2 + 0) * a.n_kv + kvh), &k_full[st]);
+                tma_load_3d(Ks + kst * KV_BYTES + h * HALF_KV + p * ps * 128, &map_kv, h * 64, 0,
+                            (int)((page * 2 + 0) * a.n_kv + kvh), &k_full[kst]);
             // values
             ok = __all_sync(0xffffffffu, mbar_wait(&v_empty[st], par, gave_up));
             if (!ok) break;
@@ -247,18 +252,18 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
         bool ok = mbar_wait(q_full, 0, gave_up);
         auto issue_s = [&](int j) {
-            const int st = j & 1;
+            const int st = j & 1, kst = j % FA_KS;
             // the S buffer of this parity is free: the softmax of two tiles back has read it (p_ready was seen)
-            if (!mbar_wait(&k_full[st], (j >> 1) & 1, gave_up)) return false;
+            if (!mbar_wait(&k_full[kst], (j / FA_KS) & 1, gave_up)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
                 const uint64_t ad = desc_k_major(Qs + (kk / 4) * HALF_Q) + (uint64_t)((kk % 4) * 2);
-                const uint64_t bd = desc_k_major(Ks + st * KV_BYTES + (kk / 4) * HALF_KV) + (uint64_t)((kk % 4) * 2);
+                const uint64_t bd = desc_k_major(Ks + kst * KV_BYTES + (kk / 4) * HALF_KV) + (uint64_t)((kk % 4) * 2);
                 umma(tmem + st * FA_BN, ad, bd, idesc_s, kk != 0);
             }
             umma_commit(&s_ready[st]);
-            umma_commit(&k_empty[st]);
+            umma_commit(&k_empty[kst]);
             return true;
         };
         if (ok) ok = issue_s(0);
