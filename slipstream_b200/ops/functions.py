@@ -121,7 +121,7 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
 
 
 def error_word(device: torch.device) -> torch.Tensor:
-    key = f"err{device}"
+    key = ("err", device)
     word = _state.get(key)
     if word is None:
         with torch.inference_mode(False):  # the word is cleared in place later, from any mode
@@ -143,7 +143,14 @@ def check_errors(device: torch.device) -> None:
         raise KernelError(f"a kernel reported: {what}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """Handle of the current CUDA stream (every wrapper below asks for it, so the short way is taken when
+    this torch has it)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -697,7 +704,7 @@ def gate_up_swiglu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | N
 
 def set_programmatic_launch(enabled: bool) -> None:
     """Turn programmatic dependent launch of this package's kernels on or off (on by default)."""
-    libs = [ops_library(), gemm_library()] + [lib for key, lib in _state.items() if key.startswith("attn")]
+    libs = [ops_library(), gemm_library()] + [lib for key, lib in _state.items() if isinstance(key, str) and key.startswith("attn")]
     for lib in libs:
         lib.ss_set_pdl.argtypes = [c_int]
         lib.ss_set_pdl.restype = None
