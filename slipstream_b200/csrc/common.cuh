@@ -124,6 +124,27 @@ static inline void ss_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 b
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Blocks along grid.x grouped into clusters of `cluster_x`.
+template <typename... KArgs, typename... Args>
+static inline void ss_launch_cluster_x(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                       int cluster_x, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster_x;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ss_pdl_flag() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ void cluster_sync_all() {
     __syncwarp();
     asm volatile("barrier.cluster.arrive.release;" ::: "memory");
@@ -140,6 +161,19 @@ __device__ __forceinline__ float4 ld_cluster_f32x4(const float* local, uint32_t 
     float4 v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
     asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+    uint32_t n;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n));
+    return n;
+}
+// 64-bit word at the same shared-memory offset in block `rank` of this cluster
+__device__ __forceinline__ unsigned long long ld_cluster_u64(const unsigned long long* local, uint32_t rank) {
+    uint32_t addr = (uint32_t)__cvta_generic_to_shared(local), remote;
+    unsigned long long v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(remote) : "memory");
     return v;
 }
 // float at the same shared-memory offset in block `rank` of this cluster

@@ -2,8 +2,9 @@
 // sampling chain (slipstream/engine/sampler.py:36-146): repetition penalty, then
 // temperature, top-k, top-p, min-p, then a draw from the softmax of what is left.
 //
-// One block per row; every row carries its own parameters, so greedy and sampled
-// requests share a launch.  Differences from the reference, by design:
+// A thread-block cluster per row (up to 8 blocks, which add their histograms and compare their candidates through
+// one another's shared memory); every row carries its own parameters, so greedy and sampled requests share a
+// launch.  Differences from the reference, by design:
 //  * the draw is a Gumbel-max race (token = argmax(x_i + g_i), g_i = -log(-log u_i))
 //    over counter-based Philox4x32-10 uniforms keyed by (seed, draw index, token),
 //    which has the distribution of multinomial(softmax(x)) but needs no sort, no
@@ -145,15 +146,8 @@ __device__ __forceinline__ void philox4x32_10(uint32_t k0, uint32_t k1, uint32_t
     }
 }
 
-// Gumbel noise of token i for draw number `draw` of the stream `seed`.
-__device__ __forceinline__ float gumbel(uint64_t seed, uint64_t draw, int i) {
-    uint32_t c[4] = {(uint32_t)(i >> 2), (uint32_t)draw, (uint32_t)(draw >> 32), 0x51195u};
-    philox4x32_10((uint32_t)seed, (uint32_t)(seed >> 32), c);
-    const uint32_t x = c[i & 3];
-    const float u = ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f);  // in (0, 1), exact
-    return -logf(-logf(u));
-}
-
+// The Gumbel noise of token i for draw number `draw` of the stream `seed` is -log(-log(u)) with u from output
+// i % 4 of Philox with counter (i / 4, draw) and key seed.
 __device__ __forceinline__ uint32_t order_key(float v) {
     const uint32_t b = __float_as_uint(v);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);  // monotone: larger float, larger key
@@ -161,18 +155,136 @@ __device__ __forceinline__ uint32_t order_key(float v) {
 
 struct SampleShared {
     ArgMax arg[33];
-    float red[33];
-    unsigned long long hist[256];
+    unsigned long long total[256];  // the block's histogram of one radix step
+    unsigned long long word;        // a value the blocks of the cluster show one another
     uint32_t pick_digit;
     unsigned long long pick_above;
 };
 
+// The best candidate over all blocks of the cluster (every block gets it).
+__device__ __forceinline__ ArgMax cluster_argmax(ArgMax a, SampleShared& sh) {
+    a = block_argmax(a, sh.arg);
+    const uint32_t n = cluster_size();
+    if (n == 1) return a;
+    if (threadIdx.x == 0) sh.word = ((unsigned long long)__float_as_uint(a.v) << 32) | (uint32_t)a.i;
+    cluster_sync_all();
+    ArgMax best{-INFINITY, 0x7fffffff};
+    for (uint32_t c = 0; c < n; ++c) {
+        const unsigned long long w = ld_cluster_u64(&sh.word, c);
+        best = better(best, ArgMax{__uint_as_float((uint32_t)(w >> 32)), (int)(uint32_t)w});
+    }
+    cluster_sync_all();  // sh.word may be written again
+    return best;
+}
+
+// The sum of a 64-bit value over all threads of all blocks of the cluster (every thread gets it).
+__device__ __forceinline__ unsigned long long cluster_sum(unsigned long long v, SampleShared& sh) {
+    const int tid = threadIdx.x, warp = tid >> 5, n_warps = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((tid & 31) == 0) sh.total[warp] = v;
+    __syncthreads();
+    unsigned long long t = 0ull;
+    for (int w = 0; w < n_warps; ++w) t += sh.total[w];
+    const uint32_t n = cluster_size();
+    if (n == 1) {
+        __syncthreads();
+        return t;
+    }
+    if (tid == 0) sh.word = t;
+    cluster_sync_all();
+    unsigned long long all = 0ull;
+    for (uint32_t c = 0; c < n; ++c) all += ld_cluster_u64(&sh.word, c);
+    cluster_sync_all();
+    return all;
+}
+
 // value of token i after penalty and temperature
-__device__ __forceinline__ float tempered(const float* row, int i, const uint32_t* seen, float penalty,
-                                          float inv_t_unused, float temperature) {
+__device__ __forceinline__ float tempered(const float* row, int i, const uint32_t* seen, float penalty, float temperature) {
     float x = row[i];
     if (seen && ((seen[i >> 5] >> (i & 31)) & 1u)) x = x < 0.f ? x * penalty : x / penalty;
     return x / temperature;
+}
+
+// Histograms of a radix step.  Every warp has a histogram of its own in shared memory, and a thread adds up
+// consecutive elements that fall into the same bin before it touches shared memory: logits share their top
+// bits, so a single histogram with one atomic per element meant 150,000 atomics on two or three addresses
+// (2 ms for one row).  All sums are integers (counts, or probabilities in fixed point), so the result does
+// not depend on the order of the additions.
+struct BinRun {
+    int digit;
+    unsigned long long sum;
+};
+__device__ __forceinline__ void run_add(BinRun& run, unsigned long long* warp_hist, int digit, unsigned long long w) {
+    if (digit == run.digit) {
+        run.sum += w;
+    } else {
+        if (run.sum) atomicAdd(&warp_hist[run.digit], run.sum);
+        run.digit = digit;
+        run.sum = w;
+    }
+}
+__device__ __forceinline__ void run_flush(BinRun& run, unsigned long long* warp_hist) {
+    if (run.sum) atomicAdd(&warp_hist[run.digit], run.sum);
+    run.sum = 0ull;
+}
+
+// After the warps' histograms are complete: add them up, then find, from bin 255 downwards, the first bin d
+// at which base + (sum of the bins above d) + bin d reaches `target`; bin 0 takes what never reaches it.
+// Leaves d in sh.pick_digit and base + (sum of the bins above d) in sh.pick_above.  Called by all threads.
+__device__ __forceinline__ void select_bin(SampleShared& sh, const unsigned long long* hists, int n_warps,
+                                           unsigned long long base, unsigned long long target) {
+    const int tid = threadIdx.x, lane = tid & 31;
+    __syncthreads();
+    if (tid < 256) {
+        unsigned long long t = 0ull;
+        for (int w = 0; w < n_warps; ++w) t += hists[w * 256 + tid];
+        sh.total[tid] = t;
+    }
+    const uint32_t n_blocks = cluster_size();
+    if (n_blocks > 1) {
+        // every block adds up the histograms of all blocks, in block order, and so picks the same bin
+        cluster_sync_all();
+        unsigned long long t = 0ull;
+        if (tid < 256)
+            for (uint32_t c = 0; c < n_blocks; ++c) t += ld_cluster_u64(&sh.total[tid], c);
+        cluster_sync_all();
+        if (tid < 256) sh.total[tid] = t;
+    }
+    __syncthreads();
+    if (tid < 32) {
+        // lane l owns bins 255 - 8 l ... 248 - 8 l, highest first
+        unsigned long long mine[8], lsum = 0ull;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            mine[b] = sh.total[255 - 8 * lane - b];
+            lsum += mine[b];
+        }
+        unsigned long long incl = lsum;  // inclusive sum over lanes 0..l
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        const unsigned long long before = base + incl - lsum;
+        const bool reached = before + lsum >= target;
+        const uint32_t vote = __ballot_sync(0xffffffffu, reached);
+        const int first = vote ? __ffs(vote) - 1 : 31;
+        if (lane == first) {
+            unsigned long long acc = before;
+            int d = 255 - 8 * lane;
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                d = 255 - 8 * lane - b;
+                if (d == 0 || acc + mine[b] >= target) break;
+                acc += mine[b];
+            }
+            sh.pick_digit = (uint32_t)d;
+            sh.pick_above = acc;
+        }
+    }
+    __syncthreads();
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
@@ -185,16 +297,21 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, int32_t* __restr
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
     pdl_wait();               // nothing below runs before the kernels before this one are complete
     __shared__ SampleShared sh;
-    const int r = blockIdx.x, tid = threadIdx.x;
+    extern __shared__ unsigned long long warp_hists[];  // [warps][256]
+    // the blocks of a cluster share a row; block c of n takes elements c * blockDim + tid, + n * blockDim, ...
+    const int n_blocks = (int)cluster_size(), rank = (int)cluster_rank();
+    const int r = blockIdx.x / n_blocks, tid = threadIdx.x, warp = tid >> 5, n_warps = blockDim.x >> 5;
+    const int first = rank * blockDim.x + tid, step = n_blocks * blockDim.x;
+    unsigned long long* my_hist = warp_hists + warp * 256;
     const float* row = logits + (int64_t)r * stride;
     const float temp = temperature[r];
     uint32_t* seen_row = (seen_all && slots && slots[r] >= 0) ? seen_all + (int64_t)slots[r] * seen_words : nullptr;
 
     if (temp == 0.f || top_k[r] == 1) {  // greedy: raw logits, no filters
         ArgMax a{-INFINITY, 0x7fffffff};
-        for (int i = tid; i < vocab; i += blockDim.x) a = better(a, ArgMax{row[i], i});
-        a = block_argmax(a, sh.arg);
-        if (tid == 0) {
+        for (int i = first; i < vocab; i += step) a = better(a, ArgMax{row[i], i});
+        a = cluster_argmax(a, sh);
+        if (tid == 0 && rank == 0) {
             const int tok = a.i == 0x7fffffff ? 0 : a.i;
             out[r] = tok;
             if (seen_row) atomicOr(&seen_row[tok >> 5], 1u << (tok & 31));
@@ -213,24 +330,15 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, int32_t* __restr
         uint32_t prefix = 0, mask = 0;
         unsigned long long want = (unsigned long long)k;  // rank still to find inside the prefix
         for (int shift = 24; shift >= 0; shift -= 8) {
-            for (int b = tid; b < 256; b += blockDim.x) sh.hist[b] = 0ull;
+            for (int b = tid; b < n_warps * 256; b += blockDim.x) warp_hists[b] = 0ull;
             __syncthreads();
-            for (int i = tid; i < vocab; i += blockDim.x) {
-                const uint32_t key = order_key(tempered(row, i, seen, pen, 0.f, temp));
-                if ((key & mask) == prefix) atomicAdd(&sh.hist[(key >> shift) & 255u], 1ull);
+            BinRun run{0, 0ull};
+            for (int i = first; i < vocab; i += step) {
+                const uint32_t key = order_key(tempered(row, i, seen, pen, temp));
+                if ((key & mask) == prefix) run_add(run, my_hist, (int)((key >> shift) & 255u), 1ull);
             }
-            __syncthreads();
-            if (tid == 0) {
-                unsigned long long above = 0;
-                int d = 255;
-                for (; d > 0; --d) {
-                    if (above + sh.hist[d] >= want) break;
-                    above += sh.hist[d];
-                }
-                sh.pick_digit = (uint32_t)d;
-                sh.pick_above = above;
-            }
-            __syncthreads();
+            run_flush(run, my_hist);
+            select_bin(sh, warp_hists, n_warps, 0ull, want);
             prefix |= sh.pick_digit << shift;
             mask |= 255u << shift;
             want -= sh.pick_above;
@@ -243,54 +351,40 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, int32_t* __restr
     float vmax = -INFINITY;
     if (tp < 1.0f || mp > 0.0f) {
         ArgMax a{-INFINITY, 0x7fffffff};
-        for (int i = tid; i < vocab; i += blockDim.x) {
-            const float v = tempered(row, i, seen, pen, 0.f, temp);
+        for (int i = first; i < vocab; i += step) {
+            const float v = tempered(row, i, seen, pen, temp);
             if (order_key(v) >= floor_key) a = better(a, ArgMax{v, i});
         }
-        vmax = block_argmax(a, sh.arg).v;
+        vmax = cluster_argmax(a, sh).v;
     }
 
     // ---- top-p: keep a token iff the mass of strictly larger values is below top_p
     if (tp < 1.0f) {
         const float FIX = 1099511627776.0f;  // 2^40: exp() in (0,1] as fixed point
         // total mass
-        for (int b = tid; b < 256; b += blockDim.x) sh.hist[b] = 0ull;
-        __syncthreads();
         unsigned long long local = 0;
-        for (int i = tid; i < vocab; i += blockDim.x) {
-            const float v = tempered(row, i, seen, pen, 0.f, temp);
+        for (int i = first; i < vocab; i += step) {
+            const float v = tempered(row, i, seen, pen, temp);
             if (order_key(v) >= floor_key) local += (unsigned long long)(expf(v - vmax) * FIX);
         }
-        atomicAdd(&sh.hist[0], local);
-        __syncthreads();
-        const unsigned long long total = sh.hist[0];
+        const unsigned long long total = cluster_sum(local, sh);
         const unsigned long long limit = (unsigned long long)((double)tp * (double)total);
         __syncthreads();
         uint32_t prefix = 0, mask = 0;
         unsigned long long above = 0;  // mass of values whose key exceeds every key under the prefix
         for (int shift = 24; shift >= 0; shift -= 8) {
-            for (int b = tid; b < 256; b += blockDim.x) sh.hist[b] = 0ull;
+            for (int b = tid; b < n_warps * 256; b += blockDim.x) warp_hists[b] = 0ull;
             __syncthreads();
-            for (int i = tid; i < vocab; i += blockDim.x) {
-                const float v = tempered(row, i, seen, pen, 0.f, temp);
+            BinRun run{0, 0ull};
+            for (int i = first; i < vocab; i += step) {
+                const float v = tempered(row, i, seen, pen, temp);
                 const uint32_t key = order_key(v);
                 if (key >= floor_key && (key & mask) == prefix)
-                    atomicAdd(&sh.hist[(key >> shift) & 255u], (unsigned long long)(expf(v - vmax) * FIX));
+                    run_add(run, my_hist, (int)((key >> shift) & 255u), (unsigned long long)(expf(v - vmax) * FIX));
             }
-            __syncthreads();
-            if (tid == 0) {
-                // lowest digit whose bin still starts below the limit
-                unsigned long long acc = above;
-                int d = 255;
-                for (; d > 0; --d) {
-                    const unsigned long long next = acc + sh.hist[d];
-                    if (next >= limit) break;
-                    acc = next;
-                }
-                sh.pick_digit = (uint32_t)d;
-                sh.pick_above = acc;
-            }
-            __syncthreads();
+            run_flush(run, my_hist);
+            // lowest digit whose bin still starts below the limit
+            select_bin(sh, warp_hists, n_warps, above, limit);
             prefix |= sh.pick_digit << shift;
             mask |= 255u << shift;
             above = sh.pick_above;
@@ -303,15 +397,25 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, int32_t* __restr
     float floor_val = -INFINITY;
     if (mp > 0.0f) floor_val = vmax + logf(mp);
 
-    // ---- Gumbel-max draw over what is left
+    // ---- Gumbel-max draw over what is left: one Philox call gives the noise of four consecutive tokens
     const uint64_t seed = (uint64_t)seeds[r], draw = (uint64_t)draws[r];
     ArgMax a{-INFINITY, 0x7fffffff};
-    for (int i = tid; i < vocab; i += blockDim.x) {
-        const float v = tempered(row, i, seen, pen, 0.f, temp);
-        if (order_key(v) >= floor_key && v >= floor_val) a = better(a, ArgMax{v + gumbel(seed, draw, i), i});
+    for (int i4 = first * 4; i4 < vocab; i4 += step * 4) {
+        uint32_t c[4] = {(uint32_t)(i4 >> 2), (uint32_t)draw, (uint32_t)(draw >> 32), 0x51195u};
+        philox4x32_10((uint32_t)seed, (uint32_t)(seed >> 32), c);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = i4 + e;
+            if (i >= vocab) break;
+            const float v = tempered(row, i, seen, pen, temp);
+            if (order_key(v) >= floor_key && v >= floor_val) {
+                const float u = ((float)(c[e] >> 8) + 0.5f) * (1.0f / 16777216.0f);  // in (0, 1), exact
+                a = better(a, ArgMax{v + (-logf(-logf(u))), i});
+            }
+        }
     }
-    a = block_argmax(a, sh.arg);
-    if (tid == 0) {
+    a = cluster_argmax(a, sh);
+    if (tid == 0 && rank == 0) {
         const int tok = a.i == 0x7fffffff ? 0 : a.i;
         out[r] = tok;
         if (seen_row) atomicOr(&seen_row[tok >> 5], 1u << (tok & 31));
@@ -324,7 +428,13 @@ extern "C" int ss_sample(const float* logits, int64_t stride, int32_t* out, cons
                          uint32_t* seen, int seen_words, const int32_t* slots, int rows, int vocab,
                          cudaStream_t stream) {
     if (rows <= 0) return 0;
-    ss_launch(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, stride, out, temperature, top_k, top_p,
+    constexpr int smem = (SAMPLE_THREADS / 32) * 256 * 8;  // a histogram per warp
+    static int configured = (int)cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (configured != 0) return configured;
+    // blocks per row: as many as fill the GPU once (two blocks of 1,024 threads fit on an SM), at most 8
+    int per_row = (2 * 148) / rows;
+    per_row = per_row >= 8 ? 8 : (per_row >= 4 ? 4 : (per_row >= 2 ? 2 : 1));
+    ss_launch_cluster_x(sample_kernel, dim3(rows * per_row), dim3(SAMPLE_THREADS), smem, stream, per_row, logits, stride, out, temperature, top_k, top_p,
                                                        min_p, penalty, seeds, draws, seen, seen_words,
                                                        slots, vocab);
     return SS_LAUNCH_CHECK();

@@ -63,16 +63,25 @@ class Sampler:
         if all(r.params.is_greedy for r in rows):
             return self.greedy(logits)
         m = len(rows)
-        floats = np.empty((4, m), dtype=np.float32)
-        ints = np.empty((2, m), dtype=np.int32)
-        longs = np.empty((2, m), dtype=np.int64)
-        for i, r in enumerate(rows):
-            p = r.params
-            floats[:, i] = (0.0 if p.is_greedy else p.temperature, p.top_p, p.min_p, p.repetition_penalty)
-            ints[:, i] = (p.top_k, r.slot if p.repetition_penalty != 1.0 else -1)
-            longs[:, i] = (np.int64(np.uint64(r.seed & 0xFFFFFFFFFFFFFFFF).astype(np.int64)), r.draw)
-        f = torch.from_numpy(floats).to(self.device, non_blocking=True)
-        i32 = torch.from_numpy(ints).to(self.device, non_blocking=True)
-        i64 = torch.from_numpy(longs).to(self.device, non_blocking=True)
+        # every row's parameters in one pinned buffer and one copy: [4 float32 | 2 int32 | 2 int64] x m
+        host = torch.empty(40 * m, dtype=torch.uint8, pin_memory=True)
+        raw = host.numpy()
+        floats = raw[: 16 * m].view(np.float32).reshape(4, m)
+        ints = raw[16 * m: 24 * m].view(np.int32).reshape(2, m)
+        longs = raw[24 * m:].view(np.int64).reshape(2, m)
+        params = [r.params for r in rows]
+        floats[0] = [0.0 if p.is_greedy else p.temperature for p in params]
+        floats[1] = [p.top_p for p in params]
+        floats[2] = [p.min_p for p in params]
+        floats[3] = [p.repetition_penalty for p in params]
+        ints[0] = [p.top_k for p in params]
+        ints[1] = [r.slot if r.params.repetition_penalty != 1.0 else -1 for r in rows]
+        longs[0] = [(r.seed & 0xFFFFFFFFFFFFFFFF) - (1 << 64) if (r.seed & 0x8000000000000000) else (r.seed & 0xFFFFFFFFFFFFFFFF)
+                    for r in rows]
+        longs[1] = [r.draw for r in rows]
+        dev = host.to(self.device, non_blocking=True)
+        f = dev[: 16 * m].view(torch.float32).view(4, m)
+        i32 = dev[16 * m: 24 * m].view(torch.int32).view(2, m)
+        i64 = dev[24 * m:].view(torch.int64).view(2, m)
         return ops.sample(logits, temperature=f[0], top_p=f[1], min_p=f[2], penalty=f[3], top_k=i32[0],
                           slots=i32[1], seeds=i64[0], draws=i64[1], seen=self.seen)
