@@ -203,7 +203,7 @@ def main() -> int:
         json.dump(dict(shape, architectures=["Qwen2ForCausalLM"], model_type="qwen2"), f)
     ctx_len, page = shape["max_position_embeddings"], 16
     max_batch = max(64, args.batch)
-    pages = max_batch * (args.prompt_len + args.steps + args.warmup + 64) // page + 4096 // page + 64
+    pages = max_batch * (args.prompt_len + args.steps + args.warmup + 2 * max_batch + 96) // page + 4096 // page + 64
     engine = LLMEngine(EngineConfig.for_model(
         folder, dtype="bfloat16", load_format="random", max_model_len=ctx_len,
         cache=CacheConfig(block_size=page, num_gpu_blocks=pages),
@@ -274,8 +274,10 @@ def main() -> int:
     # ---- end to end through the public engine calls: host tokens in, host tokens out, every step
     for j in range(args.batch):
         engine.add_request(Request(f"e{j}", None, rng.integers(0, vocab, args.prompt_len).tolist(),
-                                   SamplingParams(max_tokens=args.steps + args.warmup + 1, temperature=0.0,
-                                                  ignore_eos=True), float(j)))
+                                   # room for the steps during which later prompts are still being admitted: no
+                                   # request may finish (and no smaller batch bucket appear) inside the timed loop
+                                   SamplingParams(max_tokens=args.steps + args.warmup + 2 * args.batch + 16,
+                                                  temperature=0.0, ignore_eos=True), float(j)))
     while any(s.num_output_tokens == 0 for s in engine.scheduler.running) or engine.scheduler.waiting:
         engine.step()
     for _ in range(args.warmup):

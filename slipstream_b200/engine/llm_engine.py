@@ -143,6 +143,11 @@ class LLMEngine:
             yield seq.output_token_ids[emitted]
             emitted += 1
 
+    def warm_up(self, max_requests: int | None = None) -> int:
+        """Capture the decode graphs of all batch sizes up to ``max_requests`` (default ``max_num_seqs``) before
+        the first request, so that no request ever waits for a capture.  Returns the number captured."""
+        return self.runner.capture_decode_graphs(max_requests)
+
     def add_request(self, request: Request) -> Sequence:
         """Queue a request; ``step`` then advances everything queued by one engine step."""
         seq = self._make_sequence(request)

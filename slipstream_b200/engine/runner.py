@@ -27,7 +27,7 @@ from slipstream_b200.weights.loader import load_weights
 from slipstream_b200.weights.random_init import random_weights_on_device
 
 from .context import StepContext, StepEntry, StepInputError, build_context, plan_step, to_device
-from .graphs import DecodeGraph, bucket_for
+from .graphs import BUCKETS, DecodeGraph, bucket_for
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -123,6 +123,23 @@ class ModelRunner:
     def _graph_bucket(self, n_requests: int) -> int | None:
         bucket = bucket_for(n_requests) if self.use_cuda_graphs else None
         return bucket if bucket is not None and bucket <= max(self.max_num_seqs, 1) * 2 else None
+
+    def capture_decode_graphs(self, max_requests: int | None = None) -> int:
+        """Capture the decode graph of every batch bucket up to ``max_requests`` (default: the most requests
+        the cache manager admits) now, instead of at the first step that needs it: a capture takes tens of
+        milliseconds, during which every running request waits.  Returns how many graphs were captured."""
+        if not self.use_cuda_graphs:
+            return 0
+        limit = self.max_num_seqs if max_requests is None else max_requests
+        made = 0
+        for bucket in BUCKETS:
+            if self._graph_bucket(bucket) != bucket or bucket in self._graphs:
+                continue
+            self._graphs[bucket] = DecodeGraph(self, bucket)
+            made += 1
+            if bucket >= limit:
+                break
+        return made
 
     def can_run_ahead(self, n_requests: int) -> bool:
         """Whether a decode-only step of this many requests goes through a captured graph (the only kind of

@@ -296,3 +296,19 @@ def test_decode_steps_that_run_ahead_of_the_host_give_the_same_tokens(model_fold
     assert got == want and got_status == want_status
     assert want[1][-1] == stop and len(want[1]) <= 8 and all(t >= 0 for out in got for t in out)
     assert list(map(len, want)) == [25, len(want[1]), 9, 1, 9]
+
+
+def test_warm_up_captures_every_decode_graph_before_the_first_request(model_folders):
+    from slipstream_b200 import SamplingParams
+    from slipstream_b200.engine.llm_engine import Request
+    folder, config, page = model_folders["A"]
+    engine = make_engine(folder, page, dtype="bfloat16", max_num_seqs=6)
+    made = engine.warm_up()
+    assert made == len(engine.runner._graphs) >= 4  # buckets 1, 2, 4, 8 hold up to 6 requests
+    prompts = [random_tokens(config.vocab_size, n, 5 + n) for n in (4, 9, 2, 7, 5)]
+    params = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    outs = engine.generate_batch([Request(f"r{i}", None, p, params, float(i)) for i, p in enumerate(prompts)])
+    assert len(engine.runner._graphs) == made, "no graph was captured while requests ran"
+    cfg, weights = plain.read_model_folder(folder, torch.float64)
+    for prompt, out in zip(prompts, outs):
+        greedy_is_consistent(cfg, weights, prompt, out, slack=3e-2)
