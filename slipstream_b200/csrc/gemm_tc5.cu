@@ -270,10 +270,11 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (g.slices == 1 && g.swiglu) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 const float* xbuf = reinterpret_cast<const float*>(tiles);
-                const int ml = quarter * 32 + lane;
-                if (ml < 64)
-                    for (int c = 0; c < BN; ++c)
-                        store_swiglu(g, m0 + ml, n0 + c, xbuf[c * TC_BM + ml], xbuf[c * TC_BM + ml + 64]);
+                // all four warps: thread t takes gate/up pair t % 64 of the even (t < 64) or odd token columns
+                const int t = quarter * 32 + lane, ml = t & 63;
+                const int n_live = min(BN, g.N - n0);
+                for (int c = t >> 6; c < n_live; c += 2)
+                    store_swiglu(g, m0 + ml, n0 + c, xbuf[c * TC_BM + ml], xbuf[c * TC_BM + ml + 64]);
             }
             if (g.slices > 1 && !g.cluster) {
                 // the block that completes the tile last adds the slices, in slice order
