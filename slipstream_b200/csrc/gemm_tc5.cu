@@ -149,7 +149,9 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+    // swapped: (token tile, weight tile); else the row tiles of the activations run fastest, so that the blocks
+    // that are resident together share a weight tile and the weights are read from memory once
+    const int m0 = (g.swapped ? blockIdx.y : blockIdx.x) * TC_BM, n0 = (g.swapped ? blockIdx.x : blockIdx.y) * BN;
     const int k_iters_total = (g.K + TC_BK - 1) / TC_BK;
     const int per = (k_iters_total + g.slices - 1) / g.slices;
     const int k_begin = blockIdx.z * per, k_end = min(k_iters_total, k_begin + per);
@@ -446,6 +448,7 @@ extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int b
     g.M = M; g.N = N; g.K = K; g.ldc = ldc; g.slices = slices; g.swapped = swapped; g.out_f32 = out_f32;
     g.bias_f32 = bias_f32; g.swiglu = swiglu; g.cluster = cluster;
     dim3 grid((N + bn - 1) / bn, (M + TC_BM - 1) / TC_BM, slices);
+    if (!swapped) grid = dim3((M + TC_BM - 1) / TC_BM, (N + bn - 1) / bn, slices);
     switch (bn) {
         case 16: return launch<16, 4>(ma, mb, g, grid, stream);  // three blocks fit on an SM
         case 32: return launch<32, 4>(ma, mb, g, grid, stream);
