@@ -70,6 +70,8 @@ _ATTN_SIGNATURES = {
 }
 
 _GEMM_SIGNATURES = {
+    "ss_gemm_tc5_many": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
+                         c_int, c_int, c_void_p, c_void_p],
     "ss_gemm_tc5": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                     c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
@@ -653,6 +655,37 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
     return out
 
 
+def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+                      out_dtype: torch.dtype | None = None, swiglu: bool = False) -> torch.Tensor:
+    """``x @ weight.T + bias`` for many rows of ``x`` (prompt portions) on the tcgen05 tensor cores: a persistent
+    kernel, one block per SM, 128 x 256 output tiles, the accumulator double-buffered in tensor memory so that
+    the epilogue of a tile overlaps the products of the next.  ``swiglu``: the weight's rows alternate 64 gate
+    and 64 up features; the result is ``silu(gate) * up`` with features / 2 columns."""
+    _need(x, torch.bfloat16, "x")
+    _need(weight, torch.bfloat16, "weight")
+    tokens, k = x.shape
+    features = weight.shape[0]
+    if weight.shape[1] != k or k % 8 != 0:
+        raise KernelError("the tensor-core matrix product needs matching K, a multiple of 8")
+    out_dtype = out_dtype or torch.bfloat16
+    if swiglu and (features % 128 or out_dtype != torch.bfloat16 or (features // 2) % 8):
+        raise KernelError("the fused SwiGLU epilogue takes a multiple of 128 weight rows and writes bfloat16")
+    out = torch.empty((tokens, features // 2 if swiglu else features), dtype=out_dtype, device=x.device)
+    if tokens == 0:
+        return out
+    bias_f32 = 0
+    if bias is not None:
+        _need(bias, None, "bias")
+        bias_f32 = int(bias.dtype == torch.float32)
+        if bias.numel() != features or bias.dtype not in (torch.float32, torch.bfloat16):
+            raise KernelError("bias has the wrong size or dtype")
+    rc = gemm_library().ss_gemm_tc5_many(x.data_ptr(), weight.data_ptr(), _ptr(bias), bias_f32, out.data_ptr(), tokens,
+                                         features, k, k, k, out.shape[1], int(out_dtype == torch.float32), int(swiglu),
+                                         error_word(x.device).data_ptr(), _stream())
+    _check(rc, "gemm_tcgen05_many")
+    return out
+
+
 SMALL_BATCH = 64  # up to this many tokens a projection may stream its weights through the tcgen05 kernel
 STREAM_TILES = 148  # ... when its 128-row weight tiles are at least as many as the SMs (no K slices needed)
 CLUSTER_BATCH = 16  # ... or, up to this many tokens, whatever its size (K slices added inside a cluster)
@@ -713,5 +746,5 @@ def set_programmatic_launch(enabled: bool) -> None:
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "gemm_tcgen05", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "gemm_tcgen05", "gemm_tcgen05_many", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
            "attention_library"]

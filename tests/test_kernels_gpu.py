@@ -335,6 +335,34 @@ def test_tcgen05_matrix_product(tokens, features, k):
     ops().check_errors(torch.device(DEV))
 
 
+@pytest.mark.parametrize("tokens, features, k", [(2048, 4608, 3584), (300, 200, 136), (129, 1024, 64), (1000, 520, 2048)])
+def test_tcgen05_persistent_product_for_many_tokens(tokens, features, k):
+    torch.manual_seed(tokens)
+    x = torch.randn(tokens, k, device=DEV).bfloat16()
+    w = (torch.randn(features, k, device=DEV) * 0.05).bfloat16()
+    b = torch.randn(features, device=DEV).bfloat16()
+    ref = x.double() @ w.double().T
+    got = ops().gemm_tcgen05_many(x, w, None, torch.float32)
+    assert rel_err(got, ref) < 2e-5, "float32 output of bfloat16 inputs is exact up to the order of additions"
+    assert rel_err(ops().gemm_tcgen05_many(x, w, b), ref + b.double()) < 6e-3
+    assert rel_err(ops().gemm_tcgen05_many(x, w, b.float(), torch.float32), ref + b.double()) < 2e-5
+    ops().check_errors(torch.device(DEV))
+
+
+@pytest.mark.parametrize("tokens, inter, k, bias", [(2048, 18944, 3584, False), (70, 192, 136, True), (513, 640, 200, True)])
+def test_tcgen05_persistent_product_with_swiglu(tokens, inter, k, bias):
+    torch.manual_seed(inter)
+    x = torch.randn(tokens, k, device=DEV).bfloat16()
+    gate, up = ((torch.randn(inter, k, device=DEV) * 0.05).bfloat16() for _ in range(2))
+    bg, bu = ((torch.randn(inter, device=DEV) * 0.5).bfloat16() for _ in range(2))
+    mix = lambda a, b: torch.stack([a.reshape(inter // 64, 64, *a.shape[1:]), b.reshape(inter // 64, 64, *b.shape[1:])], 1).reshape(2 * inter, *a.shape[1:]).contiguous()
+    g = x.double() @ gate.double().T + (bg.double() if bias else 0)
+    u = x.double() @ up.double().T + (bu.double() if bias else 0)
+    got = ops().gemm_tcgen05_many(x, mix(gate, up), mix(bg, bu) if bias else None, swiglu=True)
+    assert got.shape == (tokens, inter) and rel_err(got, g * torch.sigmoid(g) * u) < 8e-3
+    ops().check_errors(torch.device(DEV))
+
+
 def test_tcgen05_split_k_is_deterministic_and_leaves_its_counters_clean():
     x = torch.randn(8, 18944, device=DEV).bfloat16()
     w = (torch.randn(3584, 18944, device=DEV) * 0.02).bfloat16()
