@@ -71,7 +71,7 @@ _ATTN_SIGNATURES = {
 
 _GEMM_SIGNATURES = {
     "ss_gemm_tc5_many": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
-                         c_int, c_int, c_void_p, c_void_p],
+                         c_int, c_int, c_int, c_void_p, c_void_p],
     "ss_gemm_tc5": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                     c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
@@ -656,11 +656,14 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
 
 
 def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
-                      out_dtype: torch.dtype | None = None, swiglu: bool = False) -> torch.Tensor:
+                      out_dtype: torch.dtype | None = None, swiglu: bool = False,
+                      tile_rows: int | None = None) -> torch.Tensor:
     """``x @ weight.T + bias`` for many rows of ``x`` (prompt portions) on the tcgen05 tensor cores: a persistent
-    kernel, one block per SM, 128 x 256 output tiles, the accumulator double-buffered in tensor memory so that
-    the epilogue of a tile overlaps the products of the next.  ``swiglu``: the weight's rows alternate 64 gate
-    and 64 up features; the result is ``silu(gate) * up`` with features / 2 columns."""
+    kernel, one block per SM.  ``tile_rows`` 128: 128 x 256 output tiles, the accumulator double-buffered in
+    tensor memory so that the epilogue of a tile overlaps the products of the next; 256: 256 x 256 tiles, two
+    products sharing every weight tile (the default when there are at least twice as many such tiles as SMs).
+    ``swiglu``: the weight's rows alternate 64 gate and 64 up features; the result is ``silu(gate) * up`` with
+    features / 2 columns."""
     _need(x, torch.bfloat16, "x")
     _need(weight, torch.bfloat16, "weight")
     tokens, k = x.shape
@@ -679,9 +682,11 @@ def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor 
         bias_f32 = int(bias.dtype == torch.float32)
         if bias.numel() != features or bias.dtype not in (torch.float32, torch.bfloat16):
             raise KernelError("bias has the wrong size or dtype")
+    if tile_rows is None:
+        tile_rows = 256 if ((tokens + 255) // 256) * ((features + 255) // 256) >= 2 * 148 else 128
     rc = gemm_library().ss_gemm_tc5_many(x.data_ptr(), weight.data_ptr(), _ptr(bias), bias_f32, out.data_ptr(), tokens,
                                          features, k, k, k, out.shape[1], int(out_dtype == torch.float32), int(swiglu),
-                                         error_word(x.device).data_ptr(), _stream())
+                                         tile_rows, error_word(x.device).data_ptr(), _stream())
     _check(rc, "gemm_tcgen05_many")
     return out
 
@@ -726,12 +731,24 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     return out
 
 
+def many_tokens_swiglu_fits(tokens: int, features: int) -> bool:
+    """Where the persistent tcgen05 kernel with its fused SwiGLU epilogue is at least as fast as the library
+    product followed by the SwiGLU kernel: enough 256 x 256 tiles to keep every SM busy for several rounds
+    (2,048 tokens x 37,888 features: 376 us against 382 us, and no [tokens, 2 I] intermediate).  A block of
+    this kernel cannot feed the tensor core faster than shared memory delivers both operands of a 128 x 256
+    product (about 1.3 PFLOP/s measured against the library's 1.6 with two-SM products), so without an epilogue
+    to fuse the library product stays."""
+    return ((tokens + 255) // 256) * ((features + 255) // 256) >= 4 * 148
+
+
 def gate_up_swiglu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, block: int) -> torch.Tensor:
     """``silu(x @ Wg.T + bg) * (x @ Wu.T + bu)`` where ``weight`` [2 I, K] holds gate and up rows alternating in
     runs of ``block``.  Small bfloat16 batches with runs of 64 do it in one kernel."""
-    if (x.dtype == torch.bfloat16 and block == 64 and weight.shape[0] % 128 == 0
-            and streams_weights(x.shape[0], weight.shape[0], x.shape[1])):
-        return gemm_tcgen05(x, weight, bias, swiglu=True)
+    if x.dtype == torch.bfloat16 and block == 64 and weight.shape[0] % 128 == 0 and x.shape[1] % 8 == 0:
+        if streams_weights(x.shape[0], weight.shape[0], x.shape[1]):
+            return gemm_tcgen05(x, weight, bias, swiglu=True)
+        if many_tokens_swiglu_fits(x.shape[0], weight.shape[0]):
+            return gemm_tcgen05_many(x, weight, bias, swiglu=True)
     return swiglu(linear(x, weight, bias), block=block)
 
 
@@ -746,5 +763,5 @@ def set_programmatic_launch(enabled: bool) -> None:
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "gemm_tcgen05", "gemm_tcgen05_many", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
            "attention_library"]
