@@ -76,7 +76,15 @@ class StepContext:
         cached = self._tiles.get(key)
         if cached is None:
             req, q0 = query_tiles_host(self.q_lens_host * group, rows)
-            both = torch.from_numpy(np.concatenate([req, q0])).to(self.device, non_blocking=True)
+            # through pinned memory: a copy from pageable memory would hold the host until every kernel queued
+            # before it has run, and the first layer of the step would be launched one kernel at a time
+            if self.device.type == "cuda":
+                staged = torch.empty(2 * req.size, dtype=torch.int32, pin_memory=True)
+                staged.numpy()[: req.size] = req
+                staged.numpy()[req.size:] = q0
+            else:
+                staged = torch.from_numpy(np.concatenate([req, q0]))
+            both = staged.to(self.device, non_blocking=True)
             cached = (both[: req.size], both[req.size:])
             self._tiles[key] = cached
         return cached
