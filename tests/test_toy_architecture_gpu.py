@@ -226,3 +226,189 @@ def test_toy_architecture_steps_like_its_plain_restatement(tmp_path, dtype):
         runner.check()
     finally:
         unregister_architecture("ToyMixForCausalLM")
+
+
+# =========================================================================== a second toy: other parts again
+# A feed-forward with routing (every token goes to the one expert its router picks) and another position
+# encoding (a learned table added to the stream; queries and keys are not rotated), again defined here and
+# registered without a change to the package.
+
+@dataclass(frozen=True)
+class RoutedConfig:
+    architecture: ClassVar[str] = "ToyRoutedForCausalLM"
+    vocab_size: int = 113
+    hidden_size: int = 48
+    num_hidden_layers: int = 2
+    max_position_embeddings: int = 160
+    torch_dtype: str = "float32"
+    eos_token_id: int | None = None
+    heads: int = 3
+    kv_heads: int = 3
+    head_dim: int = 16
+    experts: int = 4
+    inter: int = 40
+    eps: float = 1e-6
+
+    @classmethod
+    def from_dict(cls, data, generation=None):
+        return cls(**{k: v for k, v in data.items() if k in cls.__dataclass_fields__})
+
+    def to_dict(self):
+        return dict(asdict(self), architectures=[self.architecture])
+
+
+def define_routed():
+    from slipstream_b200.models.decoder import DecoderLM
+    from slipstream_b200.parts import (FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, LMHead, NoPositionEncoding,
+                                       PagedAttention, PositionEncoding, PreNormBlock, RMSNorm, TokenEmbedding, WeightSpec)
+    from slipstream_b200.registry import register_architecture, unregister_architecture
+
+    FEED_FORWARDS.unregister("top1_experts")
+    POSITION_ENCODINGS.unregister("learned_table")
+
+    @FEED_FORWARDS.register("top1_experts")
+    class Top1Experts(FeedForward):
+        """y = p_e * W2_e relu(W1_e x) for the expert e with the largest router logit; p = softmax(router)."""
+
+        def __init__(self, name, hidden, inter, experts):
+            self.name, self.hidden, self.inter, self.experts = name, hidden, inter, experts
+
+        def weight_specs(self):
+            n = self.name
+            return ([WeightSpec(f"{n}.router.weight", (self.experts, self.hidden), init=("normal", 1.0))] +
+                    [WeightSpec(f"{n}.experts.{e}.w1.weight", (self.inter, self.hidden), init=("normal", 0.3)) for e in range(self.experts)] +
+                    [WeightSpec(f"{n}.experts.{e}.w2.weight", (self.hidden, self.inter), init=("normal", 0.3)) for e in range(self.experts)])
+
+        def bind(self, weights, runtime):
+            super().bind(weights, runtime)
+            n = self.name
+            self.router = weights[f"{n}.router.weight"]
+            self.w1 = torch.stack([weights[f"{n}.experts.{e}.w1.weight"] for e in range(self.experts)])
+            self.w2 = torch.stack([weights[f"{n}.experts.{e}.w2.weight"] for e in range(self.experts)])
+
+        def forward(self, x, ctx):
+            logits = x.float() @ self.router.float().T          # router logits in float32
+            probs = torch.softmax(logits, -1)
+            pick = logits.argmax(-1)
+            out = torch.zeros_like(x)
+            for e in range(self.experts):                        # tokens of one expert together
+                rows = (pick == e).nonzero().flatten()
+                if rows.numel():
+                    h = torch.relu(x[rows] @ self.w1[e].T)
+                    out[rows] = ((h @ self.w2[e].T).float() * probs[rows, e, None]).to(x.dtype)
+            return out
+
+    @POSITION_ENCODINGS.register("learned_table")
+    class LearnedTable(PositionEncoding):
+        """One learned vector per position, added to the stream after the embedding."""
+
+        def __init__(self, name, positions, hidden):
+            self.name, self.positions, self.hidden = name, positions, hidden
+
+        def weight_specs(self):
+            return [WeightSpec(f"{self.name}.weight", (self.positions, self.hidden), init=("normal", 0.5))]
+
+        def bind(self, weights, runtime):
+            super().bind(weights, runtime)
+            self.table = weights[f"{self.name}.weight"]
+
+        def on_embedding(self, residual, ctx):
+            residual += self.table[ctx.positions.long()].float()
+
+    def build(c: RoutedConfig):
+        def block(i):
+            p = f"routed.layers.{i}"
+            attn = PagedAttention(f"{p}.attn", c.hidden_size, c.heads, c.kv_heads, c.head_dim, NoPositionEncoding(), qkv_bias=True)
+            return PreNormBlock(attn, Top1Experts(f"{p}.moe", c.hidden_size, c.inter, c.experts),
+                                RMSNorm(f"{p}.norm1", c.hidden_size, c.eps), RMSNorm(f"{p}.norm2", c.hidden_size, c.eps))
+
+        return DecoderLM(c, TokenEmbedding("routed.embed", c.vocab_size, c.hidden_size),
+                         [block(i) for i in range(c.num_hidden_layers)], RMSNorm("routed.norm", c.hidden_size, c.eps),
+                         LMHead("routed.head", c.vocab_size, c.hidden_size, None),
+                         position_encoding=LearnedTable("routed.positions", c.max_position_embeddings, c.hidden_size))
+
+    unregister_architecture("ToyRoutedForCausalLM")
+    register_architecture("ToyRoutedForCausalLM", RoutedConfig, build)
+
+
+def plain_routed(c, w, tokens):
+    T = len(tokens)
+    x = w["routed.embed.weight"][torch.as_tensor(tokens)] + w["routed.positions.weight"][:T]
+    picks = []
+    for i in range(c.num_hidden_layers):
+        p = f"routed.layers.{i}"
+        h = plain.rms_norm(x, w[f"{p}.norm1.weight"], c.eps)
+        q = (h @ w[f"{p}.attn.q_proj.weight"].T + w[f"{p}.attn.q_proj.bias"]).view(T, c.heads, c.head_dim)
+        k = (h @ w[f"{p}.attn.k_proj.weight"].T + w[f"{p}.attn.k_proj.bias"]).view(T, c.kv_heads, c.head_dim)
+        v = (h @ w[f"{p}.attn.v_proj.weight"].T + w[f"{p}.attn.v_proj.bias"]).view(T, c.kv_heads, c.head_dim)
+        s = torch.einsum("ihd,jhd->hij", q, k) * c.head_dim ** -0.5
+        s = s.masked_fill(~(torch.arange(T)[None, :] <= torch.arange(T)[:, None])[None], float("-inf"))
+        x = x + torch.einsum("hij,jhd->ihd", torch.softmax(s, -1), v).reshape(T, -1) @ w[f"{p}.attn.o_proj.weight"].T
+        h = plain.rms_norm(x, w[f"{p}.norm2.weight"], c.eps)
+        logits = h @ w[f"{p}.moe.router.weight"].T
+        probs, pick = torch.softmax(logits, -1), logits.argmax(-1)
+        picks.append((pick, logits))
+        y = torch.zeros_like(x)
+        for t in range(T):
+            e = int(pick[t])
+            y[t] = probs[t, e] * (torch.relu(h[t] @ w[f"{p}.moe.experts.{e}.w1.weight"].T) @ w[f"{p}.moe.experts.{e}.w2.weight"].T)
+        x = x + y
+    return plain.rms_norm(x, w["routed.norm.weight"], c.eps) @ w["routed.head.weight"].T, picks
+
+
+def test_toy_routing_and_a_learned_position_table(tmp_path):
+    """float32: the router's pick must not flip between the engine and the plain restatement, which a
+    reduced-precision path could not promise; every expert is used."""
+    from safetensors.torch import load_file
+    from slipstream_b200.engine.runner import ModelRunner, StepEntry
+    from slipstream_b200.registry import unregister_architecture
+    from slipstream_b200.weights.random_init import write_random_model
+
+    define_routed()
+    try:
+        c = RoutedConfig()
+        write_random_model(c, tmp_path, seed=11)
+        w = {k: v.clone().double() for k, v in load_file(str(tmp_path / "model.safetensors")).items()}
+        runner = ModelRunner(str(tmp_path), dtype="float32", page_size=8, num_pages=24, max_num_seqs=2)
+        assert not runner.use_cuda_graphs  # the toy parts did not declare themselves safe to capture
+        reqs = {"a": random_tokens(c.vocab_size, 70, 4), "b": random_tokens(c.vocab_size, 33, 5)}
+        want = {}
+        used = set()
+        for k, toks in reqs.items():
+            ref, picks = plain_routed(c, w, toks)
+            want[k] = ref.float()
+            for pick, logits in picks:
+                used |= set(pick.tolist())
+                top2 = logits.topk(2, -1).values
+                assert (top2[:, 0] - top2[:, 1]).min() > 1e-4, "a router tie would make the comparison meaningless"
+        assert used == set(range(c.experts))
+
+        def check(rows, what):
+            for k, ref in want.items():
+                err = (torch.cat(rows[k]) - ref).abs().max()
+                assert err <= 3e-5 * ref.abs().max(), (what, k, err.item())
+
+        rows = {}
+        for k, toks in reqs.items():
+            rows[k] = [runner.step([StepEntry(k, toks, list(range(len(toks))))]).cpu()]
+            runner.release(k)
+        check(rows, "whole")
+        # both live: portions of one beside single tokens of the other
+        rows, at = {k: [] for k in reqs}, {k: 0 for k in reqs}
+        sizes = {"a": [30, 1, 1, 1, 2, 35], "b": [1, 1, 20, 1, 1, 9]}
+        for step in range(6):
+            entries = []
+            for k in reqs:
+                take = sizes[k][step]
+                entries.append(StepEntry(k, reqs[k][at[k]: at[k] + take], list(range(take))))
+                at[k] += take
+            out = runner.step(entries).cpu()
+            i = 0
+            for e in entries:
+                rows[e.request_id].append(out[i: i + len(e.tokens)])
+                i += len(e.tokens)
+        assert all(at[k] == len(reqs[k]) for k in reqs)
+        check(rows, "portions")
+        runner.check()
+    finally:
+        unregister_architecture("ToyRoutedForCausalLM")
