@@ -97,6 +97,14 @@ def test_rope_and_cache(dtype, n_q, n_kv, d, rot, page):
     ops().check_errors(torch.device(DEV))
 
 
+def test_gather_tokens_takes_only_the_rows_that_name_a_source():
+    ids = torch.tensor([5, 6, 7, 8, 9, 10], dtype=torch.int32, device=DEV)
+    src = torch.tensor([-1, 2, -1, 0, 1, -1], dtype=torch.int32, device=DEV)
+    pending = torch.tensor([100, 200, 300], dtype=torch.int32, device=DEV)
+    ops().gather_tokens(ids, src, pending)
+    assert ids.tolist() == [5, 300, 7, 100, 200, 10]
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu(dtype):
     x = (torch.randn(13, 2 * 1234, device=DEV) * 3).to(dtype)
