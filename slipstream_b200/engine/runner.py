@@ -26,7 +26,7 @@ from slipstream_b200.registry import load_config
 from slipstream_b200.weights.loader import load_weights
 from slipstream_b200.weights.random_init import random_weights_on_device
 
-from .context import StepContext, StepEntry, StepInputError, build_context, plan_step, to_device
+from .context import StepContext, StepEntry, StepInputError, plan_step, to_device
 from .graphs import BUCKETS, DecodeGraph, bucket_for
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
