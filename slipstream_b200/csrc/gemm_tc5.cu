@@ -722,6 +722,199 @@ gemm_tc5_many256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     }
 }
 
+// ---------------------------------------------------------------- many tokens, two SMs per product
+//
+// The same persistent scheme with tcgen05.mma.cta_group::2: the two blocks of a cluster compute one 256 x 256
+// tile.  Block r of the pair loads rows r * 128 .. of the A tile and rows r * 128 .. of the B tile (half of
+// each); the leader (block 0) issues the products, which read A and B out of both blocks' shared memory and
+// leave rows r * 128 .. of the result in block r's tensor memory.  A block thus fetches 32 KB per 64-wide K step
+// instead of 48 KB (six stages instead of four) and feeds the tensor core half of B.
+//   full[s]      in the leader: one arrival (the leader's producer, with the bytes of both blocks); the other
+//                block's copies complete their bytes on it too (cp.async.bulk.tensor .cta_group::2);
+//   empty[s]     in each block: tcgen05.commit with multicast to both;
+//   acc_full[b]  in each block: tcgen05.commit with multicast to both;
+//   acc_empty[b] in the leader: the eight epilogue warps of both blocks arrive.
+#define PR_STAGES 6
+
+__device__ __forceinline__ uint32_t leader_addr(const void* p) { return s_addr(p) & 0xFEFFFFFFu; }  // same offset in block 0 of the pair
+
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(s_addr(dst)), "l"(map), "r"(leader_addr(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {  // arrives at `bar` in both blocks of the pair
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(s_addr(bar)), "h"((unsigned short)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(leader_addr(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const ManyArgs g) {
+    constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = TC_BM * TC_BK * 2, STAGES = PR_STAGES;  // this block's halves
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * (A_BYTES + B_BYTES));
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)cluster_rank();  // 0: the leader
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int n_m = (g.M + 2 * TC_BM - 1) / (2 * TC_BM), n_n = (g.N + MT_BN - 1) / MT_BN, n_tiles = n_m * n_n;
+    const int k_iters = (g.K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 8); }
+        *gave_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // the same warp of both blocks allocates all 512 columns of the pair
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_slot)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    cluster_sync_all();  // both blocks' barriers exist before either signals the other's
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    pdl_wait();
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer (both blocks): this block's half of A and of B; bytes are counted on the leader's barrier
+        int it = 0;
+        bool ok = true;
+        for (int t = pair; t < n_tiles && ok; t += n_pairs) {
+            const int m0 = (t % n_m) * 2 * TC_BM + rank * TC_BM, n0 = (t / n_m) * MT_BN + rank * TC_BM;
+            for (int k = 0; k < k_iters; ++k, ++it) {
+                const int s = it % STAGES;
+                if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, gave_up)) { ok = false; break; }
+                if (rank == 0) mbar_expect_tx(&full[s], 2 * (A_BYTES + B_BYTES));
+                unsigned char* a_tile = tiles + s * (A_BYTES + B_BYTES);
+                tma_load_2d_pair(a_tile, &map_a, k * TC_BK, m0, &full[s]);
+                tma_load_2d_pair(a_tile + A_BYTES, &map_b, k * TC_BK, n0, &full[s]);
+            }
+        }
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ---- MMA lane of the leader: M = 256 over the pair, N = 256
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT_BN >> 3) << 17) | ((uint32_t)((2 * TC_BM) >> 4) << 24);
+        int it = 0, j = 0;
+        bool ok = true;
+        for (int t = pair; t < n_tiles && ok; t += n_pairs, ++j) {
+            const int buf = j & 1;
+            if (j >= 2 && !mbar_wait(&acc_empty[buf], ((j >> 1) - 1) & 1, gave_up)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int k = 0; k < k_iters; ++k, ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(&full[s], (it / STAGES) & 1, gave_up)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                unsigned char* a_tile = tiles + s * (A_BYTES + B_BYTES);
+                const uint64_t a_desc = smem_desc(a_tile), b_desc = smem_desc(a_tile + A_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; ++kk)
+                    umma_f16_pair(tmem + buf * MT_BN, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, (k | kk) != 0);
+                umma_commit_pair(&empty[s]);
+            }
+            umma_commit_pair(&acc_full[buf]);
+        }
+    } else if (warp >= 2) {
+        // ---- epilogue (both blocks): this block's 128 rows of the tile
+        const int quarter = warp & 3;
+        int j = 0;
+        bool ok = true;
+        for (int t = pair; t < n_tiles && ok; t += n_pairs, ++j) {
+            const int buf = j & 1;
+            const int m0 = (t % n_m) * 2 * TC_BM + rank * TC_BM, n0 = (t / n_m) * MT_BN;
+            const int m = m0 + quarter * 32 + lane;
+            ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (j >> 1) & 1, gave_up));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t acc = tmem + ((uint32_t)(quarter * 32) << 16) + buf * MT_BN;
+            if (!g.swiglu) {
+#pragma unroll 1
+                for (int c = 0; c < MT_BN; c += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(acc + c, r);
+                    if (m >= g.M || n0 + c >= g.N) continue;
+                    if (g.bias) {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) {
+                            const int f = n0 + c + e;
+                            if (f < g.N) r[e] = __float_as_uint(__uint_as_float(r[e]) + bias_many(g, f));
+                        }
+                    }
+                    if (!g.out_f32 && n0 + c + 16 <= g.N && (g.ldc % 8 == 0)) {
+                        uint32_t packed[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
+                            packed[e] = *reinterpret_cast<uint32_t*>(&v);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>((bf16*)g.C + (int64_t)m * g.ldc + n0 + c);
+                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    } else {
+                        for (int e = 0; e < 16 && n0 + c + e < g.N; ++e) {
+                            const int64_t at = (int64_t)m * g.ldc + n0 + c + e;
+                            if (g.out_f32) ((float*)g.C)[at] = __uint_as_float(r[e]);
+                            else ((bf16*)g.C)[at] = __float2bfloat16_rn(__uint_as_float(r[e]));
+                        }
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < MT_BN / 2; c += 16) {
+                    const int gc = (c / 64) * 128 + (c % 64);
+                    uint32_t gr[16], ur[16];
+                    tmem_ld16(acc + gc, gr);
+                    tmem_ld16(acc + gc + 64, ur);
+                    const int f0 = (n0 / 2) + c;
+                    if (m >= g.M || n0 + gc + 64 >= g.N) continue;
+                    uint32_t packed[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        float v0 = __uint_as_float(gr[2 * e]), v1 = __uint_as_float(gr[2 * e + 1]);
+                        float u0 = __uint_as_float(ur[2 * e]), u1 = __uint_as_float(ur[2 * e + 1]);
+                        if (g.bias) {
+                            v0 += bias_many(g, n0 + gc + 2 * e); v1 += bias_many(g, n0 + gc + 2 * e + 1);
+                            u0 += bias_many(g, n0 + gc + 64 + 2 * e); u1 += bias_many(g, n0 + gc + 64 + 2 * e + 1);
+                        }
+                        __nv_bfloat162 v = __floats2bfloat162_rn(silu_mul<true>(v0, u0), silu_mul<true>(v1, u1));
+                        packed[e] = *reinterpret_cast<uint32_t*>(&v);
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>((bf16*)g.C + (int64_t)m * g.ldc + f0);
+                    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(&acc_empty[buf]);
+        }
+    }
+    if (*gave_up && threadIdx.x == 0) atomicOr(g.err, SS_ERR_WAIT_LIMIT);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    cluster_sync_all();  // neither block leaves (or frees tensor memory) while the other may still signal it
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    }
+}
+
 // ---------------------------------------------------------------- host side
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -813,8 +1006,32 @@ extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int b
 extern "C" int ss_gemm_tc5_many(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
                                 int64_t lda, int64_t ldb, int64_t ldc, int out_f32, int swiglu, int tile_rows, int* err,
                                 cudaStream_t stream) {
-    if (tile_rows != 128 && tile_rows != 256) return -2006;
+    if (tile_rows != 128 && tile_rows != 256 && tile_rows != 512) return -2006;
     const bool big = tile_rows == 256;
+    if (tile_rows == 512) {  // 256 x 256 tiles computed by pairs of blocks (tcgen05.mma.cta_group::2)
+        CUtensorMap ma, mb;
+        int rc = make_map(&ma, A, M, K, lda, TC_BM);
+        if (rc) return rc;
+        rc = make_map(&mb, B, N, K, ldb, TC_BM);  // a block loads 128 rows of B
+        if (rc) return rc;
+        ManyArgs g;
+        g.C = C; g.bias = bias; g.err = err; g.M = M; g.N = N; g.K = K; g.ldc = ldc; g.out_f32 = out_f32;
+        g.bias_f32 = bias_f32; g.swiglu = swiglu;
+        constexpr int smem_pair = PR_STAGES * (2 * TC_BM * TC_BK * 2) + 1024 + 256;
+        static int configured_pair = (int)cudaFuncSetAttribute(gemm_tc5_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pair);
+        if (configured_pair != 0) return configured_pair;
+        int n_sms = 148;
+        {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+        }
+        const int tiles2 = ((M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((N + MT_BN - 1) / MT_BN);
+        int pairs = n_sms / 2;
+        if (tiles2 < pairs) pairs = tiles2;
+        ss_launch_cluster_x(gemm_tc5_pair_kernel, dim3(2 * pairs), dim3(TC_THREADS), smem_pair, stream, 2, ma, mb, g);
+        return SS_LAUNCH_CHECK();
+    }
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return -2003;
     if (((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2004;

@@ -664,7 +664,9 @@ def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor 
     """``x @ weight.T + bias`` for many rows of ``x`` (prompt portions) on the tcgen05 tensor cores: a persistent
     kernel, one block per SM.  ``tile_rows`` 128: 128 x 256 output tiles, the accumulator double-buffered in
     tensor memory so that the epilogue of a tile overlaps the products of the next; 256: 256 x 256 tiles, two
-    products sharing every weight tile (the default when there are at least twice as many such tiles as SMs).
+    products sharing every weight tile; 512: 256 x 256 tiles computed by pairs of SMs (``tcgen05.mma.cta_group::2``:
+    each block of a pair loads half of A and half of B), accumulator double-buffered, the fastest of the three
+    where there are many tiles (the default when there are at least twice as many tiles as SMs).
     ``swiglu``: the weight's rows alternate 64 gate and 64 up features; the result is ``silu(gate) * up`` with
     features / 2 columns."""
     _need(x, torch.bfloat16, "x")
@@ -686,7 +688,7 @@ def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor 
         if bias.numel() != features or bias.dtype not in (torch.float32, torch.bfloat16):
             raise KernelError("bias has the wrong size or dtype")
     if tile_rows is None:
-        tile_rows = 256 if ((tokens + 255) // 256) * ((features + 255) // 256) >= 2 * 148 else 128
+        tile_rows = 512 if ((tokens + 255) // 256) * ((features + 255) // 256) >= 2 * 148 else 128
     rc = gemm_library().ss_gemm_tc5_many(x.data_ptr(), weight.data_ptr(), _ptr(bias), bias_f32, out.data_ptr(), tokens,
                                          features, k, k, k, out.shape[1], int(out_dtype == torch.float32), int(swiglu),
                                          tile_rows, error_word(x.device).data_ptr(), _stream())
