@@ -17,6 +17,10 @@
 // shared memory, and after a cluster barrier block r adds, in slice order, the token columns r, r + slices, ...
 // out of the shared memory of all blocks of the cluster.  No scratch, no counters, no trip through global memory.
 //
+// Many tokens (prompt portions) have kernels of their own further down: persistent blocks that walk over output
+// tiles with the accumulator double-buffered in tensor memory, in a one-SM form and in a two-SM form
+// (tcgen05.mma.cta_group::2 over the two blocks of a cluster), both with an optional fused SwiGLU epilogue.
+//
 // Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the kernel sets SS_ERR_WAIT_LIMIT in the
 // error word, stops waiting everywhere, frees its tensor memory and returns.
 //
