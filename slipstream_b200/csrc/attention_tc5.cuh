@@ -6,9 +6,9 @@
 //   warp 0             producer: TMA loads of the Q tile and, per 64-key tile, of the K and V pages (one box
 //                      per page and 64-column half, 128-byte swizzle; each box issued by a lane of its own)
 //                      into a three-stage ring of K tiles and a two-stage ring of V tiles;
-//   warp 1 (one lane)  MMA issuer: S = Q K^T (M 128, N 64) into one of two S buffers in tensor memory,
-//                      then O += P V (M 128, N = head size, P read from tensor memory, V MN-major from
-//                      shared memory) into the O columns;
+//   warp 1 (one lane)  S issuer: S = Q K^T (M 128, N 64) into one of two S buffers in tensor memory;
+//   warp 7 (one lane)  PV issuer: O += P V (M 128, N = head size, P read from tensor memory, V MN-major
+//                      from shared memory) into the O columns;
 //   warps 2..5         softmax: one thread per row reads its S row with tcgen05.ld, scales, masks the
 //                      diagonal tile, keeps a running maximum and sum in float32, writes P (bfloat16, two
 //                      per column) with tcgen05.st over the first half of the S buffer it came from, and
@@ -23,7 +23,7 @@
 
 #include "common.cuh"
 
-#define FA_THREADS 192
+#define FA_THREADS 256  // K producer, S issuer, four softmax warps, V producer, PV issuer
 #define FA_BN 64
 #define FA_KS 3  // stages of K: a K tile is asked for two S products ahead, so that the MMA lane never waits for it
 #define FA_WAIT_LIMIT (1u << 20)
@@ -199,12 +199,14 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 0) {
-        // ---------------- producer: the whole warp.  Issuing a bulk tensor copy costs the issuing thread about a
-        // hundred cycles, and a tile is 16 of them (a page and a 64-element half of the head each, keys and
-        // values): from one thread they took 1,800 cycles a tile and bounded the kernel.  Here lane
-        // p * HALVES + h issues the copies of page p, half h, and reads that page's block-table entry itself.
-        if (lane == 0) {
+    if (warp == 0 || warp == 6) {
+        // ---------------- producers: warp 0 the Q tile and the K tiles, warp 6 the V tiles, each a whole warp.
+        // Issuing a bulk tensor copy costs the issuing thread about a hundred cycles, and a tile is 16 of them
+        // (a page and a 64-element half of the head each, keys and values): from one thread they took 1,800
+        // cycles a tile and bounded the kernel.  Here lane p * HALVES + h issues the copy of page p, half h, and
+        // reads that page's block-table entry itself; keys and values go out side by side from two warps.
+        const bool keys = warp == 0;
+        if (keys && lane == 0) {
             mbar_expect_tx(q_full, (uint32_t)(TOK * G * 128 * HALVES));
             for (int h = 0; h < HALVES; ++h)
                 tma_load_3d(Qs + h * HALF_Q, &map_q, h * 64, kvh * G, qs + tok0, q_full);
@@ -222,67 +224,81 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         int32_t next_entry = entry(0);
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
-            const int st = j & 1, kst = j % FA_KS;
-            const uint32_t par = ((j >> 1) & 1) ^ 1, kpar = ((j / FA_KS) & 1) ^ 1;
             int64_t page = next_entry;
             if (j + 1 < n_tiles) next_entry = entry(j + 1);  // in flight while this tile is issued
             if (page >= a.num_pages) { atomicOr(a.err, SS_ERR_PAGE_RANGE); page = -1; }
             if (page < 0) page = spare;
-            // keys
-            ok = __all_sync(0xffffffffu, mbar_wait(&k_empty[kst], kpar, gave_up));
-            if (!ok) break;
-            if (lane == 0) mbar_expect_tx(&k_full[kst], KV_BYTES);
-            __syncwarp();
-            if (mine)
-                tma_load_3d(Ks + kst * KV_BYTES + h * HALF_KV + p * ps * 128, &map_kv, h * 64, 0,
-                            (int)((page * 2 + 0) * a.n_kv + kvh), &k_full[kst]);
-            // values
-            ok = __all_sync(0xffffffffu, mbar_wait(&v_empty[st], par, gave_up));
-            if (!ok) break;
-            if (lane == 0) mbar_expect_tx(&v_full[st], KV_BYTES);
-            __syncwarp();
-            if (mine)
-                tma_load_3d(Vs + st * KV_BYTES + h * HALF_KV + p * ps * 128, &map_kv, h * 64, 0,
-                            (int)((page * 2 + 1) * a.n_kv + kvh), &v_full[st]);
+            if (keys) {
+                const int kst = j % FA_KS;
+                ok = __all_sync(0xffffffffu, mbar_wait(&k_empty[kst], ((j / FA_KS) & 1) ^ 1, gave_up));
+                if (!ok) break;
+                if (lane == 0) mbar_expect_tx(&k_full[kst], KV_BYTES);
+                __syncwarp();
+                if (mine)
+                    tma_load_3d(Ks + kst * KV_BYTES + h * HALF_KV + p * ps * 128, &map_kv, h * 64, 0,
+                                (int)((page * 2 + 0) * a.n_kv + kvh), &k_full[kst]);
+            } else {
+                const int st = j & 1;
+                ok = __all_sync(0xffffffffu, mbar_wait(&v_empty[st], ((j >> 1) & 1) ^ 1, gave_up));
+                if (!ok) break;
+                if (lane == 0) mbar_expect_tx(&v_full[st], KV_BYTES);
+                __syncwarp();
+                if (mine)
+                    tma_load_3d(Vs + st * KV_BYTES + h * HALF_KV + p * ps * 128, &map_kv, h * 64, 0,
+                                (int)((page * 2 + 1) * a.n_kv + kvh), &v_full[st]);
+            }
         }
     } else if (warp == 1 && lane == 0) {
-        // ---------------- MMA issuer
-        // instruction descriptors: D float32, A and B bfloat16, M = 128; S: N = 64, both K-major; PV: N = D, B MN-major
+        // ---------------- S issuer: S(j) = Q K(j)^T into S buffer j % 2.  The products of a tile are issued by two
+        // lanes of two warps (this one, and the PV issuer below): a single lane needed about 2,200 cycles per
+        // tile for its three barrier waits, twelve tcgen05.mma and four commits, one after the other, and that,
+        // not the tensor core (busy a quarter of the time), bounded the kernel.
+        // instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = 64
         constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FA_BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-        constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-        bool ok = mbar_wait(q_full, 0, gave_up);
-        auto issue_s = [&](int j) {
-            const int st = j & 1, kst = j % FA_KS;
-            // the S buffer of this parity is free: the softmax of two tiles back has read it (p_ready was seen)
-            if (!mbar_wait(&k_full[kst], (j / FA_KS) & 1, gave_up)) return false;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint64_t q_desc[HALVES], k_desc[FA_KS][HALVES];
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-                const uint64_t ad = desc_k_major(Qs + (kk / 4) * HALF_Q) + (uint64_t)((kk % 4) * 2);
-                const uint64_t bd = desc_k_major(Ks + kst * KV_BYTES + (kk / 4) * HALF_KV) + (uint64_t)((kk % 4) * 2);
-                umma(tmem + st * FA_BN, ad, bd, idesc_s, kk != 0);
-            }
+        for (int h = 0; h < HALVES; ++h) {
+            q_desc[h] = desc_k_major(Qs + h * HALF_Q);
+#pragma unroll
+            for (int s = 0; s < FA_KS; ++s) k_desc[s][h] = desc_k_major(Ks + s * KV_BYTES + h * HALF_KV);
+        }
+        bool ok = mbar_wait(q_full, 0, gave_up);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int st = j & 1, kst = j % FA_KS;
+            // the S buffer is free once the PV product of two tiles back, which read P out of it, is complete
+            if (j >= 2) ok = mbar_wait(&pv_done[st], ((j - 2) >> 1) & 1, gave_up);
+            ok = ok && mbar_wait(&k_full[kst], (j / FA_KS) & 1, gave_up);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint64_t kd[HALVES];
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) kd[h] = kst == 0 ? k_desc[0][h] : (kst == 1 ? k_desc[1][h] : k_desc[2][h]);
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk)
+                umma(tmem + st * FA_BN, q_desc[kk / 4] + (uint64_t)((kk % 4) * 2), kd[kk / 4] + (uint64_t)((kk % 4) * 2), idesc_s, kk != 0);
             umma_commit(&s_ready[st]);
             umma_commit(&k_empty[kst]);
-            return true;
-        };
-        if (ok) ok = issue_s(0);
-        if (ok && n_tiles > 1) ok = issue_s(1);
+        }
+    } else if (warp == 7 && lane == 0) {
+        // ---------------- PV issuer: O += P(j) V(j), P read from tensor memory, V MN-major from shared memory
+        constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        uint64_t v_desc[2];
+#pragma unroll
+        for (int s = 0; s < 2; ++s) v_desc[s] = desc_mn_major(Vs + s * KV_BYTES, HALF_KV);
+        bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int st = j & 1;
             ok = mbar_wait(&p_ready[st], (j >> 1) & 1, gave_up) && mbar_wait(&v_full[st], (j >> 1) & 1, gave_up);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t vd = st == 0 ? v_desc[0] : v_desc[1];
 #pragma unroll
-            for (int kk = 0; kk < FA_BN / 16; ++kk) {  // 16 keys per instruction: 8 columns of P
-                const uint64_t bd = desc_mn_major(Vs + st * KV_BYTES + kk * 16 * 128, HALF_KV);
-                umma_a_tmem(tmem + 128, tmem + st * FA_BN + kk * 8, bd, idesc_pv, (j | kk) != 0);
-            }
+            for (int kk = 0; kk < FA_BN / 16; ++kk)  // 16 keys per instruction: 8 columns of P, 16 rows (2 KB) of V
+                umma_a_tmem(tmem + 128, tmem + st * FA_BN + kk * 8, vd + (uint64_t)(kk * (16 * 128 / 16)), idesc_pv, (j | kk) != 0);
             umma_commit(&pv_done[st]);
             umma_commit(&v_empty[st]);
-            if (j + 2 < n_tiles) ok = issue_s(j + 2);
         }
-    } else if (warp >= 2) {
+    } else if (warp >= 2 && warp < 6) {
         // ---------------- softmax: one thread per row
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
