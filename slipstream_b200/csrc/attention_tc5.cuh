@@ -3,12 +3,14 @@
 //
 // A block takes up to 128 "rows" of one (request, kv head): TOK = 128 / G consecutive query tokens times the
 // G heads of the kv group, token-major, so the group shares every key/value tile.  Roles:
-//   warp 0             producer: TMA loads of the Q tile and, per 64-key tile, of the K and V pages (one box
-//                      per page and 64-column half, 128-byte swizzle; each box issued by a lane of its own)
-//                      into a three-stage ring of K tiles and a two-stage ring of V tiles;
-//   warp 1 (one lane)  S issuer: S = Q K^T (M 128, N 64) into one of two S buffers in tensor memory;
-//   warp 7 (one lane)  PV issuer: O += P V (M 128, N = head size, P read from tensor memory, V MN-major
-//                      from shared memory) into the O columns;
+//   warps 0 and 6      producers: TMA loads of the Q tile and, per 64-key tile, of the K pages (warp 0) and
+//                      the V pages (warp 6), one box per page and 64-column half, 128-byte swizzle, each box
+//                      issued by a lane of its own, into a three-stage ring of K tiles and a two-stage ring
+//                      of V tiles;
+//   warp 1             S issuer (an elected lane): S = Q K^T (M 128, N 64) into one of two S buffers in
+//                      tensor memory;
+//   warp 7             PV issuer (an elected lane): O += P V (M 128, N = head size, P read from tensor
+//                      memory, V MN-major from shared memory) into the O columns;
 //   warps 2..5         softmax: one thread per row reads its S row with tcgen05.ld, scales, masks the
 //                      diagonal tile, keeps a running maximum and sum in float32, writes P (bfloat16, two
 //                      per column) with tcgen05.st over the first half of the S buffer it came from, and
@@ -25,7 +27,7 @@
 
 #define FA_THREADS 256  // K producer, S issuer, four softmax warps, V producer, PV issuer
 #define FA_BN 64
-#define FA_KS 3  // stages of K: a K tile is asked for two S products ahead, so that the MMA lane never waits for it
+#define FA_KS 3  // stages of K: a K tile is asked for two S products ahead, so that the S issuer never waits for it
 #define FA_WAIT_LIMIT (1u << 20)
 
 namespace fa {
@@ -53,6 +55,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
     *gave_up = 1;
     return false;
+}
+// True in exactly one lane of a converged warp.  Code under it is known to the compiler to run in one lane, which
+// lets it keep the operands of tcgen05.mma in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
     asm volatile(
@@ -248,11 +257,13 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                                 (int)((page * 2 + 1) * a.n_kv + kvh), &v_full[st]);
             }
         }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
         // ---------------- S issuer: S(j) = Q K(j)^T into S buffer j % 2.  The products of a tile are issued by two
-        // lanes of two warps (this one, and the PV issuer below): a single lane needed about 2,200 cycles per
-        // tile for its three barrier waits, twelve tcgen05.mma and four commits, one after the other, and that,
-        // not the tensor core (busy a quarter of the time), bounded the kernel.
+        // warps (this one, and the PV issuer below): one lane needed about 2,200 cycles per tile for its three
+        // barrier waits, twelve tcgen05.mma and four commits, one after the other, and that, not the tensor core
+        // (busy a quarter of the time), bounded the kernel.  The whole warp runs the loop and elects the issuing
+        // lane around the instructions: under `lane == 0` alone the eight products took 870 cycles to issue,
+        // under elect.sync 350.
         // instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = 64
         constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FA_BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
         uint64_t q_desc[HALVES], k_desc[FA_KS][HALVES];
@@ -262,24 +273,28 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
             for (int s = 0; s < FA_KS; ++s) k_desc[s][h] = desc_k_major(Ks + s * KV_BYTES + h * HALF_KV);
         }
-        bool ok = mbar_wait(q_full, 0, gave_up);
+        bool ok = __all_sync(0xffffffffu, mbar_wait(q_full, 0, gave_up));
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int st = j & 1, kst = j % FA_KS;
+            ok = mbar_wait(&k_full[kst], (j / FA_KS) & 1, gave_up);
             // the S buffer is free once the PV product of two tiles back, which read P out of it, is complete
-            if (j >= 2) ok = mbar_wait(&pv_done[st], ((j - 2) >> 1) & 1, gave_up);
-            ok = ok && mbar_wait(&k_full[kst], (j / FA_KS) & 1, gave_up);
+            if (j >= 2) ok = ok && mbar_wait(&pv_done[st], ((j - 2) >> 1) & 1, gave_up);
+            ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint64_t kd[HALVES];
 #pragma unroll
             for (int h = 0; h < HALVES; ++h) kd[h] = kst == 0 ? k_desc[0][h] : (kst == 1 ? k_desc[1][h] : k_desc[2][h]);
+            if (elect_one()) {
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk)
-                umma(tmem + st * FA_BN, q_desc[kk / 4] + (uint64_t)((kk % 4) * 2), kd[kk / 4] + (uint64_t)((kk % 4) * 2), idesc_s, kk != 0);
-            umma_commit(&s_ready[st]);
-            umma_commit(&k_empty[kst]);
+                for (int kk = 0; kk < D / 16; ++kk)
+                    umma(tmem + st * FA_BN, q_desc[kk / 4] + (uint64_t)((kk % 4) * 2), kd[kk / 4] + (uint64_t)((kk % 4) * 2), idesc_s, kk != 0);
+                umma_commit(&s_ready[st]);
+                umma_commit(&k_empty[kst]);
+            }
+            __syncwarp();
         }
-    } else if (warp == 7 && lane == 0) {
+    } else if (warp == 7) {
         // ---------------- PV issuer: O += P(j) V(j), P read from tensor memory, V MN-major from shared memory
         constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
         uint64_t v_desc[2];
@@ -288,15 +303,19 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int st = j & 1;
-            ok = mbar_wait(&p_ready[st], (j >> 1) & 1, gave_up) && mbar_wait(&v_full[st], (j >> 1) & 1, gave_up);
+            ok = mbar_wait(&v_full[st], (j >> 1) & 1, gave_up);
+            ok = __all_sync(0xffffffffu, ok && mbar_wait(&p_ready[st], (j >> 1) & 1, gave_up));
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t vd = st == 0 ? v_desc[0] : v_desc[1];
+            if (elect_one()) {
 #pragma unroll
-            for (int kk = 0; kk < FA_BN / 16; ++kk)  // 16 keys per instruction: 8 columns of P, 16 rows (2 KB) of V
-                umma_a_tmem(tmem + 128, tmem + st * FA_BN + kk * 8, vd + (uint64_t)(kk * (16 * 128 / 16)), idesc_pv, (j | kk) != 0);
-            umma_commit(&pv_done[st]);
-            umma_commit(&v_empty[st]);
+                for (int kk = 0; kk < FA_BN / 16; ++kk)  // 16 keys per instruction: 8 columns of P, 16 rows (2 KB) of V
+                    umma_a_tmem(tmem + 128, tmem + st * FA_BN + kk * 8, vd + (uint64_t)(kk * (16 * 128 / 16)), idesc_pv, (j | kk) != 0);
+                umma_commit(&pv_done[st]);
+                umma_commit(&v_empty[st]);
+            }
+            __syncwarp();
         }
     } else if (warp >= 2 && warp < 6) {
         // ---------------- softmax: one thread per row

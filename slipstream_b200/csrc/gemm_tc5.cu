@@ -85,6 +85,12 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint6
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
         ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// True in exactly one lane of a converged warp (the same lane every time).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_addr(bar)) : "memory");
 }
@@ -201,23 +207,30 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             tma_load_2d(a_tile, &map_a, (k_begin + it) * TC_BK, m0, &full[s]);
             tma_load_2d(a_tile + A_BYTES, &map_b, (k_begin + it) * TC_BK, n0, &full[s]);
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer.  Instruction descriptor: D float32, A and B bfloat16, both K-major, N = BN, M = 128.
+    } else if (warp == 1) {
+        // ---- MMA issuer: the whole warp walks the stages and elects the lane that issues (under `lane == 0`
+        // alone the compiler cannot keep the operands of tcgen05.mma in uniform registers, and an instruction
+        // costs its thread two to three times as long).  Instruction descriptor: D float32, A and B bfloat16,
+        // both K-major, N = BN, M = 128.
         constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
         bool ok = true;
         for (int it = 0; it < k_iters && ok; ++it) {
             const int s = it % STAGES;
-            ok = mbar_wait(&full[s], (it / STAGES) & 1, gave_up);
+            ok = __all_sync(0xffffffffu, mbar_wait(&full[s], (it / STAGES) & 1, gave_up));
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             unsigned char* a_tile = tiles + s * (A_BYTES + B_BYTES);
             const uint64_t a_desc = smem_desc(a_tile), b_desc = smem_desc(a_tile + A_BYTES);
+            if (elect_one()) {
 #pragma unroll
-            for (int kk = 0; kk < TC_BK / 16; ++kk)  // 16 K elements = 32 bytes further along the swizzled row
-                umma_f16(tmem_acc, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, (it | kk) != 0);
-            umma_commit(&empty[s]);
+                for (int kk = 0; kk < TC_BK / 16; ++kk)  // 16 K elements = 32 bytes further along the swizzled row
+                    umma_f16(tmem_acc, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, (it | kk) != 0);
+                umma_commit(&empty[s]);
+            }
+            __syncwarp();
         }
-        umma_commit(acc_ready);
+        if (elect_one()) umma_commit(acc_ready);
+        __syncwarp();
     } else if (warp >= 2) {
         // ---- epilogue: warp w reads lanes 32 * (w % 4) .. + 31 of the accumulator
         const int quarter = warp & 3;
@@ -456,27 +469,31 @@ gemm_tc5_many_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 tma_load_2d(a_tile + A_BYTES, &map_b, k * TC_BK, n0, &full[s]);
             }
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---- MMA lane
+    } else if (warp == 1) {
+        // ---- MMA issuer: the warp walks the tiles, an elected lane issues
         constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
         int it = 0, j = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++j) {
             const int buf = j & 1;
-            if (j >= 2 && !mbar_wait(&acc_empty[buf], ((j >> 1) - 1) & 1, gave_up)) break;
+            if (j >= 2 && !__all_sync(0xffffffffu, mbar_wait(&acc_empty[buf], ((j >> 1) - 1) & 1, gave_up))) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             for (int k = 0; k < k_iters; ++k, ++it) {
                 const int s = it % STAGES;
-                if (!mbar_wait(&full[s], (it / STAGES) & 1, gave_up)) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(&full[s], (it / STAGES) & 1, gave_up))) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 unsigned char* a_tile = tiles + s * (A_BYTES + B_BYTES);
                 const uint64_t a_desc = smem_desc(a_tile), b_desc = smem_desc(a_tile + A_BYTES);
+                if (elect_one()) {
 #pragma unroll
-                for (int kk = 0; kk < TC_BK / 16; ++kk)
-                    umma_f16(tmem + buf * MT_BN, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, (k | kk) != 0);
-                umma_commit(&empty[s]);
+                    for (int kk = 0; kk < TC_BK / 16; ++kk)
+                        umma_f16(tmem + buf * MT_BN, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, (k | kk) != 0);
+                    umma_commit(&empty[s]);
+                }
+                __syncwarp();
             }
-            umma_commit(&acc_full[buf]);
+            if (elect_one()) umma_commit(&acc_full[buf]);
+            __syncwarp();
         }
     } else if (warp >= 2) {
         // ---- epilogue: warp w reads lanes 32 * (w % 4) .. + 31 of the accumulator: one output row per thread
@@ -616,28 +633,32 @@ gemm_tc5_many256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 tma_load_2d(a_tile + A_BYTES, &map_b, k * TC_BK, n0, &full[s]);
             }
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---- MMA lane
+    } else if (warp == 1) {
+        // ---- MMA issuer: the warp walks the tiles, an elected lane issues
         constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
         int it = 0, j = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++j) {
-            if (j >= 1 && !mbar_wait(&acc_empty[0], (j - 1) & 1, gave_up)) break;
+            if (j >= 1 && !__all_sync(0xffffffffu, mbar_wait(&acc_empty[0], (j - 1) & 1, gave_up))) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             for (int k = 0; k < k_iters; ++k, ++it) {
                 const int s = it % STAGES;
-                if (!mbar_wait(&full[s], (it / STAGES) & 1, gave_up)) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(&full[s], (it / STAGES) & 1, gave_up))) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 unsigned char* a_tile = tiles + s * (A_BYTES + B_BYTES);
                 const uint64_t a_desc = smem_desc(a_tile), a2_desc = smem_desc(a_tile + A_BYTES / 2), b_desc = smem_desc(a_tile + A_BYTES);
+                if (elect_one()) {
 #pragma unroll
-                for (int kk = 0; kk < TC_BK / 16; ++kk) {
-                    umma_f16(tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, (k | kk) != 0);
-                    umma_f16(tmem + MT_BN, a2_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, (k | kk) != 0);
+                    for (int kk = 0; kk < TC_BK / 16; ++kk) {
+                        umma_f16(tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, (k | kk) != 0);
+                        umma_f16(tmem + MT_BN, a2_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, (k | kk) != 0);
+                    }
+                    umma_commit(&empty[s]);
                 }
-                umma_commit(&empty[s]);
+                __syncwarp();
             }
-            umma_commit(&acc_full[0]);
+            if (elect_one()) umma_commit(&acc_full[0]);
+            __syncwarp();
         }
     } else if (warp >= 2) {
         // ---- epilogue: warp w reads lanes 32 * (w % 4) .. + 31 of the accumulator: one output row per thread
@@ -813,27 +834,31 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 tma_load_2d_pair(a_tile + A_BYTES, &map_b, k * TC_BK, n0, &full[s]);
             }
         }
-    } else if (warp == 1 && lane == 0 && rank == 0) {
-        // ---- MMA lane of the leader: M = 256 over the pair, N = 256
+    } else if (warp == 1 && rank == 0) {
+        // ---- MMA issuer of the leader (an elected lane of the warp): M = 256 over the pair, N = 256
         constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT_BN >> 3) << 17) | ((uint32_t)((2 * TC_BM) >> 4) << 24);
         int it = 0, j = 0;
         bool ok = true;
         for (int t = pair; t < n_tiles && ok; t += n_pairs, ++j) {
             const int buf = j & 1;
-            if (j >= 2 && !mbar_wait(&acc_empty[buf], ((j >> 1) - 1) & 1, gave_up)) break;
+            if (j >= 2 && !__all_sync(0xffffffffu, mbar_wait(&acc_empty[buf], ((j >> 1) - 1) & 1, gave_up))) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             for (int k = 0; k < k_iters; ++k, ++it) {
                 const int s = it % STAGES;
-                if (!mbar_wait(&full[s], (it / STAGES) & 1, gave_up)) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(&full[s], (it / STAGES) & 1, gave_up))) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 unsigned char* a_tile = tiles + s * (A_BYTES + B_BYTES);
                 const uint64_t a_desc = smem_desc(a_tile), b_desc = smem_desc(a_tile + A_BYTES);
+                if (elect_one()) {
 #pragma unroll
-                for (int kk = 0; kk < TC_BK / 16; ++kk)
-                    umma_f16_pair(tmem + buf * MT_BN, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, (k | kk) != 0);
-                umma_commit_pair(&empty[s]);
+                    for (int kk = 0; kk < TC_BK / 16; ++kk)
+                        umma_f16_pair(tmem + buf * MT_BN, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, (k | kk) != 0);
+                    umma_commit_pair(&empty[s]);
+                }
+                __syncwarp();
             }
-            umma_commit_pair(&acc_full[buf]);
+            if (elect_one()) umma_commit_pair(&acc_full[buf]);
+            __syncwarp();
         }
     } else if (warp >= 2) {
         // ---- epilogue (both blocks): this block's 128 rows of the tile
