@@ -413,6 +413,7 @@ struct ManyArgs {
     int64_t ldc;
     int out_f32, bias_f32;
     int swiglu;  // B's rows alternate 64 gate and 64 up features; C gets N / 2 columns
+    int tile_cols;  // two-SM kernel: width of a tile (256 with swiglu)
 };
 
 __device__ __forceinline__ float bias_many(const ManyArgs& g, int f) {
@@ -759,6 +760,9 @@ gemm_tc5_many256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 //   empty[s]     in each block: tcgen05.commit with multicast to both;
 //   acc_full[b]  in each block: tcgen05.commit with multicast to both;
 //   acc_empty[b] in the leader: the eight epilogue warps of both blocks arrive.
+// The tile's width is a parameter (a multiple of 16 up to 256; the instruction's N).  The host picks it so that
+// the tiles fill whole rounds of the pairs: 2,048 x 3,584 outputs are 112 tiles of 256 x 256, one and a half rounds
+// of 74 pairs that cost two, but 144 tiles of 256 x 208, two rounds less 4 tiles that cost 0.81 of the former each.
 #define PR_STAGES 6
 
 __device__ __forceinline__ uint32_t leader_addr(const void* p) { return s_addr(p) & 0xFEFFFFFFu; }  // same offset in block 0 of the pair
@@ -798,7 +802,8 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rank = (int)cluster_rank();  // 0: the leader
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    const int n_m = (g.M + 2 * TC_BM - 1) / (2 * TC_BM), n_n = (g.N + MT_BN - 1) / MT_BN, n_tiles = n_m * n_n;
+    const int bn = g.tile_cols;  // the tile's width: a multiple of 16 up to 256, chosen by the host so that the tiles fill the pairs
+    const int n_m = (g.M + 2 * TC_BM - 1) / (2 * TC_BM), n_n = (g.N + bn - 1) / bn, n_tiles = n_m * n_n;
     const int k_iters = (g.K + TC_BK - 1) / TC_BK;
 
     if (threadIdx.x == 0) {
@@ -824,11 +829,11 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         int it = 0;
         bool ok = true;
         for (int t = pair; t < n_tiles && ok; t += n_pairs) {
-            const int m0 = (t % n_m) * 2 * TC_BM + rank * TC_BM, n0 = (t / n_m) * MT_BN + rank * TC_BM;
+            const int m0 = (t % n_m) * 2 * TC_BM + rank * TC_BM, n0 = (t / n_m) * bn + rank * (bn / 2);
             for (int k = 0; k < k_iters; ++k, ++it) {
                 const int s = it % STAGES;
                 if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, gave_up)) { ok = false; break; }
-                if (rank == 0) mbar_expect_tx(&full[s], 2 * (A_BYTES + B_BYTES));
+                if (rank == 0) mbar_expect_tx(&full[s], 2 * (A_BYTES + (bn / 2) * TC_BK * 2));
                 unsigned char* a_tile = tiles + s * (A_BYTES + B_BYTES);
                 tma_load_2d_pair(a_tile, &map_a, k * TC_BK, m0, &full[s]);
                 tma_load_2d_pair(a_tile + A_BYTES, &map_b, k * TC_BK, n0, &full[s]);
@@ -836,7 +841,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         }
     } else if (warp == 1 && rank == 0) {
         // ---- MMA issuer of the leader (an elected lane of the warp): M = 256 over the pair, N = 256
-        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT_BN >> 3) << 17) | ((uint32_t)((2 * TC_BM) >> 4) << 24);
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)((2 * TC_BM) >> 4) << 24);
         int it = 0, j = 0;
         bool ok = true;
         for (int t = pair; t < n_tiles && ok; t += n_pairs, ++j) {
@@ -867,7 +872,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         bool ok = true;
         for (int t = pair; t < n_tiles && ok; t += n_pairs, ++j) {
             const int buf = j & 1;
-            const int m0 = (t % n_m) * 2 * TC_BM + rank * TC_BM, n0 = (t / n_m) * MT_BN;
+            const int m0 = (t % n_m) * 2 * TC_BM + rank * TC_BM, n0 = (t / n_m) * bn;
             const int m = m0 + quarter * 32 + lane;
             ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (j >> 1) & 1, gave_up));
             if (!ok) break;
@@ -875,7 +880,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             const uint32_t acc = tmem + ((uint32_t)(quarter * 32) << 16) + buf * MT_BN;
             if (!g.swiglu) {
 #pragma unroll 1
-                for (int c = 0; c < MT_BN; c += 16) {
+                for (int c = 0; c < bn; c += 16) {
                     uint32_t r[16];
                     tmem_ld16(acc + c, r);
                     if (m >= g.M || n0 + c >= g.N) continue;
@@ -1031,40 +1036,59 @@ extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int b
 
 // C = A * B^T (+ bias) for many rows of A (prompt portions): A [M, K] activations, B [N, K] weights, both
 // bfloat16 and K-major, K a multiple of 8.  swiglu: B's rows alternate 64 gate and 64 up features (N a multiple of
-// 128); C [M, N / 2] = silu(gate) * up.  One persistent block per SM.
+// 128); C [M, N / 2] = silu(gate) * up.  One persistent block per SM.  tile_rows 128 or 256: one-SM kernels;
+// 512: pairs of SMs, tiles of 256 rows and tile_cols columns (0: chosen here).
 extern "C" int ss_gemm_tc5_many(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
-                                int64_t lda, int64_t ldb, int64_t ldc, int out_f32, int swiglu, int tile_rows, int* err,
-                                cudaStream_t stream) {
+                                int64_t lda, int64_t ldb, int64_t ldc, int out_f32, int swiglu, int tile_rows, int tile_cols,
+                                int* err, cudaStream_t stream) {
     if (tile_rows != 128 && tile_rows != 256 && tile_rows != 512) return -2006;
     const bool big = tile_rows == 256;
-    if (tile_rows == 512) {  // 256 x 256 tiles computed by pairs of blocks (tcgen05.mma.cta_group::2)
-        CUtensorMap ma, mb;
-        int rc = make_map(&ma, A, M, K, lda, TC_BM);
-        if (rc) return rc;
-        rc = make_map(&mb, B, N, K, ldb, TC_BM);  // a block loads 128 rows of B
-        if (rc) return rc;
-        ManyArgs g;
-        g.C = C; g.bias = bias; g.err = err; g.M = M; g.N = N; g.K = K; g.ldc = ldc; g.out_f32 = out_f32;
-        g.bias_f32 = bias_f32; g.swiglu = swiglu;
-        constexpr int smem_pair = PR_STAGES * (2 * TC_BM * TC_BK * 2) + 1024 + 256;
-        static int configured_pair = (int)cudaFuncSetAttribute(gemm_tc5_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pair);
-        if (configured_pair != 0) return configured_pair;
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return -2003;
+    if (((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2004;
+    if (swiglu && (N % 128 != 0 || out_f32 || ldc % 8 != 0 || ((uintptr_t)C & 15))) return -2007;
+    if (tile_rows == 512) {  // 256-row tiles computed by pairs of blocks (tcgen05.mma.cta_group::2)
         int n_sms = 148;
         {
             int dev = 0;
             cudaGetDevice(&dev);
             cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
         }
-        const int tiles2 = ((M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((N + MT_BN - 1) / MT_BN);
-        int pairs = n_sms / 2;
-        if (tiles2 < pairs) pairs = tiles2;
+        const int max_pairs = n_sms / 2 > 0 ? n_sms / 2 : 1;
+        const int n_m = (M + 2 * TC_BM - 1) / (2 * TC_BM);
+        // The width whose tiles take the least time: rounds of the pairs times the time of a tile.  Per 16-wide K
+        // step a block's tensor core needs w / 2 cycles, and its shared memory 64 + w / 4 (4 KB of A and 16 w
+        // bytes of B, written by the copies and read by the product, at 128 bytes a cycle): narrower tiles are
+        // bound by shared memory, so they only pay where they save a round (measured at 2,048 x 3,584 x 18,944:
+        // 210 us at 256, 198 us at 208).  256 stays unless another width is 5 % better.
+        int bn = tile_cols > 0 ? tile_cols : MT_BN;
+        if (tile_cols <= 0 && !swiglu) {
+            auto cost = [&](int w) {
+                const int tiles = n_m * ((N + w - 1) / w);
+                const int per_tile = (w / 2 > 64 + w / 4 ? w / 2 : 64 + w / 4) + 4;
+                return (int64_t)((tiles + max_pairs - 1) / max_pairs) * per_tile;
+            };
+            int64_t best = cost(MT_BN) * 95 / 100;
+            for (int w = MT_BN - 16; w >= 64; w -= 16)
+                if (cost(w) < best) { best = cost(w); bn = w; }
+        }
+        if (bn < 16 || bn > MT_BN || bn % 16 != 0 || (swiglu && bn != MT_BN)) return -2006;
+        CUtensorMap ma, mb;
+        int rc = make_map(&ma, A, M, K, lda, TC_BM);
+        if (rc) return rc;
+        rc = make_map(&mb, B, N, K, ldb, bn / 2);  // a block loads half of the tile's rows of B
+        if (rc) return rc;
+        ManyArgs g;
+        g.C = C; g.bias = bias; g.err = err; g.M = M; g.N = N; g.K = K; g.ldc = ldc; g.out_f32 = out_f32;
+        g.bias_f32 = bias_f32; g.swiglu = swiglu; g.tile_cols = bn;
+        constexpr int smem_pair = PR_STAGES * (2 * TC_BM * TC_BK * 2) + 1024 + 256;
+        static int configured_pair = (int)cudaFuncSetAttribute(gemm_tc5_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pair);
+        if (configured_pair != 0) return configured_pair;
+        const int tiles2 = n_m * ((N + bn - 1) / bn);
+        const int pairs = tiles2 < max_pairs ? tiles2 : max_pairs;
         ss_launch_cluster_x(gemm_tc5_pair_kernel, dim3(2 * pairs), dim3(TC_THREADS), smem_pair, stream, 2, ma, mb, g);
         return SS_LAUNCH_CHECK();
     }
-    if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return -2003;
-    if (((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2004;
-    if (swiglu && (N % 128 != 0 || out_f32 || ldc % 8 != 0 || ((uintptr_t)C & 15))) return -2007;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, M, K, lda, TC_BM);
     if (rc) return rc;
@@ -1072,7 +1096,7 @@ extern "C" int ss_gemm_tc5_many(const void* A, const void* B, const void* bias, 
     if (rc) return rc;
     ManyArgs g;
     g.C = C; g.bias = bias; g.err = err; g.M = M; g.N = N; g.K = K; g.ldc = ldc; g.out_f32 = out_f32;
-    g.bias_f32 = bias_f32; g.swiglu = swiglu;
+    g.bias_f32 = bias_f32; g.swiglu = swiglu; g.tile_cols = MT_BN;
     constexpr int smem = MT_STAGES * (TC_BM * TC_BK * 2 + MT_BN * TC_BK * 2) + 1024 + 256;
     static int configured = (int)cudaFuncSetAttribute(gemm_tc5_many_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (configured != 0) return configured;

@@ -71,7 +71,7 @@ _ATTN_SIGNATURES = {
 
 _GEMM_SIGNATURES = {
     "ss_gemm_tc5_many": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
-                         c_int, c_int, c_int, c_void_p, c_void_p],
+                         c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "ss_gemm_tc5": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                     c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
@@ -660,13 +660,15 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
 
 def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
                       out_dtype: torch.dtype | None = None, swiglu: bool = False,
-                      tile_rows: int | None = None) -> torch.Tensor:
+                      tile_rows: int | None = None, tile_cols: int = 0) -> torch.Tensor:
     """``x @ weight.T + bias`` for many rows of ``x`` (prompt portions) on the tcgen05 tensor cores: a persistent
     kernel, one block per SM.  ``tile_rows`` 128: 128 x 256 output tiles, the accumulator double-buffered in
     tensor memory so that the epilogue of a tile overlaps the products of the next; 256: 256 x 256 tiles, two
     products sharing every weight tile; 512: 256 x 256 tiles computed by pairs of SMs (``tcgen05.mma.cta_group::2``:
     each block of a pair loads half of A and half of B), accumulator double-buffered, the fastest of the three
-    where there are many tiles (the default when there are at least twice as many tiles as SMs).
+    where there are many tiles (the default when there are at least twice as many tiles as SMs).  ``tile_cols``
+    (with 512 rows only): the tiles' width, a multiple of 16 up to 256; 0 lets the launcher take the width whose
+    tiles fill whole rounds of the 74 pairs best.
     ``swiglu``: the weight's rows alternate 64 gate and 64 up features; the result is ``silu(gate) * up`` with
     features / 2 columns."""
     _need(x, torch.bfloat16, "x")
@@ -691,7 +693,7 @@ def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor 
         tile_rows = 512 if ((tokens + 255) // 256) * ((features + 255) // 256) >= 2 * 148 else 128
     rc = gemm_library().ss_gemm_tc5_many(x.data_ptr(), weight.data_ptr(), _ptr(bias), bias_f32, out.data_ptr(), tokens,
                                          features, k, k, k, out.shape[1], int(out_dtype == torch.float32), int(swiglu),
-                                         tile_rows, error_word(x.device).data_ptr(), _stream())
+                                         tile_rows, tile_cols, error_word(x.device).data_ptr(), _stream())
     _check(rc, "gemm_tcgen05_many")
     return out
 

@@ -358,6 +358,24 @@ def test_tcgen05_persistent_product_for_many_tokens(tokens, features, k):
     ops().check_errors(torch.device(DEV))
 
 
+@pytest.mark.parametrize("tokens, features, k", [(2048, 3584, 3584), (600, 1000, 264)])
+def test_tcgen05_two_sm_product_at_every_tile_width(tokens, features, k):
+    """The pairs of SMs compute tiles of 256 rows and any multiple of 16 columns; the launcher picks the width
+    whose tiles fill whole rounds of the pairs (208 for 2,048 x 3,584 outputs), and every width gives the same."""
+    torch.manual_seed(features)
+    x = torch.randn(tokens, k, device=DEV).bfloat16()
+    w = (torch.randn(features, k, device=DEV) * 0.05).bfloat16()
+    b = torch.randn(features, device=DEV).bfloat16()
+    ref = x.double() @ w.double().T + b.double()
+    for cols in (0, 16, 48, 64, 112, 208, 240, 256):
+        got = ops().gemm_tcgen05_many(x, w, b, torch.float32, tile_rows=512, tile_cols=cols)
+        assert rel_err(got, ref) < 2e-5, cols
+    for cols in (8, 24, 272):
+        with pytest.raises(ops().KernelError):
+            ops().gemm_tcgen05_many(x, w, b, torch.float32, tile_rows=512, tile_cols=cols)
+    ops().check_errors(torch.device(DEV))
+
+
 @pytest.mark.parametrize("tokens, inter, k, bias", [(2048, 18944, 3584, False), (70, 192, 136, True), (513, 640, 200, True)])
 def test_tcgen05_persistent_product_with_swiglu(tokens, inter, k, bias):
     torch.manual_seed(inter)
