@@ -70,11 +70,18 @@ def inverse_frequencies(head_dim, theta):
 
 def rotary_tables(positions, head_dim, theta, dtype):
     """slipstream/models/layers/rope.py:93-106: angles = position * inv_freq in
-    float32, duplicated over both halves; cos and sin of them."""
+    float32, duplicated over both halves; cos and sin of them.  The reference takes
+    cosine and sine in float32; here each float32 angle goes through ``math.cos`` /
+    ``math.sin`` (double precision, one value at a time), which differs from that by
+    at most the rounding of the result to float32.  The vectorised float32 cosine of
+    the CPU library gave, in about one process in twenty on the test machines, values
+    that were off by 1e-4 on its first call; this oracle must not depend on that."""
     inv_freq = inverse_frequencies(head_dim, theta)
     freqs = positions.to(torch.float32)[:, None] * inv_freq[None, :]
-    emb = torch.cat((freqs, freqs), dim=-1)
-    return emb.cos().to(dtype), emb.sin().to(dtype)
+    angles = [[float(a) for a in row] for row in freqs.tolist()]
+    cos = torch.tensor([[math.cos(a) for a in row] for row in angles], dtype=torch.float64).reshape(freqs.shape)
+    sin = torch.tensor([[math.sin(a) for a in row] for row in angles], dtype=torch.float64).reshape(freqs.shape)
+    return torch.cat((cos, cos), dim=-1).to(dtype), torch.cat((sin, sin), dim=-1).to(dtype)
 
 
 def rotate_half(x):
