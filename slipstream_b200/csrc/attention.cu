@@ -130,8 +130,10 @@ extern "C" int ss_attn_decode_tma(const void* q, int64_t q_stride, void* out, in
                                   float* part_lse, int* counters, int* err, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (page_size % 8 != 0 || 64 % page_size != 0) return -3003;
-    const int cluster = n_slices >= 2 && n_slices <= 8;
-    if (n_slices < 1 || (n_slices > 1 && !cluster && (!part_o || !part_lse || !counters))) return (int)cudaErrorInvalidValue;
+    // up to 8 slices: one cluster; a multiple of 8 beyond: clusters of 8 whose results meet in scratch memory;
+    // any other count: single blocks and scratch memory
+    const int cluster = n_slices <= 8 ? n_slices : (n_slices % 8 == 0 ? 8 : 1);
+    if (n_slices < 1 || (n_slices > 8 && (!part_o || !part_lse || !counters))) return (int)cudaErrorInvalidValue;
     if (fused && (rot_dim < 0 || rot_dim > HEAD_DIM || rot_dim % 2 || (rot_dim > 0 && !inv_freq))) return (int)cudaErrorInvalidValue;
     CUtensorMap map_kv;
     int rc = fa::make_map3(&map_kv, kv, HEAD_DIM, (uint64_t)page_size, (uint64_t)num_pages * 2 * n_kv, (uint64_t)HEAD_DIM * 2,
@@ -148,7 +150,7 @@ extern "C" int ss_attn_decode_tma(const void* q, int64_t q_stride, void* out, in
     if (configured != 0) return configured;
     const int G = n_q / n_kv;
     dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
-    if (cluster) ss_launch_cluster(attn_decode_tma<HEAD_DIM>, dim3(grid), dim3(DT_THREADS), smem, stream, n_slices, map_kv, a);
+    if (cluster > 1) ss_launch_cluster(attn_decode_tma<HEAD_DIM>, dim3(grid), dim3(DT_THREADS), smem, stream, cluster, map_kv, a);
     else ss_launch(attn_decode_tma<HEAD_DIM>, dim3(grid), dim3(DT_THREADS), smem, stream, map_kv, a);
     return SS_LAUNCH_CHECK();
 }

@@ -4,7 +4,9 @@
 // The arithmetic is that of attn_decode_mma (attention_mma.cuh): a block takes the (up to 16) heads of one
 // (request, kv head) and one slice of the keys; its four consumer warps take different 16-key parts of each
 // 64-key tile (mma.sync m16n8k16, float32 online softmax) and merge at the end; the slices of a head block
-// are a thread-block cluster and merge through shared memory (or, beyond 8 slices, through scratch memory).
+// are a thread-block cluster and merge through shared memory; beyond 8 slices they form several clusters of 8,
+// whose results pass through scratch memory to the block that finishes last (few requests with long contexts:
+// one request of 32,768 tokens is 64 slices on 4 kv heads, 256 blocks instead of 32).
 // What differs is how a tile gets into shared memory.  There every thread issued sixteen 16-byte cp.async per
 // tile, and issuing them took three times as long as the arithmetic on the tile (1.5 us against 0.5 us per
 // tile and block, measured), whatever the memory did.  Here a fifth warp's first lane issues one
@@ -44,7 +46,7 @@ struct DecodeTmaArgs {
     int n_q, n_kv, page_size;
     int64_t num_pages;
     float scale;
-    int window, n_slices, cluster;
+    int window, n_slices, cluster;  // cluster: blocks per thread-block cluster along the slices (1: none)
     const float* inv_freq;
     int rot_dim, fused;
     float* part_o;
@@ -88,6 +90,7 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
     const int r = blockIdx.x, kvh = blockIdx.y / hblocks, g0 = (blockIdx.y % hblocks) * 16;
     const int heads_here = min(16, G - g0);
     const int slice = blockIdx.z;
+    const int cs = a.cluster, n_groups = n_slices / cs, group = slice / cs;  // slices per cluster, clusters, this one
     const int row_q = a.q_start[r], seq_len = a.seq_lens[r];
     const int pos = seq_len - 1;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
@@ -308,28 +311,29 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
         const float val = ll > 0.f ? acc / ll : 0.f;
         if (n_slices == 1) {
             a.out[(int64_t)row_q * a.out_stride + (head0 + row) * D + d] = __float2bfloat16_rn(val);
-        } else if (a.cluster) {
+        } else if (cs > 1) {
             Pc[row * D + d] = val;
             if (d == 0) Lc[row] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
         } else {
-            a.part_o[(((int64_t)r * n_q + head0 + row) * n_slices + slice) * D + d] = val;
-            if (d == 0) a.part_lse[((int64_t)r * n_q + head0 + row) * n_slices + slice] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
+            a.part_o[(((int64_t)r * n_q + head0 + row) * n_groups + group) * D + d] = val;
+            if (d == 0) a.part_lse[((int64_t)r * n_q + head0 + row) * n_groups + group] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
         }
     }
     if (*gave_up && tid == 0) atomicOr(a.err, SS_ERR_WAIT_LIMIT);
     if (n_slices == 1) return;
 
-    if (a.cluster) {
+    if (cs > 1) {
+        // the slices of a cluster are combined through its shared memory; rank k takes rows k, k + cs, ...
         cluster_sync_all();
         const int rank = (int)cluster_rank();
-        const int mine = heads_here > rank ? (heads_here - 1 - rank) / n_slices + 1 : 0;
+        const int mine = heads_here > rank ? (heads_here - 1 - rank) / cs + 1 : 0;
         for (int idx = tid; idx < mine * D; idx += DT_THREADS) {
-            const int row = rank + (idx / D) * n_slices, d = idx % D;
+            const int row = rank + (idx / D) * cs, d = idx % D;
             float lse[8], p[8];
 #pragma unroll
             for (int sl = 0; sl < 8; ++sl) {
-                lse[sl] = sl < n_slices ? ld_cluster_f32(Lc + row, (uint32_t)sl) : -INFINITY;
-                p[sl] = sl < n_slices ? ld_cluster_f32(Pc + row * D + d, (uint32_t)sl) : 0.f;
+                lse[sl] = sl < cs ? ld_cluster_f32(Lc + row, (uint32_t)sl) : -INFINITY;
+                p[sl] = sl < cs ? ld_cluster_f32(Pc + row * D + d, (uint32_t)sl) : 0.f;
             }
             float mx = -INFINITY, den = 0.f;
 #pragma unroll
@@ -343,13 +347,19 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
             float acc = 0.f;
 #pragma unroll
             for (int sl = 0; sl < 8; ++sl) acc += p[sl] * (lse[sl] * inv);
-            a.out[(int64_t)row_q * a.out_stride + (head0 + row) * D + d] = __float2bfloat16_rn(acc);
+            if (n_groups == 1) {
+                a.out[(int64_t)row_q * a.out_stride + (head0 + row) * D + d] = __float2bfloat16_rn(acc);
+            } else {  // several clusters share the keys of this head block: the cluster's result goes to scratch
+                a.part_o[(((int64_t)r * n_q + head0 + row) * n_groups + group) * D + d] = acc;
+                if (d == 0) a.part_lse[((int64_t)r * n_q + head0 + row) * n_groups + group] = den > 0.f ? mx + log2f(den) : -INFINITY;
+            }
         }
         cluster_sync_all();  // nobody leaves while its shared memory is still being read
-        return;
+        if (n_groups == 1) return;
     }
 
-    // more than 8 slices: through scratch memory; the block that finishes a head block last combines them
+    // several groups (clusters, or single blocks): through scratch memory; the block that finishes a head block
+    // last combines them
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -361,32 +371,32 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    float* W = reinterpret_cast<float*>(base);  // [16][n_slices]
-    for (int idx = tid; idx < heads_here * n_slices; idx += DT_THREADS) {
-        const int row = idx / n_slices, sl = idx - row * n_slices;
-        W[row * n_slices + sl] = __ldcg(a.part_lse + ((int64_t)r * n_q + head0 + row) * n_slices + sl);
+    float* W = reinterpret_cast<float*>(base);  // [16][n_groups]
+    for (int idx = tid; idx < heads_here * n_groups; idx += DT_THREADS) {
+        const int row = idx / n_groups, sl = idx - row * n_groups;
+        W[row * n_groups + sl] = __ldcg(a.part_lse + ((int64_t)r * n_q + head0 + row) * n_groups + sl);
     }
     __syncthreads();
     if (tid < heads_here) {
-        float* w = W + tid * n_slices;
+        float* w = W + tid * n_groups;
         float mx = -INFINITY, den = 0.f;
-        for (int sl = 0; sl < n_slices; ++sl) mx = fmaxf(mx, w[sl]);
-        for (int sl = 0; sl < n_slices; ++sl) {
+        for (int sl = 0; sl < n_groups; ++sl) mx = fmaxf(mx, w[sl]);
+        for (int sl = 0; sl < n_groups; ++sl) {
             const float e = mx == -INFINITY ? 0.f : exp2f(w[sl] - mx);
             w[sl] = e;
             den += e;
         }
         const float inv = den > 0.f ? 1.f / den : 0.f;
-        for (int sl = 0; sl < n_slices; ++sl) w[sl] *= inv;
+        for (int sl = 0; sl < n_groups; ++sl) w[sl] *= inv;
     }
     __syncthreads();
     for (int idx = tid; idx < heads_here * D; idx += DT_THREADS) {
         const int row = idx / D, d = idx - row * D;
-        const float* po = a.part_o + ((int64_t)r * n_q + head0 + row) * n_slices * D + d;
-        const float* w = W + row * n_slices;
+        const float* po = a.part_o + ((int64_t)r * n_q + head0 + row) * n_groups * D + d;
+        const float* w = W + row * n_groups;
         float acc = 0.f;
 #pragma unroll 8
-        for (int sl = 0; sl < n_slices; ++sl) acc += __ldcg(po + (int64_t)sl * D) * w[sl];
+        for (int sl = 0; sl < n_groups; ++sl) acc += __ldcg(po + (int64_t)sl * D) * w[sl];
         a.out[(int64_t)row_q * a.out_stride + (head0 + row) * D + d] = __float2bfloat16_rn(acc);
     }
 }

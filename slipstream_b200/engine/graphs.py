@@ -36,9 +36,10 @@ def bucket_for(n: int) -> int | None:
 
 
 class DecodeGraph:
-    def __init__(self, runner, bucket: int) -> None:
+    def __init__(self, runner, bucket: int, wide: bool = False) -> None:
         self.runner = runner
         self.bucket = bucket
+        self.wide = wide  # captured for long contexts: attention may cut the keys into more than 8 slices
         cache = runner.cache
         self.n_groups = len(cache.groups)
         self.max_blocks = max(1, (runner.max_model_len + cache.page_size - 1) // cache.page_size)
@@ -71,6 +72,7 @@ class DecodeGraph:
                                groups=groups, q_lens_host=ones, seq_lens_host=ones, request_ids=[], device=device,
                                num_logits=B)
         self.ctx.extras["static_max_seq_len"] = runner.max_model_len
+        self.ctx.extras["decode_wide"] = wide
         arange = torch.arange(B, dtype=torch.int32, device=device)
         self.ctx._tiles[(16, 1)] = (arange, torch.zeros(B, dtype=torch.int32, device=device))
         self._fill(self.hosts[0].numpy(), None)

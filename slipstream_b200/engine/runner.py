@@ -80,7 +80,7 @@ class ModelRunner:
         self.last_h2d_bytes = 0
         self.use_cuda_graphs = (use_cuda_graphs and self.device.type == "cuda"
                                 and all(getattr(p, "cuda_graph_safe", False) for p in self.model.parts()))
-        self._graphs: dict[int, DecodeGraph] = {}
+        self._graphs: dict[tuple[int, bool], DecodeGraph] = {}  # (batch bucket, captured for long contexts)
 
     # ------------------------------------------------------------------ requests
     def admit(self, request_id: object) -> None:
@@ -106,9 +106,7 @@ class ModelRunner:
         plan = plan_step(entries, self.cache, self.config.vocab_size)
         bucket = self._graph_bucket(plan.num_requests) if plan.is_decode_only else None
         if bucket is not None:
-            graph = self._graphs.get(bucket)
-            if graph is None:
-                graph = self._graphs[bucket] = DecodeGraph(self, bucket)
+            graph = self._decode_graph(bucket, plan)
             self.last_h2d_bytes = graph.h2d_bytes
             logits = graph.run(plan)
         else:
@@ -119,6 +117,16 @@ class ModelRunner:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
         return logits
+
+    def _decode_graph(self, bucket: int, plan) -> DecodeGraph:
+        """The captured step for this bucket; a second one per bucket serves steps whose longest request has
+        reached a long context (``ops.is_long_context``) (few long requests want more slices of the keys than many
+        short ones, and the number of slices is fixed when a graph is captured)."""
+        wide = ops.is_long_context(int(plan.seq_lens.max()))
+        graph = self._graphs.get((bucket, wide))
+        if graph is None:
+            graph = self._graphs[(bucket, wide)] = DecodeGraph(self, bucket, wide)
+        return graph
 
     def _graph_bucket(self, n_requests: int) -> int | None:
         bucket = bucket_for(n_requests) if self.use_cuda_graphs else None
@@ -133,9 +141,9 @@ class ModelRunner:
         limit = self.max_num_seqs if max_requests is None else max_requests
         made = 0
         for bucket in BUCKETS:
-            if self._graph_bucket(bucket) != bucket or bucket in self._graphs:
+            if self._graph_bucket(bucket) != bucket or (bucket, False) in self._graphs:
                 continue
-            self._graphs[bucket] = DecodeGraph(self, bucket)
+            self._graphs[(bucket, False)] = DecodeGraph(self, bucket)
             made += 1
             if bucket >= limit:
                 break
@@ -155,10 +163,7 @@ class ModelRunner:
         plan = plan_step(entries, self.cache, self.config.vocab_size)
         if not plan.is_decode_only or not self.can_run_ahead(plan.num_requests):
             raise StepInputError("step_decode takes decode-only steps that fit a captured graph")
-        bucket = self._graph_bucket(plan.num_requests)
-        graph = self._graphs.get(bucket)
-        if graph is None:
-            graph = self._graphs[bucket] = DecodeGraph(self, bucket)
+        graph = self._decode_graph(self._graph_bucket(plan.num_requests), plan)
         self.last_h2d_bytes = graph.h2d_bytes
         logits = graph.run(plan, pending=pending, src_rows=src_rows, keep=False)
         for e in entries:

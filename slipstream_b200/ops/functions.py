@@ -416,8 +416,9 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
                            rope: tuple[torch.Tensor | None, int] | None = None, tma: bool | None = None) -> None:
     """bfloat16 attention for requests that bring ONE token each, the keys of every request cut into
     ``n_slices`` slices that run in parallel.  Up to 8 slices form a thread-block cluster and are combined
-    through shared memory; with more, the partial results pass through ``scratch`` (see ``decode_scratch``)
-    and the block that finishes a head block last combines them.
+    through shared memory; with more, the partial results (of every cluster of 8 in the TMA-fed kernel when the
+    count is a multiple of 8, else of every slice) pass through ``scratch`` (see ``decode_scratch``) and the
+    block that finishes a head block last combines them.
 
     ``rope`` = (inverse frequencies, rotary_dim): ``q`` is then the stacked projection output
     [N, (n_q + 2 n_kv) * D] as projected, and the kernel itself rotates queries and the newest key by each
@@ -467,15 +468,32 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
                                   error_word(q.device).data_ptr(), _stream()), "paged_attention_decode")
 
 
-def decode_slices(n_requests: int, n_kv: int, group: int, max_seq_len: int) -> int:
+WIDE_CONTEXT = 8192  # from this many cached tokens a decode step of few requests may use more than 8 slices
+
+
+def is_long_context(seq_len: int) -> bool:
+    return seq_len >= WIDE_CONTEXT
+
+
+def decode_slices(n_requests: int, n_kv: int, group: int, max_seq_len: int, wide: bool = False) -> int:
     """How many slices to cut the keys into: as many as keep all blocks resident at once (two per SM on
-    148 SMs), so that the step is one wave of blocks; at most 8, the size of a thread-block cluster."""
+    148 SMs), so that the step is one wave of blocks; at most 8, the size of a thread-block cluster.
+
+    ``wide`` (the TMA-fed kernel, long contexts): few requests leave most SMs idle with 8 slices (one request on
+    4 kv heads: 32 blocks), so the slices become 2, 4 or 8 clusters of 8 whose results meet in scratch memory,
+    as long as a slice keeps 8 tiles of 64 keys and all blocks still fit one wave.  One request of 32,768 tokens:
+    64.7 us with 8 slices, 23.4 us with 64; two of 16,384: 35.8 against 27.7 with 32; with 32 blocks or more
+    (8 requests) 8 slices are the fastest at every length."""
     blocks = n_requests * n_kv * ((group + 15) // 16)
     tiles = max(1, (max_seq_len + 63) // 64)
     most = max(1, min((2 * 148) // blocks, tiles, 8))
     # a power of two: clusters of 3 blocks pack the SMs of a GPC badly (24 requests x 4 kv heads: 24.8 us with 3
     # slices, 17.2 us with 2)
-    return 1 << (most.bit_length() - 1)
+    slices = 1 << (most.bit_length() - 1)
+    if wide and slices == 8:
+        clusters = max(1, min((2 * 148) // (blocks * 8), tiles // 64, 8))
+        slices = 8 * (1 << (clusters.bit_length() - 1))
+    return slices
 
 
 def fuses_rope(qkv: torch.Tensor, ctx, head_dim: int, n_q: int, n_kv: int, page_size: int) -> bool:
@@ -511,8 +529,11 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
         return
     group = n_q // n_kv
     if ctx.is_decode_only:
-        longest = ctx.extras.get("static_max_seq_len") or ctx.max_seq_len  # fixed when the step is captured
-        slices = decode_slices(ctx.num_requests, n_kv, group, min(longest, window or longest))
+        static = ctx.extras.get("static_max_seq_len")  # fixed when the step is captured
+        longest = static or ctx.max_seq_len
+        wide = ctx.extras.get("decode_wide", False) if static else is_long_context(ctx.max_seq_len)
+        wide = bool(wide) and tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], 0)
+        slices = decode_slices(ctx.num_requests, n_kv, group, min(longest, window or longest), wide)
         scratch = ctx.extras.get(("decode_scratch", n_q, head_dim))
         paged_attention_decode(qkv, qkv.shape[1], out, kv, block_tables, ctx.q_start, ctx.seq_lens,
                                ctx.num_requests, n_q, n_kv, head_dim, scale, window, slices, scratch, rope)
@@ -770,5 +791,5 @@ def set_programmatic_launch(enabled: bool) -> None:
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
            "attention_library"]

@@ -233,7 +233,7 @@ def test_paged_attention_tiled_kernels(dtype, case):
     ops().check_errors(torch.device(DEV))
 
 
-@pytest.mark.parametrize("slices", [1, 2, 5, 32])
+@pytest.mark.parametrize("slices", [1, 2, 5, 16, 32, 64])  # one cluster; 2, 4, 8 clusters of 8 (TMA-fed kernel) or single blocks
 @pytest.mark.parametrize("n_q, n_kv, d, page, window", [(28, 4, 128, 16, 0), (6, 6, 16, 4, 0), (40, 2, 64, 7, 0),
                                                          (8, 2, 32, 16, 100), (3, 1, 256, 16, 0), (40, 2, 64, 8, 0),
                                                          (9, 3, 128, 64, 150), (4, 4, 64, 32, 33)])
@@ -251,7 +251,7 @@ def test_split_decode_attention(slices, n_q, n_kv, d, page, window):
     ops().check_errors(torch.device(DEV))
 
 
-@pytest.mark.parametrize("slices", [1, 3, 8, 11])
+@pytest.mark.parametrize("slices", [1, 3, 8, 11, 24])
 @pytest.mark.parametrize("n_q, n_kv, d, rot, page, window", [(28, 4, 128, 128, 16, 0), (6, 6, 16, 8, 4, 0),
                                                               (40, 2, 64, 64, 7, 0), (8, 2, 32, 0, 16, 100),
                                                               (40, 2, 64, 32, 8, 0), (9, 3, 128, 128, 64, 150)])
@@ -268,16 +268,13 @@ def test_decode_attention_that_rotates_and_writes_the_newest_token_itself(slices
     pages_of = table.long()[torch.arange(R, device=DEV), (positions // page).long()]
     slots = (pages_of * page + positions % page).int()
     scale = d ** -0.5
-    # two steps
-    qkv_a, kv_a = qkv.clone(), kv.clone()
-    ops().rope_and_cache(qkv_a, positions, slots, inv_freq, kv_a, n_q, n_kv, d, rot)
-    out_a = torch.full((R, n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
-    ops().paged_attention_decode(qkv_a, qkv_a.shape[1], out_a, kv_a, table, q_start, seq_lens, R, n_q, n_kv, d, scale,
-                                 window, n_slices=slices)
-    ops().paged_attention_decode(qkv_a, qkv_a.shape[1], out_a, kv_a, table, q_start, seq_lens, R, n_q, n_kv, d, scale,
-                                 window, n_slices=slices, tma=False)
-    # one step, with either way of moving the tiles
     for tma in [False] + ([True] if ops().tcgen05_attention_fits(d, n_q, n_kv, page, 0) else []):
+        # two steps, then one step, with the same way of moving the tiles (cp.async, or TMA)
+        qkv_a, kv_a = qkv.clone(), kv.clone()
+        ops().rope_and_cache(qkv_a, positions, slots, inv_freq, kv_a, n_q, n_kv, d, rot)
+        out_a = torch.full((R, n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+        ops().paged_attention_decode(qkv_a, qkv_a.shape[1], out_a, kv_a, table, q_start, seq_lens, R, n_q, n_kv, d, scale,
+                                     window, n_slices=slices, tma=tma)
         qkv_b, kv_b = qkv.clone(), kv.clone()
         out_b = torch.full_like(out_a, float("nan"))
         ops().paged_attention_decode(qkv_b, qkv_b.shape[1], out_b, kv_b, table, q_start, seq_lens, R, n_q, n_kv, d,

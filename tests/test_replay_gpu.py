@@ -124,3 +124,43 @@ def test_trace_run_program(model_folders, requests_for, tmp_path, dtype):
     rows["r3"] = rows["r3"][:n3]
     compare(rows, want, dtype, f"trace_run {dtype} mixed")
     compare(again, {"r3": want["r3"]}, dtype, f"trace_run {dtype} tail")
+
+
+def test_long_requests_decode_through_a_graph_with_more_slices(tmp_path, monkeypatch):
+    """From 8,192 cached tokens a decode step of few requests cuts the keys into more than 8 slices (several
+    thread-block clusters whose results meet in scratch memory) and runs a graph captured for that.  The
+    logits are those of the same steps with 8 slices, up to the order of the additions."""
+    from slipstream_b200 import ops
+    from slipstream_b200.config.model_config import Qwen2Config
+    from slipstream_b200.engine.runner import ModelRunner, StepEntry
+    from slipstream_b200.weights.random_init import write_random_model
+    from conftest import sharpen
+
+    config = Qwen2Config(vocab_size=300, hidden_size=128, num_hidden_layers=2, max_position_embeddings=16384,
+                         torch_dtype="bfloat16", intermediate_size=256, num_attention_heads=8, num_key_value_heads=2,
+                         head_dim=64, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False)
+    write_random_model(config, tmp_path, seed=3)
+    sharpen(tmp_path, factor=4.0)
+    prompts = {"long": random_tokens(300, 8300, 1), "short": random_tokens(300, 40, 2)}
+    tails = {rid: random_tokens(300, 6, 10 + i) for i, rid in enumerate(prompts)}
+
+    def run(wide_from):
+        monkeypatch.setattr(ops.functions, "WIDE_CONTEXT", wide_from)
+        runner = ModelRunner(str(tmp_path), dtype="bfloat16", page_size=16, num_pages=600, max_num_seqs=4)
+        for rid, tokens in prompts.items():
+            for i in range(0, len(tokens), 2048):
+                runner.step([StepEntry(rid, tokens[i:i + 2048], [])])
+        rows = []
+        for k in range(6):  # the long request alone (bucket 1), then both (bucket 2)
+            ids = ["long"] if k < 3 else ["long", "short"]
+            rows.append(runner.step([StepEntry(rid, [tails[rid][k]], [0]) for rid in ids]).float().cpu().numpy())
+        runner.check()
+        return rows, sorted(runner._graphs)
+
+    wide_rows, wide_graphs = run(8192)
+    narrow_rows, narrow_graphs = run(10 ** 9)
+    assert wide_graphs == [(1, True), (2, True)] and narrow_graphs == [(1, False), (2, False)]
+    assert ops.decode_slices(1, 2, 4, 16384, wide=True) > 8 == ops.decode_slices(1, 2, 4, 16384)
+    for a, b in zip(wide_rows, narrow_rows):
+        assert np.abs(a - b).max() <= 0.5 * TOLERANCE["bfloat16"] * np.abs(b).max()
+        assert not np.array_equal(a, b), "both runs took the same path"
