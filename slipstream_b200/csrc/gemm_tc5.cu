@@ -17,9 +17,9 @@
 // shared memory, and after a cluster barrier block r adds, in slice order, the token columns r, r + slices, ...
 // out of the shared memory of all blocks of the cluster.  No scratch, no counters, no trip through global memory.
 //
-// Many tokens (prompt portions) have kernels of their own further down: persistent blocks that walk over output
-// tiles with the accumulator double-buffered in tensor memory, in a one-SM form and in a two-SM form
-// (tcgen05.mma.cta_group::2 over the two blocks of a cluster), both with an optional fused SwiGLU epilogue.
+// Many tokens (prompt portions) have a kernel of their own further down: persistent pairs of blocks that walk
+// over output tiles with tcgen05.mma.cta_group::2, the accumulator double-buffered in tensor memory, with an
+// optional fused SwiGLU epilogue.
 //
 // Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the kernel sets SS_ERR_WAIT_LIMIT in the
 // error word, stops waiting everywhere, frees its tensor memory and returns.
@@ -394,16 +394,30 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
 }
 
-// ---------------------------------------------------------------- many tokens: a persistent kernel
+// ---------------------------------------------------------------- many tokens: a persistent kernel on pairs of SMs
 //
 // C[M, N] = A[M, K] * B[N, K]^T for prompt portions (A: activations, hundreds to thousands of rows; B: weights).
-// One block per SM walks over 128 x 256 tiles, row tiles fastest, so that the blocks at work at any moment share
-// a handful of weight tiles (the weights are read from memory once) and the activations stay in L2.  The
-// accumulator is double-buffered in tensor memory (2 x 256 columns, all of an SM's): while the four epilogue
-// warps read one tile out, add the bias (or form silu(gate) * up) and store it, the MMA lane already works on
-// the next.  Producer, MMA lane and epilogue warps run through the same list of tiles and meet at mbarriers.
+// The two blocks of a cluster compute one 256-row tile with tcgen05.mma.cta_group::2 and walk over the tiles,
+// row tiles fastest, so that the pairs at work at any moment share a handful of weight tiles (the weights are
+// read from memory once) and the activations stay in L2.  Block r of the pair loads rows r * 128 .. of the A tile
+// and half of the B tile's rows; the leader (block 0) issues the products, which read A and B out of both blocks'
+// shared memory and leave rows r * 128 .. of the result in block r's tensor memory: 32 KB per block and 64-wide K
+// step, six stages.  The accumulator is double-buffered in tensor memory (2 x 256 columns, all of an SM's): while
+// the four epilogue warps of each block read one tile out, add the bias (or form silu(gate) * up) and store it,
+// the leader already issues the next.  Producer, MMA warp and epilogue warps run through the same list of tiles
+// and meet at mbarriers:
+//   full[s]      in the leader: one arrival (the leader's producer, with the bytes of both blocks); the other
+//                block's copies complete their bytes on it too (cp.async.bulk.tensor .cta_group::2);
+//   empty[s]     in each block: tcgen05.commit with multicast to both;
+//   acc_full[b]  in each block: tcgen05.commit with multicast to both;
+//   acc_empty[b] in the leader: the eight epilogue warps of both blocks arrive.
+// One-SM forms of this kernel (128 x 256 tiles with a double-buffered accumulator; 256 x 256 tiles as two products
+// per K step) kept the tensor pipe busy 77 % of the time, this one 92 %: a block of a pair fetches and feeds
+// half of B.
+// The tile's width is a parameter (a multiple of 16 up to 256; the instruction's N).  The host picks it so that
+// the tiles fill whole rounds of the pairs: 2,048 x 3,584 outputs are 112 tiles of 256 x 256, one and a half rounds
+// of 74 pairs that cost two, but 144 tiles of 256 x 208, two rounds less 4 tiles that cost 0.81 of the former each.
 #define MT_BN 256
-#define MT_STAGES 4
 
 struct ManyArgs {
     void* C;
@@ -413,356 +427,13 @@ struct ManyArgs {
     int64_t ldc;
     int out_f32, bias_f32;
     int swiglu;  // B's rows alternate 64 gate and 64 up features; C gets N / 2 columns
-    int tile_cols;  // two-SM kernel: width of a tile (256 with swiglu)
+    int tile_cols;  // width of a tile (256 with swiglu)
 };
 
 __device__ __forceinline__ float bias_many(const ManyArgs& g, int f) {
     return g.bias_f32 ? ((const float*)g.bias)[f] : to_float(((const bf16*)g.bias)[f]);
 }
 
-__global__ void __launch_bounds__(TC_THREADS)
-gemm_tc5_many_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const ManyArgs g) {
-    constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = MT_BN * TC_BK * 2, STAGES = MT_STAGES;
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * (A_BYTES + B_BYTES));
-    uint64_t* empty = full + STAGES;
-    uint64_t* acc_full = empty + STAGES;   // 2: the MMA lane has finished a tile in this accumulator
-    uint64_t* acc_empty = acc_full + 2;    // 2: the epilogue has read it out
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-    volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-    pdl_launch_dependents();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_m = (g.M + TC_BM - 1) / TC_BM, n_n = (g.N + MT_BN - 1) / MT_BN, n_tiles = n_m * n_n;
-    const int k_iters = (g.K + TC_BK - 1) / TC_BK;
-
-    if (threadIdx.x == 0) {
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
-        *gave_up = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_slot)), "r"(512));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = *tmem_slot;
-    pdl_wait();
-
-    if (warp == 0 && lane == 0) {
-        // ---- producer: one stream of K tiles across all of this block's output tiles
-        int it = 0;
-        bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-            const int m0 = (t % n_m) * TC_BM, n0 = (t / n_m) * MT_BN;
-            for (int k = 0; k < k_iters; ++k, ++it) {
-                const int s = it % STAGES;
-                if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, gave_up)) { ok = false; break; }
-                mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                unsigned char* a_tile = tiles + s * (A_BYTES + B_BYTES);
-                tma_load_2d(a_tile, &map_a, k * TC_BK, m0, &full[s]);
-                tma_load_2d(a_tile + A_BYTES, &map_b, k * TC_BK, n0, &full[s]);
-            }
-        }
-    } else if (warp == 1) {
-        // ---- MMA issuer: the warp walks the tiles, an elected lane issues
-        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-        int it = 0, j = 0;
-        bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++j) {
-            const int buf = j & 1;
-            if (j >= 2 && !__all_sync(0xffffffffu, mbar_wait(&acc_empty[buf], ((j >> 1) - 1) & 1, gave_up))) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            for (int k = 0; k < k_iters; ++k, ++it) {
-                const int s = it % STAGES;
-                if (!__all_sync(0xffffffffu, mbar_wait(&full[s], (it / STAGES) & 1, gave_up))) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                unsigned char* a_tile = tiles + s * (A_BYTES + B_BYTES);
-                const uint64_t a_desc = smem_desc(a_tile), b_desc = smem_desc(a_tile + A_BYTES);
-                if (elect_one()) {
-#pragma unroll
-                    for (int kk = 0; kk < TC_BK / 16; ++kk)
-                        umma_f16(tmem + buf * MT_BN, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, (k | kk) != 0);
-                    umma_commit(&empty[s]);
-                }
-                __syncwarp();
-            }
-            if (elect_one()) umma_commit(&acc_full[buf]);
-            __syncwarp();
-        }
-    } else if (warp >= 2) {
-        // ---- epilogue: warp w reads lanes 32 * (w % 4) .. + 31 of the accumulator: one output row per thread
-        const int quarter = warp & 3;
-        int j = 0;
-        bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++j) {
-            const int buf = j & 1;
-            const int m0 = (t % n_m) * TC_BM, n0 = (t / n_m) * MT_BN;
-            const int m = m0 + quarter * 32 + lane;
-            ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (j >> 1) & 1, gave_up));
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t acc = tmem + ((uint32_t)(quarter * 32) << 16) + buf * MT_BN;
-            if (!g.swiglu) {
-#pragma unroll 1
-                for (int c = 0; c < MT_BN; c += 16) {
-                    uint32_t r[16];
-                    tmem_ld16(acc + c, r);
-                    if (m >= g.M || n0 + c >= g.N) continue;
-                    if (g.bias) {
-#pragma unroll
-                        for (int e = 0; e < 16; ++e) {
-                            const int f = n0 + c + e;
-                            if (f < g.N) r[e] = __float_as_uint(__uint_as_float(r[e]) + (g.bias_f32 ? ((const float*)g.bias)[f] : to_float(((const bf16*)g.bias)[f])));
-                        }
-                    }
-                    if (!g.out_f32 && n0 + c + 16 <= g.N && (g.ldc % 8 == 0)) {
-                        uint32_t packed[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
-                            packed[e] = *reinterpret_cast<uint32_t*>(&v);
-                        }
-                        uint4* dst = reinterpret_cast<uint4*>((bf16*)g.C + (int64_t)m * g.ldc + n0 + c);
-                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                    } else {
-                        for (int e = 0; e < 16 && n0 + c + e < g.N; ++e) {
-                            const int64_t at = (int64_t)m * g.ldc + n0 + c + e;
-                            if (g.out_f32) ((float*)g.C)[at] = __uint_as_float(r[e]);
-                            else ((bf16*)g.C)[at] = __float2bfloat16_rn(__uint_as_float(r[e]));
-                        }
-                    }
-                }
-            } else {
-                // columns [0,64) gate, [64,128) the matching up, [128,192) gate, [192,256) up
-#pragma unroll 1
-                for (int c = 0; c < MT_BN / 2; c += 16) {
-                    const int gc = (c / 64) * 128 + (c % 64);  // column of the gate features in the tile
-                    uint32_t gr[16], ur[16];
-                    tmem_ld16(acc + gc, gr);
-                    tmem_ld16(acc + gc + 64, ur);
-                    const int f0 = (n0 / 2) + c;  // first output feature
-                    if (m >= g.M || n0 + gc + 64 >= g.N) continue;
-                    uint32_t packed[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        float v0 = __uint_as_float(gr[2 * e]), v1 = __uint_as_float(gr[2 * e + 1]);
-                        float u0 = __uint_as_float(ur[2 * e]), u1 = __uint_as_float(ur[2 * e + 1]);
-                        if (g.bias) {
-                            v0 += bias_many(g, n0 + gc + 2 * e); v1 += bias_many(g, n0 + gc + 2 * e + 1);
-                            u0 += bias_many(g, n0 + gc + 64 + 2 * e); u1 += bias_many(g, n0 + gc + 64 + 2 * e + 1);
-                        }
-                        __nv_bfloat162 v = __floats2bfloat162_rn(silu_mul<true>(v0, u0), silu_mul<true>(v1, u1));
-                        packed[e] = *reinterpret_cast<uint32_t*>(&v);
-                    }
-                    uint4* dst = reinterpret_cast<uint4*>((bf16*)g.C + (int64_t)m * g.ldc + f0);
-                    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                }
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
-        }
-    }
-    if (*gave_up && threadIdx.x == 0) atomicOr(g.err, SS_ERR_WAIT_LIMIT);
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 1) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
-    }
-}
-
-// The same with 256 x 256 tiles: two 128-row products per K step share the weight tile (it is fetched once for 256
-// rows), both accumulators are in use, so the next tile's products wait for the epilogue.
-__global__ void __launch_bounds__(TC_THREADS)
-gemm_tc5_many256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const ManyArgs g) {
-    constexpr int A_BYTES = 2 * TC_BM * TC_BK * 2, B_BYTES = MT_BN * TC_BK * 2, STAGES = 3;  // A: two 128-row sub-tiles
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * (A_BYTES + B_BYTES));
-    uint64_t* empty = full + STAGES;
-    uint64_t* acc_full = empty + STAGES;   // 2: the MMA lane has finished a tile in this accumulator
-    uint64_t* acc_empty = acc_full + 2;    // 2: the epilogue has read it out
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-    volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-    pdl_launch_dependents();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_m = (g.M + 2 * TC_BM - 1) / (2 * TC_BM), n_n = (g.N + MT_BN - 1) / MT_BN, n_tiles = n_m * n_n;
-    const int k_iters = (g.K + TC_BK - 1) / TC_BK;
-
-    if (threadIdx.x == 0) {
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
-        *gave_up = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_slot)), "r"(512));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = *tmem_slot;
-    pdl_wait();
-
-    if (warp == 0 && lane == 0) {
-        // ---- producer: one stream of K tiles across all of this block's output tiles
-        int it = 0;
-        bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-            const int m0 = (t % n_m) * 2 * TC_BM, n0 = (t / n_m) * MT_BN;
-            for (int k = 0; k < k_iters; ++k, ++it) {
-                const int s = it % STAGES;
-                if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, gave_up)) { ok = false; break; }
-                mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                unsigned char* a_tile = tiles + s * (A_BYTES + B_BYTES);
-                tma_load_2d(a_tile, &map_a, k * TC_BK, m0, &full[s]);
-                tma_load_2d(a_tile + A_BYTES / 2, &map_a, k * TC_BK, m0 + TC_BM, &full[s]);
-                tma_load_2d(a_tile + A_BYTES, &map_b, k * TC_BK, n0, &full[s]);
-            }
-        }
-    } else if (warp == 1) {
-        // ---- MMA issuer: the warp walks the tiles, an elected lane issues
-        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-        int it = 0, j = 0;
-        bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++j) {
-            if (j >= 1 && !__all_sync(0xffffffffu, mbar_wait(&acc_empty[0], (j - 1) & 1, gave_up))) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            for (int k = 0; k < k_iters; ++k, ++it) {
-                const int s = it % STAGES;
-                if (!__all_sync(0xffffffffu, mbar_wait(&full[s], (it / STAGES) & 1, gave_up))) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                unsigned char* a_tile = tiles + s * (A_BYTES + B_BYTES);
-                const uint64_t a_desc = smem_desc(a_tile), a2_desc = smem_desc(a_tile + A_BYTES / 2), b_desc = smem_desc(a_tile + A_BYTES);
-                if (elect_one()) {
-#pragma unroll
-                    for (int kk = 0; kk < TC_BK / 16; ++kk) {
-                        umma_f16(tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, (k | kk) != 0);
-                        umma_f16(tmem + MT_BN, a2_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, (k | kk) != 0);
-                    }
-                    umma_commit(&empty[s]);
-                }
-                __syncwarp();
-            }
-            if (elect_one()) umma_commit(&acc_full[0]);
-            __syncwarp();
-        }
-    } else if (warp >= 2) {
-        // ---- epilogue: warp w reads lanes 32 * (w % 4) .. + 31 of the accumulator: one output row per thread
-        const int quarter = warp & 3;
-        int j = 0;
-        bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++j) {
-            const int n0 = (t / n_m) * MT_BN;
-            ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[0], j & 1, gave_up));
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            for (int sub = 0; sub < 2; ++sub) {
-            const int m0 = (t % n_m) * 2 * TC_BM + sub * TC_BM;
-            const int m = m0 + quarter * 32 + lane;
-            const uint32_t acc = tmem + ((uint32_t)(quarter * 32) << 16) + sub * MT_BN;
-            if (!g.swiglu) {
-#pragma unroll 1
-                for (int c = 0; c < MT_BN; c += 16) {
-                    uint32_t r[16];
-                    tmem_ld16(acc + c, r);
-                    if (m >= g.M || n0 + c >= g.N) continue;
-                    if (g.bias) {
-#pragma unroll
-                        for (int e = 0; e < 16; ++e) {
-                            const int f = n0 + c + e;
-                            if (f < g.N) r[e] = __float_as_uint(__uint_as_float(r[e]) + (g.bias_f32 ? ((const float*)g.bias)[f] : to_float(((const bf16*)g.bias)[f])));
-                        }
-                    }
-                    if (!g.out_f32 && n0 + c + 16 <= g.N && (g.ldc % 8 == 0)) {
-                        uint32_t packed[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
-                            packed[e] = *reinterpret_cast<uint32_t*>(&v);
-                        }
-                        uint4* dst = reinterpret_cast<uint4*>((bf16*)g.C + (int64_t)m * g.ldc + n0 + c);
-                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                    } else {
-                        for (int e = 0; e < 16 && n0 + c + e < g.N; ++e) {
-                            const int64_t at = (int64_t)m * g.ldc + n0 + c + e;
-                            if (g.out_f32) ((float*)g.C)[at] = __uint_as_float(r[e]);
-                            else ((bf16*)g.C)[at] = __float2bfloat16_rn(__uint_as_float(r[e]));
-                        }
-                    }
-                }
-            } else {
-                // columns [0,64) gate, [64,128) the matching up, [128,192) gate, [192,256) up
-#pragma unroll 1
-                for (int c = 0; c < MT_BN / 2; c += 16) {
-                    const int gc = (c / 64) * 128 + (c % 64);  // column of the gate features in the tile
-                    uint32_t gr[16], ur[16];
-                    tmem_ld16(acc + gc, gr);
-                    tmem_ld16(acc + gc + 64, ur);
-                    const int f0 = (n0 / 2) + c;  // first output feature
-                    if (m >= g.M || n0 + gc + 64 >= g.N) continue;
-                    uint32_t packed[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        float v0 = __uint_as_float(gr[2 * e]), v1 = __uint_as_float(gr[2 * e + 1]);
-                        float u0 = __uint_as_float(ur[2 * e]), u1 = __uint_as_float(ur[2 * e + 1]);
-                        if (g.bias) {
-                            v0 += bias_many(g, n0 + gc + 2 * e); v1 += bias_many(g, n0 + gc + 2 * e + 1);
-                            u0 += bias_many(g, n0 + gc + 64 + 2 * e); u1 += bias_many(g, n0 + gc + 64 + 2 * e + 1);
-                        }
-                        __nv_bfloat162 v = __floats2bfloat162_rn(silu_mul<true>(v0, u0), silu_mul<true>(v1, u1));
-                        packed[e] = *reinterpret_cast<uint32_t*>(&v);
-                    }
-                    uint4* dst = reinterpret_cast<uint4*>((bf16*)g.C + (int64_t)m * g.ldc + f0);
-                    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                }
-            }
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[0]);
-        }
-    }
-    if (*gave_up && threadIdx.x == 0) atomicOr(g.err, SS_ERR_WAIT_LIMIT);
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 1) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
-    }
-}
-
-// ---------------------------------------------------------------- many tokens, two SMs per product
-//
-// The same persistent scheme with tcgen05.mma.cta_group::2: the two blocks of a cluster compute one 256 x 256
-// tile.  Block r of the pair loads rows r * 128 .. of the A tile and rows r * 128 .. of the B tile (half of
-// each); the leader (block 0) issues the products, which read A and B out of both blocks' shared memory and
-// leave rows r * 128 .. of the result in block r's tensor memory.  A block thus fetches 32 KB per 64-wide K step
-// instead of 48 KB (six stages instead of four) and feeds the tensor core half of B.
-//   full[s]      in the leader: one arrival (the leader's producer, with the bytes of both blocks); the other
-//                block's copies complete their bytes on it too (cp.async.bulk.tensor .cta_group::2);
-//   empty[s]     in each block: tcgen05.commit with multicast to both;
-//   acc_full[b]  in each block: tcgen05.commit with multicast to both;
-//   acc_empty[b] in the leader: the eight epilogue warps of both blocks arrive.
-// The tile's width is a parameter (a multiple of 16 up to 256; the instruction's N).  The host picks it so that
-// the tiles fill whole rounds of the pairs: 2,048 x 3,584 outputs are 112 tiles of 256 x 256, one and a half rounds
-// of 74 pairs that cost two, but 144 tiles of 256 x 208, two rounds less 4 tiles that cost 0.81 of the former each.
 #define PR_STAGES 6
 
 __device__ __forceinline__ uint32_t leader_addr(const void* p) { return s_addr(p) & 0xFEFFFFFFu; }  // same offset in block 0 of the pair
@@ -1036,85 +707,53 @@ extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int b
 
 // C = A * B^T (+ bias) for many rows of A (prompt portions): A [M, K] activations, B [N, K] weights, both
 // bfloat16 and K-major, K a multiple of 8.  swiglu: B's rows alternate 64 gate and 64 up features (N a multiple of
-// 128); C [M, N / 2] = silu(gate) * up.  One persistent block per SM.  tile_rows 128 or 256: one-SM kernels;
-// 512: pairs of SMs, tiles of 256 rows and tile_cols columns (0: chosen here).
+// 128); C [M, N / 2] = silu(gate) * up.  One persistent block per SM, in pairs; tiles of 256 rows and tile_cols
+// columns (0: chosen here).
 extern "C" int ss_gemm_tc5_many(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
-                                int64_t lda, int64_t ldb, int64_t ldc, int out_f32, int swiglu, int tile_rows, int tile_cols,
+                                int64_t lda, int64_t ldb, int64_t ldc, int out_f32, int swiglu, int tile_cols,
                                 int* err, cudaStream_t stream) {
-    if (tile_rows != 128 && tile_rows != 256 && tile_rows != 512) return -2006;
-    const bool big = tile_rows == 256;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return -2003;
     if (((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2004;
     if (swiglu && (N % 128 != 0 || out_f32 || ldc % 8 != 0 || ((uintptr_t)C & 15))) return -2007;
-    if (tile_rows == 512) {  // 256-row tiles computed by pairs of blocks (tcgen05.mma.cta_group::2)
-        int n_sms = 148;
-        {
-            int dev = 0;
-            cudaGetDevice(&dev);
-            cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
-        }
-        const int max_pairs = n_sms / 2 > 0 ? n_sms / 2 : 1;
-        const int n_m = (M + 2 * TC_BM - 1) / (2 * TC_BM);
-        // The width whose tiles take the least time: rounds of the pairs times the time of a tile.  Per 16-wide K
-        // step a block's tensor core needs w / 2 cycles, and its shared memory 64 + w / 4 (4 KB of A and 16 w
-        // bytes of B, written by the copies and read by the product, at 128 bytes a cycle): narrower tiles are
-        // bound by shared memory, so they only pay where they save a round (measured at 2,048 x 3,584 x 18,944:
-        // 210 us at 256, 198 us at 208).  256 stays unless another width is 5 % better.
-        int bn = tile_cols > 0 ? tile_cols : MT_BN;
-        if (tile_cols <= 0 && !swiglu) {
-            auto cost = [&](int w) {
-                const int tiles = n_m * ((N + w - 1) / w);
-                const int per_tile = (w / 2 > 64 + w / 4 ? w / 2 : 64 + w / 4) + 4;
-                return (int64_t)((tiles + max_pairs - 1) / max_pairs) * per_tile;
-            };
-            int64_t best = cost(MT_BN) * 95 / 100;
-            for (int w = MT_BN - 16; w >= 64; w -= 16)
-                if (cost(w) < best) { best = cost(w); bn = w; }
-        }
-        if (bn < 16 || bn > MT_BN || bn % 16 != 0 || (swiglu && bn != MT_BN)) return -2006;
-        CUtensorMap ma, mb;
-        int rc = make_map(&ma, A, M, K, lda, TC_BM);
-        if (rc) return rc;
-        rc = make_map(&mb, B, N, K, ldb, bn / 2);  // a block loads half of the tile's rows of B
-        if (rc) return rc;
-        ManyArgs g;
-        g.C = C; g.bias = bias; g.err = err; g.M = M; g.N = N; g.K = K; g.ldc = ldc; g.out_f32 = out_f32;
-        g.bias_f32 = bias_f32; g.swiglu = swiglu; g.tile_cols = bn;
-        constexpr int smem_pair = PR_STAGES * (2 * TC_BM * TC_BK * 2) + 1024 + 256;
-        static int configured_pair = (int)cudaFuncSetAttribute(gemm_tc5_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pair);
-        if (configured_pair != 0) return configured_pair;
-        const int tiles2 = n_m * ((N + bn - 1) / bn);
-        const int pairs = tiles2 < max_pairs ? tiles2 : max_pairs;
-        ss_launch_cluster_x(gemm_tc5_pair_kernel, dim3(2 * pairs), dim3(TC_THREADS), smem_pair, stream, 2, ma, mb, g);
-        return SS_LAUNCH_CHECK();
+    int n_sms = 148;
+    {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
     }
+    const int max_pairs = n_sms / 2 > 0 ? n_sms / 2 : 1;
+    const int n_m = (M + 2 * TC_BM - 1) / (2 * TC_BM);
+    // The width whose tiles take the least time: rounds of the pairs times the time of a tile.  Per 16-wide K
+    // step a block's tensor core needs w / 2 cycles, and its shared memory 64 + w / 4 (4 KB of A and 16 w
+    // bytes of B, written by the copies and read by the product, at 128 bytes a cycle): narrower tiles are
+    // bound by shared memory, so they only pay where they save a round (measured at 2,048 x 3,584 x 18,944:
+    // 210 us at 256, 198 us at 208).  256 stays unless another width is 5 % better.
+    int bn = tile_cols > 0 ? tile_cols : MT_BN;
+    if (tile_cols <= 0 && !swiglu) {
+        auto cost = [&](int w) {
+            const int tiles = n_m * ((N + w - 1) / w);
+            const int per_tile = (w / 2 > 64 + w / 4 ? w / 2 : 64 + w / 4) + 4;
+            return (int64_t)((tiles + max_pairs - 1) / max_pairs) * per_tile;
+        };
+        int64_t best = cost(MT_BN) * 95 / 100;
+        for (int w = MT_BN - 16; w >= 64; w -= 16)
+            if (cost(w) < best) { best = cost(w); bn = w; }
+    }
+    if (bn < 16 || bn > MT_BN || bn % 16 != 0 || (swiglu && bn != MT_BN)) return -2006;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, M, K, lda, TC_BM);
     if (rc) return rc;
-    rc = make_map(&mb, B, N, K, ldb, MT_BN);
+    rc = make_map(&mb, B, N, K, ldb, bn / 2);  // a block loads half of the tile's rows of B
     if (rc) return rc;
     ManyArgs g;
     g.C = C; g.bias = bias; g.err = err; g.M = M; g.N = N; g.K = K; g.ldc = ldc; g.out_f32 = out_f32;
-    g.bias_f32 = bias_f32; g.swiglu = swiglu; g.tile_cols = MT_BN;
-    constexpr int smem = MT_STAGES * (TC_BM * TC_BK * 2 + MT_BN * TC_BK * 2) + 1024 + 256;
-    static int configured = (int)cudaFuncSetAttribute(gemm_tc5_many_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (configured != 0) return configured;
-    static int configured2 = (int)cudaFuncSetAttribute(gemm_tc5_many256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (configured2 != 0) return configured2;
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms <= 0) sms = 148;
-    }
-    if (big) {
-        const int tiles2 = ((M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((N + MT_BN - 1) / MT_BN);
-        ss_launch(gemm_tc5_many256_kernel, dim3(tiles2 < sms ? tiles2 : sms), dim3(TC_THREADS), smem, stream, ma, mb, g);
-        return SS_LAUNCH_CHECK();
-    }
-    const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + MT_BN - 1) / MT_BN);
-    ss_launch(gemm_tc5_many_kernel, dim3(tiles < sms ? tiles : sms), dim3(TC_THREADS), smem, stream, ma, mb, g);
+    g.bias_f32 = bias_f32; g.swiglu = swiglu; g.tile_cols = bn;
+    constexpr int smem_pair = PR_STAGES * (2 * TC_BM * TC_BK * 2) + 1024 + 256;
+    static int configured_pair = (int)cudaFuncSetAttribute(gemm_tc5_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pair);
+    if (configured_pair != 0) return configured_pair;
+    const int tiles2 = n_m * ((N + bn - 1) / bn);
+    const int pairs = tiles2 < max_pairs ? tiles2 : max_pairs;
+    ss_launch_cluster_x(gemm_tc5_pair_kernel, dim3(2 * pairs), dim3(TC_THREADS), smem_pair, stream, 2, ma, mb, g);
     return SS_LAUNCH_CHECK();
 }

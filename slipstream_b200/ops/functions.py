@@ -71,7 +71,7 @@ _ATTN_SIGNATURES = {
 
 _GEMM_SIGNATURES = {
     "ss_gemm_tc5_many": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
-                         c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                         c_int, c_int, c_int, c_void_p, c_void_p],
     "ss_gemm_tc5": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                     c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
@@ -680,18 +680,14 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
 
 
 def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
-                      out_dtype: torch.dtype | None = None, swiglu: bool = False,
-                      tile_rows: int | None = None, tile_cols: int = 0) -> torch.Tensor:
+                      out_dtype: torch.dtype | None = None, swiglu: bool = False, tile_cols: int = 0) -> torch.Tensor:
     """``x @ weight.T + bias`` for many rows of ``x`` (prompt portions) on the tcgen05 tensor cores: a persistent
-    kernel, one block per SM.  ``tile_rows`` 128: 128 x 256 output tiles, the accumulator double-buffered in
-    tensor memory so that the epilogue of a tile overlaps the products of the next; 256: 256 x 256 tiles, two
-    products sharing every weight tile; 512: 256 x 256 tiles computed by pairs of SMs (``tcgen05.mma.cta_group::2``:
-    each block of a pair loads half of A and half of B), accumulator double-buffered, the fastest of the three
-    where there are many tiles (the default when there are at least twice as many tiles as SMs).  ``tile_cols``
-    (with 512 rows only): the tiles' width, a multiple of 16 up to 256; 0 lets the launcher take the width whose
-    tiles fill whole rounds of the 74 pairs best.
+    kernel, one block per SM, the blocks in pairs (``tcgen05.mma.cta_group::2``: each block of a pair loads half
+    of A and half of B) that compute tiles of 256 rows with the accumulator double-buffered in tensor memory, so
+    that the epilogue of a tile overlaps the products of the next.  ``tile_cols``: the tiles' width, a multiple
+    of 16 up to 256; 0 lets the launcher take the width whose tiles fill whole rounds of the 74 pairs best.
     ``swiglu``: the weight's rows alternate 64 gate and 64 up features; the result is ``silu(gate) * up`` with
-    features / 2 columns."""
+    features / 2 columns (tiles of 256 columns)."""
     _need(x, torch.bfloat16, "x")
     _need(weight, torch.bfloat16, "weight")
     tokens, k = x.shape
@@ -710,11 +706,9 @@ def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor 
         bias_f32 = int(bias.dtype == torch.float32)
         if bias.numel() != features or bias.dtype not in (torch.float32, torch.bfloat16):
             raise KernelError("bias has the wrong size or dtype")
-    if tile_rows is None:
-        tile_rows = 512 if ((tokens + 255) // 256) * ((features + 255) // 256) >= 2 * 148 else 128
     rc = gemm_library().ss_gemm_tc5_many(x.data_ptr(), weight.data_ptr(), _ptr(bias), bias_f32, out.data_ptr(), tokens,
                                          features, k, k, k, out.shape[1], int(out_dtype == torch.float32), int(swiglu),
-                                         tile_rows, tile_cols, error_word(x.device).data_ptr(), _stream())
+                                         tile_cols, error_word(x.device).data_ptr(), _stream())
     _check(rc, "gemm_tcgen05_many")
     return out
 
@@ -761,11 +755,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
 
 def many_tokens_swiglu_fits(tokens: int, features: int) -> bool:
     """Where the persistent tcgen05 kernel with its fused SwiGLU epilogue is at least as fast as the library
-    product followed by the SwiGLU kernel: enough 256 x 256 tiles to keep every SM busy for several rounds
-    (2,048 tokens x 37,888 features: 376 us against 382 us, and no [tokens, 2 I] intermediate).  A block of
-    this kernel cannot feed the tensor core faster than shared memory delivers both operands of a 128 x 256
-    product (about 1.3 PFLOP/s measured against the library's 1.6 with two-SM products), so without an epilogue
-    to fuse the library product stays."""
+    product followed by the SwiGLU kernel: enough 256 x 256 tiles to keep every pair of SMs busy for several
+    rounds (2,048 tokens x 37,888 features: 347 us against 348 + 40 us, and no [tokens, 2 I] intermediate; 1,024
+    tokens: 205 against 179 + 20; 512 tokens: 108 against 95 + 10, where the library stays).  Without an epilogue
+    to fuse, the library product is as fast as ours or up to 10 % faster, and stays."""
     return ((tokens + 255) // 256) * ((features + 255) // 256) >= 4 * 148
 
 

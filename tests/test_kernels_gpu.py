@@ -347,11 +347,10 @@ def test_tcgen05_persistent_product_for_many_tokens(tokens, features, k):
     w = (torch.randn(features, k, device=DEV) * 0.05).bfloat16()
     b = torch.randn(features, device=DEV).bfloat16()
     ref = x.double() @ w.double().T
-    for rows in (128, 256, 512):  # 128 x 256 tiles, accumulator double-buffered; 256 x 256 tiles; 256 x 256 tiles by pairs of SMs
-        got = ops().gemm_tcgen05_many(x, w, None, torch.float32, tile_rows=rows)
-        assert rel_err(got, ref) < 2e-5, "float32 output of bfloat16 inputs is exact up to the order of additions"
-        assert rel_err(ops().gemm_tcgen05_many(x, w, b, tile_rows=rows), ref + b.double()) < 6e-3
-        assert rel_err(ops().gemm_tcgen05_many(x, w, b.float(), torch.float32, tile_rows=rows), ref + b.double()) < 2e-5
+    got = ops().gemm_tcgen05_many(x, w, None, torch.float32)
+    assert rel_err(got, ref) < 2e-5, "float32 output of bfloat16 inputs is exact up to the order of additions"
+    assert rel_err(ops().gemm_tcgen05_many(x, w, b), ref + b.double()) < 6e-3
+    assert rel_err(ops().gemm_tcgen05_many(x, w, b.float(), torch.float32), ref + b.double()) < 2e-5
     ops().check_errors(torch.device(DEV))
 
 
@@ -365,11 +364,11 @@ def test_tcgen05_two_sm_product_at_every_tile_width(tokens, features, k):
     b = torch.randn(features, device=DEV).bfloat16()
     ref = x.double() @ w.double().T + b.double()
     for cols in (0, 16, 48, 64, 112, 208, 240, 256):
-        got = ops().gemm_tcgen05_many(x, w, b, torch.float32, tile_rows=512, tile_cols=cols)
+        got = ops().gemm_tcgen05_many(x, w, b, torch.float32, tile_cols=cols)
         assert rel_err(got, ref) < 2e-5, cols
     for cols in (8, 24, 272):
         with pytest.raises(ops().KernelError):
-            ops().gemm_tcgen05_many(x, w, b, torch.float32, tile_rows=512, tile_cols=cols)
+            ops().gemm_tcgen05_many(x, w, b, torch.float32, tile_cols=cols)
     ops().check_errors(torch.device(DEV))
 
 
@@ -382,9 +381,8 @@ def test_tcgen05_persistent_product_with_swiglu(tokens, inter, k, bias):
     mix = lambda a, b: torch.stack([a.reshape(inter // 64, 64, *a.shape[1:]), b.reshape(inter // 64, 64, *b.shape[1:])], 1).reshape(2 * inter, *a.shape[1:]).contiguous()
     g = x.double() @ gate.double().T + (bg.double() if bias else 0)
     u = x.double() @ up.double().T + (bu.double() if bias else 0)
-    for rows in (128, 256, 512):
-        got = ops().gemm_tcgen05_many(x, mix(gate, up), mix(bg, bu) if bias else None, swiglu=True, tile_rows=rows)
-        assert got.shape == (tokens, inter) and rel_err(got, g * torch.sigmoid(g) * u) < 8e-3, rows
+    got = ops().gemm_tcgen05_many(x, mix(gate, up), mix(bg, bu) if bias else None, swiglu=True)
+    assert got.shape == (tokens, inter) and rel_err(got, g * torch.sigmoid(g) * u) < 8e-3
     ops().check_errors(torch.device(DEV))
 
 
