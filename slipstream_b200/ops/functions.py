@@ -713,6 +713,12 @@ def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor 
     return out
 
 
+# From this many tokens every bfloat16 projection runs the persistent two-SM kernel.  Against the library at the 7B
+# sizes (us, ours / library): 1,024 tokens q/k/v 29.3 / 26.5, o 25.0 / 26.0, down 100.5 / 103.9; 2,048 tokens
+# 49.6 / 45.1, 41.6-47.7 / 45.4-52.8, 191.9-198.2 / 191.6-208.7; a whole 2,048-token prefill takes 22.1 to 25.5 ms
+# either way (the GPU sits at its power cap), and its first call 35 ms instead of 160.  At 512 tokens and below
+# the library, which splits K, is 1.3 to 2 times faster.
+MANY_TOKENS = 1024
 SMALL_BATCH = 64  # up to this many tokens a projection may stream its weights through the tcgen05 kernel
 STREAM_TILES = 148  # ... when its 128-row weight tiles are at least as many as the SMs (no K slices needed)
 CLUSTER_BATCH = 16  # ... or, up to this many tokens, whatever its size (K slices added inside a cluster)
@@ -737,12 +743,15 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
 
     float32 runs the CUDA-core kernel (no reduced-precision matrix mode).  bfloat16 with few tokens (decode
     steps) and a large weight runs the hand-written tcgen05 kernel, which streams the weights once and
-    overlaps its first fetches with the kernel before it; other bfloat16 products run the library matrix
-    product, as the reference's nn.Linear does (slipstream/models/layers/attention.py:132-135)."""
+    overlaps its first fetches with the kernel before it; from ``MANY_TOKENS`` tokens (prompt portions) the
+    persistent two-SM tcgen05 kernel; what lies between runs the library matrix product, as the reference's
+    nn.Linear does (slipstream/models/layers/attention.py:132-135)."""
     if x.dtype == torch.float32:
         return gemm_simt(x, weight, bias, out_dtype)
     if streams_weights(x.shape[0], weight.shape[0], x.shape[1]):
         return gemm_tcgen05(x, weight, bias, out_dtype)
+    if x.shape[0] >= MANY_TOKENS and x.shape[1] % 8 == 0:
+        return gemm_tcgen05_many(x, weight, bias, out_dtype)
     if out_dtype is None or out_dtype == x.dtype:
         if bias is not None:
             return torch.addmm(bias, x, weight.t())
