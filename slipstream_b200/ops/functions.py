@@ -713,12 +713,16 @@ def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor 
     return out
 
 
-# From this many tokens every bfloat16 projection runs the persistent two-SM kernel.  Against the library at the 7B
-# sizes (us, ours / library): 1,024 tokens q/k/v 29.3 / 26.5, o 25.0 / 26.0, down 100.5 / 103.9; 2,048 tokens
-# 49.6 / 45.1, 41.6-47.7 / 45.4-52.8, 191.9-198.2 / 191.6-208.7; a whole 2,048-token prefill takes 22.1 to 25.5 ms
-# either way (the GPU sits at its power cap), and its first call 35 ms instead of 160.  At 512 tokens and below
-# the library, which splits K, is 1.3 to 2 times faster.
-MANY_TOKENS = 1024
+# From this many tokens a bfloat16 projection whose weight is at least MANY_WIDTH on both sides runs the persistent
+# two-SM kernel.  Against the library (us, ours / library) at 2,048 tokens: 7B sizes q/k/v 49.6 / 45.1, o 41.6-47.7 /
+# 45.4-52.8, down 191.9-198.2 / 191.6-208.7; 14B sizes 109.4 / 114.6, 79.7 / 77.0, 200.3 / 207.2; a whole 2,048-token
+# prefill of the 7B shape takes 22.1 to 25.5 ms either way (the GPU sits at its power cap), and its first call 35
+# ms instead of 160.  With fewer tokens or smaller weights there are too few 256-row tiles for the 74 pairs and
+# the library, which splits K, wins: 1,024 tokens at 14B sizes by up to 18 %, 0.5B and 1.5B sizes at any number
+# of tokens by up to 50 %, 512 tokens and below by 1.3 to 2 times.  (Cutting K into parts inside this kernel,
+# with the parts' sums meeting in scratch memory, was tried for those cases and did not beat narrower tiles.)
+MANY_TOKENS = 2048
+MANY_WIDTH = 3584
 SMALL_BATCH = 64  # up to this many tokens a projection may stream its weights through the tcgen05 kernel
 STREAM_TILES = 148  # ... when its 128-row weight tiles are at least as many as the SMs (no K slices needed)
 CLUSTER_BATCH = 16  # ... or, up to this many tokens, whatever its size (K slices added inside a cluster)
@@ -743,14 +747,15 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
 
     float32 runs the CUDA-core kernel (no reduced-precision matrix mode).  bfloat16 with few tokens (decode
     steps) and a large weight runs the hand-written tcgen05 kernel, which streams the weights once and
-    overlaps its first fetches with the kernel before it; from ``MANY_TOKENS`` tokens (prompt portions) the
-    persistent two-SM tcgen05 kernel; what lies between runs the library matrix product, as the reference's
+    overlaps its first fetches with the kernel before it; from ``MANY_TOKENS`` tokens (prompt portions) and with
+    a weight of ``MANY_WIDTH`` or more on both sides the persistent two-SM tcgen05 kernel; everything else runs the
+    library matrix product, as the reference's
     nn.Linear does (slipstream/models/layers/attention.py:132-135)."""
     if x.dtype == torch.float32:
         return gemm_simt(x, weight, bias, out_dtype)
     if streams_weights(x.shape[0], weight.shape[0], x.shape[1]):
         return gemm_tcgen05(x, weight, bias, out_dtype)
-    if x.shape[0] >= MANY_TOKENS and x.shape[1] % 8 == 0:
+    if x.shape[0] >= MANY_TOKENS and min(weight.shape) >= MANY_WIDTH and x.shape[1] % 8 == 0:
         return gemm_tcgen05_many(x, weight, bias, out_dtype)
     if out_dtype is None or out_dtype == x.dtype:
         if bias is not None:
