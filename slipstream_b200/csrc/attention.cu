@@ -96,10 +96,11 @@ extern "C" int ss_attn_prefill_tc5(const void* q, int64_t q_stride, int n_tokens
                                    const void* kv, const int32_t* block_tables, int max_blocks,
                                    const int32_t* tile_req, const int32_t* tile_tok0, int n_tiles,
                                    const int32_t* q_start, const int32_t* seq_lens, int n_q, int n_kv, int page_size,
-                                   int64_t num_pages, float scale, int* err, cudaStream_t stream) {
+                                   int64_t num_pages, float scale, int splits, int* err, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     const int G = n_q / n_kv;
     if (G < 1 || G > 128 || page_size % 8 != 0 || 64 % page_size != 0 || q_stride % 8 != 0) return -3003;
+    if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -3004;
     const int TOK = 128 / G;
     CUtensorMap map_q, map_kv;
     int rc = fa::make_map3(&map_q, q, HEAD_DIM, (uint64_t)n_q, (uint64_t)n_tokens, (uint64_t)HEAD_DIM * 2,
@@ -115,7 +116,11 @@ extern "C" int ss_attn_prefill_tc5(const void* q, int64_t q_stride, int n_tokens
     constexpr int smem = fa::smem_bytes<HEAD_DIM>();
     static int configured = set_smem(fa::attn_prefill_tc5<HEAD_DIM>, smem);
     if (configured != 0) return configured;
-    ss_launch(fa::attn_prefill_tc5<HEAD_DIM>, dim3(n_tiles, n_kv), dim3(FA_THREADS), smem, stream, map_q, map_kv, a);
+    // splits > 1: the key tiles of every query tile are shared by a thread-block cluster of that many blocks
+    if (splits > 1)
+        ss_launch_cluster(fa::attn_prefill_tc5<HEAD_DIM>, dim3(n_tiles, n_kv, splits), dim3(FA_THREADS), smem, stream, splits, map_q, map_kv, a);
+    else
+        ss_launch(fa::attn_prefill_tc5<HEAD_DIM>, dim3(n_tiles, n_kv), dim3(FA_THREADS), smem, stream, map_q, map_kv, a);
     return SS_LAUNCH_CHECK();
 }
 

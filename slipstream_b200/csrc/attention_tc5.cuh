@@ -184,7 +184,14 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int rows_valid = toks_here * G;
     const int pos0 = seq_len - q_len + tok0;           // position of the tile's first token
     const int last_pos = pos0 + toks_here - 1;
-    const int n_tiles = last_pos / FA_BN + 1;          // key tiles 0 .. n_tiles - 1
+    // The key tiles 0 .. last_pos / 64 of this query tile are shared by the blocks of a thread-block cluster along z
+    // (one block when the grid has one layer): block `part` takes tiles t_lo .. t_lo + n_tiles - 1, and the
+    // blocks' results are combined through their shared memory at the end.
+    const int splits = gridDim.z, part = blockIdx.z;
+    const int all_tiles = last_pos / FA_BN + 1;
+    const int per_part = (all_tiles + splits - 1) / splits;
+    const int t_lo = min(part * per_part, all_tiles);
+    const int n_tiles = min(all_tiles, t_lo + per_part) - t_lo;  // may be 0
     const int32_t* table = a.block_tables + (int64_t)r * a.max_blocks;
 
     if (threadIdx.x == 0) {
@@ -215,7 +222,7 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         // cycles a tile and bounded the kernel.  Here lane p * HALVES + h issues the copy of page p, half h, and
         // reads that page's block-table entry itself; keys and values go out side by side from two warps.
         const bool keys = warp == 0;
-        if (keys && lane == 0) {
+        if (keys && lane == 0 && n_tiles > 0) {
             mbar_expect_tx(q_full, (uint32_t)(TOK * G * 128 * HALVES));
             for (int h = 0; h < HALVES; ++h)
                 tma_load_3d(Qs + h * HALF_Q, &map_q, h * 64, kvh * G, qs + tok0, q_full);
@@ -227,7 +234,7 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         int64_t spare = __ldg(table);  // keys past the request's end are masked; any finite page will do
         if (spare < 0 || spare >= a.num_pages) spare = 0;
         auto entry = [&](int j) -> int32_t {  // the raw entry: it is looked at one tile later, when it has arrived
-            const int blk = j * pages_per_tile + p;
+            const int blk = (t_lo + j) * pages_per_tile + p;
             return (mine && blk < live_blocks) ? __ldg(table + blk) : -1;
         };
         int32_t next_entry = entry(0);
@@ -273,7 +280,7 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
             for (int s = 0; s < FA_KS; ++s) k_desc[s][h] = desc_k_major(Ks + s * KV_BYTES + h * HALF_KV);
         }
-        bool ok = __all_sync(0xffffffffu, mbar_wait(q_full, 0, gave_up));
+        bool ok = n_tiles == 0 || __all_sync(0xffffffffu, mbar_wait(q_full, 0, gave_up));
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int st = j & 1, kst = j % FA_KS;
             ok = mbar_wait(&k_full[kst], (j / FA_KS) & 1, gave_up);
@@ -339,10 +346,11 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             tmem_ld32(tmem + lane_base + st * FA_BN + 32, sr[1]);
             tmem_ld_wait();
             // raw scores; the scale is folded into the exponent below.  Four running maxima keep the chain short.
-            if (j * FA_BN + FA_BN - 1 > pos) {  // the diagonal tile: keys after the row's own position are masked
+            const int key0 = (t_lo + j) * FA_BN;
+            if (key0 + FA_BN - 1 > pos) {  // the diagonal tile: keys after the row's own position are masked
 #pragma unroll
                 for (int c = 0; c < 64; ++c)
-                    if (j * FA_BN + c > pos) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
+                    if (key0 + c > pos) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -378,10 +386,13 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             // next, which reuses the buffer, is issued behind that PV product.
             uint32_t packed[32];
             float l4[4] = {0.f, 0.f, 0.f, 0.f};
+            // a row that has seen no key yet (its block's part of the keys may begin behind the row's position)
+            // has no maximum: its masked scores must give 0, not exp2(-inf + inf)
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
 #pragma unroll
             for (int c = 0; c < 64; c += 2) {
-                const float p0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), scale_log2, -m_ref));
-                const float p1 = ex2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), scale_log2, -m_ref));
+                const float p0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), scale_log2, -m_use));
+                const float p1 = ex2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), scale_log2, -m_use));
                 l4[(c >> 1) & 3] += p0 + p1;
                 __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
                 packed[c >> 1] = *reinterpret_cast<uint32_t*>(&v);
@@ -394,31 +405,103 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             if (lane == 0) mbar_arrive(&p_ready[st]);  // one arrival per softmax warp
         }
         // ---------------- epilogue: O / l for the rows that hold a query
-        if (ok) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, gave_up);
+        if (ok && n_tiles > 0) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, gave_up);
         ok = __all_sync(0xffffffffu, ok);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            bf16* dst = a.out + (int64_t)(qs + tok0 + tok) * a.out_stride + (int64_t)(kvh * G + g) * D;
+        if (splits == 1) {
+            if (ok) {
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                bf16* dst = a.out + (int64_t)(qs + tok0 + tok) * a.out_stride + (int64_t)(kvh * G + g) * D;
 #pragma unroll 1
-            for (int c = 0; c < D; c += 32) {
-                uint32_t o[32];
-                tmem_ld32(tmem + lane_base + 128 + c, o);
-                tmem_ld_wait();
-                if (valid) {
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem + lane_base + 128 + c, o);
+                    tmem_ld_wait();
+                    if (valid) {
 #pragma unroll
-                    for (int e = 0; e < 32; e += 8) {
-                        uint32_t packed[4];
+                        for (int e = 0; e < 32; e += 8) {
+                            uint32_t packed[4];
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(o[e + 2 * k]) * inv, __uint_as_float(o[e + 2 * k + 1]) * inv);
-                            packed[k] = *reinterpret_cast<uint32_t*>(&v);
+                            for (int k = 0; k < 4; ++k) {
+                                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(o[e + 2 * k]) * inv, __uint_as_float(o[e + 2 * k + 1]) * inv);
+                                packed[k] = *reinterpret_cast<uint32_t*>(&v);
+                            }
+                            *reinterpret_cast<uint4*>(dst + c + e) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                         }
-                        *reinterpret_cast<uint4*>(dst + c + e) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                     }
                 }
             }
+        } else {
+            // Several blocks share this query tile's keys: leave the unnormalised O (column-major, so that a warp's
+            // 32 rows lie side by side), the reference maximum and the sum in shared memory, over the Q and K tiles
+            // (every product that read them is complete), for the blocks of the cluster to combine below.
+            float* Osm = reinterpret_cast<float*>(base);
+            float* Msm = Osm + D * 128;
+            float* Lsm = Msm + 128;
+            const bool have = ok && n_tiles > 0;
+#pragma unroll 1
+            for (int c = 0; c < D; c += 32) {
+                uint32_t o[32];
+                if (n_tiles > 0) {
+                    tmem_ld32(tmem + lane_base + 128 + c, o);
+                    tmem_ld_wait();
+                }
+#pragma unroll
+                for (int e = 0; e < 32; ++e) Osm[(c + e) * 128 + row] = have ? __uint_as_float(o[e]) : 0.f;
+            }
+            Msm[row] = have ? m_ref : -INFINITY;
+            Lsm[row] = have ? l : 0.f;
         }
+    }
+    if (splits > 1) {
+        cluster_sync_all();  // every block's O, maximum and sum are in its shared memory
+        if (warp >= 2 && warp < 6) {
+            // block `part` combines columns part * D / splits .. of all rows: thread = row, as in the softmax
+            const int row = (warp & 3) * 32 + lane;
+            const float* Osm = reinterpret_cast<const float*>(base);
+            const float* Msm = Osm + D * 128;
+            const float* Lsm = Msm + 128;
+            float ms[8], w[8];
+            float m_all = -INFINITY, l_all = 0.f;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+                ms[sp] = sp < splits ? ld_cluster_f32(Msm + row, (uint32_t)sp) : -INFINITY;
+                m_all = fmaxf(m_all, ms[sp]);
+            }
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+                w[sp] = (sp < splits && ms[sp] != -INFINITY) ? ex2(ms[sp] - m_all) : 0.f;
+                if (sp < splits) l_all += w[sp] * ld_cluster_f32(Lsm + row, (uint32_t)sp);
+            }
+            const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+            const int cols = D / splits, c0 = part * cols;  // D / splits is a multiple of 8: 8 bfloat16 per store
+            const bool valid = row < rows_valid;
+            const int tok = valid ? row / G : 0, g = valid ? row - tok * G : 0;
+            bf16* dst = a.out + (int64_t)(qs + tok0 + tok) * a.out_stride + (int64_t)(kvh * G + g) * D + c0;
+#pragma unroll 1
+            for (int c = 0; c < cols; c += 8) {
+                float acc[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+                for (int sp = 0; sp < 8; ++sp) {
+                    if (sp < splits) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[e] += w[sp] * ld_cluster_f32(Osm + (c0 + c + e) * 128 + row, (uint32_t)sp);
+                    }
+                }
+                if (valid) {
+                    uint32_t packed[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        __nv_bfloat162 v = __floats2bfloat162_rn(acc[2 * k] * inv, acc[2 * k + 1] * inv);
+                        packed[k] = *reinterpret_cast<uint32_t*>(&v);
+                    }
+                    *reinterpret_cast<uint4*>(dst + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                }
+            }
+        }
+        cluster_sync_all();  // nobody leaves while its shared memory is still being read
     }
     if (*gave_up && threadIdx.x == 0) atomicOr(a.err, SS_ERR_WAIT_LIMIT);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

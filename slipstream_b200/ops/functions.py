@@ -16,6 +16,7 @@ import ctypes
 import functools
 from ctypes import c_float, c_int, c_int64, c_void_p
 
+import numpy as np
 import torch
 
 from .library import KernelBuildError, load_library, require_cuda
@@ -59,7 +60,7 @@ _ATTN_SIGNATURES = {
                             c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float,
                             c_int, c_void_p, c_void_p],
     "ss_attn_prefill_tc5": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
-                            c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_void_p,
+                            c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_void_p,
                             c_void_p],
     "ss_attn_decode_tma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
@@ -368,10 +369,12 @@ def tcgen05_attention_fits(head_dim: int, n_q: int, n_kv: int, page_size: int, w
 def paged_attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
                                     block_tables: torch.Tensor, tile_req: torch.Tensor, tile_tok0: torch.Tensor,
                                     q_start: torch.Tensor, seq_lens: torch.Tensor, n_q: int, n_kv: int,
-                                    head_dim: int, scale: float) -> None:
+                                    head_dim: int, scale: float, key_parts: int = 1) -> None:
     """bfloat16 causal attention for prompt portions and mixed batches on the tcgen05 tensor cores (Q, K, V
     tiles by TMA, S and O in tensor memory).  A tile is ``128 // (n_q // n_kv)`` consecutive query tokens of
-    one request: ``tile_req`` / ``tile_tok0`` list (request index, first token within the request's rows)."""
+    one request: ``tile_req`` / ``tile_tok0`` list (request index, first token within the request's rows).
+    ``key_parts`` (1, 2, 4 or 8): the keys of every query tile are shared by that many blocks, a thread-block
+    cluster whose results are combined through shared memory (see ``prefill_key_parts``)."""
     _need(out, torch.bfloat16, "attention output")
     _need(kv, torch.bfloat16, "kv pages")
     if q.dtype != torch.bfloat16:
@@ -385,8 +388,29 @@ def paged_attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.T
     _check(lib.ss_attn_prefill_tc5(q.data_ptr(), q_stride, q.shape[0], out.data_ptr(), out.shape[1], kv.data_ptr(),
                                    block_tables.data_ptr(), block_tables.shape[1], tile_req.data_ptr(),
                                    tile_tok0.data_ptr(), tile_req.numel(), q_start.data_ptr(), seq_lens.data_ptr(),
-                                   n_q, n_kv, kv.shape[3], kv.shape[0], float(scale),
+                                   n_q, n_kv, kv.shape[3], kv.shape[0], float(scale), int(key_parts),
                                    error_word(q.device).data_ptr(), _stream()), "paged_attention_prefill_tcgen05")
+
+
+def prefill_key_parts(q_lens: np.ndarray, seq_lens: np.ndarray, tile_tokens: int, n_kv: int) -> int:
+    """Into how many parts the tcgen05 prefill kernel should cut the keys of its query tiles.  A block walks its
+    key tiles one after the other, about a microsecond each, so a step with few query tiles lasts as long as its
+    longest one while most SMs idle: a portion of 64 tokens behind 4,096 cached ones is 16 blocks of 64 key
+    tiles, 47.5 us; with the keys of every query tile shared by 8 blocks 19.3 us; 512 tokens behind 4,096: 52.3
+    against 41.5 us with 2.  Parts are only worth it while all blocks still run at once (every block pays for
+    its own set-up and for the combination: a whole prompt of 2,048 tokens, 456 blocks, takes 47.5 us in one
+    part and 59.3 in two) and while a part keeps 8 key tiles."""
+    q_lens = np.asarray(q_lens, dtype=np.int64)
+    seq_lens = np.asarray(seq_lens, dtype=np.int64)
+    if q_lens.size == 0:
+        return 1
+    counts = (q_lens + tile_tokens - 1) // tile_tokens
+    blocks = int(counts.sum()) * n_kv
+    longest = int(seq_lens.max() - 1) // 64 + 1  # key tiles of the last query tile of the longest request
+    parts = 1
+    while parts < 8 and blocks * parts * 2 <= 2 * 148 and longest >= 16 * parts:
+        parts *= 2
+    return parts
 
 
 _DECODE_COUNTERS = 65536
@@ -540,8 +564,12 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
         return
     if tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], window):
         tile_req, tile_tok0 = ctx.query_tiles(128 // group, 1)
+        key = ("prefill_key_parts", 128 // group, n_kv)
+        parts = ctx.extras.get(key)
+        if parts is None:  # the same for every layer of the step
+            parts = ctx.extras[key] = prefill_key_parts(ctx.q_lens_host, ctx.seq_lens_host, 128 // group, n_kv)
         paged_attention_prefill_tcgen05(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_tok0, ctx.q_start,
-                                        ctx.seq_lens, n_q, n_kv, head_dim, scale)
+                                        ctx.seq_lens, n_q, n_kv, head_dim, scale, parts)
         return
     tile_req, tile_row0 = ctx.query_tiles(64, group)
     paged_attention_prefill(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_row0, ctx.q_start,
@@ -798,5 +826,5 @@ def set_programmatic_launch(enabled: bool) -> None:
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
            "attention_library"]

@@ -436,10 +436,11 @@ def test_tcgen05_prefill_attention(case):
     from slipstream_b200.engine.context import query_tiles_host
     tok = 128 // (n_q // n_kv)
     req, t0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(np.asarray(q_lens, dtype=np.int32), tok))
-    out = torch.full((q.shape[0], n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
-    ops().paged_attention_prefill_tcgen05(q.view(q.shape[0], -1), n_q * d, out, kv, table, req, t0, q_start, seq_lens,
-                                          n_q, n_kv, d, scale)
-    assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2
+    for parts in (1, 2, 4, 8):  # blocks of a cluster that share the keys of a query tile (some get none of them)
+        out = torch.full((q.shape[0], n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+        ops().paged_attention_prefill_tcgen05(q.view(q.shape[0], -1), n_q * d, out, kv, table, req, t0, q_start, seq_lens,
+                                              n_q, n_kv, d, scale, parts)
+        assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2, parts
     ops().check_errors(torch.device(DEV))
 
 
@@ -456,9 +457,10 @@ def test_tcgen05_prefill_attention_with_growing_maxima():
     ref = attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, scale, 0)
     from slipstream_b200.engine.context import query_tiles_host
     req, t0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(np.asarray([n], dtype=np.int32), 128 // 7))
-    out = torch.full((n, n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
-    ops().paged_attention_prefill_tcgen05(q.view(n, -1), n_q * d, out, kv, table, req, t0, q_start, seq_lens, n_q, n_kv, d, scale)
-    assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2
+    for parts in (1, 4):
+        out = torch.full((n, n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+        ops().paged_attention_prefill_tcgen05(q.view(n, -1), n_q * d, out, kv, table, req, t0, q_start, seq_lens, n_q, n_kv, d, scale, parts)
+        assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2, parts
     ops().check_errors(torch.device(DEV))
 
 
@@ -489,6 +491,9 @@ def test_a_standout_key_at_a_page_or_tile_edge(dtype, sharp):
             req, t0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(ql, 64))
             ops().paged_attention_prefill_tcgen05(q.view(q.shape[0], -1), n_q * d, out, kv, table, req, t0, q_start, seq_lens, n_q, n_kv, d, 1.0)
             outs["tcgen05"] = out
+            out = torch.zeros_like(out)
+            ops().paged_attention_prefill_tcgen05(q.view(q.shape[0], -1), n_q * d, out, kv, table, req, t0, q_start, seq_lens, n_q, n_kv, d, 1.0, 8)
+            outs["tcgen05, keys in 8 parts"] = out
         for name, o in outs.items():
             assert o[row].float().min() > 4.9, (name, q_len)
             assert rel_err(o.view_as(ref).cpu(), ref) < tol(dtype, 3e-6, 1e-2), (name, q_len)

@@ -164,3 +164,34 @@ def test_long_requests_decode_through_a_graph_with_more_slices(tmp_path, monkeyp
     for a, b in zip(wide_rows, narrow_rows):
         assert np.abs(a - b).max() <= 0.5 * TOLERANCE["bfloat16"] * np.abs(b).max()
         assert not np.array_equal(a, b), "both runs took the same path"
+
+
+def test_short_portions_behind_a_long_prefix_share_their_keys_among_blocks(tmp_path):
+    """A portion of a few dozen tokens behind a thousand cached ones is a handful of query tiles with many key
+    tiles each: the tcgen05 prefill kernel then cuts the keys of every query tile into parts that a thread-block
+    cluster combines.  Portions of 40 to 636 tokens behind 1,060 to 2,100 cached ones (2 and 4 parts at these
+    lengths; the kernel tests cover 8) against the oracle."""
+    from slipstream_b200 import ops
+    from slipstream_b200.config.model_config import Qwen2Config
+    from slipstream_b200.engine.runner import ModelRunner
+    from slipstream_b200.weights.random_init import write_random_model
+    from conftest import sharpen
+
+    config = Qwen2Config(vocab_size=211, hidden_size=96, num_hidden_layers=2, max_position_embeddings=4096,
+                         torch_dtype="bfloat16", intermediate_size=136, num_attention_heads=6, num_key_value_heads=2,
+                         head_dim=64, rms_norm_eps=1e-6, rope_theta=10000.0, tie_word_embeddings=True)
+    write_random_model(config, tmp_path, seed=9)
+    sharpen(tmp_path, factor=4.0)
+    tokens = random_tokens(211, 2400, 4)
+    want = oracle(str(tmp_path), {"r": tokens}, "bfloat16")["r"]
+    assert ops.prefill_key_parts([40], [1100], 42, 2) == 2 and ops.prefill_key_parts([300], [2400], 42, 2) == 4
+    runner = ModelRunner(str(tmp_path), dtype="bfloat16", page_size=16, num_pages=160, max_num_seqs=2)
+    cuts = [1060, 40, 64, 300, 636, 300]
+    steps, at = [], 0
+    for n in cuts:
+        steps.append({"entries": [{"id": "r", "tokens": tokens[at:at + n], "want": list(range(n))}], "end": []})
+        at += n
+    assert at == len(tokens)
+    steps[-1]["end"] = ["r"]
+    rows = plans.collect(steps, run_plan(runner, steps))
+    compare(rows, {"r": want}, "bfloat16", "portions behind a long prefix")
