@@ -43,3 +43,40 @@ def test_two_layers_of_the_7b_shape(big_folder, dtype, tol):
     err = (got - want).abs().max(dim=1).values
     assert err.max() <= tol * want.abs().max(), (dtype, int(err.argmax()), err.max().item(), want.abs().max().item())
     runner.check()
+
+
+def test_a_portion_of_2048_tokens_runs_every_projection_on_the_two_sm_kernel(big_folder, monkeypatch):
+    """From 2,048 tokens the q/k/v, o and down projections of a prompt portion leave the library for the
+    persistent two-SM tcgen05 kernel (gate/up with its SwiGLU is there already).  A prompt of 2,100 tokens as
+    portions of 2,048 and 52; logits of rows of both portions against the plain implementation."""
+    from slipstream_b200 import ops
+    from slipstream_b200.engine.runner import ModelRunner, StepEntry
+    folder, config = big_folder
+    n = 2100
+    tokens = random_tokens(config.vocab_size, n, 12)
+    assert n - 52 >= ops.functions.MANY_TOKENS and config.hidden_size >= ops.functions.MANY_WIDTH
+    cfg, weights = plain.read_model_folder(folder, torch.float32)
+    s = plain.sizes(cfg)
+    x = weights["model.embed_tokens.weight"][torch.as_tensor(tokens)]
+    for index in range(s["layers"]):
+        x = plain.decoder_layer(x, torch.arange(n), weights, index, s)
+    rows = [0, 1, 63, 64, 1000, 2047, 2048, 2049, 2099]
+    want = plain.rms_norm(x[rows], weights["model.norm.weight"], s["eps"]) @ weights["lm_head.weight"].T
+    del weights, x
+    runner = ModelRunner(folder, dtype="bfloat16", page_size=16, num_pages=160, max_num_seqs=2)
+    def library_product(*args, **kwargs):
+        raise AssertionError("a library matrix product ran in a 2,048-token portion")
+
+    before = ops.launch_count()
+    with monkeypatch.context() as patch:
+        patch.setattr(torch, "mm", library_product)
+        patch.setattr(torch, "addmm", library_product)
+        first = runner.step([StepEntry("r", tokens[:2048], [r for r in rows if r < 2048])]).float().cpu()
+    launches = ops.launch_count() - before
+    second = runner.step([StepEntry("r", tokens[2048:], [r - 2048 for r in rows if r >= 2048])]).float().cpu()
+    got = torch.cat([first, second])
+    err = (got - want).abs().max(dim=1).values
+    assert err.max() <= 3e-2 * want.abs().max(), (int(err.argmax()), err.max().item(), want.abs().max().item())
+    # embedding + per layer (norm, q/k/v, rotary, attention, o, norm, gate/up, down) + final norm + LM head: all ours
+    assert launches == 1 + 8 * s["layers"] + 2, launches
+    runner.check()
