@@ -16,6 +16,9 @@
 //                      per column) with tcgen05.st over the first half of the S buffer it came from, and
 //                      rescales O in tensor memory only when the maximum has grown by more than 2^8 (the
 //                      sum carries the same reference).
+// With a grid of several layers (z) the blocks of a thread-block cluster share the key tiles of a query tile
+// and combine their unnormalised O, maxima and sums through distributed shared memory at the end: a step with
+// few query tiles behind a long prefix would otherwise last as long as its longest query tile.
 // Masking is the packed-index causal rule of slipstream/models/layers/attention.py:46-51; softmax is float32
 // (:64-88).  No window here: windowed layers, other head sizes and page sizes that do not divide 64 run the
 // mma.sync kernel of attention_mma.cuh.  Every mbarrier wait is bounded (see gemm_tc5.cu).
