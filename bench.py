@@ -9,6 +9,10 @@ out every step; ``prefill`` is one 2,048-token prompt in one step; ``roofline`` 
 decode step must read (every weight once, plus the cache of the live requests) with the measured
 copy bandwidth; ``points`` holds decode at batch 1 and 64.  Peaks come from MEASURED_PEAKS.json
 beside this file when present.  One GPU only: for --gpus above 1 it says so and exits with 2.
+
+``--only decode|prefill`` runs one part and prints a short line (profiling, and measurements beside the
+headline): ``--only decode --batch 1 --prompt-len 32000 --context-len 32768`` is a decode step behind a long
+context, ``--only prefill --chunk 512 --prefix 8192 --context-len 32768`` a prompt portion behind cached tokens.
 """
 
 from __future__ import annotations
@@ -171,6 +175,10 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=SHAPE_7B["num_hidden_layers"])
+    ap.add_argument("--context-len", type=int, default=SHAPE_7B["max_position_embeddings"],
+                    help="positions of the model (with --only: measurements at longer contexts)")
+    ap.add_argument("--chunk", type=int, default=2048, help="--only prefill: tokens of the timed prompt portion")
+    ap.add_argument("--prefix", type=int, default=0, help="--only prefill: tokens already cached in front of it")
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--no-graphs", action="store_true")
@@ -197,13 +205,15 @@ def main() -> int:
     from slipstream_b200.engine.runner import StepEntry
 
     pk, pk_kind = peaks()
-    shape = dict(SHAPE_7B, num_hidden_layers=args.layers)
+    shape = dict(SHAPE_7B, num_hidden_layers=args.layers, max_position_embeddings=args.context_len)
     folder = tempfile.mkdtemp(prefix="bench_qwen7b_")
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(dict(shape, architectures=["Qwen2ForCausalLM"], model_type="qwen2"), f)
     ctx_len, page = shape["max_position_embeddings"], 16
     max_batch = max(64, args.batch)
     pages = max_batch * (args.prompt_len + args.steps + args.warmup + 2 * max_batch + 96) // page + 4096 // page + 64
+    if args.only:  # one batch, or one prompt behind a prefix: the pool need not hold 64 requests
+        pages = (max(args.batch * (args.prompt_len + args.steps + args.warmup + 16), args.prefix + args.chunk) + 4096) // page + 64
     engine = LLMEngine(EngineConfig.for_model(
         folder, dtype="bfloat16", load_format="random", max_model_len=ctx_len,
         cache=CacheConfig(block_size=page, num_gpu_blocks=pages),
@@ -217,6 +227,11 @@ def main() -> int:
     def fill(batch: int, tag: str) -> list[str]:
         """Prefill ``batch`` requests of prompt_len random tokens (untimed)."""
         ids = [f"{tag}{i}" for i in range(batch)]
+        if args.prompt_len > 4096:  # long prompts go in portions of 2,048 tokens
+            for r in ids:
+                for at in range(0, args.prompt_len, 2048):
+                    runner.step([StepEntry(r, rng.integers(0, vocab, min(2048, args.prompt_len - at)).tolist(), [])])
+            return ids
         per_step = max(1, 4096 // args.prompt_len)
         for i in range(0, batch, per_step):
             runner.step([StepEntry(r, rng.integers(0, vocab, args.prompt_len).tolist(), [])
@@ -253,10 +268,13 @@ def main() -> int:
                           "ms_per_step": round(ms_step, 4), "gpu_launches": launches}))
         return 0
     if args.only == "prefill":
-        T = 2048
+        T = args.chunk
         all_ms = []
         for w in range(args.warmup + args.steps):
+            for at in range(0, args.prefix, 2048):  # untimed: the tokens in front of the timed portion
+                runner.step([StepEntry(f"p{w}", rng.integers(0, vocab, min(2048, args.prefix - at)).tolist(), [])])
             toks = rng.integers(0, vocab, T).tolist()
+            torch.cuda.synchronize()
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
             runner.step([StepEntry(f"p{w}", toks, [T - 1])])
@@ -264,7 +282,7 @@ def main() -> int:
             torch.cuda.synchronize()
             runner.release(f"p{w}")
             all_ms.append(round(start.elapsed_time(stop), 3))
-        print(json.dumps({"only": "prefill", "tokens": T, "ms_last": all_ms[-1], "ms_each": all_ms}))
+        print(json.dumps({"only": "prefill", "tokens": T, "prefix": args.prefix, "ms_last": all_ms[-1], "ms_each": all_ms}))
         return 0
 
     # ---- prefill of one 2,048-token prompt in one step (median of five).  It is the one phase that runs at the
