@@ -217,7 +217,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[D / 16][4], const
 template <int D>
 constexpr int mma_smem_bytes(int q_rows = 64, int stages = 2) {
     const int tiles = (q_rows * (D + 8) + stages * 2 * MMA_BN * (D + 8)) * 2;  // Q tile + stages of K and V
-    const int merge = (4 * 16 * (D + 8) + 2 * 4 * 16 + 16 * D + 16) * 4;       // the decode kernel's merge buffers
+    const int merge = (4 * 16 * (D + 8) + 2 * 4 * 16 + 16 * D + 16 + 6 * 16) * 4;  // the decode kernel's merge buffers
     return tiles > merge ? tiles : merge;
 }
 
@@ -527,20 +527,30 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
         }
     }
     __syncthreads();
-    for (int idx = tid; idx < heads_here * D; idx += MMA_THREADS) {
-        const int row = idx / D, d = idx - row * D;
+    // per row: the maximum over the four warps, each warp's factor and the sum, once per row
+    float* Fm = Lc + 16;                                     // [4][16]: exp2(m_w - m)
+    float* MLm = Fm + 4 * 16;                                // [2][16]: m, l
+    if (tid < 16) {
         float mm = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, Mm[w * 16 + row]);
-        float acc = 0.f, ll = 0.f;
-        if (mm != -INFINITY) {
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, Mm[w * 16 + tid]);
+        float ll = 0.f;
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const float f = exp2f(Mm[w * 16 + row] - mm);
-                acc += Om[(w * 16 + row) * OSTR + d] * f;
-                ll += Lm[w * 16 + row] * f;
-            }
+        for (int w = 0; w < 4; ++w) {
+            const float f = mm != -INFINITY ? exp2f(Mm[w * 16 + tid] - mm) : 0.f;
+            Fm[w * 16 + tid] = f;
+            ll += Lm[w * 16 + tid] * f;
         }
+        MLm[tid] = mm;
+        MLm[16 + tid] = ll;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < heads_here * D; idx += MMA_THREADS) {
+        const int row = idx / D, d = idx - row * D;
+        const float mm = MLm[row], ll = MLm[16 + row];
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) acc += Om[(w * 16 + row) * OSTR + d] * Fm[w * 16 + row];
         const float val = ll > 0.f ? acc / ll : 0.f;
         const int head = kvh * G + g0 + row;
         if (n_slices == 1) {
