@@ -1,6 +1,5 @@
-"""The reference arm of bench.py: the UNMODIFIED reference engine (installed under baseline/_ref by
-``python -m pip install --no-index --no-build-isolation --no-deps --find-links /opt/wheelhouse --target
-baseline/_ref <reference checkout>``) run through its own public API, ``LLMEngine(EngineConfig).generate_batch``,
+"""The reference arm of bench.py: the UNMODIFIED reference engine (an offline ``pip install --no-deps --target
+baseline/_ref`` of the reference checkout) run through its own public API, ``LLMEngine(EngineConfig).generate_batch``,
 on the same model shape, batch, prompt length and random weights as this repository's arm.
 
 None of this repository's models, kernels or engine is on that path; only its random-weights writer is used,
@@ -55,7 +54,7 @@ def run_reference(args, shape: dict, ref_path: str) -> dict:
     batch, prompt_len, steps, warm = args.batch, args.prompt_len, args.steps, max(3, args.warmup)
     blocks = batch * (prompt_len + steps + warm + 64) // 16 + 64
     config = EngineConfig(
-        model=ModelConfig(model_id=folder, dtype="bfloat16", max_model_len=4096),
+        model=ModelConfig(model_id=folder, dtype="bfloat16", max_model_len=args.context_len),
         cache=CacheConfig(block_size=16, num_gpu_blocks=blocks, enable_prefix_caching=False),
         scheduler=SchedulerConfig(max_num_seqs=max(batch, 8), max_num_batched_tokens=8192))
     engine = LLMEngine(config)
@@ -92,9 +91,13 @@ def run_reference(args, shape: dict, ref_path: str) -> dict:
         "value": round(batch * 1000.0 / ms_step, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warm,
         "ms_per_step": round(ms_step, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random token ids, random-init weights N(0, 0.02)",
-        "config": {"model": "Qwen2.5-7B shape", "global_batch": batch, "seq_len": prompt_len, "context_len": 4096,
+        "config": {"model": "Qwen2.5-7B shape", "global_batch": batch, "seq_len": prompt_len, "context_len": args.context_len,
                    "parallelism": "single GPU", "layers": layers, "layers_of_model": shape["num_hidden_layers"],
                    "kv_block": 16, "timing": "host clock around generate_batch, difference of two lengths"},
-        "e2e": {"value": round(batch * 1000.0 / ms_step, 1), "unit": "tokens/s"},
+        # generate_batch takes token lists from the host and returns token lists: per decode step one new token id
+        # per request comes back (the engine reads its arg-max with .tolist()) and goes in again (a [B, 1] tensor
+        # built from Python lists), 8 bytes each as the reference's int64 tensors
+        "e2e": {"value": round(batch * 1000.0 / ms_step, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 8 * batch},
         "prefill": {"value": round(2048 * 1000.0 / prefill_ms, 1), "tokens": 2048, "ms": round(prefill_ms, 2)},
     }

@@ -26,20 +26,19 @@ class SamplingParams:
     extra: dict[str, object] = field(default_factory=dict, hash=False, compare=False)
 
     def __post_init__(self) -> None:
-        if self.max_tokens < 1:
-            raise ValueError("max_tokens must be >= 1")
-        if self.temperature < 0.0:
-            raise ValueError("temperature must be >= 0")
-        if self.top_k == 0 or self.top_k < -1:
-            raise ValueError("top_k must be -1 or >= 1")
-        if not (0.0 < self.top_p <= 1.0):
-            raise ValueError("top_p must be in (0, 1]")
-        if not (0.0 <= self.min_p <= 1.0):
-            raise ValueError("min_p must be in [0, 1]")
-        if self.repetition_penalty <= 0.0:
-            raise ValueError("repetition_penalty must be > 0")
-        if self.n != 1:
-            raise ValueError("n must be 1: parallel sampling of one prompt is not implemented")
+        # (field, admissible?, what to say): the ranges of slipstream/core/sampling_params.py:30-44
+        rules = (
+            ("max_tokens", self.max_tokens >= 1, "at least 1"),
+            ("temperature", self.temperature >= 0.0, "zero (greedy) or positive"),
+            ("top_k", self.top_k == -1 or self.top_k >= 1, "-1 (off) or at least 1"),
+            ("top_p", 0.0 < self.top_p <= 1.0, "above 0 and at most 1"),
+            ("min_p", 0.0 <= self.min_p <= 1.0, "between 0 and 1"),
+            ("repetition_penalty", self.repetition_penalty > 0.0, "positive"),
+            ("n", self.n == 1, "1: several samples of one prompt are not implemented"),
+        )
+        for name, ok, wanted in rules:
+            if not ok:
+                raise ValueError(f"{name}={getattr(self, name)!r}: must be {wanted}")
         object.__setattr__(self, "stop_token_ids", tuple(int(t) for t in self.stop_token_ids))
         object.__setattr__(self, "stop_strings", tuple(self.stop_strings))
 

@@ -73,9 +73,9 @@ def rotary_tables(positions, head_dim, theta, dtype):
     float32, duplicated over both halves; cos and sin of them.  The reference takes
     cosine and sine in float32; here each float32 angle goes through ``math.cos`` /
     ``math.sin`` (double precision, one value at a time), which differs from that by
-    at most the rounding of the result to float32.  The vectorised float32 cosine of
-    the CPU library gave, in about one process in twenty on the test machines, values
-    that were off by 1e-4 on its first call; this oracle must not depend on that."""
+    at most the rounding of the result to float32.  A vectorised float32 cosine
+    of a CPU math library may be less exact than that on some inputs (errors of 1e-4 have
+    been seen); going through double precision keeps the oracle independent of it."""
     inv_freq = inverse_frequencies(head_dim, theta)
     freqs = positions.to(torch.float32)[:, None] * inv_freq[None, :]
     angles = [[float(a) for a in row] for row in freqs.tolist()]

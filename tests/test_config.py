@@ -41,10 +41,18 @@ def test_rope_theta_inside_rope_scaling_and_generation_config_ids():
     ({"rope_scaling": {"rope_type": "llama3"}}, "rope type"), ({"use_sliding_window": True}, "sliding"),
     ({"tie_word_embeddings": 1}, "tie_word_embeddings"), ({"num_attention_heads": 5}, "divisible"),
     ({"head_dim": 7}, "even"), ({"rms_norm_eps": True}, "rms_norm_eps"),
+    ({"torch_dtype": "float16"}, "float16"), ({"torch_dtype": "half"}, "not supported"), ({"dtype": "fp8"}, "fp8"),
+    ({"eos_token_id": True}, "boolean"), ({"rope_scaling": 3}, "object"), ({"num_hidden_layers": 2.5}, "integer"),
 ])
 def test_bad_values_are_refused(patch, word):
     with pytest.raises(ConfigError, match=word):
         Qwen2Config.from_dict(dict(BASE, **patch))
+
+
+def test_whole_numbers_written_as_floats_and_unknown_keys_survive():
+    c = Qwen2Config.from_dict(dict(BASE, max_position_embeddings=512.0, dtype="bf16", something_else=[1, 2]))
+    assert c.max_position_embeddings == 512 and c.torch_dtype == "bfloat16"
+    assert c.to_dict()["something_else"] == [1, 2]
 
 
 def test_registry(tmp_path):
