@@ -28,10 +28,9 @@ extern "C" int ss_attn_simt(const void* q, int64_t q_stride, void* out, int64_t 
 
 #include "attention_mma.cuh"
 
-template <typename K>
-static int set_smem(K kernel, int bytes) {
-    return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-}
+// Most slices a decode call may ask for: the last block of a head block lines up one weight per (head, slice) in
+// shared memory, and the launchers' policies never ask for more.
+#define SS_DECODE_MAX_SLICES 64
 
 // Prompt portions and mixed batches, bfloat16.  Tiles: 64 rows of (token, head of the group) pairs of one
 // request, listed by the host as (request, first row); the grid's second axis is the kv head.
@@ -43,8 +42,8 @@ extern "C" int ss_attn_prefill_mma(const void* q, int64_t q_stride, void* out, i
                                    cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     constexpr int smem = mma_smem_bytes<HEAD_DIM>();
-    static int configured = set_smem(attn_prefill_mma<HEAD_DIM>, smem);
-    if (configured != 0) return configured;
+    static SsPerDevice opted;
+    if (int rc_smem = ss_opt_in_smem(attn_prefill_mma<HEAD_DIM>, smem, opted)) return rc_smem;
     dim3 grid(n_tiles, n_kv);
     ss_launch(attn_prefill_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_tables, max_blocks, tile_req,
@@ -66,10 +65,11 @@ extern "C" int ss_attn_decode_mma(const void* q, int64_t q_stride, void* out, in
     if (n_requests <= 0) return 0;
     const int cluster = n_slices >= 2 && n_slices <= 8;  // the slices are combined through shared memory
     if (fused && (rot_dim < 0 || rot_dim > HEAD_DIM || rot_dim % 2 || (rot_dim > 0 && !inv_freq))) return (int)cudaErrorInvalidValue;
-    if (n_slices < 1 || (n_slices > 1 && !cluster && (!part_o || !part_lse || !counters))) return (int)cudaErrorInvalidValue;
+    if (n_slices < 1 || n_slices > SS_DECODE_MAX_SLICES) return (int)cudaErrorInvalidValue;
+    if (n_slices > 1 && !cluster && (!part_o || !part_lse || !counters)) return (int)cudaErrorInvalidValue;
     constexpr int smem = mma_smem_bytes<HEAD_DIM>(16, DECODE_STAGES);
-    static int configured = set_smem(attn_decode_mma<HEAD_DIM>, smem);
-    if (configured != 0) return configured;
+    static SsPerDevice opted;
+    if (int rc_smem = ss_opt_in_smem(attn_decode_mma<HEAD_DIM>, smem, opted)) return rc_smem;
     const int G = n_q / n_kv;
     dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
     if (cluster)
@@ -114,8 +114,8 @@ extern "C" int ss_attn_prefill_tc5(const void* q, int64_t q_stride, int n_tokens
     a.tile_req = tile_req; a.tile_tok0 = tile_tok0; a.q_start = q_start; a.seq_lens = seq_lens;
     a.n_q = n_q; a.n_kv = n_kv; a.page_size = page_size; a.num_pages = num_pages; a.scale = scale; a.err = err;
     constexpr int smem = fa::smem_bytes<HEAD_DIM>();
-    static int configured = set_smem(fa::attn_prefill_tc5<HEAD_DIM>, smem);
-    if (configured != 0) return configured;
+    static SsPerDevice opted;
+    if (int rc_smem = ss_opt_in_smem(fa::attn_prefill_tc5<HEAD_DIM>, smem, opted)) return rc_smem;
     // splits > 1: the key tiles of every query tile are shared by a thread-block cluster of that many blocks
     if (splits > 1)
         ss_launch_cluster(fa::attn_prefill_tc5<HEAD_DIM>, dim3(n_tiles, n_kv, splits), dim3(FA_THREADS), smem, stream, splits, map_q, map_kv, a);
@@ -138,7 +138,8 @@ extern "C" int ss_attn_decode_tma(const void* q, int64_t q_stride, void* out, in
     // up to 8 slices: one cluster; a multiple of 8 beyond: clusters of 8 whose results meet in scratch memory;
     // any other count: single blocks and scratch memory
     const int cluster = n_slices <= 8 ? n_slices : (n_slices % 8 == 0 ? 8 : 1);
-    if (n_slices < 1 || (n_slices > 8 && (!part_o || !part_lse || !counters))) return (int)cudaErrorInvalidValue;
+    if (n_slices < 1 || n_slices > SS_DECODE_MAX_SLICES) return (int)cudaErrorInvalidValue;
+    if (n_slices > 8 && (!part_o || !part_lse || !counters)) return (int)cudaErrorInvalidValue;
     if (fused && (rot_dim < 0 || rot_dim > HEAD_DIM || rot_dim % 2 || (rot_dim > 0 && !inv_freq))) return (int)cudaErrorInvalidValue;
     CUtensorMap map_kv;
     int rc = fa::make_map3(&map_kv, kv, HEAD_DIM, (uint64_t)page_size, (uint64_t)num_pages * 2 * n_kv, (uint64_t)HEAD_DIM * 2,
@@ -151,8 +152,8 @@ extern "C" int ss_attn_decode_tma(const void* q, int64_t q_stride, void* out, in
     a.n_slices = n_slices; a.cluster = cluster; a.inv_freq = inv_freq; a.rot_dim = rot_dim; a.fused = fused;
     a.part_o = part_o; a.part_lse = part_lse; a.counters = counters; a.err = err;
     constexpr int smem = decode_tma_smem_bytes<HEAD_DIM>();
-    static int configured = set_smem(attn_decode_tma<HEAD_DIM>, smem);
-    if (configured != 0) return configured;
+    static SsPerDevice opted;
+    if (int rc_smem = ss_opt_in_smem(attn_decode_tma<HEAD_DIM>, smem, opted)) return rc_smem;
     const int G = n_q / n_kv;
     dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
     if (cluster > 1) ss_launch_cluster(attn_decode_tma<HEAD_DIM>, dim3(grid), dim3(DT_THREADS), smem, stream, cluster, map_kv, a);
@@ -165,6 +166,7 @@ extern "C" int ss_attn_prefill_tc5_supported() { return 0; }
 
 // ---------------------------------------------------------------- the entry point that allocates nothing
 #include "no_alloc.h"
+static_assert(SS_NOALLOC_MAX_SLICES == SS_DECODE_MAX_SLICES, "both entry points take the same slice counts");
 
 // Scratch of ss_attn_decode_noalloc.  In host code this name is only a handle for
 // cudaGetSymbolAddress, never a device address.
@@ -188,7 +190,8 @@ extern "C" const char* ss_attn_decode_noalloc_message(int code) {
         case SS_NOALLOC_TOO_LARGE:
             return "the call needs more than the 8 MiB of built-in scratch (n_requests * n_q * n_slices * "
                    "(head size + 1) floats): use fewer slices or requests, or ss_attn_decode_mma with scratch of your own";
-        case SS_NOALLOC_BAD_ARGUMENT: return "a count is not positive or n_q is not a multiple of n_kv";
+        case SS_NOALLOC_BAD_ARGUMENT:
+            return "a count is not positive, n_q is not a multiple of n_kv, or n_slices is above 64";
         case SS_NOALLOC_SETUP_FAILED: return "could not look up the scratch array on the current device";
         default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown code";
     }
@@ -199,7 +202,8 @@ extern "C" int ss_attn_decode_noalloc(const void* q, int64_t q_stride, void* out
                                       int n_requests, const int32_t* q_start, const int32_t* seq_lens, int n_q,
                                       int n_kv, int page_size, int64_t num_pages, float scale, int window,
                                       int n_slices, int* err, cudaStream_t stream) {
-    if (n_requests <= 0 || n_q <= 0 || n_kv <= 0 || n_slices < 1 || n_q % n_kv != 0 || page_size <= 0)
+    if (n_requests <= 0 || n_q <= 0 || n_kv <= 0 || n_slices < 1 || n_slices > SS_NOALLOC_MAX_SLICES ||
+        n_q % n_kv != 0 || page_size <= 0)
         return SS_NOALLOC_BAD_ARGUMENT;
     const int64_t floats = ss_attn_decode_noalloc_floats(n_requests, n_q, n_slices);
     if (floats > (int64_t)SS_NOALLOC_SCRATCH_FLOATS) return SS_NOALLOC_TOO_LARGE;
@@ -225,8 +229,8 @@ extern "C" int ss_attn_decode_noalloc(const void* q, int64_t q_stride, void* out
     float* part_lse = scratch + (int64_t)n_requests * n_q * n_slices * HEAD_DIM;
 
     constexpr int smem = mma_smem_bytes<HEAD_DIM>(16, DECODE_STAGES);
-    static int configured = set_smem(attn_decode_mma<HEAD_DIM>, smem);
-    if (configured != 0) return configured;
+    static SsPerDevice opted;
+    if (int rc_smem = ss_opt_in_smem(attn_decode_mma<HEAD_DIM>, smem, opted)) return rc_smem;
     const int G = n_q / n_kv;
     dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
     ss_launch(attn_decode_mma<HEAD_DIM>, dim3(grid), dim3(MMA_THREADS), smem, stream, 

@@ -176,13 +176,8 @@ int launch_attn_simt(const void* q, int64_t q_stride, void* out, int64_t out_str
                      float scale, int window, int* err, cudaStream_t stream) {
     static_assert(ATT_RPW == 4, "the kernel packs four rows per warp into a float4");
     constexpr int smem = att_simt_smem_bytes<D>();
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_simt_kernel<T, D>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static SsPerDevice opted;
+    if (int rc_smem = ss_opt_in_smem(attn_simt_kernel<T, D>, smem, opted)) return rc_smem;
     dim3 grid(n_tiles, n_q);
     ss_launch(attn_simt_kernel<T, D>, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, 
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)kv, block_tables, max_blocks, tile_req,

@@ -72,6 +72,45 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 
 #define SS_LAUNCH_CHECK() (int)cudaGetLastError()
 
+// ---------------------------------------------------------------- per-device set-up
+// A kernel's opt-in to more than 48 KB of dynamic shared memory (cudaFuncSetAttribute) holds for one device
+// only, so it is remembered per device, not per process.  Two host threads that make their first call on a device
+// at the same moment both do the (idempotent) opt-in; nothing else is shared.
+#define SS_MAX_DEVICES 64
+struct SsPerDevice {
+    unsigned char done[SS_MAX_DEVICES];
+};
+
+static inline int ss_current_device() {
+    int dev = -1;
+    return (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < SS_MAX_DEVICES) ? dev : -1;
+}
+
+template <typename K>
+static inline int ss_opt_in_smem(K kernel, int bytes, SsPerDevice& state) {
+    const int dev = ss_current_device();
+    if (dev < 0) return (int)cudaErrorInvalidDevice;
+    if (!state.done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) return (int)e;
+        state.done[dev] = 1;
+    }
+    return 0;
+}
+
+// Streaming multiprocessors of the current device (asked once per device).
+static inline int ss_sm_count() {
+    static int count[SS_MAX_DEVICES];
+    const int dev = ss_current_device();
+    if (dev < 0) return 1;
+    if (count[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 1;
+        count[dev] = n;
+    }
+    return count[dev];
+}
+
 // ---------------------------------------------------------------- programmatic dependent launch
 // Kernels are launched so that the next kernel in the stream may start while this one is still running
 // (cudaLaunchAttributeProgrammaticStreamSerialization).  A kernel calls pdl_launch_dependents() as early

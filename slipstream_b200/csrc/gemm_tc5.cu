@@ -655,8 +655,8 @@ static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K,
 template <int BN, int STAGES>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, dim3 grid, cudaStream_t stream) {
     constexpr int smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 256;
-    static int configured = (int)cudaFuncSetAttribute(gemm_tc5_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (configured != 0) return configured;
+    static SsPerDevice opted;
+    if (int rc_smem = ss_opt_in_smem(gemm_tc5_kernel<BN, STAGES>, smem, opted)) return rc_smem;
     if (g.cluster)
         ss_launch_cluster(gemm_tc5_kernel<BN, STAGES>, dim3(grid), dim3(TC_THREADS), smem, stream, g.slices, ma, mb, g);
     else
@@ -716,12 +716,7 @@ extern "C" int ss_gemm_tc5_many(const void* A, const void* B, const void* bias, 
     if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return -2003;
     if (((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2004;
     if (swiglu && (N % 128 != 0 || out_f32 || ldc % 8 != 0 || ((uintptr_t)C & 15))) return -2007;
-    int n_sms = 148;
-    {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
-    }
+    const int n_sms = ss_sm_count();
     const int max_pairs = n_sms / 2 > 0 ? n_sms / 2 : 1;
     const int n_m = (M + 2 * TC_BM - 1) / (2 * TC_BM);
     // The width whose tiles take the least time: rounds of the pairs times the time of a tile.  Per 16-wide K
@@ -750,8 +745,8 @@ extern "C" int ss_gemm_tc5_many(const void* A, const void* B, const void* bias, 
     g.C = C; g.bias = bias; g.err = err; g.M = M; g.N = N; g.K = K; g.ldc = ldc; g.out_f32 = out_f32;
     g.bias_f32 = bias_f32; g.swiglu = swiglu; g.tile_cols = bn;
     constexpr int smem_pair = PR_STAGES * (2 * TC_BM * TC_BK * 2) + 1024 + 256;
-    static int configured_pair = (int)cudaFuncSetAttribute(gemm_tc5_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pair);
-    if (configured_pair != 0) return configured_pair;
+    static SsPerDevice opted_pair;
+    if (int rc_smem = ss_opt_in_smem(gemm_tc5_pair_kernel, smem_pair, opted_pair)) return rc_smem;
     const int tiles2 = n_m * ((N + bn - 1) / bn);
     const int pairs = tiles2 < max_pairs ? tiles2 : max_pairs;
     ss_launch_cluster_x(gemm_tc5_pair_kernel, dim3(2 * pairs), dim3(TC_THREADS), smem_pair, stream, 2, ma, mb, g);

@@ -12,11 +12,21 @@
 // key slices) from the caller, who usually gets it from an allocator.  This variant
 // instead keeps that scratch in a fixed array inside the library.
 //
-// What it does: exactly what ss_attn_decode_mma does for the same arguments; the
-// inputs and the output are still the caller's.  It calls no cudaMalloc, cudaFree or
-// any allocating library routine.
+// What it does: the same attention as ss_attn_decode_mma for the same arguments; the
+// inputs and the output are still the caller's.  The slices always meet in the scratch
+// array and the block that finishes a group of heads last adds them up in slice order.
+// ss_attn_decode_mma takes that route only for more than 8 slices (with 2 to 8 it
+// combines them inside a thread-block cluster, a different order of additions), so the
+// two agree bit for bit above 8 slices and to rounding below.  It calls no cudaMalloc,
+// cudaFree or any allocating library routine.
 //
 // Limits and rules:
+//  * n_slices is at most SS_NOALLOC_MAX_SLICES (64); more is refused with
+//    SS_NOALLOC_BAD_ARGUMENT before anything is launched.
+//  * One GPU per call: the device that is current when the call is made.  Every device
+//    has its own copy of the array, and the per-device set-up (the array's address, the
+//    kernel's shared-memory opt-in) happens at the first call on that device.  First
+//    calls on one device from two host threads at once must not overlap.
 //  * The scratch array holds SS_NOALLOC_SCRATCH_FLOATS floats (8 MiB) per GPU, from
 //    the moment the library is loaded on that GPU until the process exits.  A call
 //    needs n_requests * n_q * n_slices * (HEAD_DIM + 1) floats; a call that needs
@@ -38,6 +48,7 @@
 
 #define SS_NOALLOC_SCRATCH_FLOATS (2u * 1024u * 1024u)
 #define SS_NOALLOC_COUNTERS 16384u
+#define SS_NOALLOC_MAX_SLICES 64
 #define SS_NOALLOC_TOO_LARGE (-1001)   // the call needs more scratch than the array holds
 #define SS_NOALLOC_BAD_ARGUMENT (-1002)
 #define SS_NOALLOC_SETUP_FAILED (-1003)  // cudaGetDevice / cudaGetSymbolAddress failed

@@ -394,13 +394,13 @@ static void launch_swiglu(const void* in, void* out, int64_t n, int inter, int b
     const int threads = 256;
     if (sizeof(T) == 2 && inter % 8 == 0 && block % 8 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0) {
         int64_t blocks = (n * (inter / 8) + threads - 1) / threads;
-        if (blocks > 148 * 16) blocks = 148 * 16;
+        if (blocks > ss_sm_count() * 16) blocks = ss_sm_count() * 16;
         ss_launch(swiglu_bf16x8_kernel, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)in, (bf16*)out, n, inter, block);
         return;
     }
     const int vec = (inter % 4 == 0 && block % 4 == 0) ? 4 : 1;
     int64_t blocks = (n * (inter / vec) + threads - 1) / threads;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (blocks > ss_sm_count() * 32) blocks = ss_sm_count() * 32;
     if (vec == 4) ss_launch(swiglu_kernel<T, 4>, dim3((int)blocks), dim3(threads), 0, stream, (const T*)in, (T*)out, n, inter, block);
     else ss_launch(swiglu_kernel<T, 1>, dim3((int)blocks), dim3(threads), 0, stream, (const T*)in, (T*)out, n, inter, block);
 }

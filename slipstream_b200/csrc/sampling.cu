@@ -110,7 +110,10 @@ argmax_partial_kernel(const float* __restrict__ logits, unsigned long long* __re
     if (threadIdx.x == 0) partial[(int64_t)blockIdx.x * ARGMAX_CHUNKS + blockIdx.y] = best;
 }
 
-__global__ void argmax_final_kernel(const unsigned long long* __restrict__ partial, int32_t* __restrict__ out) {
+// status (optional): the device error word; its value goes to out[rows], behind the tokens, so that the one copy
+// that brings the tokens to the host also says whether a kernel of the step flagged anything.
+__global__ void argmax_final_kernel(const unsigned long long* __restrict__ partial, int32_t* __restrict__ out,
+                                    const int* __restrict__ status) {
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
     pdl_wait();               // nothing below runs before the kernels before this one are complete
     unsigned long long v = partial[(int64_t)blockIdx.x * ARGMAX_CHUNKS + threadIdx.x];  // 32 threads
@@ -120,15 +123,16 @@ __global__ void argmax_final_kernel(const unsigned long long* __restrict__ parti
         v = other > v ? other : v;
     }
     if (threadIdx.x == 0) out[blockIdx.x] = v == 0ull ? 0 : (int32_t)(0xFFFFFFFFu - (uint32_t)(v & 0xFFFFFFFFull));
+    if (status != nullptr && blockIdx.x == 0 && threadIdx.x == 0) out[gridDim.x] = __ldcg(status);
 }
 
 // scratch: rows * ARGMAX_CHUNKS 64-bit words of the caller
 extern "C" int ss_argmax(const float* logits, int32_t* out, int rows, int vocab, int64_t stride,
-                         unsigned long long* scratch, cudaStream_t stream) {
+                         unsigned long long* scratch, const int* status, cudaStream_t stream) {
     if (rows <= 0) return 0;
     static_assert(ARGMAX_CHUNKS == 32, "the final kernel reduces one warp of partial results");
     ss_launch(argmax_partial_kernel, dim3(dim3(rows, ARGMAX_CHUNKS)), dim3(ARGMAX_THREADS), 0, stream, logits, scratch, vocab, stride);
-    ss_launch(argmax_final_kernel, dim3(rows), dim3(32), 0, stream, scratch, out);
+    ss_launch(argmax_final_kernel, dim3(rows), dim3(32), 0, stream, scratch, out, status);
     return SS_LAUNCH_CHECK();
 }
 
@@ -293,9 +297,11 @@ sample_kernel(const float* __restrict__ logits, int64_t stride, int32_t* __restr
               const float* __restrict__ top_p, const float* __restrict__ min_p,
               const float* __restrict__ penalty, const int64_t* __restrict__ seeds,
               const int64_t* __restrict__ draws, uint32_t* __restrict__ seen_all,
-              int seen_words, const int32_t* __restrict__ slots, int vocab) {
+              int seen_words, const int32_t* __restrict__ slots, int vocab, const int* __restrict__ status,
+              int rows) {
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
     pdl_wait();               // nothing below runs before the kernels before this one are complete
+    if (status != nullptr && blockIdx.x == 0 && threadIdx.x == 0) out[rows] = __ldcg(status);  // as in arg-max
     __shared__ SampleShared sh;
     extern __shared__ unsigned long long warp_hists[];  // [warps][256]
     // the blocks of a cluster share a row; block c of n takes elements c * blockDim + tid, + n * blockDim, ...
@@ -426,17 +432,17 @@ extern "C" int ss_sample(const float* logits, int64_t stride, int32_t* out, cons
                          const int32_t* top_k, const float* top_p, const float* min_p,
                          const float* penalty, const int64_t* seeds, const int64_t* draws,
                          uint32_t* seen, int seen_words, const int32_t* slots, int rows, int vocab,
-                         cudaStream_t stream) {
+                         const int* status, cudaStream_t stream) {
     if (rows <= 0) return 0;
     constexpr int smem = (SAMPLE_THREADS / 32) * 256 * 8;  // a histogram per warp
-    static int configured = (int)cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (configured != 0) return configured;
+    static SsPerDevice opted;
+    if (int rc_smem = ss_opt_in_smem(sample_kernel, smem, opted)) return rc_smem;
     // blocks per row: as many as fill the GPU once (two blocks of 1,024 threads fit on an SM), at most 8
-    int per_row = (2 * 148) / rows;
+    int per_row = (2 * ss_sm_count()) / rows;
     per_row = per_row >= 8 ? 8 : (per_row >= 4 ? 4 : (per_row >= 2 ? 2 : 1));
     ss_launch_cluster_x(sample_kernel, dim3(rows * per_row), dim3(SAMPLE_THREADS), smem, stream, per_row, logits, stride, out, temperature, top_k, top_p,
                                                        min_p, penalty, seeds, draws, seen, seen_words,
-                                                       slots, vocab);
+                                                       slots, vocab, status, rows);
     return SS_LAUNCH_CHECK();
 }
 

@@ -26,6 +26,7 @@ import torch
 
 from slipstream_b200.config.engine_config import CacheConfig, EngineConfig, SchedulerConfig
 from slipstream_b200.config.sampling_params import SamplingParams
+from slipstream_b200 import ops
 from slipstream_b200.sampling.sampler import SampleRow, Sampler
 
 from .context import StepEntry
@@ -81,7 +82,7 @@ class InFlight:
 
     seqs: list[Sequence]
     where: list[int]  # index into each sequence's output of the placeholder this step fills
-    tokens_dev: torch.Tensor  # int32 [len(seqs)] on the device
+    tokens_dev: torch.Tensor  # int32 [len(seqs) + 1] on the device: the tokens, then the device error word
     tokens_host: torch.Tensor  # pinned copy, valid once ``ready`` has happened
     ready: torch.cuda.Event
 
@@ -121,6 +122,10 @@ class LLMEngine:
         self._inflight: InFlight | None = None
         self._zombies: list[Sequence] = []  # stopped while their next token was already being computed
         self.run_ahead = True  # decode steps are launched before the tokens of the step before reach the host
+        # pinned buffers and events of the steps in flight, made once (a step in flight and the one being launched)
+        self._token_ring = [torch.empty(s.max_num_seqs + 1, dtype=torch.int32, pin_memory=True) for _ in range(3)]
+        self._event_ring = [torch.cuda.Event() for _ in range(3)]
+        self._ring_turn = 0
 
     # ------------------------------------------------------------------ public calls
     def generate(self, request: Request) -> list[int]:
@@ -225,6 +230,7 @@ class LLMEngine:
         """Read the tokens of a launched step, put them in place of their placeholders, finish what is done."""
         flight.ready.synchronize()
         tokens = flight.tokens_host.tolist()
+        self._check_status(tokens.pop(), flight.seqs)
         for seq, at, token in zip(flight.seqs, flight.where, tokens):
             if seq in self._zombies:  # stopped one token earlier; this token was computed for nothing
                 self._zombies.remove(seq)
@@ -242,6 +248,21 @@ class LLMEngine:
             elif not ahead and (seq.num_output_tokens >= seq.max_new_tokens or seq.num_tokens >= self.max_model_len):
                 seq.status = SequenceStatus.FINISHED_LENGTH
                 self.scheduler.finish(seq)
+
+    def _check_status(self, status: int, seqs: list[Sequence]) -> None:
+        """``status`` is the device error word as the step's sampling kernel saw it.  Non-zero: a kernel met a
+        token id, cache slot or block-table entry out of range, or a bounded wait inside a kernel gave up; the
+        tokens of that step cannot be trusted.  Everything that was running is aborted (its pages go back) and
+        ``KernelError`` is raised."""
+        if not status:
+            return
+        self._inflight = None
+        for seq in list(self.scheduler.running) + [s for s in seqs if s not in self.scheduler.running]:
+            if not seq.is_finished:
+                seq.status = SequenceStatus.FINISHED_ABORTED
+            self.scheduler.finish(seq)
+        self._zombies.clear()
+        ops.raise_for_status(status, self.runner.device)
 
     def drain(self) -> None:
         """Wait for the tokens of the decode step that is still running, if one is, and put them in place."""
@@ -289,10 +310,11 @@ class LLMEngine:
             self.runner.cache.reserve(seq.seq_id, 1)
         logits = self.runner.step_decode(entries, prev.tokens_dev if prev is not None else None,
                                          np.asarray(src_rows, dtype=np.int32))
-        tokens_dev = self.sampler.sample(logits, rows)
-        tokens_host = torch.empty(len(todo), dtype=torch.int32, pin_memory=True)
+        tokens_dev = self.sampler.sample(logits, rows, with_status=True)
+        turn = self._ring_turn = (self._ring_turn + 1) % len(self._token_ring)
+        tokens_host = self._token_ring[turn][: len(todo) + 1]
         tokens_host.copy_(tokens_dev, non_blocking=True)
-        ready = torch.cuda.Event()
+        ready = self._event_ring[turn]
         ready.record()
         for seq in todo:  # the host's view moves on at once; the token's value follows
             seq.num_computed_tokens += 1
@@ -346,7 +368,9 @@ class LLMEngine:
         if sampling:
             rows = [SampleRow(i.seq.sampling_params, i.seq.seed, i.seq.num_output_tokens,
                               self.runner.cache.get(i.seq.seq_id).slot) for i in sampling]
-            tokens = self.sampler.sample(logits, rows).tolist()  # the step's one device-to-host copy
+            # the step's one device-to-host copy: the tokens and, behind them, the device error word
+            tokens = self.sampler.sample(logits, rows, with_status=True).tolist()
+            self._check_status(tokens.pop(), [i.seq for i in plan.scheduled])
         for item in plan.scheduled:
             item.seq.num_computed_tokens += item.take
         for item, token in zip(sampling, tokens):

@@ -44,6 +44,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--min-p", type=float, default=0.0)
     p.add_argument("--repetition-penalty", type=float, default=1.0)
     p.add_argument("--stop-token-ids", default="", help="comma-separated token ids")
+    p.add_argument("--stop", action="append", default=None,
+                   help="stop string (needs tokenizer.json); generation ends once the output text holds it; repeatable")
     p.add_argument("--ignore-eos", action="store_true")
     p.add_argument("--sample-seed", type=int, default=None, help="SamplingParams.seed")
     # random-weights folder
@@ -80,7 +82,7 @@ def main(argv: list[str] | None = None) -> int:
         max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
         min_p=args.min_p, repetition_penalty=args.repetition_penalty,
         stop_token_ids=tuple(int(t) for t in args.stop_token_ids.split(",") if t.strip()),
-        ignore_eos=args.ignore_eos, seed=args.sample_seed)
+        stop_strings=tuple(args.stop or ()), ignore_eos=args.ignore_eos, seed=args.sample_seed)
     llm = LLM(args.model, dtype=args.dtype, max_model_len=args.max_model_len, block_size=args.block_size,
               num_gpu_blocks=args.num_gpu_blocks, gpu_memory_utilization=args.gpu_memory_utilization,
               max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,

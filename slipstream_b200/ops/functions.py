@@ -46,9 +46,9 @@ _OPS_SIGNATURES = {
     "ss_swiglu": [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p],
     "ss_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64,
                      c_int64, c_int, c_int, c_void_p],
-    "ss_argmax": [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p],
+    "ss_argmax": [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p],
     "ss_sample": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                  c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+                  c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "ss_mark_seen": [c_void_p, c_void_p, c_int, c_int, c_void_p],
 }
 
@@ -137,13 +137,16 @@ _ERR_NAMES = {1: "a token id outside the vocabulary", 2: "a cache slot outside t
               4: "a block-table entry outside the pool", 8: "a bounded wait gave up"}
 
 
-def check_errors(device: torch.device) -> None:
-    word = error_word(device)
-    value = int(word.item())
+def raise_for_status(value: int, device: torch.device) -> None:
+    """Raise ``KernelError`` for a non-zero value of the error word (already on the host) and clear the word."""
     if value:
-        word.zero_()
-        what = "; ".join(text for bit, text in _ERR_NAMES.items() if value & bit)
+        error_word(device).zero_()
+        what = "; ".join(text for bit, text in _ERR_NAMES.items() if value & bit) or f"status {value}"
         raise KernelError(f"a kernel reported: {what}")
+
+
+def check_errors(device: torch.device) -> None:
+    raise_for_status(int(error_word(device).item()), device)
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
@@ -578,24 +581,31 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
 
 # --------------------------------------------------------------------------- sampling
 
-def argmax(logits: torch.Tensor) -> torch.Tensor:
-    """Index of the largest value of each row of float32 ``logits`` [M, V]; the lowest index wins ties."""
+def argmax(logits: torch.Tensor, with_status: bool = False) -> torch.Tensor:
+    """Index of the largest value of each row of float32 ``logits`` [M, V]; the lowest index wins ties.
+
+    ``with_status``: the result has M + 1 elements, the last being the device error word as it stood when the
+    kernel ran (``raise_for_status`` reads it on the host), so that the copy that fetches the tokens also tells
+    whether a kernel of the step flagged anything."""
     _need(logits, torch.float32, "logits")
     m, v = logits.shape
-    out = torch.empty(m, dtype=torch.int32, device=logits.device)
+    out = torch.empty(m + int(with_status), dtype=torch.int32, device=logits.device)
     scratch = torch.empty(m * 32, dtype=torch.int64, device=logits.device)  # one packed word per (row, chunk)
+    status = error_word(logits.device).data_ptr() if with_status else None
     _check(ops_library().ss_argmax(logits.data_ptr(), out.data_ptr(), m, v, logits.stride(0), scratch.data_ptr(),
-                                   _stream()), "argmax")
+                                   status, _stream()), "argmax")
     _launches[0] += 1  # two kernels
     return out
 
 
 def sample(logits: torch.Tensor, *, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
            min_p: torch.Tensor, penalty: torch.Tensor, seeds: torch.Tensor, draws: torch.Tensor,
-           slots: torch.Tensor | None = None, seen: torch.Tensor | None = None) -> torch.Tensor:
+           slots: torch.Tensor | None = None, seen: torch.Tensor | None = None,
+           with_status: bool = False) -> torch.Tensor:
     """One token per row of float32 ``logits`` [M, V] with per-row parameters (device tensors [M]):
     repetition penalty (needs ``seen`` int32 [slots, ceil(V/32)] and ``slots``), temperature (0 = arg-max),
-    top-k (-1 off), top-p, min-p, then a Gumbel-max draw keyed by (seed, draw index)."""
+    top-k (-1 off), top-p, min-p, then a Gumbel-max draw keyed by (seed, draw index).  ``with_status`` as in
+    ``argmax``."""
     _need(logits, torch.float32, "logits")
     m, v = logits.shape
     for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
@@ -612,11 +622,12 @@ def sample(logits: torch.Tensor, *, temperature: torch.Tensor, top_k: torch.Tens
         seen_words = seen.shape[1]
         if seen_words * 32 < v:
             raise KernelError("the seen-token mask is narrower than the vocabulary")
-    out = torch.empty(m, dtype=torch.int32, device=logits.device)
+    out = torch.empty(m + int(with_status), dtype=torch.int32, device=logits.device)
+    status = error_word(logits.device).data_ptr() if with_status else None
     _check(ops_library().ss_sample(logits.data_ptr(), logits.stride(0), out.data_ptr(), temperature.data_ptr(),
                                    top_k.data_ptr(), top_p.data_ptr(), min_p.data_ptr(), penalty.data_ptr(),
                                    seeds.data_ptr(), draws.data_ptr(), _ptr(seen), seen_words,
-                                   _ptr(slots) if seen is not None else None, m, v, _stream()), "sample")
+                                   _ptr(slots) if seen is not None else None, m, v, status, _stream()), "sample")
     return out
 
 
@@ -826,5 +837,5 @@ def set_programmatic_launch(enabled: bool) -> None:
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "raise_for_status", "error_word", "ops_library",
            "attention_library"]

@@ -125,6 +125,11 @@ def compile_library(name: str, sources: list[str], defines: dict[str, object] | 
         tmp.unlink(missing_ok=True)
         raise KernelBuildError(f"nvcc failed for {label} (exit {proc.returncode}):\n{log}")
     os.replace(tmp, out)
+    # builds of earlier sources of the same library are of no further use
+    stem = out.name[: -len(out.name.rsplit("_", 1)[1])]
+    for old in out.parent.glob(stem + "*.so"):
+        if old != out and len(old.name) == len(out.name) and ".tmp" not in old.name:
+            old.unlink(missing_ok=True)
     print(f"[slipstream_b200] compiled {label} in {time.time() - start:.1f} s", file=sys.stderr,
           flush=True)
     if verbose and log:

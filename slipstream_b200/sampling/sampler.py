@@ -53,15 +53,16 @@ class Sampler:
             ops.mark_seen(self.seen[slot], ids, self.vocab_size)
 
     # ------------------------------------------------------------------ selection
-    def greedy(self, logits: torch.Tensor) -> torch.Tensor:
-        return ops.argmax(logits)
+    def greedy(self, logits: torch.Tensor, with_status: bool = False) -> torch.Tensor:
+        return ops.argmax(logits, with_status)
 
-    def sample(self, logits: torch.Tensor, rows: list[SampleRow]) -> torch.Tensor:
-        """int32 [M] token ids on the device for float32 ``logits`` [M, vocab]."""
+    def sample(self, logits: torch.Tensor, rows: list[SampleRow], with_status: bool = False) -> torch.Tensor:
+        """int32 [M] token ids on the device for float32 ``logits`` [M, vocab]; ``with_status`` appends the device
+        error word as element M (``ops.argmax``)."""
         if logits.shape[0] != len(rows):
             raise ValueError(f"{logits.shape[0]} logit rows but {len(rows)} sampling rows")
         if all(r.params.is_greedy for r in rows):
-            return self.greedy(logits)
+            return self.greedy(logits, with_status)
         m = len(rows)
         # every row's parameters in one pinned buffer and one copy: [4 float32 | 2 int32 | 2 int64] x m
         host = torch.empty(40 * m, dtype=torch.uint8, pin_memory=True)
@@ -84,4 +85,4 @@ class Sampler:
         i32 = dev[16 * m: 24 * m].view(torch.int32).view(2, m)
         i64 = dev[24 * m:].view(torch.int64).view(2, m)
         return ops.sample(logits, temperature=f[0], top_p=f[1], min_p=f[2], penalty=f[3], top_k=i32[0],
-                          slots=i32[1], seeds=i64[0], draws=i64[1], seen=self.seen)
+                          slots=i32[1], seeds=i64[0], draws=i64[1], seen=self.seen, with_status=with_status)
