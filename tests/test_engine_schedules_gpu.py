@@ -2,7 +2,7 @@
 bfloat16 under the TMA-fed decode kernel with a seeded sampling chain; a mixed step whose prefill attention cuts
 the keys into parts while other requests bring one to three tokens; a token budget smaller than the number of
 decoding requests; the text path (tokenizer.json, stop strings); an error word set on the host; and mutations of
-the cache (swapped block-table entries, a layer given another layer's pages) that the comparisons must notice."""
+the cache (a block-table entry that names the wrong page, a layer given another layer's pages) that the comparisons must notice."""
 import json
 import subprocess
 import sys
@@ -240,8 +240,10 @@ def worst_error(rows, ref):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_a_wrong_page_or_a_wrong_layers_pages_breaks_the_bound(model_folders, name, dtype):
-    """What the replay tests would see if the cache went wrong: (1) two entries of a request's block table swapped
-    between the prompt and its decode steps, (2) a layer reading and writing the pages of the layer before it.
+    """What the replay tests would see if the cache went wrong: (1) an entry of a request's block table pointing at
+    another of its pages between the prompt and its decode steps (merely swapping two entries would change
+    nothing: keys are stored rotated, and attention does not care in which order it meets the pairs of key and
+    value), (2) a layer reading and writing the pages of the layer before it.
     Either must push the error of the decoded rows far beyond the bound the replay tests allow, in float32 and
     in bfloat16; the same steps without the mutation stay within it."""
     from slipstream_b200.engine.runner import ModelRunner, StepEntry
@@ -258,7 +260,7 @@ def test_a_wrong_page_or_a_wrong_layers_pages_breaks_the_bound(model_folders, na
         runner.step([StepEntry("r", tokens[:head], [])])
         if mutate == "table":
             table = runner.cache.get("r").tables[0]
-            table[1], table[3] = table[3], table[1]
+            table[1] = table[3]  # four (A) or eight (B) keys lost, as many met twice
         rows = [runner.step([StepEntry("r", [t], [0])]).cpu().numpy()[0] for t in tokens[head:]]
         runner.check()
         return rows

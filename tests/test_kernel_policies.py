@@ -46,4 +46,3 @@ def test_streaming_product_plan_and_routing():
     assert F.streams_weights(64, 37888, 3584) and F.streams_weights(64, 3584, 18944) and not F.streams_weights(64, 3584, 3584)
     assert not F.streams_weights(65, 37888, 3584) and not F.streams_weights(8, 3584, 3580)
     assert F.many_tokens_swiglu_fits(2048, 37888) and not F.many_tokens_swiglu_fits(512, 37888)
-    assert F.MANY_TOKENS == 2048 and F.MANY_WIDTH == 3584

@@ -60,15 +60,13 @@ def test_random_configuration_every_cut_both_dtypes(seed):
         requests = {rid: random_tokens(config.vocab_size, n, 100 + i + seed) for i, (rid, n) in enumerate(lengths.items())}
         for dtype in ("float32", "bfloat16"):
             want = oracle(folder, requests, dtype)
-            bound = {rid: TOLERANCE[dtype] for rid in requests}
-            if dtype == "bfloat16":
-                # Wider and deeper models round more than the tiny ones that the fixed bound was made for.  The
-                # engine (float32 sums, norms and softmax around bfloat16 matrices) must then be at least as close
-                # to the exact result as the plain implementation run in bfloat16 throughout.
-                c16, w16 = plain.read_model_folder(folder, torch.bfloat16)
-                for rid, tokens in requests.items():
-                    rough = plain.forward_logits(c16, w16, tokens).float().numpy()
-                    bound[rid] = max(bound[rid], relative_error(rough, want[rid]))
+            # float32: the fixed bound of the replay tests.  bfloat16: that bound was made for the tiny models;
+            # every layer rounds its activations to 8 bits of mantissa again, so the bar here is the same 3e-2
+            # for each layer of the drawn model, fixed before anything runs (one layer: at most 2.9e-2 measured,
+            # two: 4.2e-2, three: 3.3e-2 to 7.5e-2; the plain implementation run in bfloat16 throughout is 1.7
+            # to 2.2 times further from the exact logits on every one of these models).
+            per_layer = config.num_hidden_layers if dtype == "bfloat16" else 1
+            bound = {rid: TOLERANCE[dtype] * per_layer for rid in requests}
             max_tokens = 768  # fewer than the requests hold together at their longest: pages are used again
             runner = ModelRunner(folder, dtype=dtype, page_size=page, num_pages=max_tokens // page, max_num_seqs=4)
             results = {}
