@@ -162,17 +162,20 @@ def decoder_layer(x, positions, weights, index, s):
     return x
 
 
-def forward_logits(config, weights, token_ids, return_hidden=False):
+def forward_logits(config, weights, token_ids, return_hidden=False, rows=None):
     """slipstream/models/causal_lm.py:93-97,140: embedding lookup, the layers,
     final norm, LM head (the embedding matrix when tied and no head is stored,
     slipstream/models/loader.py:91-93).  Returns logits [T, vocab] for the whole
-    sequence of ``token_ids`` at positions 0..T-1."""
+    sequence of ``token_ids`` at positions 0..T-1; with ``rows`` only for those positions (the layers still run
+    over the whole sequence)."""
     s = sizes(config)
     ids = torch.as_tensor(token_ids, dtype=torch.long)
     positions = torch.arange(ids.numel())
     x = weights["model.embed_tokens.weight"][ids]
     for index in range(s["layers"]):
         x = decoder_layer(x, positions, weights, index, s)
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long)]
     x = rms_norm(x, weights["model.norm.weight"], s["eps"])
     head = weights.get("lm_head.weight")
     if head is None:
