@@ -1,9 +1,10 @@
 """Cache manager: pages of keys and values, block tables, fixed-size state slots.
 
 Layers are grouped by what they need from the cache (``CacheSpec``: key/value
-heads, head size, window).  Each group has its own page pool and each request has
-one block table per group; a page id is valid for every layer of its group, as
-in the reference's single pool (slipstream/memory/paged_cache.py:13-28).  Pages
+heads, head size, window, page size).  Each group has its own page pool, with its
+own page size and number of pages, and each request has one block table per group;
+a page id is valid for every layer of its group, as in the reference's single pool
+(slipstream/memory/paged_cache.py:13-28).  Pages
 come from a LIFO free list (slipstream/memory/block_manager.py:42,272-280), so a
 page given back is the next one handed out.  Pages return when a request is
 released (:169-181) or, in a windowed group, as soon as no later query can see
@@ -40,10 +41,13 @@ class OutOfPages(CacheError):
 
 @dataclass
 class GroupLayout:
-    """One cache group: the spec its layers share and how many of them write pages."""
+    """One cache group: the spec its layers share, how many of them write pages, and (once the runner has sized
+    the pools) its page size and number of pages."""
 
     spec: CacheSpec
     num_entries: int = 0
+    page_size: int = 0
+    num_pages: int = 0
 
 
 class PagePool:
@@ -95,19 +99,66 @@ class RequestPages:
     first_block: list[int] = field(default_factory=list)  # per group: first block still held
 
 
+def pool_sizes(groups: list[GroupLayout], page_sizes: list[int], tokens: int, max_num_seqs: int,
+               max_model_len: int, max_step_tokens: int) -> list[int]:
+    """Pages each group needs so that the cache holds ``tokens`` tokens of live requests.  A group that keeps every
+    key gets ``tokens / page size`` pages.  A windowed group never holds more of a request than its window plus
+    the tokens of one step (pages are reserved for a whole step before the window moves on), so it gets at most
+    that for ``max_num_seqs`` requests: its pool is smaller than its neighbours'."""
+    sizes = []
+    for layout, page in zip(groups, page_sizes):
+        pages = max(1, -(-tokens // page))
+        window = layout.spec.window
+        if window is not None:
+            span = min(max_model_len, window + max(1, max_step_tokens))
+            pages = min(pages, max_num_seqs * (-(-span // page) + 1))
+        sizes.append(pages)
+    return sizes
+
+
+def tokens_that_fit(groups: list[GroupLayout], page_sizes: list[int], bytes_per_token: list[int], budget: int,
+                    max_num_seqs: int, max_model_len: int, max_step_tokens: int) -> int:
+    """The most tokens whose pools (``pool_sizes``) fit into ``budget`` bytes, at most what ``max_num_seqs``
+    requests of ``max_model_len`` tokens need."""
+    def cost(tokens: int) -> int:
+        pools = pool_sizes(groups, page_sizes, tokens, max_num_seqs, max_model_len, max_step_tokens)
+        return sum(n * page * per for n, page, per in zip(pools, page_sizes, bytes_per_token))
+
+    low, high = 1, max_num_seqs * (max_model_len + max(page_sizes, default=1))
+    if cost(high) <= budget:
+        return high
+    while low < high:
+        mid = (low + high + 1) // 2
+        if cost(mid) <= budget:
+            low = mid
+        else:
+            high = mid - 1
+    return low
+
+
+def _per_group(value, n: int, what: str) -> list[int]:
+    values = [int(v) for v in value] if isinstance(value, (list, tuple)) else [int(value)] * n
+    if len(values) != n:
+        raise ValueError(f"{what}: {len(values)} values for {n} cache groups")
+    return values
+
+
 class CacheManager:
-    def __init__(self, groups: list[GroupLayout], num_pages: int, page_size: int, max_num_seqs: int,
-                 max_model_len: int) -> None:
-        if page_size < 1:
+    def __init__(self, groups: list[GroupLayout], num_pages: "int | list[int]", page_size: "int | list[int]",
+                 max_num_seqs: int, max_model_len: int) -> None:
+        """``num_pages`` and ``page_size``: one value for every group, or one per group."""
+        self.groups = groups
+        self.page_sizes = _per_group(page_size, len(groups), "page_size")
+        counts = _per_group(num_pages, len(groups), "num_pages")
+        if any(p < 1 for p in self.page_sizes):
             raise ValueError("page_size must be >= 1")
         if max_num_seqs < 1:
             raise ValueError("max_num_seqs must be >= 1")
-        self.groups = groups
-        self.page_size = page_size
-        self.num_pages = num_pages
+        for layout, size, count in zip(groups, self.page_sizes, counts):
+            layout.page_size, layout.num_pages = size, count
         self.max_num_seqs = max_num_seqs
         self.max_model_len = max_model_len
-        self.pools = [PagePool(num_pages) for _ in groups]
+        self.pools = [PagePool(count) for count in counts]
         self._free_slots = list(range(max_num_seqs - 1, -1, -1))
         self._requests: dict[object, RequestPages] = {}
 
@@ -127,24 +178,40 @@ class CacheManager:
     def length(self, request_id: object) -> int:
         return self.get(request_id).length
 
+    @property
+    def page_size(self) -> int:
+        """Page size of the first group (the only one of a model whose layers all need the same)."""
+        return self.page_sizes[0] if self.page_sizes else 1
+
+    @property
+    def num_pages(self) -> int:
+        return self.pools[0].num_pages if self.pools else 0
+
     def num_free_pages(self, group: int = 0) -> int:
         return self.pools[group].num_free if self.pools else 0
 
+    def free_pages(self) -> list[int]:
+        return [pool.num_free for pool in self.pools]
+
+    def all_pages_free(self) -> bool:
+        return all(pool.num_free == pool.num_pages for pool in self.pools)
+
     def min_free_pages(self) -> int:
-        return min((p.num_free for p in self.pools), default=self.num_pages)
+        return min((p.num_free for p in self.pools), default=0)
 
     def num_free_slots(self) -> int:
         return len(self._free_slots)
 
-    def blocks_for(self, tokens: int) -> int:
-        return 0 if tokens <= 0 else (tokens + self.page_size - 1) // self.page_size
+    def blocks_for(self, tokens: int, group: int = 0) -> int:
+        size = self.page_sizes[group]
+        return 0 if tokens <= 0 else (tokens + size - 1) // size
 
     def _first_needed_block(self, group: int, length: int) -> int:
         """First block that a query at position >= ``length`` can still see."""
         window = self.groups[group].spec.window
         if window is None:
             return 0
-        return max(0, length - window + 1) // self.page_size
+        return max(0, length - window + 1) // self.page_sizes[group]
 
     def pages_needed(self, request_id: object, new_tokens: int) -> list[int]:
         """Pages each group must still hand out to cover ``new_tokens`` more tokens."""
@@ -152,34 +219,44 @@ class CacheManager:
         target = req.length + new_tokens
         if target <= req.reserved:
             return [0] * len(self.groups)
-        return [self.blocks_for(target) - len(table) for table in req.tables]
+        return [self.blocks_for(target, g) - len(table) for g, table in enumerate(req.tables)]
 
     def peak_pages(self, group: int, total_tokens: int, chunk: int) -> int:
         """Most pages of ``group`` a request of ``total_tokens`` holds at any time when it is fed
         at most ``chunk`` tokens a step."""
         window = self.groups[group].spec.window
         if window is None:
-            return self.blocks_for(total_tokens)
+            return self.blocks_for(total_tokens, group)
         span = min(total_tokens, window + max(chunk, 1))
-        return min(self.blocks_for(total_tokens), self.blocks_for(span) + 1)
+        return min(self.blocks_for(total_tokens, group), self.blocks_for(span, group) + 1)
 
     def can_admit(self, total_tokens: int, first_tokens: int, chunk: int) -> AllocStatus:
         """Three-way answer of slipstream/memory/block_manager.py:108-128: NEVER when the request at
         its full length (``total_tokens`` = prompt + output cap, capped by the context) cannot fit in
-        an empty pool; LATER when pages or a slot for its first ``first_tokens`` are missing now."""
+        an empty pool of some group; LATER when pages of some group or a slot for its first
+        ``first_tokens`` are missing now."""
         total = min(total_tokens, self.max_model_len)
-        for g in range(len(self.groups)):
-            if self.peak_pages(g, total, chunk) > self.num_pages:
+        for g, pool in enumerate(self.pools):
+            if self.peak_pages(g, total, chunk) > pool.num_pages:
                 return AllocStatus.NEVER
         if not self._free_slots:
             return AllocStatus.LATER
-        need = self.blocks_for(first_tokens)
-        if any(need > pool.num_free for pool in self.pools):
+        if any(self.blocks_for(first_tokens, g) > pool.num_free for g, pool in enumerate(self.pools)):
             return AllocStatus.LATER
         return AllocStatus.OK
 
     def can_reserve(self, request_id: object, new_tokens: int) -> bool:
         return all(n <= pool.num_free for n, pool in zip(self.pages_needed(request_id, new_tokens), self.pools))
+
+    def can_reserve_all(self, wanted: "list[tuple[object, int]]") -> bool:
+        """Whether every (request, new tokens) of ``wanted`` can be served together from what is free now."""
+        left = [pool.num_free for pool in self.pools]
+        for request_id, new_tokens in wanted:
+            for g, need in enumerate(self.pages_needed(request_id, new_tokens)):
+                left[g] -= need
+                if left[g] < 0:
+                    return False
+        return True
 
     # ------------------------------------------------------------------ changes
     def admit(self, request_id: object) -> RequestPages:
@@ -241,8 +318,9 @@ class CacheManager:
         for req in self._requests.values():
             for g, table in enumerate(req.tables):
                 pages = sum(1 for p in table if p >= 0)
-                held += pages * self.page_size
-                useful += min(req.length - req.first_block[g] * self.page_size, pages * self.page_size)
+                size = self.page_sizes[g]
+                held += pages * size
+                useful += min(req.length - req.first_block[g] * size, pages * size)
         return 1.0 if held == 0 else useful / held
 
     def check_invariants(self) -> None:

@@ -19,16 +19,17 @@ from .manager import GroupLayout
 
 
 class PagedStore:
-    def __init__(self, layouts: list[GroupLayout], num_pages: int, page_size: int, dtype: torch.dtype,
-                 device: torch.device, state_specs: list[list[StateSpec]], max_num_seqs: int) -> None:
-        self.num_pages = num_pages
-        self.page_size = page_size
+    def __init__(self, layouts: list[GroupLayout], dtype: torch.dtype, device: torch.device,
+                 state_specs: list[list[StateSpec]], max_num_seqs: int) -> None:
+        """``layouts`` carry each group's page size and number of pages (the cache manager fills them in)."""
         self.dtype = dtype
         self.kv: list[torch.Tensor] = []
         for layout in layouts:
             spec = layout.spec
+            if layout.page_size < 1 or layout.num_pages < 1:
+                raise ValueError("a cache group has no page size or number of pages yet")
             self.kv.append(torch.zeros(
-                (max(layout.num_entries, 1), num_pages, 2, spec.num_kv_heads, page_size, spec.head_dim),
+                (max(layout.num_entries, 1), layout.num_pages, 2, spec.num_kv_heads, layout.page_size, spec.head_dim),
                 dtype=dtype, device=device))
         self.state: list[dict[str, torch.Tensor]] = []
         for specs in state_specs:
@@ -45,10 +46,10 @@ class PagedStore:
         return total
 
     @staticmethod
-    def bytes_per_page(layouts: list[GroupLayout], page_size: int, dtype: torch.dtype) -> int:
+    def bytes_per_token(layout: GroupLayout, dtype: torch.dtype) -> int:
+        """Bytes of one cached token in one group, over the group's entries."""
         size = torch.empty((), dtype=dtype).element_size()
-        return sum(max(l.num_entries, 1) * 2 * l.spec.num_kv_heads * page_size * l.spec.head_dim * size
-                   for l in layouts)
+        return max(layout.num_entries, 1) * 2 * layout.spec.num_kv_heads * layout.spec.head_dim * size
 
     def zero_state(self, slot: int) -> None:
         for entry in self.state:

@@ -56,6 +56,35 @@ extern "C" int ss_gather_tokens(int32_t* ids, const int32_t* src, const int32_t*
     return SS_LAUNCH_CHECK();
 }
 
+// What a replayed decode step needs done in front of it, in one launch: (1) rows whose token was sampled by the
+// step before and has not reached the host take it from `pending`; (2) the block tables, which stay on the
+// device from step to step, receive this step's changes: tables[patch_idx[i]] = patch_val[i] for i < *n_patches
+// (a request's newly reserved page, the pages a window has passed, or a whole row when another request takes it).
+__global__ void prepare_decode_kernel(int32_t* __restrict__ ids, const int32_t* __restrict__ src,
+                                      const int32_t* __restrict__ pending, int n, int32_t* __restrict__ tables,
+                                      const int32_t* __restrict__ patch_idx, const int32_t* __restrict__ patch_val,
+                                      const int32_t* __restrict__ n_patches, int max_patches, int64_t table_len) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pending != nullptr && i < n && src[i] >= 0) ids[i] = pending[src[i]];
+    const int count = min(*n_patches, max_patches);
+    if (i < count) {
+        const int at = patch_idx[i];
+        if (at >= 0 && at < table_len) tables[at] = patch_val[i];
+    }
+}
+
+extern "C" int ss_prepare_decode(int32_t* ids, const int32_t* src, const int32_t* pending, int n, int32_t* tables,
+                                 const int32_t* patch_idx, const int32_t* patch_val, const int32_t* n_patches,
+                                 int max_patches, int64_t table_len, cudaStream_t stream) {
+    const int threads = n > max_patches ? n : max_patches;
+    if (threads <= 0) return 0;
+    ss_launch(prepare_decode_kernel, dim3((threads + 127) / 128), dim3(128), 0, stream, ids, src, pending, n, tables,
+              patch_idx, patch_val, n_patches, max_patches, table_len);
+    return SS_LAUNCH_CHECK();
+}
+
 // ---------------------------------------------------------------- add + RMSNorm
 
 // One block per output row.  residual (float32) += delta, y = weight * round(x_hat).

@@ -89,6 +89,10 @@ class StepContext:
             self._tiles[key] = cached
         return cached
 
+    def set_query_tiles(self, rows: int, group: int, tile_req: torch.Tensor, tile_first: torch.Tensor) -> None:
+        """Fix the answer of ``query_tiles(rows, group)`` (a part does this for the static context of a graph)."""
+        self._tiles[(rows, group)] = (tile_req, tile_first)
+
 
 def query_tiles_host(q_lens: np.ndarray, rows: int) -> tuple[np.ndarray, np.ndarray]:
     counts = (q_lens + rows - 1) // rows
@@ -115,9 +119,10 @@ class HostPlan:
     slots: np.ndarray
     first: np.ndarray
     logit_rows: np.ndarray
-    tables: np.ndarray  # [groups, R, max_blocks]
+    tables: list[np.ndarray]  # per cache group [R, max_blocks of that group]
     slot_maps: np.ndarray  # [groups, N]
-    page_size: int
+    page_sizes: list[int]  # per cache group
+    requests: list = field(default_factory=list)  # the cache manager's record of each entry's request
 
     @property
     def num_requests(self) -> int:
@@ -132,8 +137,11 @@ class HostPlan:
         return bool((self.q_lens == 1).all())
 
 
-def plan_step(entries: list[StepEntry], cache: CacheManager, vocab_size: int, reserve: bool = True) -> HostPlan:
-    """Check the entries, reserve their pages and lay the step's metadata out in host arrays."""
+def plan_step(entries: list[StepEntry], cache: CacheManager, vocab_size: int, reserve: bool = True,
+              with_tables: bool = True) -> HostPlan:
+    """Check the entries, reserve their pages and lay the step's metadata out in host arrays.  ``with_tables``
+    False leaves the block tables out (``plan.tables`` is empty and ``plan.requests`` holds the cache manager's
+    records instead): a replayed decode graph keeps its tables on the device and only patches them."""
     if not entries:
         raise StepInputError("a step needs at least one entry")
     seen: set[object] = set()
@@ -167,29 +175,42 @@ def plan_step(entries: list[StepEntry], cache: CacheManager, vocab_size: int, re
     slots = np.fromiter((r.slot for r in reqs), dtype=np.int32, count=R)
     first = (before == 0).astype(np.int32)
 
-    ps = cache.page_size
     n_groups = len(cache.groups)
-    max_blocks = max(1, int((int(seq_lens.max()) + ps - 1) // ps))
-    tables = np.full((n_groups, R, max_blocks), -1, dtype=np.int32)
+    longest = int(seq_lens.max())
+    tables = []
     slot_maps = np.empty((n_groups, N), dtype=np.int32)
     for g in range(n_groups):
+        ps = cache.page_sizes[g]
+        if not with_tables:  # one token per request, or few: look the pages up directly
+            try:
+                pages = np.fromiter((reqs[i].tables[g][p // ps] for i, p in zip(row_req.tolist(), positions.tolist())),
+                                    dtype=np.int32, count=N)
+            except IndexError:
+                raise StepInputError("a new token falls on a block without a page") from None
+            if (pages < 0).any():
+                raise StepInputError("a new token falls on a block without a page")
+            slot_maps[g] = pages * ps + positions % ps
+            continue
+        max_blocks = max(1, (longest + ps - 1) // ps)
+        table = np.full((R, max_blocks), -1, dtype=np.int32)
         for i, r in enumerate(reqs):
             t = r.tables[g][:max_blocks]
-            tables[g, i, : len(t)] = t
-        pages = tables[g][row_req, positions // ps]
+            table[i, : len(t)] = t
+        pages = table[row_req, positions // ps]
         if (pages < 0).any():
             raise StepInputError("a new token falls on a block without a page")
         slot_maps[g] = pages * ps + positions % ps
+        tables.append(table)
     return HostPlan(entries, q_lens, token_ids.astype(np.int32), positions, q_start, seq_lens, slots, first,
-                    logit_rows, tables, slot_maps, ps)
+                    logit_rows, tables, slot_maps, list(cache.page_sizes), reqs)
 
 
 def to_device(plan: HostPlan, device: torch.device) -> StepContext:
     """One host buffer, one copy, then views of it."""
     R, N = plan.num_requests, plan.num_tokens
-    n_groups, _, max_blocks = plan.tables.shape
+    n_groups = len(plan.tables)
     parts = [plan.token_ids, plan.positions, plan.q_start, plan.seq_lens, plan.slots, plan.first,
-             plan.logit_rows, plan.tables.reshape(-1), plan.slot_maps.reshape(-1)]
+             plan.logit_rows, plan.slot_maps.reshape(-1)] + [t.reshape(-1) for t in plan.tables]
     sizes = [p.size for p in parts]
     host = torch.empty(int(sum(sizes)), dtype=torch.int32, pin_memory=torch.cuda.is_available())
     np.concatenate(parts, out=host.numpy())
@@ -198,9 +219,9 @@ def to_device(plan: HostPlan, device: torch.device) -> StepContext:
     cut = [dev[offs[i]: offs[i + 1]] for i in range(len(parts))]
     groups = []
     for g in range(n_groups):
-        groups.append(GroupMeta(
-            block_tables=cut[7][g * R * max_blocks: (g + 1) * R * max_blocks].view(R, max_blocks),
-            slot_mapping=cut[8][g * N: (g + 1) * N], page_size=plan.page_size, max_blocks=max_blocks))
+        max_blocks = plan.tables[g].shape[1]
+        groups.append(GroupMeta(block_tables=cut[8 + g].view(R, max_blocks), slot_mapping=cut[7][g * N: (g + 1) * N],
+                                page_size=plan.page_sizes[g], max_blocks=max_blocks))
     ctx = StepContext(num_tokens=N, num_requests=R, token_ids=cut[0], positions=cut[1], q_start=cut[2],
                       seq_lens=cut[3], state_slots=cut[4], first_chunk=cut[5], logit_rows=cut[6],
                       groups=groups, q_lens_host=plan.q_lens, seq_lens_host=plan.seq_lens,

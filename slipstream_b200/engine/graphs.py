@@ -3,11 +3,24 @@
 A step in which every request brings one token launches a few hundred small
 kernels; at batch 1 the launches cost more than the kernels.  For such steps the
 runner captures the whole forward once per batch-size bucket and replays it.
-The captured step reads its metadata (token ids, positions, lengths, block
-tables, slot mapping) from a static device buffer that is refilled by one copy
-before each replay; rows beyond the live requests are padding (length 0, slot
--1), which every kernel skips.  The split of the decode attention over the keys
-is fixed per bucket, so grids do not depend on the lengths.
+The captured step reads its metadata (token ids, positions, lengths, slot
+mapping) from a small static device buffer that is refilled by one copy before
+each replay; rows beyond the live requests are padding (length 0, slot -1), which
+every kernel skips.
+
+The block tables stay on the device from step to step.  A decode step changes at
+most one entry per request and cache group (a newly reserved page; in a windowed
+group also the pages the window has passed), so the host sends only those changes
+as (index, value) patches inside the same small copy, and the kernel in front of
+the replay applies them.  When a row of the batch goes to another request its whole
+row is patched; a step with more changes than the patch area holds (many requests
+arriving at once) copies the host's mirror of the tables instead.
+
+What a part's forward would take from the host-side lengths of a step (how many
+slices the decode attention cuts the keys into, say) is fixed when the graph is
+captured: every part gets ``prepare_capture`` on the static context, and parts whose
+best form depends on the lengths say so through ``capture_variant``; the runner keeps
+one graph per bucket and combination of variants.
 
 The reference has a ``CudaGraphPool`` keyed by batch size that was never wired
 into its serving loop (slipstream/engine/cuda_graph.py:1-93).
@@ -36,25 +49,39 @@ def bucket_for(n: int) -> int | None:
 
 
 class DecodeGraph:
-    def __init__(self, runner, bucket: int, wide: bool = False) -> None:
+    def __init__(self, runner, bucket: int, variants: tuple = ()) -> None:
         self.runner = runner
         self.bucket = bucket
-        self.wide = wide  # captured for long contexts: attention may cut the keys into more than 8 slices
+        self.variants = variants
         cache = runner.cache
-        self.n_groups = len(cache.groups)
-        self.max_blocks = max(1, (runner.max_model_len + cache.page_size - 1) // cache.page_size)
-        B, G, MB = bucket, self.n_groups, self.max_blocks
+        G = self.n_groups = len(cache.groups)
+        B = bucket
+        self.max_blocks = [max(1, (runner.max_model_len + ps - 1) // ps) for ps in cache.page_sizes]
+        self.table_offsets = np.concatenate([[0], np.cumsum([B * mb for mb in self.max_blocks])]).astype(np.int64)
+        self.max_patches = max(64, 4 * B * max(G, 1))
+        P = self.max_patches
         names = ["token_ids", "positions", "q_start", "seq_lens", "slots", "first", "logit_rows", "src_rows",
-                 "tables", "slot_maps"]
-        sizes = [B, B, B + 1, B, B, B, B, B, G * B * MB, G * B]
+                 "slot_maps", "n_patches", "patch_idx", "patch_val"]
+        sizes = [B, B, B + 1, B, B, B, B, B, G * B, 1, P, P]
         self.offsets = dict(zip(names, np.concatenate([[0], np.cumsum(sizes)])[:-1].tolist()))
         self.sizes = dict(zip(names, sizes))
         total = int(sum(sizes))
         device = runner.device
         self.static = torch.zeros(total, dtype=torch.int32, device=device)
         self.hosts = [torch.zeros(total, dtype=torch.int32, pin_memory=True) for _ in range(HOST_RING)]
-        self.events: list[torch.cuda.Event | None] = [None] * HOST_RING
+        self.events: list[torch.cuda.Event] = [torch.cuda.Event() for _ in range(HOST_RING)]
+        self.used = [False] * HOST_RING
         self.turn = 0
+        # block tables: on the device for good, mirrored on the host
+        n_table = max(1, int(self.table_offsets[-1]))
+        self.tables_dev = torch.full((n_table,), -1, dtype=torch.int32, device=device)
+        self.tables_host = torch.full((n_table,), -1, dtype=torch.int32, pin_memory=True)
+        self.mirror = self.tables_host.numpy()
+        self.mirror_event: torch.cuda.Event | None = None  # a copy of the whole mirror that may still be running
+        self.row_owner: list[object] = [None] * B  # the cache manager's record of the request whose table each row holds
+        self.row_synced = [[0] * B for _ in range(G)]  # entries of the request's table that the row holds
+        self.row_first = [[0] * B for _ in range(G)]  # first block not yet given back, as the row knows it
+        self.full_copies = 0
 
         def view(name: str) -> torch.Tensor:
             o = self.offsets[name]
@@ -62,19 +89,21 @@ class DecodeGraph:
 
         groups = []
         for g in range(G):
-            groups.append(GroupMeta(block_tables=view("tables")[g * B * MB: (g + 1) * B * MB].view(B, MB),
+            mb, o = self.max_blocks[g], int(self.table_offsets[g])
+            groups.append(GroupMeta(block_tables=self.tables_dev[o: o + B * mb].view(B, mb),
                                     slot_mapping=view("slot_maps")[g * B: (g + 1) * B],
-                                    page_size=cache.page_size, max_blocks=MB))
+                                    page_size=cache.page_sizes[g], max_blocks=mb))
         ones = np.ones(B, dtype=np.int32)
         self.ctx = StepContext(num_tokens=B, num_requests=B, token_ids=view("token_ids"),
                                positions=view("positions"), q_start=view("q_start"), seq_lens=view("seq_lens"),
                                state_slots=view("slots"), first_chunk=view("first"), logit_rows=view("logit_rows"),
                                groups=groups, q_lens_host=ones, seq_lens_host=ones, request_ids=[], device=device,
                                num_logits=B)
-        self.ctx.extras["static_max_seq_len"] = runner.max_model_len
-        self.ctx.extras["decode_wide"] = wide
-        arange = torch.arange(B, dtype=torch.int32, device=device)
-        self.ctx._tiles[(16, 1)] = (arange, torch.zeros(B, dtype=torch.int32, device=device))
+        self._views = {name: view(name) for name in ("token_ids", "src_rows", "n_patches", "patch_idx", "patch_val")}
+        # what the parts want fixed for this bucket and these variants
+        variant_of = {part.capture_group(): variant for part, variant in zip(runner.variant_parts, variants)}
+        for part in runner.model.parts():
+            part.prepare_capture(self.ctx, variant_of.get(part.capture_group()), runner.max_model_len)
         self._fill(self.hosts[0].numpy(), None)
         self.static.copy_(self.hosts[0])
         # warm up outside the capture (library handles, lazily compiled kernels), then capture
@@ -99,13 +128,13 @@ class DecodeGraph:
                 gc.enable()
         self.kernels = ops.launch_count() - before
 
+    # ------------------------------------------------------------------ per step
     def _fill(self, host: np.ndarray, plan: HostPlan | None) -> None:
-        B, MB, G = self.bucket, self.max_blocks, self.n_groups
+        B, G = self.bucket, self.n_groups
         o = self.offsets
-        host[:] = 0
+        host[: o["patch_idx"]] = 0
         host[o["q_start"]: o["q_start"] + B + 1] = np.arange(B + 1, dtype=np.int32)
         host[o["logit_rows"]: o["logit_rows"] + B] = np.arange(B, dtype=np.int32)
-        host[o["tables"]: o["tables"] + G * B * MB] = -1
         host[o["slot_maps"]: o["slot_maps"] + G * B] = -1
         host[o["src_rows"]: o["src_rows"] + B] = -1
         if plan is None:
@@ -114,42 +143,81 @@ class DecodeGraph:
         for name, arr in (("token_ids", plan.token_ids), ("positions", plan.positions),
                           ("seq_lens", plan.seq_lens), ("slots", plan.slots), ("first", plan.first)):
             host[o[name]: o[name] + R] = arr
-        mb = plan.tables.shape[2]
-        tables = host[o["tables"]: o["tables"] + G * B * MB].reshape(G, B, MB)
-        tables[:, :R, :mb] = plan.tables
         host[o["slot_maps"]: o["slot_maps"] + G * B].reshape(G, B)[:, :R] = plan.slot_maps
+
+    def _table_changes(self, plan: HostPlan) -> tuple[list[int], list[int]]:
+        """Bring the host's mirror of the block tables up to this step and return what changed as (flat index,
+        value) lists.  Row i of the batch holds the table of ``plan.requests[i]``."""
+        idx: list[int] = []
+        val: list[int] = []
+        if self.mirror_event is not None:  # the mirror must not change under a copy of it
+            self.mirror_event.synchronize()
+            self.mirror_event = None
+        mirror = self.mirror
+        for i, req in enumerate(plan.requests):
+            # the manager's record itself, not the request's name: a request that was preempted and admitted again
+            # keeps its name but starts a new table
+            fresh = self.row_owner[i] is not req
+            if fresh:
+                self.row_owner[i] = req
+            for g in range(self.n_groups):
+                table = req.tables[g]
+                base = int(self.table_offsets[g]) + i * self.max_blocks[g]
+                synced = 0 if fresh else self.row_synced[g][i]
+                first_known = 0 if fresh else self.row_first[g][i]
+                first = req.first_block[g]
+                if first > first_known and not fresh:  # pages a window has passed
+                    for b in range(first_known, min(first, synced)):
+                        idx.append(base + b)
+                        val.append(-1)
+                        mirror[base + b] = -1
+                if len(table) > synced:
+                    new = table[synced:]
+                    idx.extend(range(base + synced, base + len(table)))
+                    val.extend(new)
+                    mirror[base + synced: base + len(table)] = new
+                self.row_synced[g][i] = len(table)
+                self.row_first[g][i] = first
+        return idx, val
 
     def run(self, plan: HostPlan, pending: torch.Tensor | None = None, src_rows: np.ndarray | None = None,
             keep: bool = True) -> torch.Tensor:
-        """Refill the static metadata, replay the step, return the logits of the wanted rows.
+        """Refill the static metadata, patch the tables, replay the step, return the logits of the wanted rows.
 
         ``pending`` / ``src_rows``: token ids that are still on the device (sampled by the step before): row r
         takes ``pending[src_rows[r]]`` where ``src_rows[r] >= 0``.  ``keep`` False returns a view of the static
         logits buffer, valid until the next replay."""
         i = self.turn
         self.turn = (i + 1) % HOST_RING
-        if self.events[i] is not None:
+        if self.used[i]:
             self.events[i].synchronize()  # the copy that last used this host buffer has run
         host = self.hosts[i].numpy()
         self._fill(host, plan)
+        o = self.offsets
         if src_rows is not None:
-            o = self.offsets["src_rows"]
-            host[o: o + src_rows.size] = src_rows
+            host[o["src_rows"]: o["src_rows"] + src_rows.size] = src_rows
+        idx, val = self._table_changes(plan)
+        if len(idx) <= self.max_patches:
+            host[o["n_patches"]] = len(idx)
+            host[o["patch_idx"]: o["patch_idx"] + len(idx)] = idx
+            host[o["patch_val"]: o["patch_val"] + len(idx)] = val
+        else:  # too many changes for the patch area: send the whole mirror
+            self.tables_dev.copy_(self.tables_host, non_blocking=True)
+            self.mirror_event = torch.cuda.Event()
+            self.mirror_event.record()
+            self.full_copies += 1
         self.static.copy_(self.hosts[i], non_blocking=True)
-        event = torch.cuda.Event()
-        event.record()
-        self.events[i] = event
-        if pending is not None:
-            o = self.offsets
-            ops.gather_tokens(self.static[o["token_ids"]: o["token_ids"] + self.bucket],
-                              self.static[o["src_rows"]: o["src_rows"] + self.bucket], pending)
+        self.events[i].record()
+        self.used[i] = True
+        v = self._views
+        ops.prepare_decode(v["token_ids"], v["src_rows"], pending, self.tables_dev, v["patch_idx"], v["patch_val"],
+                           v["n_patches"])
         self.graph.replay()
         ops.count_launches(self.kernels)
         R = plan.num_requests
-        if not keep and plan.logit_rows.size == R and bool((plan.logit_rows == np.arange(R)).all()):
-            return self.logits[:R]
-        if plan.logit_rows.size == R and bool((plan.logit_rows == np.arange(R)).all()):
-            return self.logits[:R].clone()
+        in_order = plan.logit_rows.size == R and bool((plan.logit_rows == np.arange(R)).all())
+        if in_order:
+            return self.logits[:R] if not keep else self.logits[:R].clone()
         if plan.logit_rows.size == 0:
             return self.logits[:0].clone()
         rows = torch.from_numpy(plan.logit_rows.astype(np.int64)).to(self.runner.device)
@@ -157,4 +225,5 @@ class DecodeGraph:
 
     @property
     def h2d_bytes(self) -> int:
+        """Bytes the host sends per replay (the small static buffer; the tables travel as patches inside it)."""
         return self.static.numel() * 4

@@ -106,7 +106,9 @@ class LLMEngine:
             m.model_id, dtype=m.dtype, page_size=c.block_size, num_pages=c.num_gpu_blocks,
             gpu_memory_utilization=c.gpu_memory_utilization, max_num_seqs=s.max_num_seqs,
             max_model_len=m.max_model_len, load_format=m.load_format, seed=config.seed,
-            use_cuda_graphs=config.use_cuda_graphs)
+            use_cuda_graphs=config.use_cuda_graphs,
+            max_step_tokens=min(s.max_num_batched_tokens,
+                                s.prefill_chunk_size if s.enable_chunked_prefill else s.max_num_batched_tokens))
         self.model_config = self.runner.config
         self.max_model_len = self.runner.max_model_len
         self.scheduler = Scheduler(s, self.runner.cache)
@@ -286,10 +288,7 @@ class LLMEngine:
         todo = [s for s in live if s.num_output_tokens < s.max_new_tokens and s.num_tokens < self.max_model_len]
         if not todo or not self.runner.can_run_ahead(len(todo)):
             return None
-        if not all(self.runner.cache.can_reserve(s.seq_id, 1) for s in todo):
-            return None
-        need = [n for s in todo for n in self.runner.cache.pages_needed(s.seq_id, 1)]
-        if sum(need) > self.runner.cache.min_free_pages():
+        if not self.runner.cache.can_reserve_all([(s.seq_id, 1) for s in todo]):
             return None  # growing needs a preemption: the ordinary path decides that
         return todo
 

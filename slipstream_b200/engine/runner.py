@@ -20,7 +20,7 @@ import numpy as np
 import torch
 
 from slipstream_b200 import ops
-from slipstream_b200.cache import CacheManager, PagedStore
+from slipstream_b200.cache import CacheManager, PagedStore, pool_sizes, tokens_that_fit
 from slipstream_b200.parts.base import Runtime
 from slipstream_b200.registry import load_config
 from slipstream_b200.weights.loader import load_weights
@@ -34,9 +34,15 @@ _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 class ModelRunner:
     def __init__(self, model_dir: str | Path, *, dtype: str | None = None, page_size: int = 16,
-                 num_pages: int | None = None, gpu_memory_utilization: float = 0.9, max_num_seqs: int = 256,
-                 max_model_len: int | None = None, load_format: str = "safetensors", seed: int = 0,
-                 device: str | torch.device = "cuda:0", use_cuda_graphs: bool = True) -> None:
+                 num_pages: "int | list[int] | None" = None, gpu_memory_utilization: float = 0.9,
+                 max_num_seqs: int = 256, max_model_len: int | None = None, load_format: str = "safetensors",
+                 seed: int = 0, device: str | torch.device = "cuda:0", use_cuda_graphs: bool = True,
+                 max_step_tokens: int | None = None) -> None:
+        """``page_size``: tokens per page for cache groups whose mixers do not ask for a size of their own.
+        ``num_pages``: pages of that size the cache should hold (groups with another page size get as many pages
+        as hold the same tokens; a windowed group at most what ``max_num_seqs`` requests can keep of their windows
+        when a step feeds up to ``max_step_tokens`` tokens of a request), or one count per cache group, or None
+        to size the pools from the free device memory."""
         ops.require_cuda()
         self.device = torch.device(device)
         if self.device.type == "cuda":
@@ -61,26 +67,40 @@ class ModelRunner:
         del weights
 
         layouts = self.model.group_layouts
-        if num_pages is None:
-            torch.cuda.synchronize(self.device)
-            torch.cuda.empty_cache()
-            free, _total = torch.cuda.mem_get_info(self.device)
-            per_page = max(1, PagedStore.bytes_per_page(layouts, page_size, self.runtime.dtype))
-            # leave room for activations of the largest step beside the pages
-            num_pages = max(1, int(free * gpu_memory_utilization * 0.9) // per_page)
-            cap = max_num_seqs * ((self.max_model_len + page_size - 1) // page_size)
-            num_pages = min(num_pages, cap)
-        self.num_pages = num_pages
-        self.cache = CacheManager(layouts, num_pages, page_size, max_num_seqs, self.max_model_len)
-        self.store = PagedStore(layouts, num_pages, page_size, self.runtime.dtype, self.device,
-                                self.model.entry_state, max_num_seqs)
+        page_sizes = [layout.spec.page_size or page_size for layout in layouts]
+        step_tokens = max_step_tokens or self.max_model_len
+        if isinstance(num_pages, (list, tuple)):
+            pools = [int(n) for n in num_pages]
+        else:
+            if num_pages is None:
+                torch.cuda.synchronize(self.device)
+                torch.cuda.empty_cache()
+                free, _total = torch.cuda.mem_get_info(self.device)
+                per_token = [PagedStore.bytes_per_token(layout, self.runtime.dtype) for layout in layouts]
+                # leave room for activations of the largest step beside the pages
+                tokens = tokens_that_fit(layouts, page_sizes, per_token, int(free * gpu_memory_utilization * 0.9),
+                                         max_num_seqs, self.max_model_len, step_tokens)
+            else:
+                tokens = int(num_pages) * page_size
+            pools = pool_sizes(layouts, page_sizes, tokens, max_num_seqs, self.max_model_len, step_tokens)
+        self.cache = CacheManager(layouts, pools, page_sizes, max_num_seqs, self.max_model_len)
+        self.num_pages = self.cache.num_pages
+        self.store = PagedStore(layouts, self.runtime.dtype, self.device, self.model.entry_state, max_num_seqs)
         self.model.attach_store(self.store)
         self.has_state = any(self.model.entry_state)
         self.steps_run = 0
         self.last_h2d_bytes = 0
         self.use_cuda_graphs = (use_cuda_graphs and self.device.type == "cuda"
                                 and all(getattr(p, "cuda_graph_safe", False) for p in self.model.parts()))
-        self._graphs: dict[tuple[int, bool], DecodeGraph] = {}  # (batch bucket, captured for long contexts)
+        # parts whose captured form depends on the lengths of a step (``Part.capture_variant``)
+        from slipstream_b200.parts.base import Part
+        seen: set[object] = set()
+        self.variant_parts = []
+        for part in self.model.parts():
+            if type(part).capture_variant is not Part.capture_variant and part.capture_group() not in seen:
+                seen.add(part.capture_group())
+                self.variant_parts.append(part)
+        self._graphs: dict[tuple, DecodeGraph] = {}  # (batch bucket, the parts' variants)
 
     # ------------------------------------------------------------------ requests
     def admit(self, request_id: object) -> None:
@@ -103,8 +123,9 @@ class ModelRunner:
         for e in entries:
             if e.request_id not in self.cache:
                 self.admit(e.request_id)
-        plan = plan_step(entries, self.cache, self.config.vocab_size)
-        bucket = self._graph_bucket(plan.num_requests) if plan.is_decode_only else None
+        decode_only = all(len(e.tokens) == 1 for e in entries)
+        bucket = self._graph_bucket(len(entries)) if decode_only else None
+        plan = plan_step(entries, self.cache, self.config.vocab_size, with_tables=bucket is None)
         if bucket is not None:
             graph = self._decode_graph(bucket, plan)
             self.last_h2d_bytes = graph.h2d_bytes
@@ -119,13 +140,14 @@ class ModelRunner:
         return logits
 
     def _decode_graph(self, bucket: int, plan) -> DecodeGraph:
-        """The captured step for this bucket; a second one per bucket serves steps whose longest request has
-        reached a long context (``ops.is_long_context``) (few long requests want more slices of the keys than many
-        short ones, and the number of slices is fixed when a graph is captured)."""
-        wide = ops.is_long_context(int(plan.seq_lens.max()))
-        graph = self._graphs.get((bucket, wide))
+        """The captured step for this bucket and for the form each part wants at these lengths (a decode
+        attention, say, cuts the keys of few long requests into more slices than those of many short ones, and
+        the number of slices is fixed when a graph is captured)."""
+        longest = int(plan.seq_lens.max())
+        variants = tuple(part.capture_variant(longest) for part in self.variant_parts)
+        graph = self._graphs.get((bucket, variants))
         if graph is None:
-            graph = self._graphs[(bucket, wide)] = DecodeGraph(self, bucket, wide)
+            graph = self._graphs[(bucket, variants)] = DecodeGraph(self, bucket, variants)
         return graph
 
     def _graph_bucket(self, n_requests: int) -> int | None:
@@ -141,9 +163,10 @@ class ModelRunner:
         limit = self.max_num_seqs if max_requests is None else max_requests
         made = 0
         for bucket in BUCKETS:
-            if self._graph_bucket(bucket) != bucket or (bucket, False) in self._graphs:
+            variants = tuple(part.capture_variant(1) for part in self.variant_parts)  # the form for short requests
+            if self._graph_bucket(bucket) != bucket or (bucket, variants) in self._graphs:
                 continue
-            self._graphs[(bucket, False)] = DecodeGraph(self, bucket)
+            self._graphs[(bucket, variants)] = DecodeGraph(self, bucket, variants)
             made += 1
             if bucket >= limit:
                 break
@@ -160,9 +183,9 @@ class ModelRunner:
         """A decode-only step whose token ids may still be on the device: row r takes
         ``pending[src_rows[r]]`` where ``src_rows[r] >= 0`` (its entry's token is then a placeholder).
         Returns logits of every row as a view that is valid until the next step."""
-        plan = plan_step(entries, self.cache, self.config.vocab_size)
-        if not plan.is_decode_only or not self.can_run_ahead(plan.num_requests):
+        if any(len(e.tokens) != 1 for e in entries) or not self.can_run_ahead(len(entries)):
             raise StepInputError("step_decode takes decode-only steps that fit a captured graph")
+        plan = plan_step(entries, self.cache, self.config.vocab_size, with_tables=False)
         graph = self._decode_graph(self._graph_bucket(plan.num_requests), plan)
         self.last_h2d_bytes = graph.h2d_bytes
         logits = graph.run(plan, pending=pending, src_rows=src_rows, keep=False)

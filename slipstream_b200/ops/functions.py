@@ -39,6 +39,8 @@ def _code(dtype: torch.dtype) -> int:
 _OPS_SIGNATURES = {
     "ss_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "ss_gather_tokens": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "ss_prepare_decode": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64,
+                          c_void_p],
     "ss_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                        c_float, c_int, c_void_p],
     "ss_rope_cache": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -215,6 +217,23 @@ def gather_tokens(token_ids: torch.Tensor, src_rows: torch.Tensor, pending: torc
         _need(t, torch.int32, name)
     _check(ops_library().ss_gather_tokens(token_ids.data_ptr(), src_rows.data_ptr(), pending.data_ptr(),
                                           src_rows.numel(), _stream()), "gather_tokens")
+
+
+def prepare_decode(token_ids: torch.Tensor, src_rows: torch.Tensor, pending: torch.Tensor | None,
+                   tables: torch.Tensor, patch_idx: torch.Tensor, patch_val: torch.Tensor,
+                   n_patches: torch.Tensor) -> None:
+    """The launch in front of a replayed decode step: ``gather_tokens`` (when ``pending`` is given) and
+    ``tables.view(-1)[patch_idx[i]] = patch_val[i]`` for ``i < n_patches[0]`` (all int32 tensors on the device;
+    the number of patches is read on the device, so the launch is the same every step)."""
+    for name, t in (("token_ids", token_ids), ("src_rows", src_rows), ("tables", tables), ("patch_idx", patch_idx),
+                    ("patch_val", patch_val), ("n_patches", n_patches)):
+        _need(t, torch.int32, name)
+    if pending is not None:
+        _need(pending, torch.int32, "pending")
+    _check(ops_library().ss_prepare_decode(token_ids.data_ptr(), src_rows.data_ptr(), _ptr(pending),
+                                           src_rows.numel(), tables.data_ptr(), patch_idx.data_ptr(),
+                                           patch_val.data_ptr(), n_patches.data_ptr(), patch_idx.numel(),
+                                           tables.numel(), _stream()), "prepare_decode")
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
@@ -837,5 +856,5 @@ def set_programmatic_launch(enabled: bool) -> None:
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "raise_for_status", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "prepare_decode", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "raise_for_status", "error_word", "ops_library",
            "attention_library"]

@@ -4,8 +4,9 @@ Biased q/k/v projections (stacked into one product at load), rotary encoding of
 queries and keys, the write of keys and values to their pages, causal attention
 of the step's rows over each request's pages, and the output projection
 (slipstream/models/layers/attention.py:98-191).  ``window`` None attends over all
-earlier keys; an integer W over the last W.  Every size is a constructor
-parameter; the part does not know which model it is in.
+earlier keys; an integer W over the last W.  ``page_size`` asks for cache pages of
+that many tokens for this layer (layers that ask alike share a pool).  Every size is
+a constructor parameter; the part does not know which model it is in.
 """
 
 from __future__ import annotations
@@ -23,7 +24,7 @@ class PagedAttention(Mixer):
 
     def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: PositionEncoding, qkv_bias: bool = True, out_bias: bool = False,
-                 window: int | None = None, scale: float | None = None) -> None:
+                 window: int | None = None, scale: float | None = None, page_size: int | None = None) -> None:
         if num_heads % num_kv_heads != 0:
             raise ValueError(f"num_heads ({num_heads}) must be divisible by num_kv_heads ({num_kv_heads})")
         if head_dim % 16 != 0 or not 16 <= head_dim <= 256:
@@ -39,6 +40,7 @@ class PagedAttention(Mixer):
         self.qkv_bias = qkv_bias
         self.out_bias = out_bias
         self.window = window
+        self.page_size = page_size  # tokens per cache page this layer wants; None: the engine's default
         self.scale = head_dim ** -0.5 if scale is None else float(scale)
 
     def weight_specs(self) -> list[WeightSpec]:
@@ -56,7 +58,7 @@ class PagedAttention(Mixer):
         return specs
 
     def cache_spec(self) -> CacheSpec:
-        return CacheSpec(self.num_kv_heads, self.head_dim, self.window)
+        return CacheSpec(self.num_kv_heads, self.head_dim, self.window, self.page_size)
 
     def bind(self, weights: dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(weights, runtime)
@@ -69,6 +71,24 @@ class PagedAttention(Mixer):
         self.o_b = weights[f"{n}.o_proj.bias"].to(runtime.dtype) if self.out_bias else None
         self.position_encoding.bind(weights, runtime)
         ops.attention_library(self.head_dim)  # compile now, not inside the first step
+
+    # ------------------------------------------------------------------ decode steps replayed from a graph
+    def capture_variant(self, longest: int) -> object:
+        """Long contexts of few requests want the keys cut into more slices than fit one thread-block cluster
+        (``ops.decode_slices``); that form is captured as a graph of its own."""
+        return bool(self.runtime.dtype == torch.bfloat16 and ops.is_long_context(longest))
+
+    def capture_group(self) -> object:
+        return "paged_attention"
+
+    def prepare_capture(self, ctx, variant: object, max_model_len: int) -> None:
+        # the number of slices must not follow the lengths of the step that happens to be captured
+        ctx.extras["static_max_seq_len"] = max_model_len
+        ctx.extras["decode_wide"] = bool(variant)
+        # the float32 kernel's list of query tiles: one tile per row of the batch
+        rows = ctx.num_requests
+        ctx.set_query_tiles(16, 1, torch.arange(rows, dtype=torch.int32, device=ctx.device),
+                            torch.zeros(rows, dtype=torch.int32, device=ctx.device))
 
     def weight_bytes(self) -> int:
         return (self.qkv_weight.numel() + self.o_weight.numel()) * self.o_weight.element_size()

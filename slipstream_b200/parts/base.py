@@ -48,11 +48,14 @@ class WeightSpec:
 class CacheSpec:
     """Pages of keys and values one mixer needs per token.  ``window`` None means
     every earlier key stays visible; an integer W means only the last W keys are,
-    so pages wholly before the window are given back."""
+    so pages wholly before the window are given back.  ``page_size``: tokens per page this mixer's kernels
+    want; None takes the engine's default.  Mixers whose specs are equal share a cache group (one page pool, one
+    block table per request); a group has its own page size and its own number of pages."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    page_size: int | None = None
 
 
 @dataclass(frozen=True)
@@ -97,6 +100,26 @@ class Part:
     def weight_bytes(self) -> int:
         """Bytes of weights one step reads from this part (for the roofline)."""
         return 0
+
+    # -- decode steps replayed from a CUDA graph.  Inside a replay nothing is known on the host about the step
+    # -- but its bucket (the number of rows), so whatever a part's forward derives from the step's lengths has to
+    # -- be fixed when the graph is captured.  A part that needs this overrides the two methods below.
+    def capture_variant(self, longest: int) -> object:
+        """Which captured form of this part a decode step whose longest request holds ``longest`` tokens should
+        run (any hashable; None: there is only one form).  The runner keeps one graph per bucket and combination
+        of variants."""
+        return None
+
+    def capture_group(self) -> object:
+        """Parts that return the same value here always answer ``capture_variant`` alike (every attention layer
+        of a model, say), so the runner asks one of them per step."""
+        return id(self)
+
+    def prepare_capture(self, ctx: "StepContext", variant: object, max_model_len: int) -> None:
+        """Called once on the static context of a decode graph before it is captured: store in ``ctx.extras``
+        (or through ``ctx.set_query_tiles``) what the forward must not take from the host-side lengths of the
+        step, for the form ``variant`` (the value ``capture_variant`` returned)."""
+        return None
 
 
 class Norm(Part):

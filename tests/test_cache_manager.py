@@ -137,3 +137,56 @@ def test_random_orders_keep_the_invariants(seed, pages, page, window):
         m.release(rid)
     assert m.num_free_pages() == pages and m.num_free_slots() == 4
     m.check_invariants()
+
+
+# --------------------------------------------------------------------------- groups with pools of their own
+def hybrid(full_pages=12, window_pages=3, seqs=3, max_len=128):
+    layouts = [GroupLayout(CacheSpec(2, 16, None), 2), GroupLayout(CacheSpec(1, 32, 6, page_size=8), 1)]
+    return CacheManager(layouts, [full_pages, window_pages], [4, 8], seqs, max_len)
+
+
+def test_every_group_has_its_own_page_size_and_number_of_pages():
+    m = hybrid()
+    assert m.page_sizes == [4, 8] and [p.num_pages for p in m.pools] == [12, 3]
+    assert [(l.page_size, l.num_pages) for l in m.groups] == [(4, 12), (8, 3)]
+    m.admit("a")
+    assert m.pages_needed("a", 17) == [5, 3]
+    m.reserve("a", 17)
+    assert m.free_pages() == [7, 0] and len(m.get("a").tables[0]) == 5 and len(m.get("a").tables[1]) == 3
+    m.commit("a", 17)  # the window of 6 has left positions 0..11: the first page of 8 goes back
+    assert m.free_pages() == [7, 1] and m.get("a").tables[1][0] == -1
+    m.admit("b")
+    # admission looks at every group: 9 tokens need 3 pages of 4 (there) and 2 pages of 8 (only 1 is free)
+    assert m.can_admit(20, 9, 9) is AllocStatus.LATER
+    assert m.can_admit(20, 8, 8) is AllocStatus.OK
+    # never: the full group is too small for 64 tokens even when empty; the windowed group alone would cope
+    assert m.can_admit(64, 4, 4) is AllocStatus.NEVER and m.peak_pages(1, 64, 4) <= 3
+    assert m.can_reserve("b", 8) and not m.can_reserve("b", 9)
+    m.reserve("b", 8)
+    assert m.free_pages() == [5, 0]
+    # together: a's next token needs nothing new, b's ninth a page of the windowed group that is not there
+    assert m.can_reserve_all([("a", 1)]) and not m.can_reserve_all([("a", 1), ("b", 9)])
+    m.check_invariants()
+    assert 0.0 < m.utilization() <= 1.0
+    m.release("a"); m.release("b")
+    assert m.all_pages_free() and m.free_pages() == [12, 3]
+
+
+def test_pool_sizes_give_a_windowed_group_only_what_its_windows_can_hold():
+    from slipstream_b200.cache import pool_sizes, tokens_that_fit
+
+    layouts = [GroupLayout(CacheSpec(4, 128, None), 28), GroupLayout(CacheSpec(4, 128, 1024, page_size=64), 4)]
+    pools = pool_sizes(layouts, [16, 64], tokens=1 << 20, max_num_seqs=8, max_model_len=32768, max_step_tokens=2048)
+    assert pools == [65536, 8 * (3072 // 64 + 1)]
+    # few tokens: both follow the tokens
+    assert pool_sizes(layouts, [16, 64], 1000, 8, 32768, 2048) == [63, 16]
+    per_token = [28 * 2 * 4 * 128 * 2, 4 * 2 * 4 * 128 * 2]
+    budget = 10 << 30
+    tokens = tokens_that_fit(layouts, [16, 64], per_token, budget, 256, 32768, 2048)
+
+    def cost(t):
+        return sum(n * p * b for n, p, b in zip(pool_sizes(layouts, [16, 64], t, 256, 32768, 2048), [16, 64], per_token))
+
+    assert cost(tokens) <= budget < cost(tokens + 64)
+    # everything fits: no more than the requests can ever hold
+    assert tokens_that_fit(layouts, [16, 64], per_token, 1 << 50, 4, 4096, 512) == 4 * (4096 + 64)

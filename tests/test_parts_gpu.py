@@ -97,7 +97,7 @@ def test_attention_part_in_two_portions_and_decoding(dtype, heads, kv_heads, d, 
     part.bind(dev, runtime(dtype))
     layouts = [GroupLayout(part.cache_spec(), 1)]
     cache = CacheManager(layouts, 16, page, 2, 256)
-    store = PagedStore(layouts, 16, page, dtype, DEV, [[]], 2)
+    store = PagedStore(layouts, dtype, DEV, [[]], 2)
     binding = LayerBinding(kv=store.kv[0][0], group=0)
     x = torch.randn(n, hidden).to(dtype)
     s = {"n_q": heads, "n_kv": kv_heads, "head_dim": d, "theta": theta}
@@ -129,7 +129,7 @@ def test_pre_norm_block(dtype):
         child.bind(dev, runtime(dtype))
     layouts = [GroupLayout(block.mixer.cache_spec(), 1)]
     cache = CacheManager(layouts, 8, 4, 2, 64)
-    store = PagedStore(layouts, 8, 4, dtype, DEV, [[]], 2)
+    store = PagedStore(layouts, dtype, DEV, [[]], 2)
     x = torch.randn(n, hidden)
     s = {"n_q": heads, "n_kv": kv_heads, "head_dim": d, "theta": theta, "eps": eps}
     want = plain.decoder_layer(x.double(), torch.arange(n), ref, 0, s)

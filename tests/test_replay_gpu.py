@@ -159,7 +159,7 @@ def test_long_requests_decode_through_a_graph_with_more_slices(tmp_path, monkeyp
 
     wide_rows, wide_graphs = run(8192)
     narrow_rows, narrow_graphs = run(10 ** 9)
-    assert wide_graphs == [(1, True), (2, True)] and narrow_graphs == [(1, False), (2, False)]
+    assert wide_graphs == [(1, (True,)), (2, (True,))] and narrow_graphs == [(1, (False,)), (2, (False,))]
     assert ops.decode_slices(1, 2, 4, 16384, wide=True) > 8 == ops.decode_slices(1, 2, 4, 16384)
     for a, b in zip(wide_rows, narrow_rows):
         assert np.abs(a - b).max() <= 0.5 * TOLERANCE["bfloat16"] * np.abs(b).max()
@@ -195,3 +195,57 @@ def test_short_portions_behind_a_long_prefix_share_their_keys_among_blocks(tmp_p
     steps[-1]["end"] = ["r"]
     rows = plans.collect(steps, run_plan(runner, steps))
     compare(rows, {"r": want}, "bfloat16", "portions behind a long prefix")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_block_tables_of_replayed_decode_steps_follow_their_requests(model_folders, dtype):
+    """A replayed decode graph keeps its block tables on the device and receives only what changed.  Three
+    requests of about a hundred tokens reach their first common decode step with more changes than the patch
+    area holds (the whole mirror is copied), then grow page by page (patches), one ends and its name comes back
+    with other tokens in the same row (the row starts over), and the batch shrinks to another bucket and grows
+    again.  Every decoded row against the oracle."""
+    from slipstream_b200.engine.runner import ModelRunner, StepEntry
+
+    folder, config, page = model_folders["A"]
+    vocab = config.vocab_size
+    requests = {"x": random_tokens(vocab, 118, 31), "y": random_tokens(vocab, 110, 32), "z": random_tokens(vocab, 125, 33),
+                "x2": random_tokens(vocab, 60, 34)}
+    want = oracle(folder, requests, dtype)
+    runner = ModelRunner(folder, dtype=dtype, page_size=page, num_pages=128, max_num_seqs=4)
+    got = {rid: {} for rid in requests}
+
+    def decode(ids, at, names=None):
+        """One decode step: request ``ids[k]`` (called ``names[k]`` by the runner) brings its token ``at[ids[k]]``."""
+        names = names or ids
+        out = runner.step([StepEntry(n, [requests[r][at[r]]], [0]) for r, n in zip(ids, names)]).cpu().numpy()
+        for k, r in enumerate(ids):
+            got[r][at[r]] = out[k]
+            at[r] += 1
+
+    at = {"x": 100, "y": 100, "z": 100, "x2": 40}
+    for rid in ("x", "y", "z"):
+        runner.step([StepEntry(rid, requests[rid][:100], [])])
+    for _ in range(6):
+        decode(["x", "y", "z"], at)
+    graph = runner._graphs[(4, tuple(False for _ in runner.variant_parts))]
+    assert graph.full_copies == 1, "75 new table entries do not fit 64 patches"
+    decode(["y", "z"], at)  # bucket 2, its own tables
+    decode(["x", "y", "z"], at)  # back: x's row is as it was, y and z grew meanwhile
+    while at["y"] < 110:
+        decode(["x", "y", "z"], at)
+    runner.release("y")
+    # another request under the name "x" takes over after x has ended: same name, same row, a table of its own
+    while at["x"] < 118:
+        decode(["x", "z"], at)
+    runner.release("x")
+    runner.step([StepEntry("x", requests["x2"][:40], [])])
+    while at["x2"] < 60:
+        decode(["x2", "z"] if at["z"] < 125 else ["x2"], at, names=["x", "z"] if at["z"] < 125 else ["x"])
+    assert graph.full_copies == 1
+    runner.check()
+    runner.cache.check_invariants()
+    for rid, rows in got.items():
+        assert rows, rid
+        for pos, row in rows.items():
+            err = np.abs(row - want[rid][pos]).max()
+            assert err <= TOLERANCE[dtype] * np.abs(want[rid]).max(), (rid, pos, err)

@@ -33,6 +33,7 @@ class ToyConfig:
     eps: float = 1e-5
     theta: float = 2000.0
     window: int = 9
+    window_page: int | None = None  # tokens per cache page of the windowed layer; None: the engine's default
 
     @classmethod
     def from_dict(cls, data, generation=None):
@@ -90,7 +91,7 @@ def define_toy():
 
         def attention(i, window):
             return PagedAttention(f"toy.layers.{i}.attn", c.hidden_size, c.heads, c.kv_heads, c.head_dim, rotary,
-                                  qkv_bias=False, window=window)
+                                  qkv_bias=False, window=window, page_size=c.window_page if window else None)
 
         blocks = [block(0, attention(0, None)), block(1, MIXERS.get("running_mean")("toy.layers.1", c.hidden_size)),
                   block(2, attention(2, c.window)), block(3, attention(3, None))]
@@ -223,6 +224,70 @@ def test_toy_architecture_steps_like_its_plain_restatement(tmp_path, dtype):
         rows = {"a": [runner.step([StepEntry("a2", reqs["a"], list(range(61)))]).cpu()]}
         err = (rows["a"][0] - want["a"]).abs().max()
         assert err <= tol * want["a"].abs().max()
+        runner.check()
+    finally:
+        unregister_architecture("ToyMixForCausalLM")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_cache_group_with_its_own_page_size_and_a_quarter_of_the_pages(tmp_path, dtype):
+    """The same toy as a hybrid whose windowed layer keeps its keys in pages of 8 tokens, 10 of them, beside the
+    other layers' 40 pages of 4: every group has its own pool, page size and block table.  Whole requests, then
+    three live requests in portions and single tokens, against the plain restatement."""
+    from slipstream_b200.engine.runner import ModelRunner, StepEntry
+    from slipstream_b200.registry import unregister_architecture
+    from slipstream_b200.weights.random_init import write_random_model
+    from conftest import sharpen
+
+    define_toy()
+    try:
+        c = ToyConfig(window_page=8)
+        write_random_model(c, tmp_path, seed=6)
+        sharpen(tmp_path, factor=10.0)
+        _, tensors = plain.read_model_folder(tmp_path, torch.float32)
+        w = {k: (v.bfloat16() if dtype == "bfloat16" and v.dim() == 2 else v).double() for k, v in tensors.items()}
+        runner = ModelRunner(str(tmp_path), dtype=dtype, page_size=4, num_pages=[40, 10], max_num_seqs=3)
+        cache = runner.cache
+        assert [(l.spec.window, l.page_size, l.num_pages) for l in runner.model.group_layouts] == [(None, 4, 40), (9, 8, 10)]
+        assert [t.shape[1] for t in runner.store.kv] == [40, 10] and [t.shape[4] for t in runner.store.kv] == [4, 8]
+        reqs = {"a": random_tokens(c.vocab_size, 61, 11), "b": random_tokens(c.vocab_size, 30, 12),
+                "c": random_tokens(c.vocab_size, 47, 13)}
+        want = {k: plain_toy(c, w, v).float() for k, v in reqs.items()}
+        tol = 3e-5 if dtype == "float32" else 4e-2
+
+        def check(rows, what):
+            for k, ref in want.items():
+                err = (torch.cat(rows[k]) - ref).abs().max(dim=1).values
+                assert err.max() <= tol * ref.abs().max(), (what, k, int(err.argmax()), err.max().item())
+
+        rows = {}
+        for k, toks in reqs.items():
+            rows[k] = [runner.step([StepEntry(k, toks, list(range(len(toks))))]).cpu()]
+            runner.release(k)
+        check(rows, "whole")
+        rows, at = {k: [] for k in reqs}, {k: 0 for k in reqs}
+        sizes = {"a": [7, 1, 1, 13, 2, 1, 14, 16, 1, 5], "b": [2, 2, 1, 1, 1, 12, 8, 3], "c": [24, 16, 1, 1, 1, 1, 1, 1, 1]}
+        fewest_free = [40, 10]
+        for step in range(10):
+            entries = []
+            for k in reqs:
+                if step < len(sizes[k]):
+                    take = sizes[k][step]
+                    entries.append(StepEntry(k, reqs[k][at[k]: at[k] + take], list(range(take))))
+                    at[k] += take
+            out = runner.step(entries).cpu()
+            i = 0
+            for e in entries:
+                rows[e.request_id].append(out[i: i + len(e.tokens)])
+                i += len(e.tokens)
+            cache.check_invariants()
+            fewest_free = [min(a, b) for a, b in zip(fewest_free, cache.free_pages())]
+        assert all(at[k] == len(reqs[k]) for k in reqs)
+        check(rows, "portions")
+        assert fewest_free[1] <= 4, "the small pool was never under pressure"
+        for k in reqs:
+            runner.release(k)
+        assert cache.all_pages_free() and cache.free_pages() == [40, 10]
         runner.check()
     finally:
         unregister_architecture("ToyMixForCausalLM")
