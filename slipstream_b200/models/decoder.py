@@ -16,9 +16,8 @@ from dataclasses import dataclass
 import torch
 
 from slipstream_b200.cache import GroupLayout
-from slipstream_b200.parts.base import (Block, CacheSpec, LayerBinding, Norm, Part, PositionEncoding,
-                                        Runtime, StateSpec, WeightSpec)
-from slipstream_b200.parts.embedding import LMHead, TokenEmbedding
+from slipstream_b200.parts.base import (Block, CacheSpec, Embedding, Head, LayerBinding, Norm, Part,
+                                        PositionEncoding, Runtime, StateSpec, WeightSpec)
 
 
 @dataclass(frozen=True)
@@ -41,8 +40,8 @@ def _walk(part: Part) -> list[Part]:
 
 
 class DecoderLM:
-    def __init__(self, config, embedding: TokenEmbedding, blocks: list[Block], final_norm: Norm,
-                 lm_head: LMHead, order: list[ExecEntry] | None = None,
+    def __init__(self, config, embedding: Embedding, blocks: list[Block], final_norm: Norm,
+                 lm_head: Head, order: list[ExecEntry] | None = None,
                  position_encoding: PositionEncoding | None = None) -> None:
         self.config = config
         self.embedding = embedding

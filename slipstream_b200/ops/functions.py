@@ -151,6 +151,22 @@ def check_errors(device: torch.device) -> None:
     raise_for_status(int(error_word(device).item()), device)
 
 
+@functools.lru_cache(maxsize=None)
+def _device_sm_count(index: int) -> int:
+    return int(torch.cuda.get_device_properties(index).multi_processor_count)
+
+
+def sm_count(device: torch.device | int | None = None) -> int:
+    """Streaming multiprocessors of ``device`` (default: the current CUDA device), asked from the device once.
+    Every rule below that sizes a grid or a split takes this number as ``sms``."""
+    if isinstance(device, torch.device):
+        device = device.index
+    if device is None:
+        require_cuda()
+        device = torch.cuda.current_device()
+    return _device_sm_count(int(device))
+
+
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
@@ -414,7 +430,8 @@ def paged_attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.T
                                    error_word(q.device).data_ptr(), _stream()), "paged_attention_prefill_tcgen05")
 
 
-def prefill_key_parts(q_lens: np.ndarray, seq_lens: np.ndarray, tile_tokens: int, n_kv: int) -> int:
+def prefill_key_parts(q_lens: np.ndarray, seq_lens: np.ndarray, tile_tokens: int, n_kv: int,
+                      sms: int | None = None) -> int:
     """Into how many parts the tcgen05 prefill kernel should cut the keys of its query tiles.  A block walks its
     key tiles one after the other, about a microsecond each, so a step with few query tiles lasts as long as its
     longest one while most SMs idle: a portion of 64 tokens behind 4,096 cached ones is 16 blocks of 64 key
@@ -429,8 +446,9 @@ def prefill_key_parts(q_lens: np.ndarray, seq_lens: np.ndarray, tile_tokens: int
     counts = (q_lens + tile_tokens - 1) // tile_tokens
     blocks = int(counts.sum()) * n_kv
     longest = int(seq_lens.max() - 1) // 64 + 1  # key tiles of the last query tile of the longest request
+    sms = sms or sm_count()
     parts = 1
-    while parts < 8 and blocks * parts * 2 <= 2 * 148 and longest >= 16 * parts:
+    while parts < 8 and blocks * parts * 2 <= 2 * sms and longest >= 16 * parts:
         parts *= 2
     return parts
 
@@ -521,23 +539,25 @@ def is_long_context(seq_len: int) -> bool:
     return seq_len >= WIDE_CONTEXT
 
 
-def decode_slices(n_requests: int, n_kv: int, group: int, max_seq_len: int, wide: bool = False) -> int:
-    """How many slices to cut the keys into: as many as keep all blocks resident at once (two per SM on
-    148 SMs), so that the step is one wave of blocks; at most 8, the size of a thread-block cluster.
+def decode_slices(n_requests: int, n_kv: int, group: int, max_seq_len: int, wide: bool = False,
+                  sms: int | None = None) -> int:
+    """How many slices to cut the keys into: as many as keep all blocks resident at once (two per SM),
+    so that the step is one wave of blocks; at most 8, the size of a thread-block cluster.
 
     ``wide`` (the TMA-fed kernel, long contexts): few requests leave most SMs idle with 8 slices (one request on
     4 kv heads: 32 blocks), so the slices become 2, 4 or 8 clusters of 8 whose results meet in scratch memory,
     as long as a slice keeps 8 tiles of 64 keys and all blocks still fit one wave.  One request of 32,768 tokens:
     64.7 us with 8 slices, 23.4 us with 64; two of 16,384: 35.8 against 27.7 with 32; with 32 blocks or more
     (8 requests) 8 slices are the fastest at every length."""
+    sms = sms or sm_count()
     blocks = n_requests * n_kv * ((group + 15) // 16)
     tiles = max(1, (max_seq_len + 63) // 64)
-    most = max(1, min((2 * 148) // blocks, tiles, 8))
+    most = max(1, min((2 * sms) // blocks, tiles, 8))
     # a power of two: clusters of 3 blocks pack the SMs of a GPC badly (24 requests x 4 kv heads: 24.8 us with 3
     # slices, 17.2 us with 2)
     slices = 1 << (most.bit_length() - 1)
     if wide and slices == 8:
-        clusters = max(1, min((2 * 148) // (blocks * 8), tiles // 64, 8))
+        clusters = max(1, min((2 * sms) // (blocks * 8), tiles // 64, 8))
         slices = 8 * (1 << (clusters.bit_length() - 1))
     return slices
 
@@ -579,7 +599,8 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
         longest = static or ctx.max_seq_len
         wide = ctx.extras.get("decode_wide", False) if static else is_long_context(ctx.max_seq_len)
         wide = bool(wide) and tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], 0)
-        slices = decode_slices(ctx.num_requests, n_kv, group, min(longest, window or longest), wide)
+        slices = decode_slices(ctx.num_requests, n_kv, group, min(longest, window or longest), wide,
+                               sm_count(qkv.device))
         scratch = ctx.extras.get(("decode_scratch", n_q, head_dim))
         paged_attention_decode(qkv, qkv.shape[1], out, kv, block_tables, ctx.q_start, ctx.seq_lens,
                                ctx.num_requests, n_q, n_kv, head_dim, scale, window, slices, scratch, rope)
@@ -589,7 +610,8 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
         key = ("prefill_key_parts", 128 // group, n_kv)
         parts = ctx.extras.get(key)
         if parts is None:  # the same for every layer of the step
-            parts = ctx.extras[key] = prefill_key_parts(ctx.q_lens_host, ctx.seq_lens_host, 128 // group, n_kv)
+            parts = ctx.extras[key] = prefill_key_parts(ctx.q_lens_host, ctx.seq_lens_host, 128 // group, n_kv,
+                                                        sm_count(qkv.device))
         paged_attention_prefill_tcgen05(qkv, qkv.shape[1], out, kv, block_tables, tile_req, tile_tok0, ctx.q_start,
                                         ctx.seq_lens, n_q, n_kv, head_dim, scale, parts)
         return
@@ -675,18 +697,22 @@ def _gemm_workspace(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
     return ws  # type: ignore[return-value]
 
 
+def gemm_plan(tokens: int, features: int, k: int, sms: int | None = None) -> tuple[bool, int, int]:
+    """(swapped, tile width, K slices) for ``x[tokens, k] @ w[features, k].T`` on ``sms`` multiprocessors."""
+    return _gemm_plan(tokens, features, k, sms or sm_count())
+
+
 @functools.lru_cache(maxsize=None)
-def gemm_plan(tokens: int, features: int, k: int) -> tuple[bool, int, int]:
-    """(swapped, tile width, K slices) for ``x[tokens, k] @ w[features, k].T`` on 148 SMs."""
+def _gemm_plan(tokens: int, features: int, k: int, sms: int) -> tuple[bool, int, int]:
     k_iters = (k + 63) // 64
     if tokens <= 64:
         bn = 16 if tokens <= 16 else (32 if tokens <= 32 else 64)
         tiles = (features + 127) // 128
         # at most 8 slices: they then form one thread-block cluster and are added through shared memory
-        slices = max(1, min(k_iters, (2 * 148 + tiles - 1) // tiles if tiles < 148 else 1, 8))
+        slices = max(1, min(k_iters, (2 * sms + tiles - 1) // tiles if tiles < sms else 1, 8))
         # the widest tile leaves room for two blocks per SM, and clusters do not pack an SM's last slot: stay
         # within one wave of blocks (36 tiles x 8 slices ran as two waves: 18.1 us against 13.2 with 7 slices)
-        while bn == 64 and slices > 1 and tiles * slices > 256:
+        while bn == 64 and slices > 1 and tiles * slices > sms + (3 * sms) // 4:
             slices -= 1
         return True, bn, slices
     bn = 256 if features >= 256 else (128 if features >= 128 else (64 if features >= 64 else (32 if features >= 32 else 16)))
@@ -721,7 +747,7 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
         bias_f32 = int(bias.dtype == torch.float32)
         if bias.numel() != features or bias.dtype not in (torch.float32, torch.bfloat16):
             raise KernelError("bias has the wrong size or dtype")
-    swapped, bn, slices = plan or gemm_plan(tokens, features, k)
+    swapped, bn, slices = plan or gemm_plan(tokens, features, k, sm_count(x.device))
     partial = counters = None
     if slices > 1 and not (swapped and slices <= 8 and tokens <= bn):
         partial, counters = _gemm_workspace(x.device)
@@ -743,7 +769,7 @@ def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor 
     kernel, one block per SM, the blocks in pairs (``tcgen05.mma.cta_group::2``: each block of a pair loads half
     of A and half of B) that compute tiles of 256 rows with the accumulator double-buffered in tensor memory, so
     that the epilogue of a tile overlaps the products of the next.  ``tile_cols``: the tiles' width, a multiple
-    of 16 up to 256; 0 lets the launcher take the width whose tiles fill whole rounds of the 74 pairs best.
+    of 16 up to 256; 0 lets the launcher take the width whose tiles fill whole rounds of the pairs of SMs best.
     ``swiglu``: the weight's rows alternate 64 gate and 64 up features; the result is ``silu(gate) * up`` with
     features / 2 columns (tiles of 256 columns)."""
     _need(x, torch.bfloat16, "x")
@@ -775,19 +801,19 @@ def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor 
 # two-SM kernel.  Against the library (us, ours / library) at 2,048 tokens: 7B sizes q/k/v 49.6 / 45.1, o 41.6-47.7 /
 # 45.4-52.8, down 191.9-198.2 / 191.6-208.7; 14B sizes 109.4 / 114.6, 79.7 / 77.0, 200.3 / 207.2; a whole 2,048-token
 # prefill of the 7B shape takes 22.1 to 25.5 ms either way (the GPU sits at its power cap), and its first call 35
-# ms instead of 160.  With fewer tokens or smaller weights there are too few 256-row tiles for the 74 pairs and
+# ms instead of 160.  With fewer tokens or smaller weights there are too few 256-row tiles for the pairs of SMs and
 # the library, which splits K, wins: 1,024 tokens at 14B sizes by up to 18 %, 0.5B and 1.5B sizes at any number
 # of tokens by up to 50 %, 512 tokens and below by 1.3 to 2 times.  (Cutting K into parts inside this kernel,
 # with the parts' sums meeting in scratch memory, was tried for those cases and did not beat narrower tiles.)
 MANY_TOKENS = 2048
 MANY_WIDTH = 3584
 SMALL_BATCH = 64  # up to this many tokens a projection may stream its weights through the tcgen05 kernel
-STREAM_TILES = 148  # ... when its 128-row weight tiles are at least as many as the SMs (no K slices needed)
+# ... when its 128-row weight tiles are at least as many as the SMs (no K slices needed)
 CLUSTER_BATCH = 16  # ... or, up to this many tokens, whatever its size (K slices added inside a cluster)
 DEEP_K = 8192  # ... or when K is at least this deep: every block then streams enough to pay for its set-up
 
 
-def streams_weights(tokens: int, features: int, k: int) -> bool:
+def streams_weights(tokens: int, features: int, k: int, sms: int | None = None) -> bool:
     """True where the hand-written tcgen05 kernel is the faster way to run a bfloat16 projection.  Measured
     on the 7B shape inside a decode step: with enough weight tiles to give every SM one (gate/up, LM head) it
     wins up to 64 tokens (43 us against the library's 46.5 us at 8 tokens); the smaller products (q/k/v, o,
@@ -796,7 +822,7 @@ def streams_weights(tokens: int, features: int, k: int) -> bool:
     down product still wins (25.6 and 28.0 us against 29.1 and 30.8), q/k/v and o lose by 1 to 9 us."""
     if k % 8 != 0 or tokens > SMALL_BATCH:
         return False
-    return tokens <= CLUSTER_BATCH or (features + 127) // 128 >= STREAM_TILES or k >= DEEP_K
+    return tokens <= CLUSTER_BATCH or (features + 127) // 128 >= (sms or sm_count()) or k >= DEEP_K
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
@@ -811,7 +837,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     nn.Linear does (slipstream/models/layers/attention.py:132-135)."""
     if x.dtype == torch.float32:
         return gemm_simt(x, weight, bias, out_dtype)
-    if streams_weights(x.shape[0], weight.shape[0], x.shape[1]):
+    sms = sm_count(x.device)
+    if streams_weights(x.shape[0], weight.shape[0], x.shape[1], sms):
         return gemm_tcgen05(x, weight, bias, out_dtype)
     if x.shape[0] >= MANY_TOKENS and min(weight.shape) >= MANY_WIDTH and x.shape[1] % 8 == 0:
         return gemm_tcgen05_many(x, weight, bias, out_dtype)
@@ -825,22 +852,23 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     return out
 
 
-def many_tokens_swiglu_fits(tokens: int, features: int) -> bool:
+def many_tokens_swiglu_fits(tokens: int, features: int, sms: int | None = None) -> bool:
     """Where the persistent tcgen05 kernel with its fused SwiGLU epilogue is at least as fast as the library
     product followed by the SwiGLU kernel: enough 256 x 256 tiles to keep every pair of SMs busy for several
     rounds (2,048 tokens x 37,888 features: 347 us against 348 + 40 us, and no [tokens, 2 I] intermediate; 1,024
     tokens: 205 against 179 + 20; 512 tokens: 108 against 95 + 10, where the library stays).  Without an epilogue
     to fuse, the library product is as fast as ours or up to 10 % faster, and stays."""
-    return ((tokens + 255) // 256) * ((features + 255) // 256) >= 4 * 148
+    return ((tokens + 255) // 256) * ((features + 255) // 256) >= 4 * (sms or sm_count())
 
 
 def gate_up_swiglu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, block: int) -> torch.Tensor:
     """``silu(x @ Wg.T + bg) * (x @ Wu.T + bu)`` where ``weight`` [2 I, K] holds gate and up rows alternating in
     runs of ``block``.  Small bfloat16 batches with runs of 64 do it in one kernel."""
     if x.dtype == torch.bfloat16 and block == 64 and weight.shape[0] % 128 == 0 and x.shape[1] % 8 == 0:
-        if streams_weights(x.shape[0], weight.shape[0], x.shape[1]):
+        sms = sm_count(x.device)
+        if streams_weights(x.shape[0], weight.shape[0], x.shape[1], sms):
             return gemm_tcgen05(x, weight, bias, swiglu=True)
-        if many_tokens_swiglu_fits(x.shape[0], weight.shape[0]):
+        if many_tokens_swiglu_fits(x.shape[0], weight.shape[0], sms):
             return gemm_tcgen05_many(x, weight, bias, swiglu=True)
     return swiglu(linear(x, weight, bias), block=block)
 
@@ -856,5 +884,5 @@ def set_programmatic_launch(enabled: bool) -> None:
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "prepare_decode", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "linear", "check_errors", "raise_for_status", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "prepare_decode", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "sm_count", "linear", "check_errors", "raise_for_status", "error_word", "ops_library",
            "attention_library"]

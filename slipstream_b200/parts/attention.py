@@ -93,13 +93,23 @@ class PagedAttention(Mixer):
     def weight_bytes(self) -> int:
         return (self.qkv_weight.numel() + self.o_weight.numel()) * self.o_weight.element_size()
 
+    def after_projection(self, qkv: torch.Tensor, ctx) -> None:
+        """Hook for subclasses: change the stacked projection output [N, (n_q + 2 n_kv) * D] in place before
+        queries and keys are rotated and keys and values go to their pages (a norm over each query and key head,
+        say).  A subclass that overrides it keeps every attention kernel; only the fusion of rotation and page
+        write into the decode kernel is off for it, since that kernel takes the projection output as it is."""
+        return None
+
     def forward(self, x: torch.Tensor, ctx, layer: LayerBinding) -> torch.Tensor:
         meta = ctx.groups[layer.group]
         qkv = ops.linear(x, self.qkv_weight, self.qkv_b)
+        plain_projection = type(self).after_projection is PagedAttention.after_projection
+        if not plain_projection:
+            self.after_projection(qkv, ctx)
         inv_freq, rotary_dim = self.position_encoding.rotary_table()
         # a decode step's attention kernel rotates and writes the newest key and value itself
-        fused = layer.writes_cache and ops.fuses_rope(qkv, ctx, self.head_dim, self.num_heads, self.num_kv_heads,
-                                                        layer.kv.shape[3])
+        fused = (plain_projection and layer.writes_cache
+                 and ops.fuses_rope(qkv, ctx, self.head_dim, self.num_heads, self.num_kv_heads, layer.kv.shape[3]))
         if not fused:
             ops.rope_and_cache(qkv, ctx.positions, meta.slot_mapping, inv_freq, layer.kv, self.num_heads,
                                self.num_kv_heads, self.head_dim, rotary_dim, write_cache=layer.writes_cache)

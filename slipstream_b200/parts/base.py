@@ -166,6 +166,22 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    """Token ids (int32 [N] on the device) into the float32 residual stream [N, hidden]."""
+
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Head(Part):
+    """Normalised rows of the stream (compute dtype [M, hidden]) into float32 logits [M, vocab_size]."""
+
+    vocab_size: int
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class Block(Part):
     """Arrangement of a mixer, a feed-forward and their norms around the float32
     residual stream.  ``forward`` takes the stream and a branch output that has
@@ -232,3 +248,5 @@ FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block arrangement")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("output head")

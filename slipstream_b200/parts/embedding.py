@@ -8,10 +8,11 @@ import torch
 
 from slipstream_b200 import ops
 
-from .base import Part, Runtime, WeightSpec
+from .base import EMBEDDINGS, HEADS, Embedding, Head, Runtime, WeightSpec
 
 
-class TokenEmbedding(Part):
+@EMBEDDINGS.register("token_table")
+class TokenEmbedding(Embedding):
     cuda_graph_safe = True
 
     def __init__(self, name: str, vocab_size: int, hidden_size: int) -> None:
@@ -30,7 +31,8 @@ class TokenEmbedding(Part):
         return ops.embedding(token_ids, self.weight)
 
 
-class LMHead(Part):
+@HEADS.register("linear")
+class LMHead(Head):
     cuda_graph_safe = True
 
     def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: str | None) -> None:

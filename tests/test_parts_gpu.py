@@ -111,6 +111,45 @@ def test_attention_part_in_two_portions_and_decoding(dtype, heads, kv_heads, d, 
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_an_attention_subclass_that_normalises_heads_before_the_rotation(dtype):
+    """A mixer that puts something between projection and rotation (here: every query and key head scaled to unit
+    root-mean-square) overrides one hook of the attention part and keeps its kernels: prompt portions through the
+    tiled kernels, single tokens through the split decode kernel (head size 64 and pages of 16 would otherwise
+    take the kernel that rotates by itself)."""
+    from slipstream_b200.cache import CacheManager, GroupLayout, PagedStore
+    from slipstream_b200.parts import LayerBinding, PagedAttention, RotaryEncoding
+    hidden, heads, kv_heads, d, theta, n, eps = 56, 4, 2, 64, 30000.0, 45, 1e-6
+
+    class HeadNormAttention(PagedAttention):
+        def after_projection(self, qkv, ctx):
+            qk = qkv[:, : (heads + kv_heads) * d].view(qkv.shape[0], heads + kv_heads, d)
+            qk.copy_((qk.float() * torch.rsqrt(qk.float().pow(2).mean(-1, keepdim=True) + eps)).to(qkv.dtype))
+
+    part = HeadNormAttention("a", hidden, heads, kv_heads, d, RotaryEncoding(d, theta), qkv_bias=True)
+    dev, ref = draw(part, dtype, seed=3, scale=0.5)
+    part.bind(dev, runtime(dtype))
+    layouts = [GroupLayout(part.cache_spec(), 1)]
+    cache = CacheManager(layouts, 16, 16, 2, 256)
+    store = PagedStore(layouts, dtype, DEV, [[]], 2)
+    binding = LayerBinding(kv=store.kv[0][0], group=0)
+    x = torch.randn(n, hidden).to(dtype)
+    # the plain restatement: plain.attention_block with the norm between projection and rotation
+    xd = x.double()
+    proj = {p: xd @ ref[f"a.{p}_proj.weight"].T + ref[f"a.{p}_proj.bias"] for p in "qkv"}
+    q, k, v = proj["q"].view(n, heads, d), proj["k"].view(n, kv_heads, d), proj["v"].view(n, kv_heads, d)
+    q, k = (t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) for t in (q, k))
+    cos, sin = plain.rotary_tables(torch.arange(n), d, theta, torch.float64)
+    attn = plain.causal_attention(plain.apply_rotary(q, cos, sin), plain.apply_rotary(k, cos, sin), v, d ** -0.5)
+    want = plain.proj_out(attn, ref, "a")
+    outs, i = [], 0
+    for take in (20, 13, 1, 1, 2, 1, 7):
+        ctx = single_request_ctx(cache, "r", take)
+        outs.append(part.forward(x[i:i + take].to(DEV).contiguous(), ctx, binding))
+        i += take
+    assert i == n and rel(torch.cat(outs), want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_pre_norm_block(dtype):
     from slipstream_b200.cache import CacheManager, GroupLayout, PagedStore
     from slipstream_b200.parts import (LayerBinding, PagedAttention, PreNormBlock, RMSNorm, RotaryEncoding,
