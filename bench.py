@@ -7,7 +7,8 @@ step of the whole batch through the step function, timed on the device with CUDA
 the same through the public engine calls (``add_request`` / ``step``) with host token ids in and
 out every step; ``prefill`` is one 2,048-token prompt in one step; ``roofline`` compares the bytes a
 decode step must read (every weight once, plus the cache of the live requests) with the measured
-copy bandwidth; ``points`` holds decode at batch 1 and 64.  Peaks come from MEASURED_PEAKS.json
+copy bandwidth; ``points`` holds decode at batch 1 and 64; ``kernels`` each dominant kernel alone at the
+bench shape with its own roofline fraction.  Peaks come from MEASURED_PEAKS.json
 beside this file when present.  One GPU only: for --gpus above 1 it says so and exits with 2.
 
 ``--only decode|prefill`` runs one part and prints a short line (profiling, and measurements beside the
@@ -167,6 +168,110 @@ def reference_arm(args) -> int:
     return 0
 
 
+def kernel_fractions(engine, batch: int, ctx_tokens: int, prefill_tokens: int, pk: dict) -> dict:
+    """Each dominant kernel alone at the bench shape, timed with CUDA events: the decode projections and the
+    decode attention against the bytes they must read (measured copy bandwidth), the prefill projections and the
+    prefill attention against their flops (measured bf16 peak).  A kernel runs once per layer of the model, on that
+    layer's own weights and pages, back to back as inside a step (28 x 33 MB of q/k/v weights and 28 x 17 MB of
+    pages are larger than L2, so every launch reads from memory); median of five such sweeps, per launch."""
+    import torch
+
+    from slipstream_b200 import ops
+
+    runner = engine.runner
+    c = runner.config
+    dev = runner.device
+    blocks = runner.model.blocks
+    gen = torch.Generator(device=dev).manual_seed(1)
+
+    def rand(rows: int, cols: int) -> torch.Tensor:
+        return (torch.randn(rows, cols, generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+
+    def sweep(run) -> float:
+        """Median microseconds per launch of ``run(layer)`` over all layers."""
+        for layer in range(len(blocks)):
+            run(layer)
+        times = []
+        for _ in range(5):
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for layer in range(len(blocks)):
+                run(layer)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3 / len(blocks))
+        return sorted(times)[len(times) // 2]
+
+    h, qkv_w = c.hidden_size, (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim
+    o_in, inter = c.num_attention_heads * c.head_dim, c.intermediate_size
+    out: dict[str, dict] = {}
+
+    def hbm(name: str, us: float, nbytes: float) -> None:
+        gbs = nbytes / (us * 1e-6) / 1e9
+        out[name] = {"us": round(us, 2), "gbs": round(gbs, 1), "frac": round(gbs / pk["hbm_gbs"], 3)}
+
+    def tensor(name: str, us: float, flops: float) -> None:
+        tf = flops / (us * 1e-6) / 1e12
+        out[name] = {"us": round(us, 2), "tflops": round(tf, 1), "frac": round(tf / pk["bf16_tflops"], 3)}
+
+    for tokens, tag in ((batch, "decode"), (prefill_tokens, "prefill")):
+        x_h, x_o, x_i = rand(tokens, h), rand(tokens, o_in), rand(tokens, inter)
+        shapes = {
+            "qkv": (lambda i: ops.linear(x_h, blocks[i].mixer.qkv_weight, blocks[i].mixer.qkv_b), h, qkv_w),
+            "o": (lambda i: ops.linear(x_o, blocks[i].mixer.o_weight, None), o_in, h),
+            "gate_up": (lambda i: ops.gate_up_swiglu(x_h, blocks[i].feed_forward.gate_up, None,
+                                                     blocks[i].feed_forward.block), h, 2 * inter),
+            "down": (lambda i: ops.linear(x_i, blocks[i].feed_forward.down, None), inter, h),
+        }
+        for name, (run, k, n) in shapes.items():
+            us = sweep(run)
+            if tag == "decode":
+                hbm(f"decode_{name}", us, 2.0 * k * n + 2.0 * tokens * (k + n))
+            else:
+                tensor(f"prefill_{name}", us, 2.0 * tokens * k * n)
+    # LM head: one weight, larger than L2 by itself
+    x_rows = rand(batch, h)
+    head = runner.model.lm_head
+    us = sweep(lambda i: head.forward(x_rows))
+    hbm("decode_lm_head", us, 2.0 * c.vocab_size * h + 4.0 * batch * c.vocab_size)
+
+    # attention over the engine's own pages: `batch` requests of `ctx_tokens` cached tokens (what the pages hold
+    # does not matter for the time), decode (one token each) and prefill (one request, all tokens new)
+    page = runner.cache.page_size
+    n_q, n_kv, d = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+    kv = runner.store.kv[0]
+
+    def tables(n_req: int, tokens: int) -> torch.Tensor:
+        per = (tokens + page - 1) // page
+        return torch.arange(n_req * per, dtype=torch.int32, device=dev).view(n_req, per)
+
+    qkv = rand(batch, (n_q + 2 * n_kv) * d)
+    att = torch.empty(batch, n_q * d, dtype=torch.bfloat16, device=dev)
+    table = tables(batch, ctx_tokens)
+    q_start = torch.arange(batch + 1, dtype=torch.int32, device=dev)
+    lens = torch.full((batch,), ctx_tokens, dtype=torch.int32, device=dev)
+    slices = ops.decode_slices(batch, n_kv, n_q // n_kv, ctx_tokens, False, ops.sm_count(dev))
+    us = sweep(lambda i: ops.paged_attention_decode(qkv, qkv.shape[1], att, kv[i], table, q_start, lens, batch, n_q, n_kv,
+                                                    d, d ** -0.5, 0, slices))
+    hbm("decode_attention", us, batch * ctx_tokens * 2.0 * n_kv * d * 2 + 2.0 * batch * n_q * d * 2)
+    if ops.tcgen05_attention_fits(d, n_q, n_kv, page, 0):
+        import numpy as np
+        from slipstream_b200.engine.context import query_tiles_host
+
+        T, tile = prefill_tokens, 128 // (n_q // n_kv)
+        qkv_p = rand(T, (n_q + 2 * n_kv) * d)
+        att_p = torch.empty(T, n_q * d, dtype=torch.bfloat16, device=dev)
+        req, tok0 = (torch.from_numpy(a).to(dev) for a in query_tiles_host(np.asarray([T], dtype=np.int32), tile))
+        table_p = tables(1, T)
+        q_start_p = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        lens_p = torch.tensor([T], dtype=torch.int32, device=dev)
+        us = sweep(lambda i: ops.paged_attention_prefill_tcgen05(qkv_p, qkv_p.shape[1], att_p, kv[i], table_p, req, tok0,
+                                                                 q_start_p, lens_p, n_q, n_kv, d, d ** -0.5, 1))
+        tensor("prefill_attention", us, 4.0 * n_q * d * (T * (T + 1) // 2))
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -181,6 +286,7 @@ def main() -> int:
     ap.add_argument("--prefix", type=int, default=0, help="--only prefill: tokens already cached in front of it")
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel timings")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
                     help="run another measured workload end to end through the scheduler instead")
@@ -330,6 +436,12 @@ def main() -> int:
                                                   temperature=0.0, ignore_eos=True), float(j)))
     while any(s.num_output_tokens == 0 for s in engine.scheduler.running) or engine.scheduler.waiting:
         engine.step()
+    # The prompts of all requests went in as one step of 8,192 tokens, which runs at the GPU's power cap; for some
+    # tens of milliseconds afterwards the SM clock stays at 1.3 to 1.7 GHz and a decode step takes 3.5 ms instead
+    # of 2.9.  The device-timed figure above is taken at full clocks, so this one waits until they are back.
+    engine.drain()
+    torch.cuda.synchronize()
+    time.sleep(0.5)
     for _ in range(args.warmup):
         engine.step()
     engine.drain()  # the engine launches a decode step before it has read the tokens of the step before:
@@ -350,6 +462,8 @@ def main() -> int:
         points["decode_b1"] = round(decode_device(1, pts_steps, 3, "a")[0], 1)
         points["decode_b64"] = round(decode_device(64, pts_steps, 3, "b")[0], 1)
 
+    kernels = {} if args.no_kernels else kernel_fractions(engine, args.batch, args.prompt_len, 2048, pk)
+
     line = {
         "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2048 tokens (Qwen2.5-7B bf16)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
@@ -361,7 +475,8 @@ def main() -> int:
                    "heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads, "head_dim": c.head_dim,
                    "intermediate": c.intermediate_size, "vocab": c.vocab_size, "kv_block": page,
                    "l2": "inputs larger than L2 (weights read every step)", "cuda_graphs": not args.no_graphs,
-                   "order": "prefill first, then decode", "peaks": pk_kind},
+                   "order": "prefill first, then decode", "peaks": pk_kind,
+                   "e2e_settle": "0.5 s idle between the prompt phase and the timed decode steps"},
         "e2e": {"value": round(args.batch * 1000.0 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch},
         "gpu_launches": launches,
@@ -369,6 +484,7 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
+        "kernels": kernels,
         "clocks": clock_summary,
     }
     print(json.dumps(line))

@@ -141,6 +141,7 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
             }
             const int p = lane / HALVES, h = lane % HALVES;
             const bool mine = p < ppt;
+            const uint64_t once = fa::l2_evict_first_policy();
             bool waited = false, ok = true;
             for (int kt = kt_lo; kt <= kt_hi && ok; ++kt) {
                 const int i = kt - kt_lo, st = i % NS;
@@ -162,10 +163,10 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
                         page = -1;
                     }
                     if (page < 0) page = spare;
-                    fa::tma_load_3d(Ks + h * (MMA_BN * 64) + p * page_size * 64, &map_kv, h * 64, 0,
-                                    (int)((page * 2 + 0) * n_kv + kvh), &full[st]);
-                    fa::tma_load_3d(Vs + h * (MMA_BN * 64) + p * page_size * 64, &map_kv, h * 64, 0,
-                                    (int)((page * 2 + 1) * n_kv + kvh), &full[st]);
+                    fa::tma_load_3d_once(Ks + h * (MMA_BN * 64) + p * page_size * 64, &map_kv, h * 64, 0,
+                                         (int)((page * 2 + 0) * n_kv + kvh), &full[st], once);
+                    fa::tma_load_3d_once(Vs + h * (MMA_BN * 64) + p * page_size * 64, &map_kv, h * 64, 0,
+                                         (int)((page * 2 + 1) * n_kv + kvh), &full[st], once);
                 }
             }
         }

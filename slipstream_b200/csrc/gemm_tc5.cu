@@ -69,6 +69,20 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         ::"r"(s_addr(dst)), "l"(map), "r"(s_addr(bar)), "r"(c0), "r"(c1) : "memory");
 }
 
+// The same for data that is read once per step (the weights a decode step streams): marked to be the first to
+// leave L2 again, so that they do not push out what is read again (activations, block tables, the pages of the
+// cache).  A decode step of 8 requests at the 7B sizes: 2.87 ms with the hint, 2.92 without.
+__device__ __forceinline__ void tma_load_2d_once(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(s_addr(dst)), "l"(map), "r"(s_addr(bar)), "r"(c0), "r"(c1), "l"(policy) : "memory");
+}
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+
 // Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc(const void* tile) {
     uint64_t d = 0;
@@ -192,9 +206,10 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // ---- producer.  When the block runs swapped, A is the weight matrix: a constant, so its first
         // tiles are fetched before the kernels before this one have finished; B (activations) only after.
         const int ahead = g.swapped ? min(STAGES, k_iters) : 0;
+        const uint64_t once = l2_evict_first_policy();
         for (int it = 0; it < ahead; ++it) {
             mbar_expect_tx(&full[it], A_BYTES + B_BYTES);
-            tma_load_2d(tiles + it * (A_BYTES + B_BYTES), &map_a, (k_begin + it) * TC_BK, m0, &full[it]);
+            tma_load_2d_once(tiles + it * (A_BYTES + B_BYTES), &map_a, (k_begin + it) * TC_BK, m0, &full[it], once);
         }
         pdl_wait();
         for (int it = 0; it < ahead; ++it)
@@ -204,7 +219,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, gave_up)) break;
             mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
             unsigned char* a_tile = tiles + s * (A_BYTES + B_BYTES);
-            tma_load_2d(a_tile, &map_a, (k_begin + it) * TC_BK, m0, &full[s]);
+            if (g.swapped) tma_load_2d_once(a_tile, &map_a, (k_begin + it) * TC_BK, m0, &full[s], once);  // weights
+            else tma_load_2d(a_tile, &map_a, (k_begin + it) * TC_BK, m0, &full[s]);
             tma_load_2d(a_tile + A_BYTES, &map_b, (k_begin + it) * TC_BK, n0, &full[s]);
         }
     } else if (warp == 1) {
