@@ -151,10 +151,12 @@ extern "C" int ss_attn_decode_tma(const void* q, int64_t q_stride, void* out, in
     a.n_q = n_q; a.n_kv = n_kv; a.page_size = page_size; a.num_pages = num_pages; a.scale = scale; a.window = window;
     a.n_slices = n_slices; a.cluster = cluster; a.inv_freq = inv_freq; a.rot_dim = rot_dim; a.fused = fused;
     a.part_o = part_o; a.part_lse = part_lse; a.counters = counters; a.err = err;
-    constexpr int smem = decode_tma_smem_bytes<HEAD_DIM>();
     static SsPerDevice opted;
-    if (int rc_smem = ss_opt_in_smem(attn_decode_tma<HEAD_DIM>, smem, opted)) return rc_smem;
+    // the most a launch can ask for: 16 heads in a cluster of 7 are 3 x 7 records
+    if (int rc_smem = ss_opt_in_smem(attn_decode_tma<HEAD_DIM>, decode_tma_smem_bytes<HEAD_DIM>(24, 8), opted)) return rc_smem;
     const int G = n_q / n_kv;
+    // the records a block receives from its cluster are sized by the heads it really has
+    const int smem = decode_tma_smem_bytes<HEAD_DIM>(G < 16 ? G : 16, cluster);
     dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
     if (cluster > 1) ss_launch_cluster(attn_decode_tma<HEAD_DIM>, dim3(grid), dim3(DT_THREADS), smem, stream, cluster, map_kv, a);
     else ss_launch(attn_decode_tma<HEAD_DIM>, dim3(grid), dim3(DT_THREADS), smem, stream, map_kv, a);

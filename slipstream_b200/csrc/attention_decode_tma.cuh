@@ -2,11 +2,16 @@
 // bfloat16, head size 64 or 128, page sizes 8, 16, 32 and 64.
 //
 // The arithmetic is that of attn_decode_mma (attention_mma.cuh): a block takes the (up to 16) heads of one
-// (request, kv head) and one slice of the keys; its four consumer warps take different 16-key parts of each
-// 64-key tile (mma.sync m16n8k16, float32 online softmax) and merge at the end; the slices of a head block
-// are a thread-block cluster and merge through shared memory; beyond 8 slices they form several clusters of 8,
-// whose results pass through scratch memory to the block that finishes last (few requests with long contexts:
-// one request of 32,768 tokens is 64 slices on 4 kv heads, 256 blocks instead of 32).
+// (request, kv head) and one slice of the keys (mma.sync m16n8k16, float32 online softmax).  Its four consumer
+// warps work as two pairs: pair 0 takes the even tiles of the slice (stage 0 of the ring), pair 1 the odd ones,
+// and each warp of a pair one 32-key half of the tile, so that a slice of two tiles (1,024 cached tokens in 8
+// slices) is one pass per warp instead of two dependent ones.  The warps merge at the end; the slices of a head
+// block are a thread-block cluster: every block PUSHES its unnormalised result into the shared memory of the
+// block that owns the row (st.shared::cluster), one cluster barrier makes the pushes visible, and the owner
+// combines what it received; nobody reads another block's memory, so nobody has to wait for readers before it
+// leaves.  Beyond 8 slices they form several clusters of 8, whose results pass through scratch memory to the
+// block that finishes last (few requests with long contexts: one request of 32,768 tokens is 64 slices on 4 kv
+// heads, 256 blocks instead of 32).
 // What differs is how a tile gets into shared memory.  There every thread issued sixteen 16-byte cp.async per
 // tile, and issuing them took three times as long as the arithmetic on the tile (1.5 us against 0.5 us per
 // tile and block, measured), whatever the memory did.  Here a fifth warp's first lane issues one
@@ -61,9 +66,22 @@ constexpr int decode_tma_tile_bytes() {
     const int merge = (4 * 16 * (D + 8) + 2 * 4 * 16 + 16 * D + 16) * 4;       // the merge buffers, which reuse them
     return tiles > merge ? tiles : merge;
 }
+// What the blocks of a cluster push to one another: per row a block owns (rows rank, rank + cluster, ... of the
+// head block) one record of D values, the maximum and the sum from each block of the cluster.
+constexpr int decode_tma_recv_bytes(int D, int heads, int cluster) {
+    return cluster > 1 ? ((heads + cluster - 1) / cluster) * cluster * (D + 2) * 4 : 0;
+}
 template <int D>
-constexpr int decode_tma_smem_bytes() {
-    return 1024 + decode_tma_tile_bytes<D>() + 16 * (D + 8) * 2 + 128;  // alignment slack, tiles, Q, mbarriers
+constexpr int decode_tma_smem_bytes(int heads = 16, int cluster = 8) {
+    // alignment slack, tiles, Q, mbarriers, records received from the cluster
+    return 1024 + decode_tma_tile_bytes<D>() + 16 * (D + 8) * 2 + 128 + decode_tma_recv_bytes(D, heads, cluster);
+}
+
+// two floats into the same shared-memory offset of block `rank` of this cluster
+__device__ __forceinline__ void st_cluster_f32x2(float* local, uint32_t rank, float x, float y) {
+    uint32_t addr = (uint32_t)__cvta_generic_to_shared(local), remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(remote), "f"(x), "f"(y) : "memory");
 }
 
 template <int D>
@@ -79,6 +97,8 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
     uint64_t* full = reinterpret_cast<uint64_t*>(Qs + 16 * KSTR);
     uint64_t* empty = full + NS;
     volatile int* gave_up = reinterpret_cast<volatile int*>(empty + NS);
+    float* Recv = reinterpret_cast<float*>(base + decode_tma_tile_bytes<D>() + 16 * KSTR * 2 + 128);  // [slot][block][D + 2]
+    static_assert(NS == 2, "the consumer pairs are tied to the two stages of the ring");
     __shared__ int32_t table_s[DT_TABLE_MAX];
     __shared__ float cos_s[64], sin_s[64];
     __shared__ __align__(16) bf16 newest_k[128], newest_v[128];
@@ -103,7 +123,7 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
     const bool has_newest = a.fused && work && kt_hi == kt_last;
 
     if (tid == 0) {
-        for (int s = 0; s < NS; ++s) { fa::mbar_init(&full[s], 1); fa::mbar_init(&empty[s], 4); }
+        for (int s = 0; s < NS; ++s) { fa::mbar_init(&full[s], 1); fa::mbar_init(&empty[s], 2); }  // a pair of warps per stage
         *gave_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -258,27 +278,29 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
             const float scale_log2 = a.scale * 1.4426950408889634f;
             const int p_lo = (lane >> 2) < heads_here ? pos : -1;
             const int p_hi = (lane >> 2) + 8 < heads_here ? pos : -1;
-            for (int kt = kt_lo; kt <= kt_hi; ++kt) {
-                const int i = kt - kt_lo, st = i % NS;
+            // pair (warp / 2) owns stage (warp / 2) of the ring: tiles kt_lo + pair, + 2, ...; warp % 2 is the 32-key half
+            const int pair = warp >> 1, key_off = (warp & 1) * 32;
+            for (int kt = kt_lo + pair; kt <= kt_hi; kt += 2) {
+                const int i = kt - kt_lo, st = pair;
                 bf16* Ks = KV + st * STAGE;
                 bf16* Vs = Ks + MMA_BN * D;
-                // a wait that gives up makes every later wait give up at once; the loop still runs to its end
-                // so that the barrier below is reached by all four warps or by none
+                // a wait that gives up makes every later wait give up at once
                 const bool ok = fa::mbar_wait(&full[st], (i / NS) & 1, gave_up);
-                if (a.fused && kt == kt_last) {
-                    // the newest token's row of this tile comes from the projection output, not from the page
+                const int first_key = kt * MMA_BN + key_off;
+                if (a.fused && kt == kt_last && pos >= first_key && pos < first_key + 32) {
+                    // the newest token's row of this half comes from the projection output, not from the page
                     const int prow = pos - kt_last * MMA_BN;
-                    for (int c = tid; c < 2 * (D / 8); c += MMA_THREADS) {
+                    for (int c = lane; c < 2 * (D / 8); c += 32) {
                         const int col = (c % (D / 8)) * 8;
                         if (c < D / 8) *reinterpret_cast<uint4*>(const_cast<bf16*>(tile_at<D, true>(Ks, prow, col))) = *reinterpret_cast<const uint4*>(newest_k + col);
                         else *reinterpret_cast<uint4*>(const_cast<bf16*>(tile_at<D, true>(Vs, prow, col))) = *reinterpret_cast<const uint4*>(newest_v + col);
                     }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    __syncwarp();
                 }
-                if (ok && kt * MMA_BN + warp * 16 <= pos) {
-                    const bool whole = heads_here == 16 && kt * MMA_BN + warp * 16 + 15 <= pos && kt * MMA_BN + warp * 16 >= lo;
-                    if (whole) warp_tile<D, 16, false, true>(qf, Ks, Vs, warp * 16, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
-                    else warp_tile<D, 16, true, true>(qf, Ks, Vs, warp * 16, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
+                if (ok && first_key <= pos) {
+                    const bool whole = heads_here == 16 && first_key + 31 <= pos && first_key >= lo;
+                    if (whole) warp_tile<D, 32, false, true>(qf, Ks, Vs, key_off, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
+                    else warp_tile<D, 32, true, true>(qf, Ks, Vs, key_off, kt * MMA_BN, scale_log2, p_lo, p_hi, window, m, l, o);
                 }
                 __syncwarp();
                 if (lane == 0) {
@@ -294,8 +316,7 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
     float* Om = reinterpret_cast<float*>(base);              // [4][16][OSTR]
     float* Mm = Om + 4 * 16 * OSTR;                          // [4][16]
     float* Lm = Mm + 4 * 16;                                 // [4][16]
-    float* Pc = Lm + 4 * 16;                                 // [16][D]: this slice's result, read by the cluster
-    float* Lc = Pc + 16 * D;                                 // [16]
+    float* Fm = Lm + 4 * 16;                                 // [4][16]: exp2(m_w - m)
     __syncthreads();
     if (warp < 4) {
 #pragma unroll
@@ -315,79 +336,80 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
         }
     }
     __syncthreads();
-    // per row: the maximum over the four warps, each warp's factor and the sum (once per row, not once per element:
-    // with four exp2f for each of the 896 elements this merge took 4,300 cycles, more than the tiles of a short slice)
-    float* Fm = Lc + 16;                                     // [4][16]: exp2(m_w - m)
-    float* MLm = Fm + 4 * 16;                                // [2][16]: m, l
-    if (tid < 16) {
-        float mm = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, Mm[w * 16 + tid]);
-        float ll = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float f = mm != -INFINITY ? exp2f(Mm[w * 16 + tid] - mm) : 0.f;
-            Fm[w * 16 + tid] = f;
-            ll += Lm[w * 16 + tid] * f;
-        }
-        MLm[tid] = mm;
-        MLm[16 + tid] = ll;
+    // per (warp, row): the warp's factor against the row's maximum over the four warps (once per row, not once per
+    // element: with four exp2f for each of the 896 elements this merge took 4,300 cycles)
+    if (tid < 64) {
+        const int row = tid & 15;
+        float mm = fmaxf(fmaxf(Mm[row], Mm[16 + row]), fmaxf(Mm[32 + row], Mm[48 + row]));
+        Fm[tid] = mm != -INFINITY ? fast_exp2(Mm[tid] - mm) : 0.f;
     }
     __syncthreads();
     const int64_t head0 = (int64_t)kvh * G + g0;
-    for (int idx = tid; idx < heads_here * D; idx += DT_THREADS) {
-        const int row = idx / D, d = idx - row * D;
-        const float mm = MLm[row], ll = MLm[16 + row];
-        float acc = 0.f;
+    const int rank = cs > 1 ? (int)cluster_rank() : 0;
+    for (int idx = tid; idx < heads_here * (D / 2); idx += DT_THREADS) {
+        const int row = idx / (D / 2), d = (idx - row * (D / 2)) * 2;
+        float acc0 = 0.f, acc1 = 0.f, ll = 0.f, mm = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) acc += Om[(w * 16 + row) * OSTR + d] * Fm[w * 16 + row];
-        const float val = ll > 0.f ? acc / ll : 0.f;
-        if (n_slices == 1) {
-            a.out[(int64_t)row_q * a.out_stride + (head0 + row) * D + d] = __float2bfloat16_rn(val);
-        } else if (cs > 1) {
-            Pc[row * D + d] = val;
-            if (d == 0) Lc[row] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
+        for (int w = 0; w < 4; ++w) {
+            const float f = Fm[w * 16 + row];
+            const float2 v = *reinterpret_cast<const float2*>(Om + (w * 16 + row) * OSTR + d);
+            acc0 = fmaf(v.x, f, acc0);
+            acc1 = fmaf(v.y, f, acc1);
+            ll = fmaf(Lm[w * 16 + row], f, ll);
+            mm = fmaxf(mm, Mm[w * 16 + row]);
+        }
+        if (cs > 1) {
+            // to the block of the cluster that owns this row: record [row / cs][this block] of its Recv
+            float* rec = Recv + (((row / cs) * cs + rank) * (D + 2));
+            st_cluster_f32x2(rec + d, (uint32_t)(row % cs), acc0, acc1);
+            if (d == 0) st_cluster_f32x2(rec + D, (uint32_t)(row % cs), mm, ll);
         } else {
-            a.part_o[(((int64_t)r * n_q + head0 + row) * n_groups + group) * D + d] = val;
-            if (d == 0) a.part_lse[((int64_t)r * n_q + head0 + row) * n_groups + group] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
+            const float inv = ll > 0.f ? 1.f / ll : 0.f;
+            if (n_slices == 1) {
+                *reinterpret_cast<__nv_bfloat162*>(a.out + (int64_t)row_q * a.out_stride + (head0 + row) * D + d) =
+                    __floats2bfloat162_rn(acc0 * inv, acc1 * inv);
+            } else {
+                float* po = a.part_o + (((int64_t)r * n_q + head0 + row) * n_groups + group) * D + d;
+                po[0] = acc0 * inv;
+                po[1] = acc1 * inv;
+                if (d == 0) a.part_lse[((int64_t)r * n_q + head0 + row) * n_groups + group] = ll > 0.f ? mm + log2f(ll) : -INFINITY;
+            }
         }
     }
     if (*gave_up && tid == 0) atomicOr(a.err, SS_ERR_WAIT_LIMIT);
     if (n_slices == 1) return;
 
     if (cs > 1) {
-        // the slices of a cluster are combined through its shared memory; rank k takes rows k, k + cs, ...
+        // One barrier makes every block's pushes visible; then rank k combines rows k, k + cs, ... out of its OWN
+        // shared memory (the records of the cs blocks, in block order) and is free to leave.
         cluster_sync_all();
-        const int rank = (int)cluster_rank();
         const int mine = heads_here > rank ? (heads_here - 1 - rank) / cs + 1 : 0;
-        for (int idx = tid; idx < mine * D; idx += DT_THREADS) {
-            const int row = rank + (idx / D) * cs, d = idx % D;
-            float lse[8], p[8];
-#pragma unroll
-            for (int sl = 0; sl < 8; ++sl) {
-                lse[sl] = sl < cs ? ld_cluster_f32(Lc + row, (uint32_t)sl) : -INFINITY;
-                p[sl] = sl < cs ? ld_cluster_f32(Pc + row * D + d, (uint32_t)sl) : 0.f;
-            }
-            float mx = -INFINITY, den = 0.f;
-#pragma unroll
-            for (int sl = 0; sl < 8; ++sl) mx = fmaxf(mx, lse[sl]);
-#pragma unroll
-            for (int sl = 0; sl < 8; ++sl) {
-                lse[sl] = mx == -INFINITY ? 0.f : exp2f(lse[sl] - mx);
-                den += lse[sl];
+        for (int idx = tid; idx < mine * (D / 2); idx += DT_THREADS) {
+            const int slot = idx / (D / 2), d = (idx - slot * (D / 2)) * 2;
+            const int row = rank + slot * cs;
+            const float* rec = Recv + (slot * cs) * (D + 2);
+            float mx = -INFINITY;
+            for (int sl = 0; sl < cs; ++sl) mx = fmaxf(mx, rec[sl * (D + 2) + D]);
+            float acc0 = 0.f, acc1 = 0.f, den = 0.f;
+            for (int sl = 0; sl < cs; ++sl) {  // slices in order
+                const float* one = rec + sl * (D + 2);
+                const float f = mx == -INFINITY ? 0.f : fast_exp2(one[D] - mx);
+                const float2 v = *reinterpret_cast<const float2*>(one + d);
+                acc0 = fmaf(v.x, f, acc0);
+                acc1 = fmaf(v.y, f, acc1);
+                den = fmaf(one[D + 1], f, den);
             }
             const float inv = den > 0.f ? 1.f / den : 0.f;
-            float acc = 0.f;
-#pragma unroll
-            for (int sl = 0; sl < 8; ++sl) acc += p[sl] * (lse[sl] * inv);
             if (n_groups == 1) {
-                a.out[(int64_t)row_q * a.out_stride + (head0 + row) * D + d] = __float2bfloat16_rn(acc);
+                *reinterpret_cast<__nv_bfloat162*>(a.out + (int64_t)row_q * a.out_stride + (head0 + row) * D + d) =
+                    __floats2bfloat162_rn(acc0 * inv, acc1 * inv);
             } else {  // several clusters share the keys of this head block: the cluster's result goes to scratch
-                a.part_o[(((int64_t)r * n_q + head0 + row) * n_groups + group) * D + d] = acc;
+                float* po = a.part_o + (((int64_t)r * n_q + head0 + row) * n_groups + group) * D + d;
+                po[0] = acc0 * inv;
+                po[1] = acc1 * inv;
                 if (d == 0) a.part_lse[((int64_t)r * n_q + head0 + row) * n_groups + group] = den > 0.f ? mx + log2f(den) : -INFINITY;
             }
         }
-        cluster_sync_all();  // nobody leaves while its shared memory is still being read
         if (n_groups == 1) return;
     }
 

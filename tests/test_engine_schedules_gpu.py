@@ -47,15 +47,21 @@ def test_preemption_by_recompute_in_bfloat16_with_a_seeded_sampling_chain(tmp_pa
     """Head size 128 and pages of 16 take the TMA-fed decode kernel, which writes the newest key and value to
     their page itself.  With too few pages the newest request is preempted, loses its pages, and later replays
     prompt and outputs as a prompt portion; its seen-token mask (repetition penalty) restarts from those tokens
-    and its draws continue at the same index.  The tokens are those of an engine with room for everybody."""
+    and its draws continue at the same index.  In bfloat16 a replayed key differs from the decoded one by its
+    rounding, so the tokens need not equal those of an engine with room for everybody; every token of either
+    engine must be the one the plain chain draws from the plain logits with the same noise (penalty over the
+    request's own history, temperature, draw number = index of the output token), within the rounding of the
+    logits."""
     from slipstream_b200 import SamplingParams, ops
     from slipstream_b200.engine.llm_engine import Request
+    from test_generate_gpu import gumbel_noise
 
     config = write_model(tmp_path, head_dim=128, num_attention_heads=4, num_key_value_heads=2, hidden_size=256)
     assert ops.tcgen05_attention_fits(128, 4, 2, 16, 0)
     prompts = [random_tokens(config.vocab_size, n, 70 + n) for n in (40, 25, 33)]
-    params = [SamplingParams(max_tokens=24, temperature=0.8, top_k=40, top_p=0.95, repetition_penalty=1.3,
-                             seed=1000 + i, ignore_eos=True) for i in range(3)]
+    temperature, penalty, new = 0.8, 1.3, 24
+    params = [SamplingParams(max_tokens=new, temperature=temperature, repetition_penalty=penalty, seed=1000 + i,
+                             ignore_eos=True) for i in range(3)]
 
     def run(pages):
         engine = make_engine(tmp_path, 16, "bfloat16", pages, prefill_chunk_size=32)
@@ -65,16 +71,29 @@ def test_preemption_by_recompute_in_bfloat16_with_a_seeded_sampling_chain(tmp_pa
         assert engine.runner.cache.min_free_pages() == pages
         return outs, engine.scheduler.preemptions
 
-    want, none = run(64)
-    got, preemptions = run(9)  # 144 token slots for 98 prompt + 72 new tokens
+    roomy, none = run(64)
+    tight, preemptions = run(9)  # 144 token slots for 98 prompt + 72 new tokens
     assert none == 0 and preemptions >= 1
-    assert all(len(o) == 24 for o in want)
-    assert got == want
+    cfg, weights = plain.read_model_folder(tmp_path, torch.float64)
+    weights = {k: v.to(torch.bfloat16).to(torch.float64) if v.dim() == 2 else v for k, v in weights.items()}
+    for what, outs in (("roomy", roomy), ("tight", tight)):
+        for i, (prompt, out) in enumerate(zip(prompts, outs)):
+            assert len(out) == new
+            tokens = list(prompt)
+            for d, tok in enumerate(out):
+                logits = plain.forward_logits(cfg, weights, tokens)[-1]
+                kept = plain.filtered_logits(logits, temperature=temperature, repetition_penalty=penalty, history=tokens)
+                score = kept.numpy() + gumbel_noise(1000 + i, d, config.vocab_size)
+                slack = 2 * 3e-2 * float(logits.abs().max()) / temperature
+                assert score[tok] >= score.max() - slack, (what, i, d, tok, int(score.argmax()))
+                tokens.append(tok)
+    # the requests that were never preempted run the same kernels on the same values in both engines
+    assert tight[0] == roomy[0]
     # the chain is not greedy in disguise: another seed gives other tokens
     other = make_engine(tmp_path, 16, "bfloat16", 64)
     again = other.generate(Request("x", None, prompts[0], SamplingParams(
-        max_tokens=24, temperature=0.8, top_k=40, top_p=0.95, repetition_penalty=1.3, seed=77, ignore_eos=True), 0.0))
-    assert again != want[0]
+        max_tokens=new, temperature=temperature, repetition_penalty=penalty, seed=77, ignore_eos=True), 0.0))
+    assert again != roomy[0]
 
 
 # --------------------------------------------------------------------------- key parts in a mixed step
