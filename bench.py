@@ -257,12 +257,13 @@ def kernel_fractions(engine, batch: int, ctx_tokens: int, prefill_tokens: int, p
     hbm("decode_attention", us, batch * ctx_tokens * 2.0 * n_kv * d * 2 + 2.0 * batch * n_q * d * 2)
     if ops.tcgen05_attention_fits(d, n_q, n_kv, page, 0):
         import numpy as np
-        from slipstream_b200.engine.context import query_tiles_host
+        from slipstream_b200.engine.context import query_tiles_longest_first_host
 
         T, tile = prefill_tokens, 128 // (n_q // n_kv)
         qkv_p = rand(T, (n_q + 2 * n_kv) * d)
         att_p = torch.empty(T, n_q * d, dtype=torch.bfloat16, device=dev)
-        req, tok0 = (torch.from_numpy(a).to(dev) for a in query_tiles_host(np.asarray([T], dtype=np.int32), tile))
+        req, tok0 = (torch.from_numpy(a).to(dev) for a in query_tiles_longest_first_host(
+            np.asarray([T], dtype=np.int32), np.asarray([T], dtype=np.int32), tile))
         table_p = tables(1, T)
         q_start_p = torch.tensor([0, T], dtype=torch.int32, device=dev)
         lens_p = torch.tensor([T], dtype=torch.int32, device=dev)

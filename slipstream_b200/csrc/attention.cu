@@ -118,9 +118,9 @@ extern "C" int ss_attn_prefill_tc5(const void* q, int64_t q_stride, int n_tokens
     if (int rc_smem = ss_opt_in_smem(fa::attn_prefill_tc5<HEAD_DIM>, smem, opted)) return rc_smem;
     // splits > 1: the key tiles of every query tile are shared by a thread-block cluster of that many blocks
     if (splits > 1)
-        ss_launch_cluster(fa::attn_prefill_tc5<HEAD_DIM>, dim3(n_tiles, n_kv, splits), dim3(FA_THREADS), smem, stream, splits, map_q, map_kv, a);
+        ss_launch_cluster(fa::attn_prefill_tc5<HEAD_DIM>, dim3(n_tiles * n_kv, 1, splits), dim3(FA_THREADS), smem, stream, splits, map_q, map_kv, a);
     else
-        ss_launch(fa::attn_prefill_tc5<HEAD_DIM>, dim3(n_tiles, n_kv), dim3(FA_THREADS), smem, stream, map_q, map_kv, a);
+        ss_launch(fa::attn_prefill_tc5<HEAD_DIM>, dim3(n_tiles * n_kv), dim3(FA_THREADS), smem, stream, map_q, map_kv, a);
     return SS_LAUNCH_CHECK();
 }
 

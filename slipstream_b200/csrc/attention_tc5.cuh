@@ -188,11 +188,15 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         return;
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int G = a.n_q / a.n_kv, kvh = blockIdx.y;
+    // grid.x runs over (query tile, kv head) with the kv head fastest, and the host lists the query tiles by
+    // falling number of keys: blocks start in the order of their index, so the blocks of the longest query tile
+    // start first, then those of the next longest, whatever their head or request (head by head, the short tiles
+    // of one head started before the long ones of the next and left one SM with three times the work of another:
+    // a 2,048-token prompt took 45.7 us instead of 37.3)
+    const int G = a.n_q / a.n_kv, kvh = blockIdx.x % a.n_kv;
     const int TOK = 128 / G;
     pdl_wait();  // q, the pages and the tables come from the kernels before this one
-    // the host lists tiles in token order; later tokens see more keys, so the list is walked from its end
-    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int tile = blockIdx.x / a.n_kv;
     const int r = a.tile_req[tile], tok0 = a.tile_tok0[tile];
     const int qs = a.q_start[r], q_len = a.q_start[r + 1] - qs, seq_len = a.seq_lens[r];
     const int toks_here = min(TOK, q_len - tok0);

@@ -89,6 +89,20 @@ class StepContext:
             self._tiles[key] = cached
         return cached
 
+    def query_tiles_longest_first(self, rows: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """``query_tiles(rows)`` ordered by falling number of keys a tile sees (its last token's position): a kernel
+        whose blocks take one tile each and start in index order then starts its longest blocks first."""
+        key = ("longest_first", rows)
+        cached = self._tiles.get(key)
+        if cached is None:
+            req, q0 = query_tiles_longest_first_host(self.q_lens_host, self.seq_lens_host, rows)
+            staged = torch.empty(2 * req.size, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+            staged.numpy()[: req.size] = req
+            staged.numpy()[req.size:] = q0
+            both = staged.to(self.device, non_blocking=True)
+            cached = self._tiles[key] = (both[: req.size], both[req.size:])
+        return cached
+
     def set_query_tiles(self, rows: int, group: int, tile_req: torch.Tensor, tile_first: torch.Tensor) -> None:
         """Fix the answer of ``query_tiles(rows, group)`` (a part does this for the static context of a graph)."""
         self._tiles[(rows, group)] = (tile_req, tile_first)
@@ -100,6 +114,15 @@ def query_tiles_host(q_lens: np.ndarray, rows: int) -> tuple[np.ndarray, np.ndar
     first = np.cumsum(counts) - counts
     q0 = (np.arange(int(counts.sum()), dtype=np.int32) - np.repeat(first, counts).astype(np.int32)) * rows
     return req.astype(np.int32), q0.astype(np.int32)
+
+
+def query_tiles_longest_first_host(q_lens: np.ndarray, seq_lens: np.ndarray, rows: int) -> tuple[np.ndarray, np.ndarray]:
+    """The tiles of ``query_tiles_host`` by falling position of their last token (the number of keys they see)."""
+    req, q0 = query_tiles_host(q_lens, rows)
+    q_lens = np.asarray(q_lens, dtype=np.int64)
+    last = (np.asarray(seq_lens, dtype=np.int64) - q_lens)[req] + np.minimum(q0 + rows, q_lens[req]) - 1
+    order = np.argsort(-last, kind="stable")
+    return req[order], q0[order]
 
 
 class StepInputError(ValueError):

@@ -410,7 +410,8 @@ def paged_attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.T
                                     head_dim: int, scale: float, key_parts: int = 1) -> None:
     """bfloat16 causal attention for prompt portions and mixed batches on the tcgen05 tensor cores (Q, K, V
     tiles by TMA, S and O in tensor memory).  A tile is ``128 // (n_q // n_kv)`` consecutive query tokens of
-    one request: ``tile_req`` / ``tile_tok0`` list (request index, first token within the request's rows).
+    one request: ``tile_req`` / ``tile_tok0`` list (request index, first token within the request's rows); blocks
+    start in list order, so the list should begin with the tiles that see the most keys.
     ``key_parts`` (1, 2, 4 or 8): the keys of every query tile are shared by that many blocks, a thread-block
     cluster whose results are combined through shared memory (see ``prefill_key_parts``)."""
     _need(out, torch.bfloat16, "attention output")
@@ -606,7 +607,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
                                ctx.num_requests, n_q, n_kv, head_dim, scale, window, slices, scratch, rope)
         return
     if tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], window):
-        tile_req, tile_tok0 = ctx.query_tiles(128 // group, 1)
+        tile_req, tile_tok0 = ctx.query_tiles_longest_first(128 // group)
         key = ("prefill_key_parts", 128 // group, n_kv)
         parts = ctx.extras.get(key)
         if parts is None:  # the same for every layer of the step
