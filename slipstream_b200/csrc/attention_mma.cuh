@@ -243,6 +243,7 @@ attn_prefill_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict_
     const int qs = q_start[r], q_len = q_start[r + 1] - qs, seq_len = seq_lens[r];
     const int rows_total = q_len * G;
     const int rows_here = min(64, rows_total - row0);
+    if (rows_here <= 0) return;  // a padding tile of a captured step (uniform over the block)
     const int first_pos = seq_len - q_len + row0 / G;
     const int last_pos = seq_len - q_len + (row0 + rows_here - 1) / G;
     const int lo = window > 0 ? max(0, first_pos - window + 1) : 0;

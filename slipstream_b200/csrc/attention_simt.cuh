@@ -51,6 +51,7 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, T* __restrict__ out,
     const int r = tile_req[blockIdx.x], q0 = tile_q0[blockIdx.x];
     const int qs = q_start[r], q_len = q_start[r + 1] - qs, seq_len = seq_lens[r];
     const int rows_here = min(ATT_BM, q_len - q0);
+    if (rows_here <= 0) return;  // a padding tile of a captured step (uniform over the block)
     const int pos0 = seq_len - q_len + q0;
     const int p_max = pos0 + rows_here - 1;
     const int lo_min = window > 0 ? max(0, pos0 - window + 1) : 0;

@@ -200,6 +200,8 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int r = a.tile_req[tile], tok0 = a.tile_tok0[tile];
     const int qs = a.q_start[r], q_len = a.q_start[r + 1] - qs, seq_len = a.seq_lens[r];
     const int toks_here = min(TOK, q_len - tok0);
+    // a padding tile of a captured step: uniform over the block and over its cluster, nothing is set up yet
+    if (toks_here <= 0) return;
     const int rows_valid = toks_here * G;
     const int pos0 = seq_len - q_len + tok0;           // position of the tile's first token
     const int last_pos = pos0 + toks_here - 1;

@@ -53,8 +53,11 @@ class StepContext:
     request_ids: list[object]
     device: torch.device
     num_logits: int = 0
-    _tiles: dict[tuple[int, int], tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
+    _tiles: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
     extras: dict[str, object] = field(default_factory=dict)
+    # the static context of a captured step: a function that hands out static device buffers for a list of tiles
+    # ((kind, rows, group) -> (requests, first rows)), which the graph refills before every replay
+    static_tiles: object = None
 
     @property
     def max_q_len(self) -> int:
@@ -74,6 +77,8 @@ class StepContext:
         token; with the size of a kv group it is a (token, head of the group) pair."""
         key = (rows, group)
         cached = self._tiles.get(key)
+        if cached is None and self.static_tiles is not None:  # the context of a captured step
+            cached = self._tiles[key] = self.static_tiles(("in_order", rows, group))
         if cached is None:
             req, q0 = query_tiles_host(self.q_lens_host * group, rows)
             # through pinned memory: a copy from pageable memory would hold the host until every kernel queued
@@ -94,6 +99,8 @@ class StepContext:
         whose blocks take one tile each and start in index order then starts its longest blocks first."""
         key = ("longest_first", rows)
         cached = self._tiles.get(key)
+        if cached is None and self.static_tiles is not None:
+            cached = self._tiles[key] = self.static_tiles(("longest_first", rows, 1))
         if cached is None:
             req, q0 = query_tiles_longest_first_host(self.q_lens_host, self.seq_lens_host, rows)
             staged = torch.empty(2 * req.size, dtype=torch.int32, pin_memory=self.device.type == "cuda")

@@ -227,3 +227,153 @@ class DecodeGraph:
     def h2d_bytes(self) -> int:
         """Bytes the host sends per replay (the small static buffer; the tables travel as patches inside it)."""
         return self.static.numel() * 4
+
+
+# =========================================================================== steps with prompt portions
+TOKEN_BUCKETS = ([16, 32] + [64 * k for k in range(1, 11)] + [768, 896, 1024, 1152, 1280, 1536, 1792, 2048, 2304])
+REQUEST_BUCKETS = [4, 8, 16, 32, 64, 128, 256]
+PADDING_TILE_FIRST = 1 << 24  # "first row" of a tile that holds no row: every kernel returns at once on such a tile
+
+
+def mixed_bucket(n_tokens: int, n_requests: int) -> tuple[int, int] | None:
+    tokens = next((b for b in TOKEN_BUCKETS if n_tokens <= b), None)
+    requests = next((b for b in REQUEST_BUCKETS if n_requests <= b), None)
+    return None if tokens is None or requests is None else (tokens, requests)
+
+
+class MixedGraph:
+    """A captured step of up to ``n_tokens`` tokens of up to ``n_requests`` requests, prompt portions beside
+    decoded tokens.  A step of a small model launches a few hundred kernels that the host needs longer to launch
+    than the GPU to run (a 24-layer model: 3.4 ms of launches for under 1 ms of work); replayed from a graph it
+    costs the host one copy and one launch.
+
+    The captured step always runs ``n_tokens`` rows and ``n_requests`` requests.  Rows beyond the live tokens are
+    padding (token 0, slot -1: nothing is written to the cache; their activations are computed and never read),
+    requests beyond the live ones are empty, and the lists of query tiles the attention kernels walk are padded
+    with tiles that hold no row.  All metadata, the block tables and the tile lists lie in one static device buffer
+    that one copy refills before each replay."""
+
+    def __init__(self, runner, n_tokens: int, n_requests: int, n_logits: int, variants: tuple = ()) -> None:
+        """``n_logits``: rows whose logits a step may ask for (a serving step wants one per request at most, a
+        replayed trace up to one per token)."""
+        self.runner = runner
+        self.n_tokens, self.n_requests, self.n_logits = N, R, L = n_tokens, n_requests, n_logits
+        cache = runner.cache
+        G = self.n_groups = len(cache.groups)
+        self.max_blocks = [max(1, (runner.max_model_len + ps - 1) // ps) for ps in cache.page_sizes]
+        self.tile_capacity = 2 * N + R  # entries per list: the most tiles a step has while a tile holds 64 rows of a
+        # group of up to 128 heads, or 16 tokens
+        self.max_tile_lists = 4
+        names = ["token_ids", "positions", "q_start", "seq_lens", "slots", "first", "logit_rows", "slot_maps"]
+        sizes = [N, N, R + 1, R, R, R, L, G * N]
+        names += [f"table{g}" for g in range(G)]
+        sizes += [R * mb for mb in self.max_blocks]
+        names += ["tiles"]
+        sizes += [self.max_tile_lists * 2 * self.tile_capacity]
+        self.offsets = dict(zip(names, np.concatenate([[0], np.cumsum(sizes)])[:-1].tolist()))
+        self.sizes = dict(zip(names, sizes))
+        total = int(sum(sizes))
+        device = runner.device
+        self.static = torch.zeros(total, dtype=torch.int32, device=device)
+        self.hosts = [torch.zeros(total, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.events = [torch.cuda.Event() for _ in range(2)]
+        self.used = [False, False]
+        self.turn = 0
+        self.tile_keys: list[tuple] = []  # (kind, rows, group) of every tile list the parts asked for
+
+        def view(name: str) -> torch.Tensor:
+            o = self.offsets[name]
+            return self.static[o: o + self.sizes[name]]
+
+        groups = [GroupMeta(block_tables=view(f"table{g}").view(R, self.max_blocks[g]),
+                            slot_mapping=view("slot_maps")[g * N: (g + 1) * N], page_size=cache.page_sizes[g],
+                            max_blocks=self.max_blocks[g]) for g in range(G)]
+        self.ctx = StepContext(num_tokens=N, num_requests=R, token_ids=view("token_ids"), positions=view("positions"),
+                               q_start=view("q_start"), seq_lens=view("seq_lens"), state_slots=view("slots"),
+                               first_chunk=view("first"), logit_rows=view("logit_rows"), groups=groups,
+                               # lengths are not known on the host inside a replay; 2 only says "not one token each"
+                               q_lens_host=np.full(R, 2, dtype=np.int32), seq_lens_host=np.zeros(R, dtype=np.int32),
+                               request_ids=[], device=device, num_logits=L, static_tiles=self._static_tiles)
+        variant_of = {part.capture_group(): variant for part, variant in zip(runner.variant_parts, variants)}
+        for part in runner.model.parts():
+            part.prepare_capture(self.ctx, variant_of.get(part.capture_group()), runner.max_model_len)
+        self._fill(self.hosts[0].numpy(), None)
+        self.static.copy_(self.hosts[0])
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            runner.model.forward(self.ctx)  # also tells which tile lists the parts want
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(device)
+        self.graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        gc.collect()
+        collector_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.logits = runner.model.forward(self.ctx)
+        finally:
+            if collector_was_on:
+                gc.enable()
+        self.kernels = ops.launch_count() - before
+
+    def _static_tiles(self, key: tuple) -> tuple[torch.Tensor, torch.Tensor]:
+        if key not in self.tile_keys:
+            if len(self.tile_keys) == self.max_tile_lists:
+                raise RuntimeError("a captured step has room for four lists of query tiles")
+            self.tile_keys.append(key)
+        o = self.offsets["tiles"] + self.tile_keys.index(key) * 2 * self.tile_capacity
+        _kind, rows, group = key
+        count = (self.n_tokens * group + rows - 1) // rows + self.n_requests  # the most tiles a step can have
+        if count > self.tile_capacity:
+            raise RuntimeError("the tile list of a captured step is too long for its buffer")
+        return self.static[o: o + count], self.static[o + self.tile_capacity: o + self.tile_capacity + count]
+
+    def _fill(self, host: np.ndarray, plan: HostPlan | None) -> None:
+        N, R, G = self.n_tokens, self.n_requests, self.n_groups
+        o = self.offsets
+        host[: o["table0"] if G else o["tiles"]] = 0
+        host[o["slot_maps"]: o["slot_maps"] + G * N] = -1
+        tiles = host[o["tiles"]: o["tiles"] + self.sizes["tiles"]].reshape(self.max_tile_lists, 2, self.tile_capacity)
+        tiles[:, 0, :] = 0
+        tiles[:, 1, :] = PADDING_TILE_FIRST
+        if plan is None:
+            return
+        n, r = plan.num_tokens, plan.num_requests
+        host[o["token_ids"]: o["token_ids"] + n] = plan.token_ids
+        host[o["positions"]: o["positions"] + n] = plan.positions
+        host[o["q_start"]: o["q_start"] + r + 1] = plan.q_start
+        host[o["q_start"] + r + 1: o["q_start"] + R + 1] = n  # the requests behind the live ones are empty
+        for name, arr in (("seq_lens", plan.seq_lens), ("slots", plan.slots), ("first", plan.first)):
+            host[o[name]: o[name] + r] = arr
+        host[o["logit_rows"]: o["logit_rows"] + plan.logit_rows.size] = plan.logit_rows
+        host[o["slot_maps"]: o["slot_maps"] + G * N].reshape(G, N)[:, :n] = plan.slot_maps
+        for g in range(G):
+            table = plan.tables[g]
+            host[o[f"table{g}"]: o[f"table{g}"] + R * self.max_blocks[g]].reshape(R, self.max_blocks[g])[:r, : table.shape[1]] = table
+        from .context import query_tiles_host, query_tiles_longest_first_host
+        for i, (kind, rows, group) in enumerate(self.tile_keys):
+            if kind == "longest_first":
+                req, first = query_tiles_longest_first_host(plan.q_lens, plan.seq_lens, rows)
+            else:
+                req, first = query_tiles_host(plan.q_lens * group, rows)
+            tiles[i, 0, : req.size] = req
+            tiles[i, 1, : req.size] = first
+
+    def run(self, plan: HostPlan) -> torch.Tensor:
+        i = self.turn
+        self.turn ^= 1
+        if self.used[i]:
+            self.events[i].synchronize()
+        self._fill(self.hosts[i].numpy(), plan)
+        self.static.copy_(self.hosts[i], non_blocking=True)
+        self.events[i].record()
+        self.used[i] = True
+        self.graph.replay()
+        ops.count_launches(self.kernels)
+        return self.logits[: plan.logit_rows.size].clone()
+
+    @property
+    def h2d_bytes(self) -> int:
+        return self.static.numel() * 4

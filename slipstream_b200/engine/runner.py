@@ -27,7 +27,7 @@ from slipstream_b200.weights.loader import load_weights
 from slipstream_b200.weights.random_init import random_weights_on_device
 
 from .context import StepContext, StepEntry, StepInputError, plan_step, to_device
-from .graphs import BUCKETS, DecodeGraph, bucket_for
+from .graphs import BUCKETS, DecodeGraph, MixedGraph, bucket_for, mixed_bucket
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -101,6 +101,11 @@ class ModelRunner:
                 seen.add(part.capture_group())
                 self.variant_parts.append(part)
         self._graphs: dict[tuple, DecodeGraph] = {}  # (batch bucket, the parts' variants)
+        # steps with prompt portions: (token bucket, request bucket, logits per token?) -> graph, or the number of
+        # times the bucket has come up so far (a graph is captured at the third)
+        self._mixed_graphs: dict[tuple, "MixedGraph | int"] = {}
+        self.mixed_graph_after = 2  # steps of a bucket that run eagerly before it is captured
+        self.max_mixed_graphs = 24
 
     # ------------------------------------------------------------------ requests
     def admit(self, request_id: object) -> None:
@@ -126,10 +131,14 @@ class ModelRunner:
         decode_only = all(len(e.tokens) == 1 for e in entries)
         bucket = self._graph_bucket(len(entries)) if decode_only else None
         plan = plan_step(entries, self.cache, self.config.vocab_size, with_tables=bucket is None)
+        mixed = None if bucket is not None else self._mixed_graph(plan)
         if bucket is not None:
             graph = self._decode_graph(bucket, plan)
             self.last_h2d_bytes = graph.h2d_bytes
             logits = graph.run(plan)
+        elif mixed is not None:
+            self.last_h2d_bytes = mixed.h2d_bytes
+            logits = mixed.run(plan)
         else:
             ctx = to_device(plan, self.device)
             self.last_h2d_bytes = ctx.extras["host_buffer"].numel() * 4
@@ -144,10 +153,34 @@ class ModelRunner:
         attention, say, cuts the keys of few long requests into more slices than those of many short ones, and
         the number of slices is fixed when a graph is captured)."""
         longest = int(plan.seq_lens.max())
-        variants = tuple(part.capture_variant(longest) for part in self.variant_parts)
+        variants = tuple(part.capture_variant(longest, plan) for part in self.variant_parts)
         graph = self._graphs.get((bucket, variants))
         if graph is None:
             graph = self._graphs[(bucket, variants)] = DecodeGraph(self, bucket, variants)
+        return graph
+
+    def _mixed_graph(self, plan) -> "MixedGraph | None":
+        """The captured step that serves this plan (prompt portions beside decoded tokens), once its bucket has come
+        up often enough to be worth a capture; None: run the step kernel by kernel."""
+        if not self.use_cuda_graphs:
+            return None
+        sizes = mixed_bucket(plan.num_tokens, plan.num_requests)
+        if sizes is None:
+            return None
+        per_token = plan.logit_rows.size > sizes[1]
+        if per_token and plan.logit_rows.size > sizes[0]:
+            return None
+        variants = tuple(part.capture_variant(int(plan.seq_lens.max()), plan) for part in self.variant_parts)
+        key = (*sizes, per_token, variants)
+        seen = self._mixed_graphs.get(key, 0)
+        if isinstance(seen, MixedGraph):
+            return seen
+        if seen < self.mixed_graph_after:
+            self._mixed_graphs[key] = seen + 1
+            return None
+        if sum(isinstance(g, MixedGraph) for g in self._mixed_graphs.values()) >= self.max_mixed_graphs:
+            return None
+        graph = self._mixed_graphs[key] = MixedGraph(self, sizes[0], sizes[1], sizes[0] if per_token else sizes[1], variants)
         return graph
 
     def _graph_bucket(self, n_requests: int) -> int | None:

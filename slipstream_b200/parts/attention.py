@@ -73,15 +73,29 @@ class PagedAttention(Mixer):
         ops.attention_library(self.head_dim)  # compile now, not inside the first step
 
     # ------------------------------------------------------------------ decode steps replayed from a graph
-    def capture_variant(self, longest: int) -> object:
-        """Long contexts of few requests want the keys cut into more slices than fit one thread-block cluster
-        (``ops.decode_slices``); that form is captured as a graph of its own."""
-        return bool(self.runtime.dtype == torch.bfloat16 and ops.is_long_context(longest))
+    def capture_variant(self, longest: int, plan: object = None) -> object:
+        """Decode steps: long contexts of few requests want the keys cut into more slices than fit one thread-block
+        cluster (``ops.decode_slices``).  Steps with prompt portions: into how many parts the tcgen05 prefill kernel
+        cuts the keys of a query tile (``ops.prefill_key_parts``).  Each form is captured as a graph of its own."""
+        bf16 = self.runtime.dtype == torch.bfloat16
+        if plan is None or plan.is_decode_only:
+            return bool(bf16 and ops.is_long_context(longest))
+        group = self.num_heads // self.num_kv_heads
+        if not bf16 or not ops.tcgen05_attention_fits(self.head_dim, self.num_heads, self.num_kv_heads, self.page_size or 16,
+                                          self.window or 0):
+            return None
+        return int(ops.prefill_key_parts(plan.q_lens, plan.seq_lens, 128 // group, self.num_kv_heads,
+                                         ops.sm_count(self.runtime.device)))
 
     def capture_group(self) -> object:
         return "paged_attention"
 
     def prepare_capture(self, ctx, variant: object, max_model_len: int) -> None:
+        if not ctx.is_decode_only:
+            # a captured step with prompt portions: the number of key parts is the variant's (the choice follows the
+            # lengths of the step, which a replay does not know on the host)
+            ctx.extras[("prefill_key_parts", 128 // (self.num_heads // self.num_kv_heads), self.num_kv_heads)] = int(variant or 1)
+            return
         # the number of slices must not follow the lengths of the step that happens to be captured
         ctx.extras["static_max_seq_len"] = max_model_len
         ctx.extras["decode_wide"] = bool(variant)

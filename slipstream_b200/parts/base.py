@@ -104,10 +104,11 @@ class Part:
     # -- decode steps replayed from a CUDA graph.  Inside a replay nothing is known on the host about the step
     # -- but its bucket (the number of rows), so whatever a part's forward derives from the step's lengths has to
     # -- be fixed when the graph is captured.  A part that needs this overrides the two methods below.
-    def capture_variant(self, longest: int) -> object:
-        """Which captured form of this part a decode step whose longest request holds ``longest`` tokens should
-        run (any hashable; None: there is only one form).  The runner keeps one graph per bucket and combination
-        of variants."""
+    def capture_variant(self, longest: int, plan: object = None) -> object:
+        """Which captured form of this part a step whose longest request holds ``longest`` tokens should run
+        (any hashable; None: there is only one form).  ``plan`` is the step's host-side metadata
+        (``engine.context.HostPlan``: ``q_lens``, ``seq_lens``, ``is_decode_only``) or None.  The runner keeps one
+        graph per bucket and combination of variants."""
         return None
 
     def capture_group(self) -> object:

@@ -249,3 +249,41 @@ def test_block_tables_of_replayed_decode_steps_follow_their_requests(model_folde
         for pos, row in rows.items():
             err = np.abs(row - want[rid][pos]).max()
             assert err <= TOLERANCE[dtype] * np.abs(want[rid]).max(), (rid, pos, err)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_steps_with_prompt_portions_replayed_from_graphs(model_folders, requests_for, name, dtype):
+    """Steps with prompt portions are captured per bucket of (tokens, requests) once a bucket has come up a few
+    times, and replayed with padding rows, empty requests and empty query tiles.  Here every such step is
+    captured at once: the logits must be those of the same steps run kernel by kernel, bit for bit (the padding
+    must not reach a live row), and the plain implementation's within the usual bound."""
+    from slipstream_b200.engine.graphs import MixedGraph
+    from slipstream_b200.engine.runner import ModelRunner
+
+    folder, config, page = model_folders[name]
+    requests = requests_for(config)
+    want = oracle(folder, requests, dtype)
+    max_tokens = 256
+    results = {}
+    for captured in (False, True):
+        runner = ModelRunner(folder, dtype=dtype, page_size=page, num_pages=max_tokens // page, max_num_seqs=4)
+        runner.mixed_graph_after = 0 if captured else 10 ** 9
+        for what, steps in (("changing portions", plans.changing_portions(requests)),
+                            ("mixed", plans.mixed(requests, max_tokens, page, seed=5)),
+                            ("serving", [{"entries": [dict(e, want=e["want"][-1:]) for e in s["entries"]], "end": s["end"]}
+                                         for s in plans.mixed(requests, max_tokens, page, seed=6)])):
+            outs = run_plan(runner, steps)
+            rows = plans.collect(steps, outs)
+            if what != "serving":
+                compare(rows, want, dtype, f"{name} {dtype} {what} captured={captured}")
+            results[(what, captured)] = rows
+            assert runner.cache.num_free_pages() == max_tokens // page
+        graphs = [k for k, g in runner._mixed_graphs.items() if isinstance(g, MixedGraph)]
+        assert bool(graphs) == captured
+        if captured:  # both kinds were used: logits for every token (a replayed trace) and one per request (serving)
+            assert {k[2] for k in graphs} == {True, False}, graphs
+    for what in ("changing portions", "mixed", "serving"):
+        for rid in results[(what, True)]:
+            a, b = np.stack(results[(what, False)][rid]), np.stack(results[(what, True)][rid])
+            assert np.array_equal(a, b), (what, rid, np.abs(a - b).max())
