@@ -21,7 +21,9 @@
 // consumers.
 //
 // Keys past the request's end, before its window, or on a block without a page are masked; so that masked
-// values are finite, a block without a page is fetched from the slice's first page instead.
+// values are finite, a block without a page is fetched from the slice's first page instead (the request's own
+// data), and the value rows behind the newest token in its page, which still hold what the page's last owner
+// left, are cleared in shared memory before they are used.
 // With `fused` the kernel rotates its queries and the newest key itself and writes the newest key and value to
 // their page (see attn_decode_mma); all tiles can then be fetched before the kernels before this one have
 // finished, since the one row that is not in its page yet is put into the tile from the projection output.
@@ -294,6 +296,19 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
                         const int col = (c % (D / 8)) * 8;
                         if (c < D / 8) *reinterpret_cast<uint4*>(const_cast<bf16*>(tile_at<D, true>(Ks, prow, col))) = *reinterpret_cast<const uint4*>(newest_k + col);
                         else *reinterpret_cast<uint4*>(const_cast<bf16*>(tile_at<D, true>(Vs, prow, col))) = *reinterpret_cast<const uint4*>(newest_v + col);
+                    }
+                    __syncwarp();
+                }
+                if (ok && kt == kt_last && pos >= first_key && pos < first_key + 31) {
+                    // The rows behind the newest token hold whatever the page's last owner left there (and, for blocks
+                    // without a page, a copy of the slice's first page, which may be that same page).  Their scores
+                    // are masked, but their values still meet a weight of zero in P V, and 0 x inf is not 0:
+                    // nothing of another request may reach this one, so those value rows are cleared.
+                    const int prow = pos - kt_last * MMA_BN;
+                    const int page_end = key_off + 31;  // the end of this warp's half of the tile
+                    for (int c = lane; c < (page_end - prow) * (D / 8); c += 32) {
+                        const int row = prow + 1 + c / (D / 8), col = (c % (D / 8)) * 8;
+                        *reinterpret_cast<uint4*>(const_cast<bf16*>(tile_at<D, true>(Vs, row, col))) = make_uint4(0u, 0u, 0u, 0u);
                     }
                     __syncwarp();
                 }

@@ -332,6 +332,19 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int st = j & 1;
             ok = mbar_wait(&v_full[st], (j >> 1) & 1, gave_up);
+            if (ok && (t_lo + j) * FA_BN + FA_BN > seq_len) {
+                // The request ends inside this tile.  Rows behind its last token lie in a page that may still hold
+                // what the page's last owner left; their weights are zero, but 0 x inf is not 0, and nothing of
+                // another request may reach this one: clear those value rows (whole 128-byte rows, so the swizzle
+                // does not matter) and make the writes visible to the tensor core's reads.
+                const int first = seq_len - (t_lo + j) * FA_BN;  // 1..63
+                for (int c = lane; c < (FA_BN - first) * HALVES * 8; c += 32) {
+                    const int row = first + c / (HALVES * 8), rest = c % (HALVES * 8);
+                    *reinterpret_cast<uint4*>(Vs + st * KV_BYTES + (rest / 8) * HALF_KV + row * 128 + (rest % 8) * 16) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+            }
             ok = __all_sync(0xffffffffu, ok && mbar_wait(&p_ready[st], (j >> 1) & 1, gave_up));
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

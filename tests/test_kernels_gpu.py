@@ -527,3 +527,56 @@ def test_the_edge_of_a_window(dtype):
             req, r0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(ql * 2, 64))
             ops().paged_attention_prefill(q.view(3, -1), n_q * d, out, kv, table, req, r0, q_start, seq_lens, n_q, n_kv, d, 1.0, window)
             assert (out[0].float().min() > 4.9) == seen and rel_err(out.view_as(ref).cpu(), ref) < 1e-2
+
+
+@pytest.mark.parametrize("n_q, n_kv, d, page", [(28, 4, 128, 16), (6, 2, 64, 32), (4, 2, 32, 8)])
+def test_what_a_pages_last_owner_left_behind_reaches_nobody(n_q, n_kv, d, page):
+    """Pages are not cleared when they change hands: behind a request's newest token its last page still holds the
+    keys and values of whoever had it before, here infinities and NaN.  Their scores are masked, and their values
+    must not get into the result either (0 x inf): every attention kernel gives what it gives with clean pages."""
+    from slipstream_b200.engine.context import query_tiles_host
+    lens, q_lens = [70, 5, 130, 33, 1], [70, 5, 17, 1, 1]
+    q, kv, table, q_start, seq_lens = make_attention_case(torch.bfloat16, lens, q_lens, n_q, n_kv, d, page, seed=3)
+    scale = d ** -0.5
+    ref = attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, scale, 0)
+    dirty = kv.clone()
+    for r, n in enumerate(lens):
+        if n % page:
+            last = int(table[r, (n - 1) // page])
+            dirty[last, :, :, n % page:] = float("inf")
+            dirty[last, 1, :, n % page:, ::2] = float("nan")
+    qf = q.view(q.shape[0], -1)
+    ql = np.asarray(q_lens, dtype=np.int32)
+
+    def check(out, what):
+        assert torch.isfinite(out).all(), what
+        assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2, what
+
+    out = torch.full((q.shape[0], n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    req, q0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(ql, 16))
+    ops().paged_attention_simt(qf, n_q * d, out, dirty, table, req, q0, q_start, seq_lens, n_q, n_kv, d, scale, 0)
+    check(out, "simt")
+    out.fill_(float("nan"))
+    req, r0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(ql * (n_q // n_kv), 64))
+    ops().paged_attention_prefill(qf, n_q * d, out, dirty, table, req, r0, q_start, seq_lens, n_q, n_kv, d, scale, 0)
+    check(out, "mma.sync prefill")
+    if ops().tcgen05_attention_fits(d, n_q, n_kv, page, 0):
+        req, t0 = (torch.from_numpy(a).to(DEV) for a in query_tiles_host(ql, 128 // (n_q // n_kv)))
+        for parts in (1, 2):
+            out.fill_(float("nan"))
+            ops().paged_attention_prefill_tcgen05(qf, n_q * d, out, dirty, table, req, t0, q_start, seq_lens, n_q, n_kv, d,
+                                                  scale, parts)
+            check(out, f"tcgen05 prefill, {parts} parts")
+    # decode: every request brings its last token only
+    last_rows = (q_start[1:] - 1).long()
+    qd = qf[last_rows].contiguous()
+    refd = ref.view(q.shape[0], -1)[last_rows.cpu()]
+    starts = torch.arange(len(lens) + 1, dtype=torch.int32, device=DEV)
+    for tma in [False] + ([True] if ops().tcgen05_attention_fits(d, n_q, n_kv, page, 0) else []):
+        for slices in (1, 2, 8):
+            outd = torch.full((len(lens), n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+            ops().paged_attention_decode(qd, n_q * d, outd, dirty, table, starts, seq_lens, len(lens), n_q, n_kv, d, scale, 0,
+                                         n_slices=slices, tma=tma)
+            assert torch.isfinite(outd).all(), (tma, slices)
+            assert rel_err(outd.cpu(), refd) < 1e-2, (tma, slices)
+    ops().check_errors(torch.device(DEV))
