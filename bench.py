@@ -187,20 +187,27 @@ def kernel_fractions(engine, batch: int, ctx_tokens: int, prefill_tokens: int, p
     def rand(rows: int, cols: int) -> torch.Tensor:
         return (torch.randn(rows, cols, generator=gen, device=dev) * 0.5).to(torch.bfloat16)
 
-    def sweep(run) -> float:
-        """Median microseconds per launch of ``run(layer)`` over all layers."""
-        for layer in range(len(blocks)):
+    def sweep(run, layers: int | None = None) -> float:
+        """Median microseconds per launch of ``run(layer)`` over ``layers`` layers (default: all).  The tensor-core
+        kernels are timed as a burst, like the peak they are compared with: sweeps of a few launches, so that the
+        GPU does not reach its power cap (a 2,048-token down projection takes 199 us in a burst and 238 us in
+        the middle of thousands of launches)."""
+        n = min(layers or len(blocks), len(blocks))
+        torch.cuda.synchronize()
+        if layers is not None:
+            time.sleep(0.2)  # whatever ran before may have left the GPU at its power cap: let the clocks come back
+        for layer in range(n):
             run(layer)
         times = []
         for _ in range(5):
             torch.cuda.synchronize()
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
-            for layer in range(len(blocks)):
+            for layer in range(n):
                 run(layer)
             stop.record()
             torch.cuda.synchronize()
-            times.append(start.elapsed_time(stop) * 1e3 / len(blocks))
+            times.append(start.elapsed_time(stop) * 1e3 / n)
         return sorted(times)[len(times) // 2]
 
     h, qkv_w = c.hidden_size, (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim
@@ -225,7 +232,7 @@ def kernel_fractions(engine, batch: int, ctx_tokens: int, prefill_tokens: int, p
             "down": (lambda i: ops.linear(x_i, blocks[i].feed_forward.down, None), inter, h),
         }
         for name, (run, k, n) in shapes.items():
-            us = sweep(run)
+            us = sweep(run, None if tag == "decode" else 8)
             if tag == "decode":
                 hbm(f"decode_{name}", us, 2.0 * k * n + 2.0 * tokens * (k + n))
             else:
@@ -268,7 +275,7 @@ def kernel_fractions(engine, batch: int, ctx_tokens: int, prefill_tokens: int, p
         q_start_p = torch.tensor([0, T], dtype=torch.int32, device=dev)
         lens_p = torch.tensor([T], dtype=torch.int32, device=dev)
         us = sweep(lambda i: ops.paged_attention_prefill_tcgen05(qkv_p, qkv_p.shape[1], att_p, kv[i], table_p, req, tok0,
-                                                                 q_start_p, lens_p, n_q, n_kv, d, d ** -0.5, 1))
+                                                                 q_start_p, lens_p, n_q, n_kv, d, d ** -0.5, 1), 8)
         tensor("prefill_attention", us, 4.0 * n_q * d * (T * (T + 1) // 2))
     return out
 
