@@ -280,6 +280,72 @@ def kernel_fractions(engine, batch: int, ctx_tokens: int, prefill_tokens: int, p
     return out
 
 
+def kernel_tables(which: str) -> int:
+    """``--only gemm``: this package's tcgen05 products against the library product at prompt-portion sizes
+    (microseconds a launch, CUDA events, weights rotated so that they come from memory).  ``--only attention``: the
+    tcgen05 prefill attention at several (queries, keys), with the number of key parts the engine would choose."""
+    import numpy as np
+    import torch
+
+    from slipstream_b200 import ops
+    from slipstream_b200.engine.context import query_tiles_longest_first_host
+
+    dev = torch.device("cuda:0")
+
+    def timed(fn, n: int = 16) -> float:
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(n):
+            fn(i)
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) * 1e3 / n
+
+    if which == "gemm":
+        shapes = (("7b q/k/v", 4608, 3584), ("7b o", 3584, 3584), ("7b down", 3584, 18944), ("7b gate/up", 37888, 3584),
+                  ("0.5b q/k/v", 1152, 896), ("0.5b gate/up", 9728, 896), ("0.5b down", 896, 4864),
+                  ("14b down", 5120, 13824), ("14b q/k/v", 7168, 5120))
+        for name, features, k in shapes:
+            copies = max(2, min(8, int(300e6 // (features * k * 2))))
+            ws = [(torch.randn(features, k, device=dev) * 0.02).bfloat16() for _ in range(copies)]
+            for tokens in (128, 256, 512, 1024, 2048, 4096):
+                x = torch.randn(tokens, k, device=dev).bfloat16()
+                row = {"library": timed(lambda i: torch.mm(x, ws[i % copies].t()))}
+                for width in (64, 128, 256):
+                    if width <= features and tokens <= 1024:
+                        row[f"one-SM {width}"] = timed(lambda i: ops.gemm_tcgen05(x, ws[i % copies], plan=(False, width, 1)))
+                row["two-SM"] = timed(lambda i: ops.gemm_tcgen05_many(x, ws[i % copies]))
+                print(json.dumps({"shape": name, "features": features, "k": k, "tokens": tokens,
+                                  **{key: round(v, 1) for key, v in row.items()}}), flush=True)
+        ops.check_errors(dev)
+        return 0
+
+    n_q, n_kv, d, page = SHAPE_7B["num_attention_heads"], SHAPE_7B["num_key_value_heads"], SHAPE_7B["head_dim"], 16
+    tile = 128 // (n_q // n_kv)
+    for queries, keys in ((2048, 2048), (2048, 8192), (8192, 8192), (1024, 1024), (512, 4096), (64, 4096)):
+        pages = keys // page + 4
+        copies = max(2, min(16, int(300e6 // (pages * 2 * n_kv * page * d * 2))))
+        kvs = [torch.randn(pages, 2, n_kv, page, d, device=dev).bfloat16() for _ in range(copies)]
+        qkv = torch.randn(queries, (n_q + 2 * n_kv) * d, device=dev).bfloat16()
+        out = torch.empty(queries, n_q * d, device=dev, dtype=torch.bfloat16)
+        q_lens, seq_lens = np.asarray([queries], dtype=np.int32), np.asarray([keys], dtype=np.int32)
+        req, tok0 = (torch.from_numpy(a).to(dev) for a in query_tiles_longest_first_host(q_lens, seq_lens, tile))
+        table = torch.arange(pages, dtype=torch.int32, device=dev).view(1, -1)
+        q_start = torch.tensor([0, queries], dtype=torch.int32, device=dev)
+        lens = torch.tensor([keys], dtype=torch.int32, device=dev)
+        parts = ops.prefill_key_parts(q_lens, seq_lens, tile, n_kv)
+        us = timed(lambda i: ops.paged_attention_prefill_tcgen05(qkv, qkv.shape[1], out, kvs[i % copies], table, req, tok0,
+                                                                 q_start, lens, n_q, n_kv, d, d ** -0.5, parts), 20)
+        flops = 4.0 * n_q * d * sum(min(keys, keys - queries + t + 1) for t in range(queries))
+        print(json.dumps({"queries": queries, "keys": keys, "key_parts": parts, "us": round(us, 1),
+                          "tflops": round(flops / us / 1e6, 1)}), flush=True)
+    ops.check_errors(dev)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -298,8 +364,9 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
                     help="run another measured workload end to end through the scheduler instead")
-    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
-                    help="run just this part and print a short line (for profiling)")
+    ap.add_argument("--only", choices=["decode", "prefill", "gemm", "attention"], default=None,
+                    help="run just this part and print a short line (for profiling); gemm / attention: tables of "
+                         "single kernels at several sizes")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU only (this engine uses a single device); got --gpus {args.gpus}")
@@ -308,6 +375,8 @@ def main() -> int:
         return reference_arm(args)
     if args.workload:
         return run_workload(args.workload, args)
+    if args.only in ("gemm", "attention"):
+        return kernel_tables(args.only)
     if args.warmup < 3:
         args.warmup = 3
 
