@@ -101,10 +101,11 @@ class ModelRunner:
                 seen.add(part.capture_group())
                 self.variant_parts.append(part)
         self._graphs: dict[tuple, DecodeGraph] = {}  # (batch bucket, the parts' variants)
-        # steps with prompt portions: (token bucket, request bucket, logits per token?) -> graph, or the number of
-        # times the bucket has come up so far (a graph is captured at the third)
+        # steps with prompt portions: (token bucket, request bucket, logits per token?, variants) -> graph, or the
+        # number of times the bucket has come up so far.  A capture costs tens to hundreds of milliseconds (0.25 s
+        # for a 48-layer model), so a bucket is captured only when it keeps coming up: at its seventh step.
         self._mixed_graphs: dict[tuple, "MixedGraph | int"] = {}
-        self.mixed_graph_after = 2  # steps of a bucket that run eagerly before it is captured
+        self.mixed_graph_after = 6  # steps of a bucket that run kernel by kernel before it is captured
         self.max_mixed_graphs = 24
 
     # ------------------------------------------------------------------ requests
