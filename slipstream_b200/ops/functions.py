@@ -798,8 +798,9 @@ def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor 
     return out
 
 
-# From this many tokens a bfloat16 projection whose weight is at least MANY_WIDTH on both sides runs the persistent
-# two-SM kernel.  Against the library (us, ours / library) at 2,048 tokens: 7B sizes q/k/v 49.6 / 45.1, o 41.6-47.7 /
+# From this many tokens a bfloat16 projection whose 256 x 256 output tiles make at least a round and a half of the
+# pairs of SMs, and whose K is deep enough for a tile's first loads and its epilogue to be a small part of it
+# (``many_tokens_fits``), runs the persistent two-SM kernel.  Against the library (us, ours / library) at 2,048 tokens: 7B sizes q/k/v 49.6 / 45.1, o 41.6-47.7 /
 # 45.4-52.8, down 191.9-198.2 / 191.6-208.7; 14B sizes 109.4 / 114.6, 79.7 / 77.0, 200.3 / 207.2; a whole 2,048-token
 # prefill of the 7B shape takes 22.1 to 25.5 ms either way (the GPU sits at its power cap), and its first call 35
 # ms instead of 160.  With fewer tokens or smaller weights there are too few 256-row tiles for the pairs of SMs and
@@ -807,7 +808,19 @@ def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor 
 # of tokens by up to 50 %, 512 tokens and below by 1.3 to 2 times.  (Cutting K into parts inside this kernel,
 # with the parts' sums meeting in scratch memory, was tried for those cases and did not beat narrower tiles.)
 MANY_TOKENS = 2048
-MANY_WIDTH = 3584
+MANY_K_STEPS = 32  # 64-wide K steps a tile must have (2,048 columns)
+
+
+def many_tokens_fits(tokens: int, features: int, k: int, sms: int | None = None) -> bool:
+    """Where the persistent two-SM tcgen05 kernel is the product of a prompt portion (see the measurements above):
+    at the 7B and 14B layer sizes from 2,048 tokens (112 to 224 tiles on 74 pairs), not at the 0.5B and 1.5B sizes
+    (40 to 48 tiles, K of 896 and 1,536)."""
+    if tokens < MANY_TOKENS or k % 8 != 0 or k < 64 * MANY_K_STEPS:
+        return False
+    tiles = ((tokens + 255) // 256) * ((features + 255) // 256)
+    return 4 * tiles >= 3 * (sms or sm_count())  # a round and a half of the sms / 2 pairs
+
+
 SMALL_BATCH = 64  # up to this many tokens a projection may stream its weights through the tcgen05 kernel
 # ... when its 128-row weight tiles are at least as many as the SMs (no K slices needed)
 CLUSTER_BATCH = 16  # ... or, up to this many tokens, whatever its size (K slices added inside a cluster)
@@ -833,7 +846,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     float32 runs the CUDA-core kernel (no reduced-precision matrix mode).  bfloat16 with few tokens (decode
     steps) and a large weight runs the hand-written tcgen05 kernel, which streams the weights once and
     overlaps its first fetches with the kernel before it; from ``MANY_TOKENS`` tokens (prompt portions) and with
-    a weight of ``MANY_WIDTH`` or more on both sides the persistent two-SM tcgen05 kernel; everything else runs the
+    enough output tiles (``many_tokens_fits``) the persistent two-SM tcgen05 kernel; everything else runs the
     library matrix product, as the reference's
     nn.Linear does (slipstream/models/layers/attention.py:132-135)."""
     if x.dtype == torch.float32:
@@ -841,7 +854,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     sms = sm_count(x.device)
     if streams_weights(x.shape[0], weight.shape[0], x.shape[1], sms):
         return gemm_tcgen05(x, weight, bias, out_dtype)
-    if x.shape[0] >= MANY_TOKENS and min(weight.shape) >= MANY_WIDTH and x.shape[1] % 8 == 0:
+    if many_tokens_fits(x.shape[0], weight.shape[0], x.shape[1], sms):
         return gemm_tcgen05_many(x, weight, bias, out_dtype)
     if out_dtype is None or out_dtype == x.dtype:
         if bias is not None:
@@ -885,5 +898,5 @@ def set_programmatic_launch(enabled: bool) -> None:
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "prepare_decode", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "sm_count", "linear", "check_errors", "raise_for_status", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "prepare_decode", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_fits", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "sm_count", "linear", "check_errors", "raise_for_status", "error_word", "ops_library",
            "attention_library"]

@@ -48,3 +48,8 @@ def test_streaming_product_plan_and_routing():
     assert F.streams_weights(64, 37888, 3584, SMS) and F.streams_weights(64, 3584, 18944, SMS) and not F.streams_weights(64, 3584, 3584, SMS)
     assert not F.streams_weights(65, 37888, 3584, SMS) and not F.streams_weights(8, 3584, 3580, SMS)
     assert F.many_tokens_swiglu_fits(2048, 37888, SMS) and not F.many_tokens_swiglu_fits(512, 37888, SMS)
+    # prompt portions: the two-SM kernel from 2,048 tokens at the 7B and 14B layer sizes, the library elsewhere
+    for features, k in ((4608, 3584), (3584, 3584), (3584, 18944), (7168, 5120), (5120, 13824)):
+        assert F.many_tokens_fits(2048, features, k, SMS) and not F.many_tokens_fits(2047, features, k, SMS)
+    for features, k in ((1152, 896), (896, 4864), (2048, 1536), (3584, 3580)):
+        assert not F.many_tokens_fits(4096, features, k, SMS)
