@@ -162,14 +162,14 @@ def test_pre_norm_block(dtype):
                          RMSNorm(f"{prefix}.post_attention_layernorm", hidden, eps))
     dev, ref = {}, {}
     for k, child in enumerate(block.children()):
-        a, b = draw(child, dtype, seed=k)
-        dev.update(a); ref.update(b)
+        a, b = draw(child, dtype, seed=k, scale=0.5)  # scores of order one: with larger ones bfloat16's rounding
+        dev.update(a); ref.update(b)                  # of queries and keys alone moves the softmax by percents
     for child in block.children():
         child.bind(dev, runtime(dtype))
     layouts = [GroupLayout(block.mixer.cache_spec(), 1)]
     cache = CacheManager(layouts, 8, 4, 2, 64)
     store = PagedStore(layouts, dtype, DEV, [[]], 2)
-    x = torch.randn(n, hidden)
+    x = torch.randn(n, hidden, generator=torch.Generator().manual_seed(5))
     s = {"n_q": heads, "n_kv": kv_heads, "head_dim": d, "theta": theta, "eps": eps}
     want = plain.decoder_layer(x.double(), torch.arange(n), ref, 0, s)
     ctx = single_request_ctx(cache, "r", n)
