@@ -11,7 +11,6 @@ gathered pages, one forward for the decodes, one forward per prompt portion).
 
 from __future__ import annotations
 
-import json
 import os
 import sys
 import tempfile

@@ -1,7 +1,5 @@
 """Shared fixtures: tiny Qwen2.5 configurations that differ in every size and option,
 model folders with random weights made in a temporary folder, and the ``gpu`` marker."""
-import json
-import os
 import sys
 from pathlib import Path
 

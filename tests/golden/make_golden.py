@@ -9,7 +9,6 @@ Run once where the reference checkout is readable:
 The folder's tensors are stored in the .npz too, so the comparison in
 tests/test_plain_reference.py needs neither the reference nor the random generator.
 """
-import json
 import sys
 import tempfile
 from pathlib import Path

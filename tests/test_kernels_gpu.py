@@ -1,7 +1,6 @@
 """Each CUDA kernel alone against a plain float32/float64 PyTorch restatement of the same op, at sizes
 other than the engine's test models (widths and vocabularies that are no power of two, head sizes in
 steps of 16, odd group sizes, pages of odd size)."""
-import math
 
 import numpy as np
 import pytest

@@ -1,6 +1,5 @@
 """Each part of the model alone, built with sizes of its own and random tensors, against the plain
 functions of tests/plain_qwen2.py."""
-import numpy as np
 import pytest
 import torch
 

@@ -1,6 +1,5 @@
 """The plain implementation against the reference's own model code (stored outputs made by
 tests/golden/make_golden.py), and against itself where parts can be checked alone."""
-import io
 import json
 import math
 from pathlib import Path

@@ -7,9 +7,7 @@ import tempfile
 
 import numpy as np
 import pytest
-import torch
 
-import plain_qwen2 as plain
 import replay_plans as plans
 from conftest import random_tokens, sharpen
 from test_replay_gpu import TOLERANCE, oracle, run_plan

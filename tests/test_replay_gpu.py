@@ -5,7 +5,6 @@ implementation."""
 import json
 import subprocess
 import sys
-from pathlib import Path
 
 import numpy as np
 import pytest

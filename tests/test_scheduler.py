@@ -1,5 +1,4 @@
 """The scheduler's decisions, on the host, against a cache manager without a device."""
-import pytest
 
 from slipstream_b200.cache import CacheManager, GroupLayout
 from slipstream_b200.config.engine_config import SchedulerConfig

@@ -2,11 +2,9 @@
 a mixer with fixed-size state of its own (a running mean), an attention layer with a window, a block
 that the execution order names twice, and an entry that reads another entry's cache.  It is checked
 against a plain whole-sequence restatement written in this file, under several ways of cutting."""
-import json
 from dataclasses import asdict, dataclass
 from typing import ClassVar
 
-import numpy as np
 import pytest
 import torch
 
