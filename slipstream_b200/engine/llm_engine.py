@@ -2,8 +2,8 @@
 
     engine = LLMEngine(EngineConfig.for_model(folder))
     tokens = engine.generate(Request("r0", None, [1, 2, 3], SamplingParams(max_tokens=8), 0.0))
-    outs   = engine.generate_batch([...])         # continuous batching
-    for t in engine.stream(request): ...
+    outs   = engine.generate_batch([...])         # continuous batching; inject="arrival" releases each
+    for t in engine.stream(request): ...          # request when the wall clock reaches its arrival_ts
 
 (slipstream/engine/llm_engine.py:66-127).  ``generate`` and ``stream`` are
 ``generate_batch`` with one request.  Every step is ONE call of the step function
@@ -87,6 +87,12 @@ class InFlight:
     ready: torch.cuda.Event
 
 
+def absolute_arrival(ts: float, now: float) -> float:
+    """An arrival time on the wall clock: small values are offsets from ``now``, values from 1e9 are wall-clock
+    seconds already (slipstream/engine/llm_engine.py:38-42)."""
+    return ts if ts >= 1_000_000_000.0 else now + ts
+
+
 def capped_new_tokens(prompt_len: int, max_tokens: int, max_model_len: int) -> int:
     """New tokens that fit under the context window (slipstream/engine/llm_engine.py:56-63)."""
     if max_tokens < 1:
@@ -120,6 +126,13 @@ class LLMEngine:
 
             self.tokenizer = Tokenizer.from_file(str(folder / "tokenizer.json"))
         self.stats = StepStats()
+        # wall-clock latencies of the last generate_batch, in seconds: time to the first token of every request
+        # (from enqueue, or from its arrival with inject="arrival") and the gaps between a request's tokens, as
+        # the host comes to know them (slipstream/engine/llm_engine.py:89-90,577-598)
+        self.last_ttft_s: list[float] = []
+        self.last_itl_s: list[float] = []
+        self._started_at: dict[int, float] = {}
+        self._last_emit: dict[int, float] = {}
         self._requests_seen = 0
         self._inflight: InFlight | None = None
         self._zombies: list[Sequence] = []  # stopped while their next token was already being computed
@@ -137,6 +150,7 @@ class LLMEngine:
     def stream(self, request: Request) -> Iterator[int]:
         """Token iterator with the same tokens as ``generate``."""
         seq = self._make_sequence(request)
+        self._started_at[seq.seq_id] = time.perf_counter()
         self.scheduler.add_seq(seq)
         emitted = 0
         while self.scheduler.has_work():
@@ -165,22 +179,56 @@ class LLMEngine:
         """One engine step: schedule, one step-function call, sample, finish.  False when idle."""
         return self._step()
 
-    def generate_batch(self, requests: list[Request]) -> list[list[int]]:
-        """Continuous batching of several requests (slipstream/engine/llm_engine.py:107-119)."""
+    def generate_batch(self, requests: list[Request], *, inject: str = "all") -> list[list[int]]:
+        """Continuous batching of several requests (slipstream/engine/llm_engine.py:107-119).  ``inject="all"``
+        queues every request at once; ``inject="arrival"`` releases a request when the wall clock reaches its
+        ``arrival_ts`` (an offset from the call, or wall-clock seconds) and sleeps while nothing is due."""
+        if inject not in ("all", "arrival"):
+            raise ValueError("inject must be 'all' or 'arrival'")
         seqs = [self._make_sequence(r) for r in requests]
+        wall, perf = time.time(), time.perf_counter()
+        self.last_ttft_s.clear()
+        self.last_itl_s.clear()
+        self._started_at.clear()
+        self._last_emit.clear()
+        pending: list[Sequence] = []
         for seq in seqs:
-            self.scheduler.add_seq(seq)
-        self.run_until_done(seqs)
-        return [list(s.output_token_ids) for s in seqs]
+            if inject == "all":
+                self._started_at[seq.seq_id] = perf
+                self.scheduler.add_seq(seq)
+            else:
+                seq.arrival_ts = absolute_arrival(seq.arrival_ts, wall)
+                self._started_at[seq.seq_id] = perf + (seq.arrival_ts - wall)
+                pending.append(seq)
+        pending.sort(key=lambda q: (q.arrival_ts, q.seq_id))
+        self.run_until_done(seqs, pending)
+        return [list(q.output_token_ids) for q in seqs]
 
-    def run_until_done(self, seqs: list[Sequence]) -> None:
+    def run_until_done(self, seqs: list[Sequence], pending: list[Sequence] | None = None) -> None:
+        """Step until the scheduler is idle.  ``pending``: sequences not yet queued, sorted by their wall-clock
+        arrival; each is queued when its time has come."""
+        pending = pending if pending is not None else []
         # the reference's bound on replay storms (slipstream/engine/llm_engine.py:423-429)
-        limit = 1 + 8 * sum(s.num_prompt_tokens + s.max_new_tokens for s in seqs)
+        limit = 1 + 8 * sum(q.num_prompt_tokens + q.max_new_tokens for q in seqs)
         steps = 0
-        while self.scheduler.has_work() and steps < limit:
+        while (self.scheduler.has_work() or pending) and steps < limit:
+            if pending:
+                now = time.time()
+                due = 0
+                while due < len(pending) and pending[due].arrival_ts <= now:
+                    self.scheduler.add_seq(pending[due])
+                    due += 1
+                del pending[:due]
+                if not self.scheduler.has_work():
+                    self.drain()
+                    time.sleep(max(0.0, min(pending[0].arrival_ts - time.time(), 0.02)))
+                    continue
             steps += 1
             if not self._step():
-                break
+                if not pending:
+                    break
+                self.drain()
+                time.sleep(max(0.0, min(pending[0].arrival_ts - time.time(), 0.02)))
         self.drain()
         for seq in seqs:
             if not seq.is_finished:
@@ -214,6 +262,16 @@ class LLMEngine:
                         arrival_ts=request.arrival_ts, request_id=request.request_id, max_new_tokens=max_new,
                         seed=seed)
 
+    def _mark_emit(self, seq: Sequence, now: float) -> None:
+        """The host has just learnt a token of ``seq``: its first one gives the time to first token, every other
+        one a gap between tokens (slipstream/engine/llm_engine.py:577-598)."""
+        prev = self._last_emit.get(seq.seq_id)
+        if prev is None:
+            self.last_ttft_s.append(max(0.0, now - self._started_at.get(seq.seq_id, now)))
+        else:
+            self.last_itl_s.append(now - prev)
+        self._last_emit[seq.seq_id] = now
+
     def _is_stop(self, seq: Sequence, token: int) -> bool:
         """slipstream/engine/llm_engine.py:223-234; the stop token stays in the output."""
         params = seq.sampling_params
@@ -233,12 +291,14 @@ class LLMEngine:
         flight.ready.synchronize()
         tokens = flight.tokens_host.tolist()
         self._check_status(tokens.pop(), flight.seqs)
+        now = time.perf_counter()
         for seq, at, token in zip(flight.seqs, flight.where, tokens):
             if seq in self._zombies:  # stopped one token earlier; this token was computed for nothing
                 self._zombies.remove(seq)
                 self.scheduler.finish(seq)
                 continue
             seq.output_token_ids[at] = int(token)
+            self._mark_emit(seq, now)
             ahead = at + 1 < len(seq.output_token_ids)  # its next token is already being computed
             if self._is_stop(seq, int(token)):
                 seq.status = SequenceStatus.FINISHED_STOPPED
@@ -372,9 +432,11 @@ class LLMEngine:
             self._check_status(tokens.pop(), [i.seq for i in plan.scheduled])
         for item in plan.scheduled:
             item.seq.num_computed_tokens += item.take
+        now = time.perf_counter()
         for item, token in zip(sampling, tokens):
             seq = item.seq
             seq.output_token_ids.append(int(token))
+            self._mark_emit(seq, now)
             if self._is_stop(seq, int(token)):
                 seq.status = SequenceStatus.FINISHED_STOPPED
             elif seq.num_output_tokens >= seq.max_new_tokens or seq.num_tokens >= self.max_model_len:
@@ -423,6 +485,7 @@ class LLM:
         engine = self.engine
         seqs = [engine._make_sequence(r) for r in requests]
         for seq in seqs:
+            engine._started_at[seq.seq_id] = time.perf_counter()
             engine.scheduler.add_seq(seq)
         engine.run_until_done(seqs)
         outs = []

@@ -84,6 +84,35 @@ def test_too_few_pages_preempts_and_still_generates_the_same_tokens(model_folder
     assert outs[0] == [] and outs[1] == want[1]
 
 
+def test_requests_released_at_their_arrival_times_and_the_latency_records(model_folders):
+    """``generate_batch(..., inject="arrival")`` queues a request when the wall clock reaches its arrival (an offset
+    from the call), sleeping while nothing is due: same tokens as the closed burst, later.  Both ways leave the
+    time to first token of every request and the gaps between its tokens (slipstream/engine/llm_engine.py:107-119,
+    577-598)."""
+    import time
+    from slipstream_b200 import SamplingParams
+    from slipstream_b200.engine.llm_engine import Request, absolute_arrival
+    folder, config, page = model_folders["A"]
+    engine = make_engine(folder, page)
+    prompts = [random_tokens(config.vocab_size, n, 70 + n) for n in (9, 21, 4)]
+    params = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    arrivals = (0.0, 0.15, 0.06)
+    batch = lambda: [Request(f"r{i}", None, p, params, t) for i, (p, t) in enumerate(zip(prompts, arrivals))]
+    burst = engine.generate_batch(batch())
+    assert len(engine.last_ttft_s) == 3 and len(engine.last_itl_s) == 3 * 5
+    assert all(t >= 0 for t in engine.last_ttft_s + engine.last_itl_s)
+    t0 = time.perf_counter()
+    timed = engine.generate_batch(batch(), inject="arrival")
+    elapsed = time.perf_counter() - t0
+    assert timed == burst and elapsed >= 0.15
+    assert len(engine.last_ttft_s) == 3 and len(engine.last_itl_s) == 3 * 5
+    assert max(engine.last_ttft_s) < 0.15, "the clock of a request starts at its arrival, not at the call"
+    assert engine.runner.cache.min_free_pages() == 64 and not engine.scheduler.has_work()
+    with pytest.raises(ValueError, match="inject"):
+        engine.generate_batch(batch(), inject="sometimes")
+    assert absolute_arrival(2.5, 100.0) == 102.5 and absolute_arrival(1.7e9, 100.0) == 1.7e9
+
+
 def test_stop_rules(model_folders):
     from slipstream_b200 import SamplingParams
     from slipstream_b200.engine.llm_engine import LLM
