@@ -36,13 +36,16 @@ from .scheduler import ScheduledSeq, Scheduler, Sequence, SequenceStatus
 
 @dataclass
 class Request:
-    """slipstream/core/types.py:73-87 without the SLO fields."""
+    """slipstream/core/types.py:73-87.  The two latency targets are carried for callers that set them; the
+    first-come-first-served policy, the only one built, does not read them."""
 
     request_id: str
     prompt: str | None
     prompt_token_ids: list[int] | None
     sampling_params: SamplingParams = field(default_factory=SamplingParams)
     arrival_ts: float = 0.0
+    slo_ttft_ms: float = 2000.0
+    slo_tpot_ms: float = 100.0
 
     def __post_init__(self) -> None:
         if self.prompt is None and self.prompt_token_ids is None:
