@@ -87,3 +87,16 @@ def test_engine_config_validation():
                 lambda: SchedulerConfig(prefill_chunk_size=0), lambda: EngineConfig.for_model("x", dtype="float16")):
         with pytest.raises(ValueError):
             bad()
+    # a configuration written for the reference constructs (slipstream/core/config.py:60-134); what asks for a
+    # part that is not built is refused by name
+    from slipstream_b200 import ParallelConfig
+    config = EngineConfig.for_model("x", cache=CacheConfig(swap_space_bytes=1 << 30, enable_paging=True, num_cpu_blocks=None),
+                                    scheduler=SchedulerConfig(max_wait_ms=1e4, safety_factor=0.9, starvation_guard_ms=100.0),
+                                    parallel=ParallelConfig(tensor_parallel_size=1))
+    assert config.parallel.tensor_parallel_size == 1 and config.scheduler.policy == "fcfs"
+    for bad, word in ((lambda: CacheConfig(enable_prefix_caching=True), "prefix caching"),
+                      (lambda: CacheConfig(enable_paging=False), "unpaged"),
+                      (lambda: ParallelConfig(tensor_parallel_size=2), "one GPU"),
+                      (lambda: SchedulerConfig(safety_factor=0.0), "safety_factor")):
+        with pytest.raises(ValueError, match=word):
+            bad()
