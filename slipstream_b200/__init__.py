@@ -10,10 +10,10 @@ hand-written sm_100a CUDA kernels.
 
 __version__ = "0.1.0"
 
-from .config.engine_config import CacheConfig, EngineConfig, ModelOptions, ParallelConfig, SchedulerConfig
+from .config.engine_config import CacheConfig, EngineConfig, ModelConfig, ModelOptions, ParallelConfig, SchedulerConfig
 from .config.sampling_params import SamplingParams
 
-__all__ = ["CacheConfig", "EngineConfig", "ModelOptions", "ParallelConfig", "SchedulerConfig", "SamplingParams",
+__all__ = ["CacheConfig", "EngineConfig", "ModelConfig", "ModelOptions", "ParallelConfig", "SchedulerConfig", "SamplingParams",
            "LLM", "LLMEngine", "Request"]
 
 

@@ -35,6 +35,9 @@ class ModelOptions:
             raise ValueError(f"unknown load_format: {self.load_format}")
 
 
+ModelConfig = ModelOptions  # the reference's name for it (slipstream/core/config.py:25-57)
+
+
 @dataclass
 class CacheConfig:
     block_size: int = DEFAULT_BLOCK_SIZE
