@@ -709,11 +709,18 @@ extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int b
     g.C = C; g.bias = bias; g.partial = partial; g.counters = counters; g.err = err;
     g.M = M; g.N = N; g.K = K; g.ldc = ldc; g.slices = slices; g.swapped = swapped; g.out_f32 = out_f32;
     g.bias_f32 = bias_f32; g.swiglu = swiglu; g.cluster = cluster;
+    const bool deep = swapped && ((K + TC_BK - 1) / TC_BK + slices - 1) / slices >= 24;
     dim3 grid((N + bn - 1) / bn, (M + TC_BM - 1) / TC_BM, slices);
     if (!swapped) grid = dim3((M + TC_BM - 1) / TC_BM, (N + bn - 1) / bn, slices);
     switch (bn) {
-        case 16: return launch<16, 4>(ma, mb, g, grid, stream);  // three blocks fit on an SM (three stages: 2.91 ms a decode step instead of 2.83)
-        case 32: return launch<32, 4>(ma, mb, g, grid, stream);
+        // Swapped and many K steps per block (down, gate/up, the LM head: 37 to 56): a deeper ring, still two blocks
+        // an SM.  Such a product is bound by the bytes its blocks keep in flight: 224 blocks x 4 stages x 16 KB are
+        // 14 MB where the memory's rate times its latency asks for about 20 (down ran at 83 % of the copy
+        // bandwidth, gate/up with 296 blocks at 97 %).  A decode step of 8 requests: 2.79 ms instead of 2.84, of
+        // one request 2.69 instead of 2.76.  With few K steps per block (q/k/v, o: 7) the fourth block an SM can
+        // hold beside two of these matters more: six stages for every product took 2.96 ms.
+        case 16: return deep ? launch<16, 6>(ma, mb, g, grid, stream) : launch<16, 4>(ma, mb, g, grid, stream);
+        case 32: return launch<32, 4>(ma, mb, g, grid, stream);  // (five stages when deep: 3.27 ms instead of 3.24 at 32 requests)
         case 64: return launch<64, 4>(ma, mb, g, grid, stream);  // two blocks fit on an SM
         case 128: return launch<128, 6>(ma, mb, g, grid, stream);
         case 256: return launch<256, 4>(ma, mb, g, grid, stream);
