@@ -593,7 +593,7 @@ attn_decode_mma(const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__
             for (int sl = 0; sl < 8; ++sl) acc += p[sl] * (lse[sl] * inv);
             out[(int64_t)row_q * out_stride + (int64_t)(kvh * G + g0 + row) * D + d] = __float2bfloat16_rn(acc);
         }
-        cluster_sync_all();  // nobody leaves while its shared memory is still being read
+        cluster_sync_before_exit();  // nobody leaves while its shared memory is still being read
         return;
     }
 

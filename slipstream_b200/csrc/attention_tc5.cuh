@@ -535,7 +535,7 @@ attn_prefill_tc5(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 }
             }
         }
-        cluster_sync_all();  // nobody leaves while its shared memory is still being read
+        cluster_sync_before_exit();  // nobody leaves while its shared memory is still being read
     }
     if (*gave_up && threadIdx.x == 0) atomicOr(a.err, SS_ERR_WAIT_LIMIT);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

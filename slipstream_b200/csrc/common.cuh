@@ -189,6 +189,15 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
 }
+// The barrier before a block of a cluster leaves: every block has finished READING the others' shared memory (its
+// loads have returned: their values have been used).  Nothing written is handed over here, so the arrival need not
+// wait for the thread's stores to global memory to be acknowledged, which a releasing arrival does (about a
+// microsecond behind the output stores of a product's epilogue).
+__device__ __forceinline__ void cluster_sync_before_exit() {
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
+    asm volatile("barrier.cluster.wait;" ::: "memory");
+}
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));

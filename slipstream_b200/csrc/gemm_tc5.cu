@@ -399,7 +399,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 }
             }
         }
-        cluster_sync_all();  // nobody leaves while its shared memory is still being read
+        cluster_sync_before_exit();  // nobody leaves while its shared memory is still being read
     }
     if (*gave_up && threadIdx.x == 0) atomicOr(g.err, SS_ERR_WAIT_LIMIT);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
