@@ -202,6 +202,13 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_acc = *tmem_slot;
 
+    // the bias of the four features a lane of the epilogue warps adds up in the cluster's reduction: it does not
+    // depend on the kernels in front, so it is read before the wait for them, not behind the reduction
+    float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (warp >= 2 && g.cluster && g.bias && !g.swiglu && m0 + lane * 4 + 3 < g.M)
+        bias4 = make_float4(bias_at(g, m0 + lane * 4), bias_at(g, m0 + lane * 4 + 1), bias_at(g, m0 + lane * 4 + 2),
+                            bias_at(g, m0 + lane * 4 + 3));
+
     if (warp == 0 && lane == 0) {
         // ---- producer.  When the block runs swapped, A is the weight matrix: a constant, so its first
         // tiles are fetched before the kernels before this one have finished; B (activations) only after.
@@ -374,7 +381,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                     const int m = m0 + lane * 4, n = n0 + c;
                     if (g.swapped && !g.out_f32 && m + 3 < g.M && (g.ldc & 3) == 0) {
-                        if (g.bias) { acc.x += bias_at(g, m); acc.y += bias_at(g, m + 1); acc.z += bias_at(g, m + 2); acc.w += bias_at(g, m + 3); }
+                        acc.x += bias4.x; acc.y += bias4.y; acc.z += bias4.z; acc.w += bias4.w;
                         const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
                         uint2 packed;
                         packed.x = *reinterpret_cast<const uint32_t*>(&lo);

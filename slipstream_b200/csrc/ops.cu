@@ -122,6 +122,19 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
                                    const void* __restrict__ weight, int w_f32, T* __restrict__ y,
                                    const int32_t* __restrict__ rows, int hidden, float eps) {
     pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one itself
+    // the norm's weights do not depend on the kernels in front: they are in registers by the time those are
+    // complete (read behind the reduction, they cost every norm of a decode step a trip to L2)
+    float wpre[2][4];
+    if (VEC == 4) {
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int j = (threadIdx.x + it * blockDim.x) * 4;
+            if (j < hidden) {
+                if (w_f32) Vec4<float>::load(reinterpret_cast<const float*>(weight) + j, wpre[it]);
+                else Vec4<T>::load(reinterpret_cast<const T*>(weight) + j, wpre[it]);
+            }
+        }
+    }
     pdl_wait();               // nothing below runs before the kernels before this one are complete
     __shared__ float scratch[33];
     const int64_t src = rows ? rows[blockIdx.x] : blockIdx.x;
@@ -155,11 +168,9 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
         for (int it = 0; it < 2; ++it) {
             const int j = (threadIdx.x + it * blockDim.x) * 4;
             if (j < hidden) {
-                float w[4], o[4];
-                if (w_f32) Vec4<float>::load(reinterpret_cast<const float*>(weight) + j, w);
-                else Vec4<T>::load(reinterpret_cast<const T*>(weight) + j, w);
+                float o[4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) o[e] = w[e] * to_float(from_float<T>(v[it][e] * rstd));
+                for (int e = 0; e < 4; ++e) o[e] = wpre[it][e] * to_float(from_float<T>(v[it][e] * rstd));
                 Vec4<T>::store(out + j, o);
             }
         }
