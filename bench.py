@@ -471,21 +471,36 @@ def main() -> int:
     # ---- prefill of one 2,048-token prompt in one step (median of five).  It is the one phase that runs at the
     # power cap: single runs of the same step vary between 21.4 and 24.8 ms with the power management's state
     T = 2048
-    for w in range(3):
+    # warm-up until the step of this shape has been captured as a graph (the runner does that once a shape has
+    # come up `mixed_graph_after` times), so that the timed steps are what a running engine repeats
+    for w in range(max(3, getattr(runner, "mixed_graph_after", 0) + 2)):
         runner.step([StepEntry(f"pw{w}", rng.integers(0, vocab, T).tolist(), [T - 1])])
         runner.release(f"pw{w}")
     torch.cuda.synchronize()
-    times = []
-    for w in range(5):
-        toks = rng.integers(0, vocab, T).tolist()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        runner.step([StepEntry(f"p{w}", toks, [T - 1])])
-        stop.record()
-        torch.cuda.synchronize()
-        times.append(start.elapsed_time(stop))
-        runner.release(f"p{w}")
+
+    def timed_prefill(tag: str, pause: float) -> list[float]:
+        out = []
+        for w in range(5):
+            toks = rng.integers(0, vocab, T).tolist()
+            if pause:
+                time.sleep(pause)
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            runner.step([StepEntry(f"{tag}{w}", toks, [T - 1])])
+            stop.record()
+            torch.cuda.synchronize()
+            out.append(start.elapsed_time(stop))
+            runner.release(f"{tag}{w}")
+        return out
+
+    # A step of 2,048 prompt tokens draws the full 1,000 W: back to back, the second or third step already runs at
+    # the clock the power cap sustains (1.3 to 1.5 GHz instead of 1.97).  Both figures are taken, each against the
+    # peak that was measured the same way: a step by itself after a pause (median of five) against the burst
+    # rate of the matmul, and five steps back to back (median) against the rate sustained under the cap.
+    times = timed_prefill("p", 0.3)
+    sustained = timed_prefill("q", 0.0)
     prefill_ms = sorted(times)[len(times) // 2]
+    sustained_ms = sorted(sustained)[len(sustained) // 2]
     c = runner.config
     per_token_matmul = sum(e for e in [
         2 * c.hidden_size * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim,
@@ -497,10 +512,11 @@ def main() -> int:
     prefill = {"value": round(T * 1000.0 / prefill_ms, 1), "tokens": T, "ms": round(prefill_ms, 3),
                "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
                "tflops": round(flops / (prefill_ms * 1e-3) / 1e12, 1), "peak_tflops": pk["bf16_tflops"],
-               # five steps back to back take the GPU from its burst rate to the rate its power cap sustains: the same
-               # median against the peak measured that way, and the five times themselves
-               "frac_sustained": round(flops / (prefill_ms * 1e-3) / (pk.get("bf16_tflops_sustained", pk["bf16_tflops"]) * 1e12), 4),
-               "ms_each": [round(t, 2) for t in times]}
+               "ms_each": [round(t, 2) for t in times],
+               "sustained": {"ms": round(sustained_ms, 3), "value": round(T * 1000.0 / sustained_ms, 1),
+                             "frac": round(flops / (sustained_ms * 1e-3) / (pk.get("bf16_tflops_sustained", pk["bf16_tflops"]) * 1e12), 4),
+                             "peak_tflops": pk.get("bf16_tflops_sustained", pk["bf16_tflops"]),
+                             "ms_each": [round(t, 2) for t in sustained]}}
 
     # ---- headline: decode at --batch, device-timed, with clocks sampled
     with ClockSampler() as clocks:
@@ -557,6 +573,7 @@ def main() -> int:
                    "intermediate": c.intermediate_size, "vocab": c.vocab_size, "kv_block": page,
                    "l2": "inputs larger than L2 (weights read every step)", "cuda_graphs": not args.no_graphs,
                    "order": "prefill first, then decode", "peaks": pk_kind,
+                   "prefill_timing": "each step by itself after 0.3 s idle, against the burst peak; sustained: five back to back, against the sustained peak",
                    "e2e_settle": "0.5 s idle between the prompt phase and the timed decode steps"},
         "e2e": {"value": round(args.batch * 1000.0 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch},
