@@ -102,9 +102,24 @@ argmax_partial_kernel(const float* __restrict__ logits, unsigned long long* __re
     const int per = (vocab + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
     const int begin = blockIdx.y * per, end = min(vocab, begin + per);
     unsigned long long best = 0ull;
-    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-        const unsigned long long w = pack_arg(row[i], i);
-        best = w > best ? w : best;
+    // eight loads in flight per thread before the first comparison (one at a time, a block's 4,752 logits of a
+    // 152,064-word vocabulary were 19 trips to L2: 7.7 us)
+    constexpr int BATCH = 8;
+    for (int i0 = begin + threadIdx.x; i0 < end; i0 += blockDim.x * BATCH) {
+        float v[BATCH];
+#pragma unroll
+        for (int u = 0; u < BATCH; ++u) {
+            const int i = i0 + u * blockDim.x;
+            v[u] = i < end ? row[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < BATCH; ++u) {
+            const int i = i0 + u * blockDim.x;
+            if (i < end) {
+                const unsigned long long w = pack_arg(v[u], i);
+                best = w > best ? w : best;
+            }
+        }
     }
     best = block_max_u64(best, scratch);
     if (threadIdx.x == 0) partial[(int64_t)blockIdx.x * ARGMAX_CHUNKS + blockIdx.y] = best;
