@@ -126,19 +126,20 @@ extern "C" int ss_attn_prefill_tc5(const void* q, int64_t q_stride, int n_tokens
 
 #include "attention_decode_tma.cuh"
 
-// The decode kernel with TMA-fed tiles: arguments as ss_attn_decode_mma; page_size 8, 16, 32 or 64.
+// The decode kernel with TMA-fed tiles: arguments as ss_attn_decode_mma; page_size 8, 16, 32 or 64.  stages: 2 or 3
+// tiles of keys and values in the ring of a block (see the kernel).
 extern "C" int ss_attn_decode_tma(const void* q, int64_t q_stride, void* out, int64_t out_stride,
                                   void* kv, const int32_t* block_tables, int max_blocks, int n_requests,
                                   const int32_t* q_start, const int32_t* seq_lens, int n_q, int n_kv,
                                   int page_size, int64_t num_pages, float scale, int window, int n_slices,
                                   const float* inv_freq, int rot_dim, int fused, float* part_o,
-                                  float* part_lse, int* counters, int* err, cudaStream_t stream) {
+                                  float* part_lse, int* counters, int stages, int* err, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (page_size % 8 != 0 || 64 % page_size != 0) return -3003;
     // up to 8 slices: one cluster; a multiple of 8 beyond: clusters of 8 whose results meet in scratch memory;
     // any other count: single blocks and scratch memory
     const int cluster = n_slices <= 8 ? n_slices : (n_slices % 8 == 0 ? 8 : 1);
-    if (n_slices < 1 || n_slices > SS_DECODE_MAX_SLICES) return (int)cudaErrorInvalidValue;
+    if (n_slices < 1 || n_slices > SS_DECODE_MAX_SLICES || (stages != 2 && stages != 3)) return (int)cudaErrorInvalidValue;
     if (n_slices > 8 && (!part_o || !part_lse || !counters)) return (int)cudaErrorInvalidValue;
     if (fused && (rot_dim < 0 || rot_dim > HEAD_DIM || rot_dim % 2 || (rot_dim > 0 && !inv_freq))) return (int)cudaErrorInvalidValue;
     CUtensorMap map_kv;
@@ -151,15 +152,23 @@ extern "C" int ss_attn_decode_tma(const void* q, int64_t q_stride, void* out, in
     a.n_q = n_q; a.n_kv = n_kv; a.page_size = page_size; a.num_pages = num_pages; a.scale = scale; a.window = window;
     a.n_slices = n_slices; a.cluster = cluster; a.inv_freq = inv_freq; a.rot_dim = rot_dim; a.fused = fused;
     a.part_o = part_o; a.part_lse = part_lse; a.counters = counters; a.err = err;
-    static SsPerDevice opted;
-    // the most a launch can ask for: 16 heads in a cluster of 7 are 3 x 7 records
-    if (int rc_smem = ss_opt_in_smem(attn_decode_tma<HEAD_DIM>, decode_tma_smem_bytes<HEAD_DIM>(24, 8), opted)) return rc_smem;
     const int G = n_q / n_kv;
-    // the records a block receives from its cluster are sized by the heads it really has
-    const int smem = decode_tma_smem_bytes<HEAD_DIM>(G < 16 ? G : 16, cluster);
     dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
-    if (cluster > 1) ss_launch_cluster(attn_decode_tma<HEAD_DIM>, dim3(grid), dim3(DT_THREADS), smem, stream, cluster, map_kv, a);
-    else ss_launch(attn_decode_tma<HEAD_DIM>, dim3(grid), dim3(DT_THREADS), smem, stream, map_kv, a);
+    // the most a launch can ask for: 16 heads in a cluster of 7 are 3 x 7 records; the records a block receives from
+    // its cluster are sized by the heads it really has
+    if (stages == 3) {
+        static SsPerDevice opted3;
+        if (int rc_smem = ss_opt_in_smem(attn_decode_tma<HEAD_DIM, 3>, decode_tma_smem_bytes<HEAD_DIM, 3>(24, 8), opted3)) return rc_smem;
+        const int smem = decode_tma_smem_bytes<HEAD_DIM, 3>(G < 16 ? G : 16, cluster);
+        if (cluster > 1) ss_launch_cluster(attn_decode_tma<HEAD_DIM, 3>, dim3(grid), dim3(DT_THREADS), smem, stream, cluster, map_kv, a);
+        else ss_launch(attn_decode_tma<HEAD_DIM, 3>, dim3(grid), dim3(DT_THREADS), smem, stream, map_kv, a);
+        return SS_LAUNCH_CHECK();
+    }
+    static SsPerDevice opted;
+    if (int rc_smem = ss_opt_in_smem(attn_decode_tma<HEAD_DIM, 2>, decode_tma_smem_bytes<HEAD_DIM, 2>(24, 8), opted)) return rc_smem;
+    const int smem = decode_tma_smem_bytes<HEAD_DIM, 2>(G < 16 ? G : 16, cluster);
+    if (cluster > 1) ss_launch_cluster(attn_decode_tma<HEAD_DIM, 2>, dim3(grid), dim3(DT_THREADS), smem, stream, cluster, map_kv, a);
+    else ss_launch(attn_decode_tma<HEAD_DIM, 2>, dim3(grid), dim3(DT_THREADS), smem, stream, map_kv, a);
     return SS_LAUNCH_CHECK();
 }
 #else

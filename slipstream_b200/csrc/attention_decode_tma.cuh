@@ -36,7 +36,7 @@
 
 #define DT_THREADS 160  // four consumer warps and the producer warp
 #ifndef DT_STAGES
-#define DT_STAGES 2
+#define DT_STAGES 2  // stages of the ring unless the launch asks for three
 #endif
 #define DT_TABLE_MAX 512  // block-table entries of a slice kept in shared memory
 
@@ -62,9 +62,9 @@ struct DecodeTmaArgs {
     int* err;
 };
 
-template <int D>
+template <int D, int NS = DT_STAGES>
 constexpr int decode_tma_tile_bytes() {
-    const int tiles = DT_STAGES * 2 * MMA_BN * D * 2;                          // stages of K and V
+    const int tiles = NS * 2 * MMA_BN * D * 2;                                 // stages of K and V
     const int merge = (4 * 16 * (D + 8) + 2 * 4 * 16 + 16 * D + 16) * 4;       // the merge buffers, which reuse them
     return tiles > merge ? tiles : merge;
 }
@@ -73,10 +73,10 @@ constexpr int decode_tma_tile_bytes() {
 constexpr int decode_tma_recv_bytes(int D, int heads, int cluster) {
     return cluster > 1 ? ((heads + cluster - 1) / cluster) * cluster * (D + 2) * 4 : 0;
 }
-template <int D>
+template <int D, int NS = DT_STAGES>
 constexpr int decode_tma_smem_bytes(int heads = 16, int cluster = 8) {
     // alignment slack, tiles, Q, mbarriers, records received from the cluster
-    return 1024 + decode_tma_tile_bytes<D>() + 16 * (D + 8) * 2 + 128 + decode_tma_recv_bytes(D, heads, cluster);
+    return 1024 + decode_tma_tile_bytes<D, NS>() + 16 * (D + 8) * 2 + 128 + decode_tma_recv_bytes(D, heads, cluster);
 }
 
 // two floats into the same shared-memory offset of block `rank` of this cluster
@@ -86,21 +86,28 @@ __device__ __forceinline__ void st_cluster_f32x2(float* local, uint32_t rank, fl
     asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(remote), "f"(x), "f"(y) : "memory");
 }
 
-template <int D>
-__global__ void __launch_bounds__(DT_THREADS)
+// (with three stages the registers are held to what lets two blocks share an SM, as the shared memory does)
+template <int D, int NS>
+__global__ void __launch_bounds__(DT_THREADS, NS == 3 ? 2 : 0)
 attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs a) {
     pdl_launch_dependents();
-    constexpr int KSTR = D + 8, NS = DT_STAGES, HALVES = D / 64;
+    constexpr int KSTR = D + 8, HALVES = D / 64;
     constexpr int STAGE = 2 * MMA_BN * D;  // elements: K tile then V tile
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     bf16* KV = reinterpret_cast<bf16*>(base);
-    bf16* Qs = reinterpret_cast<bf16*>(base + decode_tma_tile_bytes<D>());
+    bf16* Qs = reinterpret_cast<bf16*>(base + decode_tma_tile_bytes<D, NS>());
     uint64_t* full = reinterpret_cast<uint64_t*>(Qs + 16 * KSTR);
-    uint64_t* empty = full + NS;
-    volatile int* gave_up = reinterpret_cast<volatile int*>(empty + NS);
-    float* Recv = reinterpret_cast<float*>(base + decode_tma_tile_bytes<D>() + 16 * KSTR * 2 + 128);  // [slot][block][D + 2]
-    static_assert(NS == 2, "the consumer pairs are tied to the two stages of the ring");
+    // Barriers of the ring.  With two stages a pair of warps owns a stage and meets each of its phases, so one
+    // barrier a stage will do.  With three, the tiles of a stage go to the two pairs in turn; a pair would see
+    // every other phase of a barrier, which a wait by parity cannot tell apart, so every (stage, pair) has barriers
+    // of its own: tile i uses number (i % 3) * 2 + (i & 1), in its phase i / 6.
+    constexpr int NB = NS == 2 ? 2 : 2 * NS;
+    uint64_t* empty = full + NB;
+    volatile int* gave_up = reinterpret_cast<volatile int*>(empty + NB);
+    auto bar_of = [](int i) { return NS == 2 ? (i & 1) : (i % NS) * 2 + (i & 1); };
+    auto phase_of = [](int i) { return NS == 2 ? (i >> 1) : i / (2 * NS); };
+    float* Recv = reinterpret_cast<float*>(base + decode_tma_tile_bytes<D, NS>() + 16 * KSTR * 2 + 128);  // [slot][block][D + 2]
     __shared__ int32_t table_s[DT_TABLE_MAX];
     __shared__ float cos_s[64], sin_s[64];
     __shared__ __align__(16) bf16 newest_k[128], newest_v[128];
@@ -125,7 +132,7 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
     const bool has_newest = a.fused && work && kt_hi == kt_last;
 
     if (tid == 0) {
-        for (int s = 0; s < NS; ++s) { fa::mbar_init(&full[s], 1); fa::mbar_init(&empty[s], 2); }  // a pair of warps per stage
+        for (int s = 0; s < NB; ++s) { fa::mbar_init(&full[s], 1); fa::mbar_init(&empty[s], 2); }  // a pair of warps per tile
         *gave_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -167,13 +174,14 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
             bool waited = false, ok = true;
             for (int kt = kt_lo; kt <= kt_hi && ok; ++kt) {
                 const int i = kt - kt_lo, st = i % NS;
-                if (i >= NS) ok = __all_sync(0xffffffffu, fa::mbar_wait(&empty[st], ((i / NS) - 1) & 1, gave_up));
+                // the tile that lay in this stage before (i - NS) has been used up
+                if (i >= NS) ok = __all_sync(0xffffffffu, fa::mbar_wait(&empty[bar_of(i - NS)], phase_of(i - NS) & 1, gave_up));
                 if (!ok) break;
                 if (!a.fused && kt == kt_last && !waited) {
                     pdl_wait();  // the newest key and value are written by the kernel before this one
                     waited = true;
                 }
-                if (lane == 0) fa::mbar_expect_tx(&full[st], STAGE * 2);
+                if (lane == 0) fa::mbar_expect_tx(&full[bar_of(i)], STAGE * 2);
                 __syncwarp();
                 if (mine) {
                     bf16* Ks = KV + st * STAGE;
@@ -186,9 +194,9 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
                     }
                     if (page < 0) page = spare;
                     fa::tma_load_3d_once(Ks + h * (MMA_BN * 64) + p * page_size * 64, &map_kv, h * 64, 0,
-                                         (int)((page * 2 + 0) * n_kv + kvh), &full[st], once);
+                                         (int)((page * 2 + 0) * n_kv + kvh), &full[bar_of(i)], once);
                     fa::tma_load_3d_once(Vs + h * (MMA_BN * 64) + p * page_size * 64, &map_kv, h * 64, 0,
-                                         (int)((page * 2 + 1) * n_kv + kvh), &full[st], once);
+                                         (int)((page * 2 + 1) * n_kv + kvh), &full[bar_of(i)], once);
                 }
             }
         }
@@ -280,14 +288,17 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
             const float scale_log2 = a.scale * 1.4426950408889634f;
             const int p_lo = (lane >> 2) < heads_here ? pos : -1;
             const int p_hi = (lane >> 2) + 8 < heads_here ? pos : -1;
-            // pair (warp / 2) owns stage (warp / 2) of the ring: tiles kt_lo + pair, + 2, ...; warp % 2 is the 32-key half
+            // pair (warp / 2) takes the tiles kt_lo + pair, + 2, ...; warp % 2 is the 32-key half.  Tile i lies in
+            // stage i % NS: with two stages a pair has one of its own, and its next tile can only be fetched once
+            // it is done with this one (a block that walks 16 tiles then moves one tile per pair in the time of a
+            // product plus a trip to memory); with three, the third is being filled while both pairs work.
             const int pair = warp >> 1, key_off = (warp & 1) * 32;
             for (int kt = kt_lo + pair; kt <= kt_hi; kt += 2) {
-                const int i = kt - kt_lo, st = pair;
+                const int i = kt - kt_lo, st = NS == 2 ? pair : i % NS;
                 bf16* Ks = KV + st * STAGE;
                 bf16* Vs = Ks + MMA_BN * D;
                 // a wait that gives up makes every later wait give up at once
-                const bool ok = fa::mbar_wait(&full[st], (i / NS) & 1, gave_up);
+                const bool ok = fa::mbar_wait(&full[bar_of(i)], phase_of(i) & 1, gave_up);
                 const int first_key = kt * MMA_BN + key_off;
                 if (a.fused && kt == kt_last && pos >= first_key && pos < first_key + 32) {
                     // the newest token's row of this half comes from the projection output, not from the page
@@ -320,7 +331,7 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
                 __syncwarp();
                 if (lane == 0) {
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // before the next copy into this stage
-                    fa::mbar_arrive(&empty[st]);
+                    fa::mbar_arrive(&empty[bar_of(i)]);
                 }
             }
         }

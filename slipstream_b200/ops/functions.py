@@ -66,7 +66,7 @@ _ATTN_SIGNATURES = {
                             c_void_p],
     "ss_attn_decode_tma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
-                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     "ss_attn_decode_mma": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
                            c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -478,7 +478,8 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
                            block_tables: torch.Tensor, q_start: torch.Tensor, seq_lens: torch.Tensor,
                            n_requests: int, n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0,
                            n_slices: int = 1, scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
-                           rope: tuple[torch.Tensor | None, int] | None = None, tma: bool | None = None) -> None:
+                           rope: tuple[torch.Tensor | None, int] | None = None, tma: bool | None = None,
+                           stages: int = 2) -> None:
     """bfloat16 attention for requests that bring ONE token each, the keys of every request cut into
     ``n_slices`` slices that run in parallel.  Up to 8 slices form a thread-block cluster and are combined
     through shared memory; with more, the partial results (of every cluster of 8 in the TMA-fed kernel when the
@@ -491,7 +492,8 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
     for other steps).
 
     ``tma``: the kernel whose tiles are moved by TMA (head size 64 or 128, pages of 8, 16, 32 or 64 tokens;
-    the default where it fits), or the one that moves them with cp.async (every head and page size)."""
+    the default where it fits), or the one that moves them with cp.async (every head and page size).
+    ``stages``: 2 or 3 tiles in the ring of the TMA-fed kernel."""
     fits = tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], 0)
     if tma is None:
         tma = fits
@@ -524,13 +526,15 @@ def paged_attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
             if inv_freq.numel() != rotary_dim // 2:
                 raise KernelError("inv_freq must hold rotary_dim / 2 values")
     lib = attention_library(head_dim)
-    entry = lib.ss_attn_decode_tma if tma else lib.ss_attn_decode_mma
-    _check(entry(q.data_ptr(), q_stride, out.data_ptr(), out.shape[1], kv.data_ptr(),
-                                  block_tables.data_ptr(), block_tables.shape[1], n_requests, q_start.data_ptr(),
-                                  seq_lens.data_ptr(), n_q, n_kv, kv.shape[3], kv.shape[0], float(scale),
-                                  int(window or 0), n_slices, _ptr(inv_freq) if rotary_dim else None, rotary_dim,
-                                  int(rope is not None), _ptr(part_o), _ptr(part_lse), _ptr(counters),
-                                  error_word(q.device).data_ptr(), _stream()), "paged_attention_decode")
+    args = (q.data_ptr(), q_stride, out.data_ptr(), out.shape[1], kv.data_ptr(), block_tables.data_ptr(),
+            block_tables.shape[1], n_requests, q_start.data_ptr(), seq_lens.data_ptr(), n_q, n_kv, kv.shape[3], kv.shape[0],
+            float(scale), int(window or 0), n_slices, _ptr(inv_freq) if rotary_dim else None, rotary_dim,
+            int(rope is not None), _ptr(part_o), _ptr(part_lse), _ptr(counters))
+    tail = (error_word(q.device).data_ptr(), _stream())
+    if tma:
+        _check(lib.ss_attn_decode_tma(*args, int(stages), *tail), "paged_attention_decode")
+    else:
+        _check(lib.ss_attn_decode_mma(*args, *tail), "paged_attention_decode")
 
 
 WIDE_CONTEXT = 8192  # from this many cached tokens a decode step of few requests may use more than 8 slices
@@ -561,6 +565,14 @@ def decode_slices(n_requests: int, n_kv: int, group: int, max_seq_len: int, wide
         clusters = max(1, min((2 * sms) // (blocks * 8), tiles // 64, 8))
         slices = 8 * (1 << (clusters.bit_length() - 1))
     return slices
+
+
+# Tiles of keys and values in the ring of a block of the TMA-fed decode attention.  With two, each pair of warps has
+# one buffer and cannot fetch its next tile before it is done with this one: a block that walks many tiles (64
+# requests of 1,024 tokens: 16 each) moves a tile per pair in the time of its products plus a trip to memory.  With
+# three the third fills while both pairs work: a decode step of 64 requests 3.68 -> 3.62 ms, of 64 at 4,000 tokens
+# 5.51 -> 5.27, of 32 at 16,000 7.78 -> 7.31, of 8 at 30,000 4.85 -> 4.65, of 8 at 1,024 2.70 -> 2.69.
+DECODE_RING_STAGES = 3
 
 
 def fuses_rope(qkv: torch.Tensor, ctx, head_dim: int, n_q: int, n_kv: int, page_size: int) -> bool:
@@ -604,7 +616,8 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, bloc
                                sm_count(qkv.device))
         scratch = ctx.extras.get(("decode_scratch", n_q, head_dim))
         paged_attention_decode(qkv, qkv.shape[1], out, kv, block_tables, ctx.q_start, ctx.seq_lens,
-                               ctx.num_requests, n_q, n_kv, head_dim, scale, window, slices, scratch, rope)
+                               ctx.num_requests, n_q, n_kv, head_dim, scale, window, slices, scratch, rope,
+                               stages=DECODE_RING_STAGES)
         return
     if tcgen05_attention_fits(head_dim, n_q, n_kv, kv.shape[3], window):
         tile_req, tile_tok0 = ctx.query_tiles_longest_first(128 // group)

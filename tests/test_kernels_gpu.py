@@ -241,12 +241,13 @@ def test_split_decode_attention(slices, n_q, n_kv, d, page, window):
     q, kv, table, q_start, seq_lens = make_attention_case(torch.bfloat16, lens, [1] * len(lens), n_q, n_kv, d, page, seed=d)
     scale = d ** -0.5
     ref = attention_reference(q, kv, table, q_start, seq_lens, n_kv, page, scale, window)
-    kernels = [False] + ([True] if ops().tcgen05_attention_fits(d, n_q, n_kv, page, 0) else [])
-    for tma in kernels:  # tiles moved by cp.async, and by TMA where the sizes allow it
+    # tiles moved by cp.async, and by TMA where the sizes allow it, through a ring of two stages and of three
+    kernels = [(False, 2)] + ([(True, 2), (True, 3)] if ops().tcgen05_attention_fits(d, n_q, n_kv, page, 0) else [])
+    for tma, stages in kernels:
         out = torch.full((q.shape[0], n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
         ops().paged_attention_decode(q.view(q.shape[0], -1), n_q * d, out, kv, table, q_start, seq_lens, len(lens),
-                                     n_q, n_kv, d, scale, window, n_slices=slices, tma=tma)
-        assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2, tma
+                                     n_q, n_kv, d, scale, window, n_slices=slices, tma=tma, stages=stages)
+        assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2, (tma, stages)
     ops().check_errors(torch.device(DEV))
 
 
@@ -267,20 +268,20 @@ def test_decode_attention_that_rotates_and_writes_the_newest_token_itself(slices
     pages_of = table.long()[torch.arange(R, device=DEV), (positions // page).long()]
     slots = (pages_of * page + positions % page).int()
     scale = d ** -0.5
-    for tma in [False] + ([True] if ops().tcgen05_attention_fits(d, n_q, n_kv, page, 0) else []):
-        # two steps, then one step, with the same way of moving the tiles (cp.async, or TMA)
+    for tma, stages in [(False, 2)] + ([(True, 2), (True, 3)] if ops().tcgen05_attention_fits(d, n_q, n_kv, page, 0) else []):
+        # two steps, then one step, with the same way of moving the tiles (cp.async, or TMA with a ring of 2 or 3)
         qkv_a, kv_a = qkv.clone(), kv.clone()
         ops().rope_and_cache(qkv_a, positions, slots, inv_freq, kv_a, n_q, n_kv, d, rot)
         out_a = torch.full((R, n_q * d), float("nan"), device=DEV, dtype=torch.bfloat16)
         ops().paged_attention_decode(qkv_a, qkv_a.shape[1], out_a, kv_a, table, q_start, seq_lens, R, n_q, n_kv, d, scale,
-                                     window, n_slices=slices, tma=tma)
+                                     window, n_slices=slices, tma=tma, stages=stages)
         qkv_b, kv_b = qkv.clone(), kv.clone()
         out_b = torch.full_like(out_a, float("nan"))
         ops().paged_attention_decode(qkv_b, qkv_b.shape[1], out_b, kv_b, table, q_start, seq_lens, R, n_q, n_kv, d,
-                                     scale, window, n_slices=slices, rope=(inv_freq, rot), tma=tma)
+                                     scale, window, n_slices=slices, rope=(inv_freq, rot), tma=tma, stages=stages)
         assert torch.equal(kv_a, kv_b), "the pages differ"
         assert not torch.equal(kv_b, kv) and torch.equal(qkv_b, qkv)
-        assert torch.equal(out_a, out_b), tma
+        assert torch.equal(out_a, out_b), (tma, stages)
     ops().check_errors(torch.device(DEV))
 
 

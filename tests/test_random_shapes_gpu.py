@@ -63,12 +63,13 @@ def test_attention_kernels_at_random_sizes_with_stale_rows_behind_every_request(
                                                       d, scale, parts)
                 assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2, (what, parts)
         if decode:
-            for tma in [False] + ([True] if ops().tcgen05_attention_fits(d, n_q, n_kv, page, 0) else []):
+            fits = ops().tcgen05_attention_fits(d, n_q, n_kv, page, 0)
+            for tma, stages in [(False, 2)] + ([(True, 2), (True, 3)] if fits else []):
                 slices = rng.choice([1, 2, 3, 5, 8, 16, 24, 64])
                 out = fresh()
                 ops().paged_attention_decode(flat, n_q * d, out, kv, table, q_start, seq_lens, R, n_q, n_kv, d, scale,
-                                             window, n_slices=slices, tma=tma)
-                assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2, (what, tma, slices)
+                                             window, n_slices=slices, tma=tma, stages=stages)
+                assert rel_err(out.view_as(ref).cpu(), ref) < 1e-2, (what, tma, stages, slices)
     ops().check_errors(torch.device(DEV))
 
 
