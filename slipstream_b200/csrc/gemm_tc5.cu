@@ -132,6 +132,21 @@ struct GemmArgs {
     int cluster;        // 1: the slices of a tile are one thread-block cluster and are added through shared memory
     int swiglu;         // 1 (swapped only): rows 0..63 of a tile are gate features, rows 64..127 the matching up
                         // features; the output has M / 2 features: out[n][tile * 64 + r] = silu(gate) * up
+    // A branch's last projection (cluster mode, M a multiple of 128) may add its output, rounded to bfloat16, to the
+    // float32 stream instead of writing C: residual[n][m] += ..., and prepare the RMS norm that follows: it leaves
+    // scaled[n][m] = round(norm_weight[m] * residual[n][m]) in bfloat16 and the sum of the squares of each tile's
+    // part of the new stream in tile_squares[n][tile of 128 features].
+    float* residual;
+    float* tile_squares;
+    bf16* scaled;
+    const void* norm_weight;
+    int norm_w_f32;
+    // The product behind that norm (swapped) takes `scaled` as its B operand and multiplies token n of its
+    // output, before the bias, by rsqrt(sum of in_squares[n][0 .. in_tiles) / K + in_eps): the norm's scale does
+    // not depend on the feature, so it can wait until the product is done.
+    const float* in_squares;
+    int in_tiles;
+    float in_eps;
 };
 
 __device__ __forceinline__ float bias_at(const GemmArgs& g, int f) {
@@ -139,8 +154,9 @@ __device__ __forceinline__ float bias_at(const GemmArgs& g, int f) {
 }
 
 // Output of the fused SwiGLU: gate and up are rows m and m + 64 of the swapped product (token n).
-__device__ __forceinline__ void store_swiglu(const GemmArgs& g, int m, int n, float gate, float up) {
+__device__ __forceinline__ void store_swiglu(const GemmArgs& g, int m, int n, float gate, float up, float scale = 1.f) {
     if (m + 64 >= g.M || n >= g.N) return;
+    gate *= scale; up *= scale;
     if (g.bias) { gate += bias_at(g, m); up += bias_at(g, m + 64); }
     const float v = silu_mul<true>(gate, up);
     const int64_t at = (int64_t)n * g.ldc + (m / TC_BM) * 64 + (m % TC_BM);
@@ -149,8 +165,9 @@ __device__ __forceinline__ void store_swiglu(const GemmArgs& g, int m, int n, fl
 }
 
 template <int BN>
-__device__ __forceinline__ void store_out(const GemmArgs& g, int m, int n, float v) {
+__device__ __forceinline__ void store_out(const GemmArgs& g, int m, int n, float v, float scale = 1.f) {
     if (m >= g.M || n >= g.N) return;
+    v *= scale;
     if (g.bias) {
         const int f = g.swapped ? m : n;
         v += g.bias_f32 ? ((const float*)g.bias)[f] : to_float(((const bf16*)g.bias)[f]);
@@ -173,6 +190,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
     volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = const_cast<int*>(gave_up) + 1;
+    float* rstd_s = reinterpret_cast<float*>(tiles + STAGES * (A_BYTES + B_BYTES) + 256);  // [BN <= 64] (in_squares)
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -208,6 +226,18 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (warp >= 2 && g.cluster && g.bias && !g.swiglu && m0 + lane * 4 + 3 < g.M)
         bias4 = make_float4(bias_at(g, m0 + lane * 4), bias_at(g, m0 + lane * 4 + 1), bias_at(g, m0 + lane * 4 + 2),
                             bias_at(g, m0 + lane * 4 + 3));
+    // likewise the weights of the norm behind a product into the stream, and (after the wait) the stream's values
+    // that this block's first token column of the reduction is added to
+    float4 nw4 = make_float4(0.f, 0.f, 0.f, 0.f), res0 = nw4;
+    if (warp >= 2 && g.residual) {
+        const int f = m0 + lane * 4;
+        if (g.norm_w_f32) nw4 = *reinterpret_cast<const float4*>((const float*)g.norm_weight + f);
+        else {
+            const uint2 w = *reinterpret_cast<const uint2*>((const bf16*)g.norm_weight + f);
+            const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&w.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&w.y);
+            nw4 = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+        }
+    }
 
     if (warp == 0 && lane == 0) {
         // ---- producer.  When the block runs swapped, A is the weight matrix: a constant, so its first
@@ -259,6 +289,37 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int quarter = warp & 3;
         const int m = m0 + quarter * 32 + lane;
         pdl_wait();  // the output, the scratch and the counters may still be in use by earlier kernels
+        if (g.residual) {
+            const int c0 = (int)cluster_rank() + quarter * g.slices;
+            if (c0 < min(BN, g.N - n0)) res0 = *reinterpret_cast<const float4*>(g.residual + (int64_t)(n0 + c0) * g.M + m0 + lane * 4);
+        }
+        if constexpr (BN <= 64) if (g.in_squares != nullptr) {
+            // 1 / rms of every token of the tile, while the products run: a warp takes tokens quarter, quarter + 4,
+            // ...; its lanes read the tiles' sums (all loads of a warp in flight at once) and add them in a fixed order
+            constexpr int PER_WARP = (BN + 3) / 4;
+            const int live = min(BN, g.N - n0);
+            float part[PER_WARP];
+#pragma unroll
+            for (int j = 0; j < PER_WARP; ++j) part[j] = 0.f;
+            for (int i0 = 0; i0 < g.in_tiles; i0 += 32) {
+                float v[PER_WARP];
+#pragma unroll
+                for (int j = 0; j < PER_WARP; ++j)
+                    v[j] = quarter + 4 * j < live && i0 + lane < g.in_tiles
+                               ? __ldcg(g.in_squares + (int64_t)(n0 + quarter + 4 * j) * g.in_tiles + i0 + lane) : 0.f;
+#pragma unroll
+                for (int j = 0; j < PER_WARP; ++j) part[j] += v[j];
+            }
+#pragma unroll
+            for (int j = 0; j < PER_WARP; ++j) {
+                float ss = part[j];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (lane == 0 && quarter + 4 * j < BN)
+                    rstd_s[quarter + 4 * j] = quarter + 4 * j < live ? 1.0f / sqrtf(ss / (float)g.K + g.in_eps) : 0.f;
+            }
+        }
+        const bool scaled_in = BN <= 64 && g.in_squares != nullptr;  // rstd_s is seen behind the barrier below
         if (k_iters > 0) mbar_wait(acc_ready, 0, gave_up);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         // one thread decides for all four epilogue warps whether the tile is good, so that the barriers
@@ -304,7 +365,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) store_out<BN>(g, m, n0 + c + j, __uint_as_float(r[j]));
+                        for (int j = 0; j < 16; ++j)
+                            store_out<BN>(g, m, n0 + c + j, __uint_as_float(r[j]), scaled_in ? rstd_s[(c + j) & 63] : 1.f);
                     }
                 } else {
                     float* dst = g.partial + (((int64_t)tile * g.slices + blockIdx.z) * BN + c) * TC_BM + quarter * 32 + lane;
@@ -319,7 +381,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int t = quarter * 32 + lane, ml = t & 63;
                 const int n_live = min(BN, g.N - n0);
                 for (int c = t >> 6; c < n_live; c += 2)
-                    store_swiglu(g, m0 + ml, n0 + c, xbuf[c * TC_BM + ml], xbuf[c * TC_BM + ml + 64]);
+                    store_swiglu(g, m0 + ml, n0 + c, xbuf[c * TC_BM + ml], xbuf[c * TC_BM + ml + 64],
+                                 scaled_in ? rstd_s[c & 63] : 1.f);
             }
             if (g.slices > 1 && !g.cluster) {
                 // the block that completes the tile last adds the slices, in slice order
@@ -353,8 +416,9 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         }
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
-                            if (!g.swiglu) store_out<BN>(g, m0 + ml, n0 + c0 + u, acc[u]);
-                            else if (ml < 64) store_swiglu(g, m0 + ml, n0 + c0 + u, acc[u], acc2[u]);
+                            const float sc = scaled_in ? rstd_s[(c0 + u) & 63] : 1.f;
+                            if (!g.swiglu) store_out<BN>(g, m0 + ml, n0 + c0 + u, acc[u], sc);
+                            else if (ml < 64) store_swiglu(g, m0 + ml, n0 + c0 + u, acc[u], acc2[u], sc);
                         }
                     }
                 }
@@ -370,8 +434,10 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int n_live = min(BN, g.N - n0);
             const int rank = (int)cluster_rank(), q = warp & 3;
             const int mine = n_live > rank ? (n_live - 1 - rank) / g.slices + 1 : 0;  // columns rank, rank + slices, ...
+            const bool scaled_in = BN <= 64 && g.in_squares != nullptr;
             for (int i = q; i < mine; i += 4) {
                 const int c = rank + i * g.slices;
+                const float sc = scaled_in ? rstd_s[c & 63] : 1.f;
                 if (!g.swiglu) {
                     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
@@ -380,16 +446,36 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
                     }
                     const int m = m0 + lane * 4, n = n0 + c;
-                    if (g.swapped && !g.out_f32 && m + 3 < g.M && (g.ldc & 3) == 0) {
-                        acc.x += bias4.x; acc.y += bias4.y; acc.z += bias4.z; acc.w += bias4.w;
+                    if (g.residual != nullptr) {
+                        // (M is a multiple of 128.)  The stream takes this part of the branch's output, rounded as
+                        // the output would have been; the norm behind it gets the stream times its weights, and
+                        // the squares of the tile's 128 features in one sum
+                        float* res = g.residual + (int64_t)n * g.M + m;
+                        float4 x = i == q ? res0 : *reinterpret_cast<const float4*>(res);
+                        x.x = __fadd_rn(x.x, to_float(__float2bfloat16_rn(acc.x + bias4.x)));
+                        x.y = __fadd_rn(x.y, to_float(__float2bfloat16_rn(acc.y + bias4.y)));
+                        x.z = __fadd_rn(x.z, to_float(__float2bfloat16_rn(acc.z + bias4.z)));
+                        x.w = __fadd_rn(x.w, to_float(__float2bfloat16_rn(acc.w + bias4.w)));
+                        *reinterpret_cast<float4*>(res) = x;
+                        const __nv_bfloat162 lo = __floats2bfloat162_rn(nw4.x * x.x, nw4.y * x.y), hi = __floats2bfloat162_rn(nw4.z * x.z, nw4.w * x.w);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+                        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+                        *reinterpret_cast<uint2*>(g.scaled + (int64_t)n * g.M + m) = packed;
+                        float sq = fmaf(x.x, x.x, fmaf(x.y, x.y, fmaf(x.z, x.z, x.w * x.w)));
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                        if (lane == 0) g.tile_squares[(int64_t)n * gridDim.y + blockIdx.y] = sq;
+                    } else if (g.swapped && !g.out_f32 && m + 3 < g.M && (g.ldc & 3) == 0) {
+                        acc.x = acc.x * sc + bias4.x; acc.y = acc.y * sc + bias4.y; acc.z = acc.z * sc + bias4.z; acc.w = acc.w * sc + bias4.w;
                         const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
                         uint2 packed;
                         packed.x = *reinterpret_cast<const uint32_t*>(&lo);
                         packed.y = *reinterpret_cast<const uint32_t*>(&hi);
                         *reinterpret_cast<uint2*>((bf16*)g.C + (int64_t)n * g.ldc + m) = packed;
                     } else {
-                        store_out<BN>(g, m, n, acc.x); store_out<BN>(g, m + 1, n, acc.y);
-                        store_out<BN>(g, m + 2, n, acc.z); store_out<BN>(g, m + 3, n, acc.w);
+                        store_out<BN>(g, m, n, acc.x, sc); store_out<BN>(g, m + 1, n, acc.y, sc);
+                        store_out<BN>(g, m + 2, n, acc.z, sc); store_out<BN>(g, m + 3, n, acc.w, sc);
                     }
                 } else if (lane < 16) {
                     float4 ga = make_float4(0.f, 0.f, 0.f, 0.f), ua = ga;
@@ -401,8 +487,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         ua.x += w.x; ua.y += w.y; ua.z += w.z; ua.w += w.w;
                     }
                     const int m = m0 + lane * 4, n = n0 + c;
-                    store_swiglu(g, m, n, ga.x, ua.x); store_swiglu(g, m + 1, n, ga.y, ua.y);
-                    store_swiglu(g, m + 2, n, ga.z, ua.z); store_swiglu(g, m + 3, n, ga.w, ua.w);
+                    store_swiglu(g, m, n, ga.x, ua.x, sc); store_swiglu(g, m + 1, n, ga.y, ua.y, sc);
+                    store_swiglu(g, m + 2, n, ga.z, ua.z, sc); store_swiglu(g, m + 3, n, ga.w, ua.w, sc);
                 }
             }
         }
@@ -677,7 +763,7 @@ static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K,
 
 template <int BN, int STAGES>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, dim3 grid, cudaStream_t stream) {
-    constexpr int smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 256;
+    constexpr int smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 512;
     static SsPerDevice opted;
     if (int rc_smem = ss_opt_in_smem(gemm_tc5_kernel<BN, STAGES>, smem, opted)) return rc_smem;
     if (g.cluster)
@@ -698,15 +784,30 @@ extern "C" int64_t ss_gemm_tc5_scratch_floats(int tiles, int slices, int bn) { r
 // 2..8 slices and N <= bn, where the slices are added through the shared memory of a thread-block cluster.
 extern "C" void ss_set_pdl(int on) { ss_pdl_flag() = on; }
 
-extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
-                           int64_t lda, int64_t ldb, int64_t ldc, int bn, int swapped, int out_f32, int slices,
-                           int swiglu, float* partial, int* counters, int* err, cudaStream_t stream) {
+struct NormEnds {  // see GemmArgs: the output added to the float32 stream, the output scaled by the norm in front
+    float* residual = nullptr;
+    float* tile_squares = nullptr;
+    void* scaled = nullptr;
+    const void* norm_weight = nullptr;
+    int norm_w_f32 = 0;
+    const float* in_squares = nullptr;
+    int in_tiles = 0;
+    float in_eps = 0.f;
+};
+
+static int gemm_tc5(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
+                    int64_t lda, int64_t ldb, int64_t ldc, int bn, int swapped, int out_f32, int slices,
+                    int swiglu, float* partial, int* counters, const NormEnds& ends, int* err, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (swiglu && (!swapped || M % TC_BM != 0)) return -2007;
     if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return -2003;
     if (((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2004;
     const int cluster = swapped && slices >= 2 && slices <= 8 && N <= bn;
     if (slices < 1 || (slices > 1 && !cluster && (!partial || !counters))) return -2005;
+    if (ends.residual && (!cluster || swiglu || M % TC_BM != 0 || !ends.tile_squares || !ends.scaled || !ends.norm_weight ||
+                          ((uintptr_t)ends.residual & 15) || ((uintptr_t)ends.scaled & 7) || ((uintptr_t)ends.norm_weight & 15)))
+        return -2008;
+    if (ends.in_squares && (!swapped || bn > 64 || ends.in_tiles < 1)) return -2009;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, M, K, lda, TC_BM);
     if (rc) return rc;
@@ -716,6 +817,9 @@ extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int b
     g.C = C; g.bias = bias; g.partial = partial; g.counters = counters; g.err = err;
     g.M = M; g.N = N; g.K = K; g.ldc = ldc; g.slices = slices; g.swapped = swapped; g.out_f32 = out_f32;
     g.bias_f32 = bias_f32; g.swiglu = swiglu; g.cluster = cluster;
+    g.residual = ends.residual; g.tile_squares = ends.tile_squares; g.scaled = (bf16*)ends.scaled;
+    g.norm_weight = ends.norm_weight; g.norm_w_f32 = ends.norm_w_f32;
+    g.in_squares = ends.in_squares; g.in_tiles = ends.in_tiles; g.in_eps = ends.in_eps;
     const bool deep = swapped && ((K + TC_BK - 1) / TC_BK + slices - 1) / slices >= 24;
     dim3 grid((N + bn - 1) / bn, (M + TC_BM - 1) / TC_BM, slices);
     if (!swapped) grid = dim3((M + TC_BM - 1) / TC_BM, (N + bn - 1) / bn, slices);
@@ -733,6 +837,39 @@ extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int b
         case 256: return launch<256, 4>(ma, mb, g, grid, stream);
         default: return -2006;
     }
+}
+
+extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
+                           int64_t lda, int64_t ldb, int64_t ldc, int bn, int swapped, int out_f32, int slices,
+                           int swiglu, float* partial, int* counters, int* err, cudaStream_t stream) {
+    return gemm_tc5(A, B, bias, bias_f32, C, M, N, K, lda, ldb, ldc, bn, swapped, out_f32, slices, swiglu, partial,
+                    counters, NormEnds(), err, stream);
+}
+
+// A branch's last projection into the float32 stream: the swapped product with its K slices as a thread-block
+// cluster (2..8 slices, N <= bn, M a multiple of 128).  residual [N, M] += the product (+ bias) rounded to bfloat16;
+// scaled [N, M] (bfloat16) = norm_weight * the new stream; tile_squares [N, M / 128] = the sums of squares of the
+// new stream per tile of 128 features.  Other shapes are refused with -2008.
+extern "C" int ss_gemm_tc5_to_stream(const void* A, const void* B, const void* bias, int bias_f32, int M, int N, int K,
+                                     int64_t lda, int64_t ldb, int bn, int slices, float* residual, float* tile_squares,
+                                     void* scaled, const void* norm_weight, int norm_w_f32, int* err, cudaStream_t stream) {
+    NormEnds ends;
+    ends.residual = residual; ends.tile_squares = tile_squares; ends.scaled = scaled;
+    ends.norm_weight = norm_weight; ends.norm_w_f32 = norm_w_f32;
+    return gemm_tc5(A, B, bias, bias_f32, nullptr, M, N, K, lda, ldb, M, bn, 1, 0, slices, 0, nullptr, nullptr, ends, err, stream);
+}
+
+// The swapped product (bn <= 64) behind the RMS norm of that stream: B is `scaled`, and token n of the output is
+// multiplied, before the bias, by rsqrt(sum of in_squares[n][0 .. in_tiles) / K + eps); everything else as
+// ss_gemm_tc5.  Other shapes are refused with -2009.
+extern "C" int ss_gemm_tc5_scaled(const void* A, const void* B, const float* in_squares, int in_tiles, float eps,
+                                  const void* bias, int bias_f32, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                                  int64_t ldc, int bn, int out_f32, int slices, int swiglu, float* partial, int* counters,
+                                  int* err, cudaStream_t stream) {
+    NormEnds ends;
+    ends.in_squares = in_squares; ends.in_tiles = in_tiles; ends.in_eps = eps;
+    return gemm_tc5(A, B, bias, bias_f32, C, M, N, K, lda, ldb, ldc, bn, 1, out_f32, slices, swiglu, partial, counters,
+                    ends, err, stream);
 }
 
 // C = A * B^T (+ bias) for many rows of A (prompt portions): A [M, K] activations, B [N, K] weights, both

@@ -134,9 +134,12 @@ class DecoderLM:
         residual = self.embedding.forward(ctx.token_ids)
         if self.position_encoding is not None:
             self.position_encoding.on_embedding(residual, ctx)
-        pending = None
-        for entry, binding in zip(self.order, self.bindings):
-            residual, pending = self.blocks[entry.block].forward(residual, pending, ctx, binding)
+        pending = normed = None
+        for pos, (entry, binding) in enumerate(zip(self.order, self.bindings)):
+            # a block's last projection may end in the first norm of the block that runs next
+            following = self.blocks[self.order[pos + 1].block].first_norm() if pos + 1 < len(self.order) else None
+            residual, pending, normed = self.blocks[entry.block].forward_chained(residual, pending, normed, following,
+                                                                                 ctx, binding)
         if ctx.num_logits == 0:
             return torch.empty((0, self.lm_head.vocab_size), dtype=torch.float32, device=residual.device)
         x = self.final_norm.add_norm(residual, pending, rows=ctx.logit_rows)

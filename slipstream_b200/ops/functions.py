@@ -13,6 +13,7 @@ synchronising copy) and raises.
 from __future__ import annotations
 
 import ctypes
+import dataclasses
 import functools
 from ctypes import c_float, c_int, c_int64, c_void_p
 
@@ -77,6 +78,10 @@ _GEMM_SIGNATURES = {
                          c_int, c_int, c_int, c_void_p, c_void_p],
     "ss_gemm_tc5": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                     c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "ss_gemm_tc5_to_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int, c_int,
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    "ss_gemm_tc5_scaled": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                           c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
 _state: dict[str, object] = {}
@@ -711,6 +716,40 @@ def _gemm_workspace(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
     return ws  # type: ignore[return-value]
 
 
+@dataclasses.dataclass
+class PendingNorm:
+    """``weight * round(stream * rsqrt(mean(stream^2) + eps))`` that has not been computed: the stream is complete
+    (the branch in front has been added), ``scaled`` holds ``round(weight * stream)`` in bfloat16 and ``squares``
+    [tokens, tiles] the sums of the stream's squares per tile of 128 features.  `linear` and `gate_up_swiglu` take it
+    in place of the activations: with few bfloat16 tokens the product runs on ``scaled`` and multiplies every
+    token's output by its ``rsqrt(...)`` at the end (the scale does not depend on the feature, so it commutes with
+    the product; the activations are then rounded once instead of twice).  Everything else calls
+    ``materialize()``, the norm kernel on the stream."""
+    stream: torch.Tensor
+    scaled: torch.Tensor
+    squares: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+    dtype: torch.dtype
+
+    @property
+    def shape(self) -> torch.Size:
+        return self.stream.shape
+
+    @property
+    def device(self) -> torch.device:
+        return self.stream.device
+
+    def materialize(self) -> torch.Tensor:
+        return add_rmsnorm(self.stream, None, self.weight, self.eps, self.dtype)
+
+
+def takes_pending_norm(x: "torch.Tensor | PendingNorm", features: int) -> bool:
+    """Whether the product of ``x`` with a [features, K] weight applies the norm's scale inside the kernel."""
+    return (isinstance(x, PendingNorm) and x.dtype == torch.bfloat16
+            and streams_weights(x.shape[0], features, x.shape[1], sm_count(x.device)))
+
+
 def gemm_plan(tokens: int, features: int, k: int, sms: int | None = None) -> tuple[bool, int, int]:
     """(swapped, tile width, K slices) for ``x[tokens, k] @ w[features, k].T`` on ``sms`` multiprocessors."""
     return _gemm_plan(tokens, features, k, sms or sm_count())
@@ -733,14 +772,25 @@ def _gemm_plan(tokens: int, features: int, k: int, sms: int) -> tuple[bool, int,
     return False, bn, 1
 
 
-def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+def gemm_tcgen05(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: torch.Tensor | None = None,
                  out_dtype: torch.dtype | None = None, plan: tuple[bool, int, int] | None = None,
-                 swiglu: bool = False) -> torch.Tensor:
+                 swiglu: bool = False, to_stream: tuple[torch.Tensor, torch.Tensor] | None = None):
     """``x @ weight.T + bias`` for bfloat16 ``x`` [tokens, K] and ``weight`` [features, K] on the tcgen05 tensor
     cores (TMA-fed, accumulator in tensor memory); output bfloat16 or float32.  K must be a multiple of 8.
 
     ``swiglu`` (at most 64 tokens, features a multiple of 128): the weight's rows alternate 64 gate and 64 up
-    features; the result is ``silu(gate) * up`` with features / 2 columns, formed in the product's epilogue."""
+    features; the result is ``silu(gate) * up`` with features / 2 columns, formed in the product's epilogue.
+
+    ``to_stream`` = (float32 stream [tokens, features], weights of the norm behind it), where `adds_to_stream`:
+    the product, rounded to bfloat16, is added to the stream in place instead of being returned, and the function
+    returns (round(norm weights * new stream) in bfloat16, sums of squares [tokens, features / 128]).
+    ``x`` may be a `PendingNorm` (at most 64 tokens, swapped plan): the product runs on its ``scaled`` and applies
+    the scale of every token in the epilogue."""
+    pending = x if isinstance(x, PendingNorm) else None
+    if pending is not None:
+        if pending.dtype != torch.bfloat16:
+            raise KernelError("a pending norm feeds the tensor-core product only in bfloat16")
+        x = pending.scaled
     _need(x, torch.bfloat16, "x")
     _need(weight, torch.bfloat16, "weight")
     tokens, k = x.shape
@@ -769,6 +819,34 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | Non
         if tiles > _GEMM_COUNTERS or tiles * slices * bn * 128 > _GEMM_SCRATCH_FLOATS:
             raise KernelError("split-K workspace too small for this problem")
     a, b = (weight, x) if swapped else (x, weight)
+    if to_stream is not None:
+        stream, norm_weight = to_stream
+        _need(stream, torch.float32, "stream")
+        _need(norm_weight, None, "norm weight")
+        if (swiglu or pending is not None or out_dtype != torch.bfloat16 or stream.shape != out.shape
+                or not (swapped and 2 <= slices <= 8 and tokens <= bn) or features % 128
+                or norm_weight.numel() != features or norm_weight.dtype not in (torch.float32, torch.bfloat16)):
+            raise KernelError("a product into the stream needs its plain bfloat16 output, K slices in a cluster, a "
+                              "width in steps of 128 and a stream of its shape")
+        scaled = torch.empty((tokens, features), dtype=torch.bfloat16, device=x.device)
+        squares = torch.empty((tokens, features // 128), dtype=torch.float32, device=x.device)
+        rc = gemm_library().ss_gemm_tc5_to_stream(a.data_ptr(), b.data_ptr(), _ptr(bias), bias_f32, a.shape[0], b.shape[0],
+                                                  k, k, k, bn, slices, stream.data_ptr(), squares.data_ptr(),
+                                                  scaled.data_ptr(), norm_weight.data_ptr(),
+                                                  int(norm_weight.dtype == torch.float32),
+                                                  error_word(x.device).data_ptr(), _stream())
+        _check(rc, "gemm_tcgen05 into the stream")
+        return scaled, squares
+    if pending is not None:
+        if not swapped or bn > 64 or pending.weight.numel() != k or pending.squares.shape[0] != tokens:
+            raise KernelError("a pending norm feeds the swapped product of at most 64 tokens, over the stream's whole width")
+        rc = gemm_library().ss_gemm_tc5_scaled(a.data_ptr(), b.data_ptr(), pending.squares.data_ptr(),
+                                               pending.squares.shape[1], float(pending.eps), _ptr(bias), bias_f32,
+                                               out.data_ptr(), a.shape[0], tokens, k, k, k, out.shape[1], bn,
+                                               int(out_dtype == torch.float32), slices, int(swiglu), _ptr(partial),
+                                               _ptr(counters), error_word(x.device).data_ptr(), _stream())
+        _check(rc, "gemm_tcgen05 behind a pending norm")
+        return out
     rc = gemm_library().ss_gemm_tc5(a.data_ptr(), b.data_ptr(), _ptr(bias), bias_f32, out.data_ptr(), a.shape[0],
                                     b.shape[0], k, k, k, out.shape[1], bn, int(swapped), int(out_dtype == torch.float32),
                                     slices, int(swiglu), _ptr(partial), _ptr(counters),
@@ -861,7 +939,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     overlaps its first fetches with the kernel before it; from ``MANY_TOKENS`` tokens (prompt portions) and with
     enough output tiles (``many_tokens_fits``) the persistent two-SM tcgen05 kernel; everything else runs the
     library matrix product, as the reference's
-    nn.Linear does (slipstream/models/layers/attention.py:132-135)."""
+    nn.Linear does (slipstream/models/layers/attention.py:132-135).  ``x`` may be a `PendingNorm`."""
+    if isinstance(x, PendingNorm):
+        if takes_pending_norm(x, weight.shape[0]):
+            return gemm_tcgen05(x, weight, bias, out_dtype)
+        x = x.materialize()
     if x.dtype == torch.float32:
         return gemm_simt(x, weight, bias, out_dtype)
     sms = sm_count(x.device)
@@ -879,6 +961,39 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     return out
 
 
+def adds_to_stream(tokens: int, features: int, k: int, sms: int | None = None) -> bool:
+    """True where a bfloat16 projection can add its output to the float32 stream itself and prepare the norm
+    behind it: the streaming tcgen05 kernel with its K slices as a thread-block cluster (decode steps), a width in
+    steps of 128."""
+    sms = sms or sm_count()
+    if not _state.get("norm_rides_along", True) or features % 128 != 0 or tokens > CLUSTER_BATCH \
+            or not streams_weights(tokens, features, k, sms):
+        return False
+    swapped, bn, slices = gemm_plan(tokens, features, k, sms)
+    return swapped and 2 <= slices <= 8 and tokens <= bn
+
+
+def set_norm_fusion(enabled: bool) -> None:
+    """Whether `linear_add_rmsnorm` may leave the norm to the products around it (on by default; off for
+    comparisons)."""
+    _state["norm_rides_along"] = bool(enabled)
+
+
+def linear_add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, residual: torch.Tensor,
+                       norm_weight: torch.Tensor, eps: float, out_dtype: torch.dtype) -> "torch.Tensor | PendingNorm":
+    """``residual += x @ weight.T + bias`` (float32 stream, in place; the branch output rounded to the compute dtype
+    first), then the RMS norm of the stream times ``norm_weight``: a branch's last projection with the add and the
+    norm that follow it.  With few bfloat16 tokens the projection adds to the stream in its epilogue and the
+    norm comes back as a `PendingNorm`, to be finished by the next product (no norm kernel); everything
+    else is `linear` followed by `add_rmsnorm`."""
+    if x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and residual.shape == (x.shape[0], weight.shape[0]) \
+            and norm_weight.numel() == weight.shape[0] \
+            and adds_to_stream(x.shape[0], weight.shape[0], x.shape[1], sm_count(x.device)):
+        scaled, squares = gemm_tcgen05(x, weight, bias, to_stream=(residual, norm_weight))
+        return PendingNorm(residual, scaled, squares, norm_weight, eps, out_dtype)
+    return add_rmsnorm(residual, linear(x, weight, bias), norm_weight, eps, out_dtype)
+
+
 def many_tokens_swiglu_fits(tokens: int, features: int, sms: int | None = None) -> bool:
     """Where the persistent tcgen05 kernel with its fused SwiGLU epilogue is at least as fast as the library
     product followed by the SwiGLU kernel: enough 256 x 256 tiles to keep every pair of SMs busy for several
@@ -890,7 +1005,11 @@ def many_tokens_swiglu_fits(tokens: int, features: int, sms: int | None = None) 
 
 def gate_up_swiglu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, block: int) -> torch.Tensor:
     """``silu(x @ Wg.T + bg) * (x @ Wu.T + bu)`` where ``weight`` [2 I, K] holds gate and up rows alternating in
-    runs of ``block``.  Small bfloat16 batches with runs of 64 do it in one kernel."""
+    runs of ``block``.  Small bfloat16 batches with runs of 64 do it in one kernel.  ``x`` may be a `PendingNorm`."""
+    if isinstance(x, PendingNorm):
+        if block == 64 and weight.shape[0] % 128 == 0 and takes_pending_norm(x, weight.shape[0]):
+            return gemm_tcgen05(x, weight, bias, swiglu=True)
+        x = x.materialize()
     if x.dtype == torch.bfloat16 and block == 64 and weight.shape[0] % 128 == 0 and x.shape[1] % 8 == 0:
         sms = sm_count(x.device)
         if streams_weights(x.shape[0], weight.shape[0], x.shape[1], sms):
@@ -911,5 +1030,5 @@ def set_programmatic_launch(enabled: bool) -> None:
 
 
 __all__ = ["KernelError", "KernelBuildError", "embedding", "add_rmsnorm", "rope_and_cache", "swiglu",
-           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "prepare_decode", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_fits", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "sm_count", "linear", "check_errors", "raise_for_status", "error_word", "ops_library",
+           "gemm_simt", "paged_attention_simt", "paged_attention", "fuses_rope", "paged_attention_prefill", "paged_attention_prefill_tcgen05", "prefill_key_parts", "tcgen05_attention_fits", "paged_attention_decode", "decode_scratch", "decode_slices", "is_long_context", "require_cuda", "argmax", "sample", "mark_seen", "gather_tokens", "prepare_decode", "gemm_tcgen05", "gemm_tcgen05_many", "many_tokens_fits", "many_tokens_swiglu_fits", "gemm_plan", "gemm_library", "gate_up_swiglu", "set_programmatic_launch", "launch_count", "count_launches", "sm_count", "linear", "linear_add_rmsnorm", "adds_to_stream", "takes_pending_norm", "PendingNorm", "set_norm_fusion", "check_errors", "raise_for_status", "error_word", "ops_library",
            "attention_library"]

@@ -1,7 +1,7 @@
 """Parts a model is put together from; importing this package registers the built-in ones."""
 
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Block, CacheSpec,
-                   Embedding, FeedForward, Head, LayerBinding, Mixer, Norm, Part, PositionEncoding, Registry, Runtime,
+                   Embedding, FeedForward, Head, IntoNorm, LayerBinding, Mixer, Norm, Part, PositionEncoding, Registry, Runtime,
                    StateSpec, WeightSpec)
 from .attention import PagedAttention
 from .block import PreNormBlock
@@ -11,6 +11,6 @@ from .norm import RMSNorm
 from .rotary import NoPositionEncoding, RotaryEncoding
 
 __all__ = ["BLOCKS", "EMBEDDINGS", "HEADS", "Embedding", "Head", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "Block", "CacheSpec",
-           "FeedForward", "LayerBinding", "Mixer", "Norm", "Part", "PositionEncoding", "Registry",
+           "FeedForward", "IntoNorm", "LayerBinding", "Mixer", "Norm", "Part", "PositionEncoding", "Registry",
            "Runtime", "StateSpec", "WeightSpec", "PagedAttention", "PreNormBlock", "LMHead",
            "TokenEmbedding", "SwiGLUFeedForward", "RMSNorm", "NoPositionEncoding", "RotaryEncoding"]

@@ -15,12 +15,14 @@ import torch
 
 from slipstream_b200 import ops
 
-from .base import MIXERS, CacheSpec, LayerBinding, Mixer, PositionEncoding, Runtime, WeightSpec
+from .base import MIXERS, CacheSpec, IntoNorm, LayerBinding, Mixer, PositionEncoding, Runtime, WeightSpec
 
 
 @MIXERS.register("paged_attention")
 class PagedAttention(Mixer):
     cuda_graph_safe = True
+    takes_into = True
+    takes_pending_norm = True
 
     def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: PositionEncoding, qkv_bias: bool = True, out_bias: bool = False,
@@ -114,7 +116,7 @@ class PagedAttention(Mixer):
         write into the decode kernel is off for it, since that kernel takes the projection output as it is."""
         return None
 
-    def forward(self, x: torch.Tensor, ctx, layer: LayerBinding) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx, layer: LayerBinding, into: IntoNorm | None = None) -> torch.Tensor:
         meta = ctx.groups[layer.group]
         qkv = ops.linear(x, self.qkv_weight, self.qkv_b)
         plain_projection = type(self).after_projection is PagedAttention.after_projection
@@ -131,4 +133,6 @@ class PagedAttention(Mixer):
         ops.paged_attention(qkv, out, layer.kv, meta.block_tables, ctx, self.num_heads, self.num_kv_heads,
                             self.head_dim, self.scale, self.window or 0,
                             rope=(inv_freq, rotary_dim) if fused else None)
+        if into is not None:
+            return into.close(out, self.o_weight, self.o_b)
         return ops.linear(out, self.o_weight, self.o_b)

@@ -134,6 +134,36 @@ class Norm(Part):
         returned, and ``residual`` is left untouched."""
         raise NotImplementedError
 
+    def add_norm_of_linear(self, residual: torch.Tensor, x: torch.Tensor, weight: torch.Tensor,
+                           bias: torch.Tensor | None):
+        """``add_norm(residual, x @ weight.T + bias)``: a branch's last projection with the add and the norm
+        that follow it.  A norm that can be split between the projection in front and the product behind it
+        overrides this and may return an ``ops.PendingNorm`` instead of a tensor; the block hands that only to a
+        part whose ``takes_pending_norm`` is True (its first product accepts it) and otherwise calls its
+        ``materialize()``."""
+        from slipstream_b200 import ops
+        return self.add_norm(residual, ops.linear(x, weight, bias))
+
+
+@dataclass
+class IntoNorm:
+    """Handed to a mixer or feed-forward whose ``takes_into`` is True: instead of returning its output it ends
+    with ``into.close(x, weight, bias)``, its last projection, and returns what that returns, the norm of the
+    stream with its output added (the add is done: the caller adds nothing), as a tensor or a pending norm."""
+
+    norm: Norm
+    residual: torch.Tensor
+
+    def close(self, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None):
+        return self.norm.add_norm_of_linear(self.residual, x, weight, bias)
+
+
+def settle(x, part: Part) -> torch.Tensor:
+    """``x`` as ``part`` can take it: a pending norm is computed now unless the part's first product accepts it."""
+    if isinstance(x, torch.Tensor) or getattr(part, "takes_pending_norm", False):
+        return x
+    return x.materialize()
+
 
 class PositionEncoding(Part):
     """Where positions enter.  ``on_embedding`` may add to the residual stream;
@@ -150,7 +180,12 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    """Mixes information across the tokens of a request (attention here)."""
+    """Mixes information across the tokens of a request (attention here).  A mixer that ends in a projection may
+    set ``takes_into`` and accept ``forward(x, ctx, layer, into=None)`` (see `IntoNorm`); one that hands ``x``
+    to ``ops.linear`` first and otherwise only asks its shape, dtype and device may set ``takes_pending_norm``."""
+
+    takes_into = False
+    takes_pending_norm = False
 
     def cache_spec(self) -> CacheSpec | None:
         return None
@@ -163,6 +198,13 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    """A feed-forward that ends in a projection may set ``takes_into`` and accept ``forward(x, ctx, into=None)``
+    (see `IntoNorm`); one that hands ``x`` to ``ops.linear`` or ``ops.gate_up_swiglu`` first may set
+    ``takes_pending_norm``."""
+
+    takes_into = False
+    takes_pending_norm = False
+
     def forward(self, x: torch.Tensor, ctx: "StepContext") -> torch.Tensor:
         raise NotImplementedError
 
@@ -194,6 +236,22 @@ class Block(Part):
     def forward(self, residual: torch.Tensor, pending: torch.Tensor | None,
                 ctx: "StepContext", layer: "LayerBinding") -> tuple[torch.Tensor, torch.Tensor | None]:
         raise NotImplementedError
+
+    def first_norm(self) -> Norm | None:
+        """The norm this block applies first to (stream + pending), if it can take that norm's result instead
+        (``forward_chained``'s ``normed``); None: the block wants the stream and the pending output."""
+        return None
+
+    def forward_chained(self, residual: torch.Tensor, pending: torch.Tensor | None, normed: torch.Tensor | None,
+                        following: Norm | None, ctx: "StepContext",
+                        layer: "LayerBinding") -> tuple[torch.Tensor, torch.Tensor | None, torch.Tensor | None]:
+        """``forward`` for a model that lets a block's last projection end in the next block's first norm.
+        ``normed``: ``first_norm()`` of the stream, already computed by the block before, as a tensor or a pending
+        norm (then ``pending`` is None and added).  ``following``: the next block's first norm, or None.  Returns (stream, pending, normed): either
+        a pending output, or, if it applied ``following``, that norm's result.  The default chains nothing."""
+        assert normed is None
+        residual, pending = self.forward(residual, pending, ctx, layer)
+        return residual, pending, None
 
 
 @dataclass

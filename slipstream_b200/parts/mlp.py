@@ -8,12 +8,14 @@ import torch
 
 from slipstream_b200 import ops
 
-from .base import FEED_FORWARDS, FeedForward, Runtime, WeightSpec
+from .base import FEED_FORWARDS, FeedForward, IntoNorm, Runtime, WeightSpec
 
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLUFeedForward(FeedForward):
     cuda_graph_safe = True
+    takes_into = True
+    takes_pending_norm = True
 
     def __init__(self, name: str, hidden_size: int, intermediate_size: int, bias: bool = False) -> None:
         self.name = name
@@ -55,6 +57,8 @@ class SwiGLUFeedForward(FeedForward):
     def weight_bytes(self) -> int:
         return (self.gate_up.numel() + self.down.numel()) * self.down.element_size()
 
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx, into: IntoNorm | None = None) -> torch.Tensor:
         hidden = ops.gate_up_swiglu(x, self.gate_up, self.gate_up_bias, self.block)
+        if into is not None:
+            return into.close(hidden, self.down, self.down_bias)
         return ops.linear(hidden, self.down, self.down_bias)

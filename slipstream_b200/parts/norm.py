@@ -39,5 +39,9 @@ class RMSNorm(Norm):
                  rows: torch.Tensor | None = None) -> torch.Tensor:
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.runtime.dtype, rows=rows)
 
+    def add_norm_of_linear(self, residual: torch.Tensor, x: torch.Tensor, weight: torch.Tensor,
+                           bias: torch.Tensor | None) -> torch.Tensor:
+        return ops.linear_add_rmsnorm(x, weight, bias, residual, self.weight, self.eps, self.runtime.dtype)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.add_norm(x, None)

@@ -418,6 +418,96 @@ def test_tcgen05_fused_swiglu(tokens, inter, k, bias):
     ops().check_errors(torch.device(DEV))
 
 
+@pytest.mark.parametrize("tokens, features, k, bias, w_f32", [(8, 3584, 3584, False, False), (1, 3584, 18944, False, False),
+                                                             (16, 896, 4864, True, True), (5, 256, 136, True, False),
+                                                             (3, 1024, 512, False, True), (11, 5120, 13824, False, False),
+                                                             (2, 3584, 3584, False, False)])
+def test_projection_into_the_stream_and_the_norm_finished_by_the_next_product(tokens, features, k, bias, w_f32):
+    """`linear_add_rmsnorm` with few bfloat16 tokens: the projection adds its output to the float32 stream in its
+    epilogue and leaves round(norm weight * stream) and the sums of squares; the norm comes back pending, and the
+    next product runs on that matrix and scales every token's output at the end.  Against float64 arithmetic with
+    the same roundings (the branch output to bfloat16 before the add, weight * stream to bfloat16), against the
+    exact norm, and against the kernels it replaces (the same stream bit for bit)."""
+    torch.manual_seed(features + tokens)
+    assert ops().adds_to_stream(tokens, features, k)
+    x = torch.randn(tokens, k, device=DEV).bfloat16()
+    w = (torch.randn(features, k, device=DEV) * 0.05).bfloat16()
+    b = torch.randn(features, device=DEV).bfloat16() if bias else None
+    nw = 1 + 0.1 * torch.randn(features, device=DEV)
+    nw = nw if w_f32 else nw.bfloat16()
+    stream0 = torch.randn(tokens, features, device=DEV) * 3
+    stream0[0] *= 30  # rows of different size: each needs its own scale
+    eps = 1e-5
+    delta = (x.double() @ w.double().T + (b.double() if bias else 0)).bfloat16().double()
+    stream_ref = (stream0.double() + delta).float()
+    launches = ops().launch_count()
+    stream = stream0.clone()
+    got = ops().linear_add_rmsnorm(x, w, b, stream, nw, eps, torch.bfloat16)
+    assert ops().launch_count() == launches + 1 and isinstance(got, ops().PendingNorm) and got.shape == stream.shape
+    # the branch output may round the other way where the float32 sum lies at a tie: a step of its bfloat16
+    assert rel_err(stream, stream_ref) < 3e-3 and (stream - stream_ref).abs().max() <= 2 ** -6 * delta.abs().max()
+    assert torch.allclose(got.squares.double().sum(1), stream.double().pow(2).sum(1), rtol=1e-5)
+    assert torch.equal(got.scaled, (nw.float() * stream).bfloat16())
+    rstd = torch.rsqrt(stream.double().pow(2).mean(-1, keepdim=True) + eps)
+    exact = nw.double() * stream.double() * rstd               # the norm without any rounding
+    ops().set_norm_fusion(False)
+    try:
+        stream2 = stream0.clone()
+        two = ops().linear_add_rmsnorm(x, w, b, stream2, nw, eps, torch.bfloat16)
+        assert ops().launch_count() == launches + 3 and isinstance(two, torch.Tensor)
+    finally:
+        ops().set_norm_fusion(True)
+    assert torch.equal(stream, stream2)
+    assert rel_err(two, exact) < 1e-2
+    # the products behind the norm: a projection with bias, and gate/up with SwiGLU, each from the pending norm
+    # (37,888 and 19,072 weight rows: a tile per SM and more, every block walks all K steps alone and stores its tile
+    # itself; the others: K slices in a cluster)
+    for features2, swiglu in ((328, False), (4608, False), (19072, False), (1024, True), (37888, True)):
+        assert ops().takes_pending_norm(got, features2)
+        if features2 > 5000 and tokens not in (1, 2, 8):
+            continue
+        w2 = (torch.randn(features2, features, device=DEV) * 0.05).bfloat16()
+        b2 = torch.randn(features2, device=DEV).bfloat16()
+        launches = ops().launch_count()
+        same_roundings = (got.scaled.double() @ w2.double().T) * rstd + b2.double()
+        unrounded = exact @ w2.double().T + b2.double()
+        if swiglu:
+            inside, after = ops().gate_up_swiglu(got, w2, b2, 64), ops().gate_up_swiglu(two, w2, b2, 64)
+
+            def act(y):
+                g, u = (y.view(tokens, -1, 2, 64)[:, :, i].reshape(tokens, -1) for i in (0, 1))
+                return g * torch.sigmoid(g) * u
+            same_roundings, unrounded = act(same_roundings), act(unrounded)
+        else:
+            inside, after = ops().linear(got, w2, b2), ops().linear(two, w2, b2)
+        assert ops().launch_count() == launches + 2, "one launch each: no norm kernel"
+        assert rel_err(inside, same_roundings) < 6e-3, (features2, swiglu)
+        # one rounding of the activations instead of two: no further from the exact result than the norm kernel's way
+        assert rel_err(inside, unrounded) <= max(rel_err(after, unrounded) * 1.2, 6e-3), (features2, swiglu)
+        assert torch.equal(inside, ops().gate_up_swiglu(got, w2, b2, 64) if swiglu else ops().linear(got, w2, b2))
+    # a product that does not stream its weights, or a part that wants a tensor, gets the norm kernel's result
+    assert rel_err(got.materialize(), exact) < 1e-2
+    wide = (torch.randn(72, features, device=DEV) * 0.05).float()
+    as_f32 = ops().PendingNorm(got.stream, got.scaled, got.squares, nw.float(), eps, torch.float32)
+    assert rel_err(ops().linear(as_f32, wide), (nw.double() * stream.double() * rstd) @ wide.double().T) < 1e-4
+    ops().check_errors(torch.device(DEV))
+
+
+def test_the_add_and_norm_stay_two_launches_where_the_product_is_not_a_cluster():
+    """float32, many tokens, a width that is no multiple of 128: `linear` then `add_rmsnorm`, same result."""
+    for dtype, tokens, features, k in ((torch.float32, 4, 128, 64), (torch.bfloat16, 40, 256, 128), (torch.bfloat16, 4, 200, 64)):
+        torch.manual_seed(tokens)
+        assert dtype == torch.float32 or not ops().adds_to_stream(tokens, features, k)
+        x = torch.randn(tokens, k, device=DEV).to(dtype)
+        w = (torch.randn(features, k, device=DEV) * 0.1).to(dtype)
+        nw = (1 + 0.1 * torch.randn(features, device=DEV)).to(dtype)
+        stream = torch.randn(tokens, features, device=DEV)
+        want_stream = stream.clone()
+        want = ops().add_rmsnorm(want_stream, ops().linear(x, w), nw, 1e-6, dtype)
+        got = ops().linear_add_rmsnorm(x, w, None, stream, nw, 1e-6, dtype)
+        assert torch.equal(got, want) and torch.equal(stream, want_stream)
+
+
 TC5_CASES = [  # lens, q_lens, n_q, n_kv, d, page
     ([200, 129], [200, 100], 6, 3, 128, 16),
     ([300, 64, 65, 1, 130], [3, 64, 1, 1, 130], 28, 4, 128, 16),   # groups of 7: 18 tokens per tile
