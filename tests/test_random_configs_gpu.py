@@ -14,8 +14,10 @@ from test_replay_gpu import TOLERANCE, oracle, run_plan
 
 pytestmark = pytest.mark.gpu
 
-# seed -> head size it draws (the draw is checked below, so that a change of the generator is noticed)
-SEEDS = {31: 16, 14: 32, 21: 48, 0: 64, 13: 80, 7: 96, 25: 112, 12: 128, 17: 160, 5: 192, 19: 256}
+# seed -> head size it draws (the draw is checked below, so that a change of the generator is noticed).  Seeds 13,
+# 100 and 167 draw widths of 128, 128 and 256: there a decode step's projections add themselves to the stream and
+# the norm behind them is finished by the next product, while prompt portions run the norm kernel.
+SEEDS = {31: 16, 14: 32, 21: 48, 0: 64, 13: 80, 7: 96, 25: 112, 12: 128, 17: 160, 5: 192, 19: 256, 100: 48, 167: 64}
 
 
 def draw(seed):
