@@ -258,6 +258,8 @@ def to_device(plan: HostPlan, device: torch.device) -> StepContext:
                       request_ids=[e.request_id for e in plan.entries], device=device,
                       num_logits=plan.logit_rows.size)
     ctx.extras["host_buffer"] = host  # keep the pinned buffer alive until the copy has run
+    # every row's logits, in order: the final norm needs no selection of rows
+    ctx.extras["every_row_wanted"] = plan.logit_rows.size == N and bool((plan.logit_rows == np.arange(N)).all())
     return ctx
 
 

@@ -99,6 +99,7 @@ class DecodeGraph:
                                state_slots=view("slots"), first_chunk=view("first"), logit_rows=view("logit_rows"),
                                groups=groups, q_lens_host=ones, seq_lens_host=ones, request_ids=[], device=device,
                                num_logits=B)
+        self.ctx.extras["every_row_wanted"] = True  # logit_rows is 0 .. B - 1 in every replay
         self._views = {name: view(name) for name in ("token_ids", "src_rows", "n_patches", "patch_idx", "patch_val")}
         # what the parts want fixed for this bucket and these variants
         variant_of = {part.capture_group(): variant for part, variant in zip(runner.variant_parts, variants)}

@@ -17,7 +17,7 @@ import torch
 
 from slipstream_b200.cache import GroupLayout
 from slipstream_b200.parts.base import (Block, CacheSpec, Embedding, Head, LayerBinding, Norm, Part,
-                                        PositionEncoding, Runtime, StateSpec, WeightSpec)
+                                        PositionEncoding, Runtime, StateSpec, WeightSpec, settle)
 
 
 @dataclass(frozen=True)
@@ -135,12 +135,16 @@ class DecoderLM:
         if self.position_encoding is not None:
             self.position_encoding.on_embedding(residual, ctx)
         pending = normed = None
+        # the last block may end in the final norm when that norm needs no selection of rows
+        closing = self.final_norm if ctx.extras.get("every_row_wanted") and ctx.num_logits else None
         for pos, (entry, binding) in enumerate(zip(self.order, self.bindings)):
             # a block's last projection may end in the first norm of the block that runs next
-            following = self.blocks[self.order[pos + 1].block].first_norm() if pos + 1 < len(self.order) else None
+            following = self.blocks[self.order[pos + 1].block].first_norm() if pos + 1 < len(self.order) else closing
             residual, pending, normed = self.blocks[entry.block].forward_chained(residual, pending, normed, following,
                                                                                  ctx, binding)
         if ctx.num_logits == 0:
             return torch.empty((0, self.lm_head.vocab_size), dtype=torch.float32, device=residual.device)
+        if normed is not None:
+            return self.lm_head.forward(settle(normed, self.lm_head))
         x = self.final_norm.add_norm(residual, pending, rows=ctx.logit_rows)
         return self.lm_head.forward(x)

@@ -217,9 +217,12 @@ class Embedding(Part):
 
 
 class Head(Part):
-    """Normalised rows of the stream (compute dtype [M, hidden]) into float32 logits [M, vocab_size]."""
+    """Normalised rows of the stream (compute dtype [M, hidden]) into float32 logits [M, vocab_size].  A head
+    that hands ``x`` to ``ops.linear`` first may set ``takes_pending_norm`` (see `IntoNorm`): when every row's
+    logits are wanted, the last block then ends in the final norm."""
 
     vocab_size: int
+    takes_pending_norm = False
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError

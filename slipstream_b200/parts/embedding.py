@@ -34,6 +34,7 @@ class TokenEmbedding(Embedding):
 @HEADS.register("linear")
 class LMHead(Head):
     cuda_graph_safe = True
+    takes_pending_norm = True  # ``forward`` hands x to ``ops.linear`` as it is
 
     def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: str | None) -> None:
         self.name = name

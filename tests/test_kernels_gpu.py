@@ -485,6 +485,10 @@ def test_projection_into_the_stream_and_the_norm_finished_by_the_next_product(to
         # one rounding of the activations instead of two: no further from the exact result than the norm kernel's way
         assert rel_err(inside, unrounded) <= max(rel_err(after, unrounded) * 1.2, 6e-3), (features2, swiglu)
         assert torch.equal(inside, ops().gate_up_swiglu(got, w2, b2, 64) if swiglu else ops().linear(got, w2, b2))
+    # float32 logits behind a final norm: every block stores its tile itself
+    head = (torch.randn(19200, features, device=DEV) * 0.05).bfloat16()
+    logits = ops().linear(got, head, None, out_dtype=torch.float32)
+    assert logits.dtype == torch.float32 and rel_err(logits, (got.scaled.double() @ head.double().T) * rstd) < 1e-4
     # a product that does not stream its weights, or a part that wants a tensor, gets the norm kernel's result
     assert rel_err(got.materialize(), exact) < 1e-2
     wide = (torch.randn(72, features, device=DEV) * 0.05).float()
