@@ -537,6 +537,19 @@ struct ManyArgs {
     int out_f32, bias_f32;
     int swiglu;  // B's rows alternate 64 gate and 64 up features; C gets N / 2 columns
     int tile_cols;  // width of a tile (256 with swiglu)
+    // As in GemmArgs: a branch's last projection adds its output (rounded to bfloat16) to the float32 stream
+    // residual [M, N] instead of writing C, and leaves scaled [M, N] = round(norm_weight * stream) in bfloat16 and
+    // tile_squares [M, tiles across N] = the sum of squares of each row's part of a tile (N a multiple of 16) ...
+    float* residual;
+    float* tile_squares;
+    bf16* scaled;
+    const void* norm_weight;
+    int norm_w_f32;
+    // ... and the product behind that norm multiplies row m of its output, before the bias, by
+    // rsqrt(sum of in_squares[m][0 .. in_tiles) / K + in_eps).
+    const float* in_squares;
+    int in_tiles;
+    float in_eps;
 };
 
 __device__ __forceinline__ float bias_many(const ManyArgs& g, int f) {
@@ -654,16 +667,101 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             const int buf = j & 1;
             const int m0 = (t % n_m) * 2 * TC_BM + rank * TC_BM, n0 = (t / n_m) * bn;
             const int m = m0 + quarter * 32 + lane;
+            // while the tile's products run: the scale of this thread's row (the norm in front), or the first
+            // chunks of the stream that the row is added to
+            float rstd = 1.f;
+            if (g.in_squares != nullptr && m < g.M) {
+                const float* sq = g.in_squares + (int64_t)m * g.in_tiles;
+                float ss = 0.f;
+                int i = 0;
+                for (; i + 4 <= g.in_tiles; i += 4) {
+                    const float a0 = __ldcg(sq + i), a1 = __ldcg(sq + i + 1), a2 = __ldcg(sq + i + 2), a3 = __ldcg(sq + i + 3);
+                    ss += a0; ss += a1; ss += a2; ss += a3;
+                }
+                for (; i < g.in_tiles; ++i) ss += __ldcg(sq + i);
+                rstd = 1.0f / sqrtf(ss / (float)g.K + g.in_eps);
+            }
+            constexpr int AHEAD = 4;  // 16-column chunks of the stream in flight per thread
+            float4 ahead[AHEAD][4];
+            auto fetch = [&](int c, float4 (&dst)[4]) {
+                if (m < g.M && c < bn && n0 + c < g.N) {
+                    const float4* p = reinterpret_cast<const float4*>(g.residual + (int64_t)m * g.N + n0 + c);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) dst[q] = __ldcs(p + q);
+                }
+            };
+            if (g.residual != nullptr) {
+#pragma unroll
+                for (int u = 0; u < AHEAD; ++u) fetch(16 * u, ahead[u]);
+            }
             ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (j >> 1) & 1, gave_up));
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = tmem + ((uint32_t)(quarter * 32) << 16) + buf * MT_BN;
-            if (!g.swiglu) {
+            if (g.residual != nullptr) {
+                float sq = 0.f;
+#pragma unroll 1
+                for (int c0 = 0; c0 < bn; c0 += 16 * AHEAD) {
+#pragma unroll
+                    for (int u = 0; u < AHEAD; ++u) {
+                        const int c = c0 + 16 * u;
+                        uint32_t r[16];
+                        if (c < bn) tmem_ld16(acc + c, r);  // (the same for the whole warp)
+                        if (c < bn && m < g.M && n0 + c < g.N) {  // N is a multiple of 16: a chunk is whole or absent
+                            float w[16], x[16];
+                            if (g.norm_w_f32) {
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    const float4 t4 = __ldg(reinterpret_cast<const float4*>((const float*)g.norm_weight + n0 + c) + q);
+                                    w[4 * q] = t4.x; w[4 * q + 1] = t4.y; w[4 * q + 2] = t4.z; w[4 * q + 3] = t4.w;
+                                }
+                            } else {
+#pragma unroll
+                                for (int q = 0; q < 2; ++q) {
+                                    const uint4 t4 = __ldg(reinterpret_cast<const uint4*>((const bf16*)g.norm_weight + n0 + c) + q);
+                                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t4);
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) { w[8 * q + 2 * e] = __low2float(h[e]); w[8 * q + 2 * e + 1] = __high2float(h[e]); }
+                                }
+                            }
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                x[4 * q] = ahead[u][q].x; x[4 * q + 1] = ahead[u][q].y; x[4 * q + 2] = ahead[u][q].z; x[4 * q + 3] = ahead[u][q].w;
+                            }
+                            uint32_t packed[8];
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) {
+                                float v = __uint_as_float(r[e]);
+                                if (g.bias) v += bias_many(g, n0 + c + e);
+                                x[e] = __fadd_rn(x[e], to_float(__float2bfloat16_rn(v)));
+                                sq = fmaf(x[e], x[e], sq);
+                            }
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const __nv_bfloat162 v = __floats2bfloat162_rn(w[2 * e] * x[2 * e], w[2 * e + 1] * x[2 * e + 1]);
+                                packed[e] = *reinterpret_cast<const uint32_t*>(&v);
+                            }
+                            float4* dst = reinterpret_cast<float4*>(g.residual + (int64_t)m * g.N + n0 + c);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) dst[q] = make_float4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
+                            uint4* sc = reinterpret_cast<uint4*>(g.scaled + (int64_t)m * g.N + n0 + c);
+                            sc[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            sc[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        }
+                        fetch(c + 16 * AHEAD, ahead[u]);
+                    }
+                }
+                if (m < g.M) g.tile_squares[(int64_t)m * n_n + t / n_m] = sq;
+            } else if (!g.swiglu) {
 #pragma unroll 1
                 for (int c = 0; c < bn; c += 16) {
                     uint32_t r[16];
                     tmem_ld16(acc + c, r);
                     if (m >= g.M || n0 + c >= g.N) continue;
+                    if (g.in_squares != nullptr) {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * rstd);
+                    }
                     if (g.bias) {
 #pragma unroll
                         for (int e = 0; e < 16; ++e) {
@@ -701,8 +799,8 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     uint32_t packed[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
-                        float v0 = __uint_as_float(gr[2 * e]), v1 = __uint_as_float(gr[2 * e + 1]);
-                        float u0 = __uint_as_float(ur[2 * e]), u1 = __uint_as_float(ur[2 * e + 1]);
+                        float v0 = __uint_as_float(gr[2 * e]) * rstd, v1 = __uint_as_float(gr[2 * e + 1]) * rstd;
+                        float u0 = __uint_as_float(ur[2 * e]) * rstd, u1 = __uint_as_float(ur[2 * e + 1]) * rstd;
                         if (g.bias) {
                             v0 += bias_many(g, n0 + gc + 2 * e); v1 += bias_many(g, n0 + gc + 2 * e + 1);
                             u0 += bias_many(g, n0 + gc + 64 + 2 * e); u1 += bias_many(g, n0 + gc + 64 + 2 * e + 1);
@@ -876,9 +974,27 @@ extern "C" int ss_gemm_tc5_scaled(const void* A, const void* B, const float* in_
 // bfloat16 and K-major, K a multiple of 8.  swiglu: B's rows alternate 64 gate and 64 up features (N a multiple of
 // 128); C [M, N / 2] = silu(gate) * up.  One persistent block per SM, in pairs; tiles of 256 rows and tile_cols
 // columns (0: chosen here).
-extern "C" int ss_gemm_tc5_many(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
-                                int64_t lda, int64_t ldb, int64_t ldc, int out_f32, int swiglu, int tile_cols,
-                                int* err, cudaStream_t stream) {
+// The width of the tiles that ss_gemm_tc5_many takes when it is given none (see there).
+extern "C" int ss_gemm_tc5_many_tile_cols(int M, int N, int swiglu) {
+    if (swiglu) return MT_BN;
+    const int n_sms = ss_sm_count();
+    const int max_pairs = n_sms / 2 > 0 ? n_sms / 2 : 1;
+    const int n_m = (M + 2 * TC_BM - 1) / (2 * TC_BM);
+    auto cost = [&](int w) {
+        const int tiles = n_m * ((N + w - 1) / w);
+        const int per_tile = (w / 2 > 64 + w / 4 ? w / 2 : 64 + w / 4) + 4;
+        return (int64_t)((tiles + max_pairs - 1) / max_pairs) * per_tile;
+    };
+    int bn = MT_BN;
+    int64_t best = cost(MT_BN) * 95 / 100;
+    for (int w = MT_BN - 16; w >= 64; w -= 16)
+        if (cost(w) < best) { best = cost(w); bn = w; }
+    return bn;
+}
+
+static int gemm_tc5_many(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
+                         int64_t lda, int64_t ldb, int64_t ldc, int out_f32, int swiglu, int tile_cols,
+                         const NormEnds& ends, int* err, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return -2003;
     if (((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -2004;
@@ -891,18 +1007,12 @@ extern "C" int ss_gemm_tc5_many(const void* A, const void* B, const void* bias, 
     // bytes of B, written by the copies and read by the product, at 128 bytes a cycle): narrower tiles are
     // bound by shared memory, so they only pay where they save a round (measured at 2,048 x 3,584 x 18,944:
     // 210 us at 256, 198 us at 208).  256 stays unless another width is 5 % better.
-    int bn = tile_cols > 0 ? tile_cols : MT_BN;
-    if (tile_cols <= 0 && !swiglu) {
-        auto cost = [&](int w) {
-            const int tiles = n_m * ((N + w - 1) / w);
-            const int per_tile = (w / 2 > 64 + w / 4 ? w / 2 : 64 + w / 4) + 4;
-            return (int64_t)((tiles + max_pairs - 1) / max_pairs) * per_tile;
-        };
-        int64_t best = cost(MT_BN) * 95 / 100;
-        for (int w = MT_BN - 16; w >= 64; w -= 16)
-            if (cost(w) < best) { best = cost(w); bn = w; }
-    }
+    const int bn = tile_cols > 0 ? tile_cols : ss_gemm_tc5_many_tile_cols(M, N, swiglu);
     if (bn < 16 || bn > MT_BN || bn % 16 != 0 || (swiglu && bn != MT_BN)) return -2006;
+    if (ends.residual && (swiglu || out_f32 || N % 16 != 0 || !ends.tile_squares || !ends.scaled || !ends.norm_weight ||
+                          ((uintptr_t)ends.residual & 15) || ((uintptr_t)ends.scaled & 15) || ((uintptr_t)ends.norm_weight & 15)))
+        return -2008;
+    if (ends.in_squares && ends.in_tiles < 1) return -2009;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, M, K, lda, TC_BM);
     if (rc) return rc;
@@ -911,6 +1021,9 @@ extern "C" int ss_gemm_tc5_many(const void* A, const void* B, const void* bias, 
     ManyArgs g;
     g.C = C; g.bias = bias; g.err = err; g.M = M; g.N = N; g.K = K; g.ldc = ldc; g.out_f32 = out_f32;
     g.bias_f32 = bias_f32; g.swiglu = swiglu; g.tile_cols = bn;
+    g.residual = ends.residual; g.tile_squares = ends.tile_squares; g.scaled = (bf16*)ends.scaled;
+    g.norm_weight = ends.norm_weight; g.norm_w_f32 = ends.norm_w_f32;
+    g.in_squares = ends.in_squares; g.in_tiles = ends.in_tiles; g.in_eps = ends.in_eps;
     constexpr int smem_pair = PR_STAGES * (2 * TC_BM * TC_BK * 2) + 1024 + 256;
     static SsPerDevice opted_pair;
     if (int rc_smem = ss_opt_in_smem(gemm_tc5_pair_kernel, smem_pair, opted_pair)) return rc_smem;
@@ -918,4 +1031,33 @@ extern "C" int ss_gemm_tc5_many(const void* A, const void* B, const void* bias, 
     const int pairs = tiles2 < max_pairs ? tiles2 : max_pairs;
     ss_launch_cluster_x(gemm_tc5_pair_kernel, dim3(2 * pairs), dim3(TC_THREADS), smem_pair, stream, 2, ma, mb, g);
     return SS_LAUNCH_CHECK();
+}
+
+extern "C" int ss_gemm_tc5_many(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
+                                int64_t lda, int64_t ldb, int64_t ldc, int out_f32, int swiglu, int tile_cols,
+                                int* err, cudaStream_t stream) {
+    return gemm_tc5_many(A, B, bias, bias_f32, C, M, N, K, lda, ldb, ldc, out_f32, swiglu, tile_cols, NormEnds(), err, stream);
+}
+
+// The same product into the float32 stream (N a multiple of 16, tile_cols given): residual [M, N] += the product
+// (+ bias) rounded to bfloat16; scaled [M, N] = norm_weight * the new stream in bfloat16; tile_squares
+// [M, ceil(N / tile_cols)] = the sums of squares of every row's part of a tile.
+extern "C" int ss_gemm_tc5_many_to_stream(const void* A, const void* B, const void* bias, int bias_f32, int M, int N, int K,
+                                          int64_t lda, int64_t ldb, int tile_cols, float* residual, float* tile_squares,
+                                          void* scaled, const void* norm_weight, int norm_w_f32, int* err, cudaStream_t stream) {
+    if (tile_cols <= 0) return -2006;
+    NormEnds ends;
+    ends.residual = residual; ends.tile_squares = tile_squares; ends.scaled = scaled;
+    ends.norm_weight = norm_weight; ends.norm_w_f32 = norm_w_f32;
+    return gemm_tc5_many(A, B, bias, bias_f32, nullptr, M, N, K, lda, ldb, N, 0, 0, tile_cols, ends, err, stream);
+}
+
+// The same product behind the RMS norm of that stream: A is `scaled`, and row m of the output is multiplied, before
+// the bias (and the SwiGLU), by rsqrt(sum of in_squares[m][0 .. in_tiles) / K + eps).
+extern "C" int ss_gemm_tc5_many_scaled(const void* A, const void* B, const float* in_squares, int in_tiles, float eps,
+                                       const void* bias, int bias_f32, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                                       int64_t ldc, int out_f32, int swiglu, int tile_cols, int* err, cudaStream_t stream) {
+    NormEnds ends;
+    ends.in_squares = in_squares; ends.in_tiles = in_tiles; ends.in_eps = eps;
+    return gemm_tc5_many(A, B, bias, bias_f32, C, M, N, K, lda, ldb, ldc, out_f32, swiglu, tile_cols, ends, err, stream);
 }

@@ -76,6 +76,11 @@ _ATTN_SIGNATURES = {
 _GEMM_SIGNATURES = {
     "ss_gemm_tc5_many": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                          c_int, c_int, c_int, c_void_p, c_void_p],
+    "ss_gemm_tc5_many_tile_cols": [c_int, c_int, c_int],
+    "ss_gemm_tc5_many_to_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int,
+                                   c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    "ss_gemm_tc5_many_scaled": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_int,
+                                c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p],
     "ss_gemm_tc5": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                     c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "ss_gemm_tc5_to_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int, c_int,
@@ -744,10 +749,17 @@ class PendingNorm:
         return add_rmsnorm(self.stream, None, self.weight, self.eps, self.dtype)
 
 
-def takes_pending_norm(x: "torch.Tensor | PendingNorm", features: int) -> bool:
-    """Whether the product of ``x`` with a [features, K] weight applies the norm's scale inside the kernel."""
-    return (isinstance(x, PendingNorm) and x.dtype == torch.bfloat16
-            and streams_weights(x.shape[0], features, x.shape[1], sm_count(x.device)))
+def takes_pending_norm(x: "torch.Tensor | PendingNorm", features: int, swiglu: bool = False) -> bool:
+    """Whether the product of ``x`` with a [features, K] weight applies the norm's scale inside the kernel: the
+    streaming kernel of decode steps, or the two-SM kernel of long prompt portions."""
+    if not isinstance(x, PendingNorm) or x.dtype != torch.bfloat16:
+        return False
+    sms = sm_count(x.device)
+    if streams_weights(x.shape[0], features, x.shape[1], sms):
+        return True
+    if swiglu:
+        return x.shape[1] % 8 == 0 and many_tokens_swiglu_fits(x.shape[0], features, sms)
+    return many_tokens_fits(x.shape[0], features, x.shape[1], sms)
 
 
 def gemm_plan(tokens: int, features: int, k: int, sms: int | None = None) -> tuple[bool, int, int]:
@@ -855,15 +867,22 @@ def gemm_tcgen05(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: to
     return out
 
 
-def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
-                      out_dtype: torch.dtype | None = None, swiglu: bool = False, tile_cols: int = 0) -> torch.Tensor:
+def gemm_tcgen05_many(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: torch.Tensor | None = None,
+                      out_dtype: torch.dtype | None = None, swiglu: bool = False, tile_cols: int = 0,
+                      to_stream: tuple[torch.Tensor, torch.Tensor] | None = None):
     """``x @ weight.T + bias`` for many rows of ``x`` (prompt portions) on the tcgen05 tensor cores: a persistent
     kernel, one block per SM, the blocks in pairs (``tcgen05.mma.cta_group::2``: each block of a pair loads half
     of A and half of B) that compute tiles of 256 rows with the accumulator double-buffered in tensor memory, so
     that the epilogue of a tile overlaps the products of the next.  ``tile_cols``: the tiles' width, a multiple
     of 16 up to 256; 0 lets the launcher take the width whose tiles fill whole rounds of the pairs of SMs best.
     ``swiglu``: the weight's rows alternate 64 gate and 64 up features; the result is ``silu(gate) * up`` with
-    features / 2 columns (tiles of 256 columns)."""
+    features / 2 columns (tiles of 256 columns).  ``to_stream`` and a `PendingNorm` for ``x``: as in
+    `gemm_tcgen05` (features a multiple of 16; the sums of squares come per tile of the chosen width)."""
+    pending = x if isinstance(x, PendingNorm) else None
+    if pending is not None:
+        if pending.dtype != torch.bfloat16:
+            raise KernelError("a pending norm feeds the tensor-core product only in bfloat16")
+        x = pending.scaled
     _need(x, torch.bfloat16, "x")
     _need(weight, torch.bfloat16, "weight")
     tokens, k = x.shape
@@ -882,6 +901,34 @@ def gemm_tcgen05_many(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor 
         bias_f32 = int(bias.dtype == torch.float32)
         if bias.numel() != features or bias.dtype not in (torch.float32, torch.bfloat16):
             raise KernelError("bias has the wrong size or dtype")
+    if to_stream is not None:
+        stream, norm_weight = to_stream
+        _need(stream, torch.float32, "stream")
+        _need(norm_weight, None, "norm weight")
+        if (swiglu or pending is not None or out_dtype != torch.bfloat16 or stream.shape != out.shape or features % 16
+                or norm_weight.numel() != features or norm_weight.dtype not in (torch.float32, torch.bfloat16)):
+            raise KernelError("a product into the stream needs its plain bfloat16 output, a width in steps of 16 and a "
+                              "stream of its shape")
+        width = tile_cols or gemm_library().ss_gemm_tc5_many_tile_cols(tokens, features, 0)
+        scaled = torch.empty((tokens, features), dtype=torch.bfloat16, device=x.device)
+        squares = torch.empty((tokens, (features + width - 1) // width), dtype=torch.float32, device=x.device)
+        rc = gemm_library().ss_gemm_tc5_many_to_stream(x.data_ptr(), weight.data_ptr(), _ptr(bias), bias_f32, tokens,
+                                                       features, k, k, k, width, stream.data_ptr(), squares.data_ptr(),
+                                                       scaled.data_ptr(), norm_weight.data_ptr(),
+                                                       int(norm_weight.dtype == torch.float32),
+                                                       error_word(x.device).data_ptr(), _stream())
+        _check(rc, "gemm_tcgen05_many into the stream")
+        return scaled, squares
+    if pending is not None:
+        if pending.weight.numel() != k or pending.squares.shape[0] != tokens:
+            raise KernelError("a pending norm feeds a product over the stream's whole width")
+        rc = gemm_library().ss_gemm_tc5_many_scaled(x.data_ptr(), weight.data_ptr(), pending.squares.data_ptr(),
+                                                    pending.squares.shape[1], float(pending.eps), _ptr(bias), bias_f32,
+                                                    out.data_ptr(), tokens, features, k, k, k, out.shape[1],
+                                                    int(out_dtype == torch.float32), int(swiglu), tile_cols,
+                                                    error_word(x.device).data_ptr(), _stream())
+        _check(rc, "gemm_tcgen05_many behind a pending norm")
+        return out
     rc = gemm_library().ss_gemm_tc5_many(x.data_ptr(), weight.data_ptr(), _ptr(bias), bias_f32, out.data_ptr(), tokens,
                                          features, k, k, k, out.shape[1], int(out_dtype == torch.float32), int(swiglu),
                                          tile_cols, error_word(x.device).data_ptr(), _stream())
@@ -941,9 +988,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     library matrix product, as the reference's
     nn.Linear does (slipstream/models/layers/attention.py:132-135).  ``x`` may be a `PendingNorm`."""
     if isinstance(x, PendingNorm):
-        if takes_pending_norm(x, weight.shape[0]):
+        if not takes_pending_norm(x, weight.shape[0]):
+            x = x.materialize()
+        elif streams_weights(x.shape[0], weight.shape[0], x.shape[1], sm_count(x.device)):
             return gemm_tcgen05(x, weight, bias, out_dtype)
-        x = x.materialize()
+        else:
+            return gemm_tcgen05_many(x, weight, bias, out_dtype)
     if x.dtype == torch.float32:
         return gemm_simt(x, weight, bias, out_dtype)
     sms = sm_count(x.device)
@@ -966,17 +1016,25 @@ def adds_to_stream(tokens: int, features: int, k: int, sms: int | None = None) -
     behind it: the streaming tcgen05 kernel with its K slices as a thread-block cluster (decode steps), a width in
     steps of 128."""
     sms = sms or sm_count()
-    if not _state.get("norm_rides_along", True) or features % 128 != 0 or tokens > CLUSTER_BATCH \
-            or not streams_weights(tokens, features, k, sms):
+    if not _state.get("norm_rides_along", True):
+        return False
+    if _state.get("norm_rides_along_long", False) and features % 16 == 0 and many_tokens_fits(tokens, features, k, sms):
+        return True  # the two-SM kernel of long prompt portions: every thread of its epilogue has a row
+    if features % 128 != 0 or tokens > CLUSTER_BATCH or not streams_weights(tokens, features, k, sms):
         return False
     swapped, bn, slices = gemm_plan(tokens, features, k, sms)
     return swapped and 2 <= slices <= 8 and tokens <= bn
 
 
-def set_norm_fusion(enabled: bool) -> None:
+def set_norm_fusion(enabled: bool, long_portions: bool = False) -> None:
     """Whether `linear_add_rmsnorm` may leave the norm to the products around it (on by default; off for
-    comparisons)."""
+    comparisons).  ``long_portions``: also in the two-SM kernel of prompt portions from 2,048 tokens.  That is off
+    unless asked for, by measurement at the 7B sizes: the o and down products with the add inside take 63.9 and
+    213.3 us where the product followed by the norm kernel takes 72.4 and 223.3, but q/k/v and gate/up with the
+    scale in their epilogue take 6 us longer each (57.8 against 51.9), and a whole 2,048-token step 21.7 ms
+    against 21.5."""
     _state["norm_rides_along"] = bool(enabled)
+    _state["norm_rides_along_long"] = bool(enabled and long_portions)
 
 
 def linear_add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, residual: torch.Tensor,
@@ -989,7 +1047,8 @@ def linear_add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor
     if x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and residual.shape == (x.shape[0], weight.shape[0]) \
             and norm_weight.numel() == weight.shape[0] \
             and adds_to_stream(x.shape[0], weight.shape[0], x.shape[1], sm_count(x.device)):
-        scaled, squares = gemm_tcgen05(x, weight, bias, to_stream=(residual, norm_weight))
+        product = gemm_tcgen05 if x.shape[0] <= SMALL_BATCH else gemm_tcgen05_many
+        scaled, squares = product(x, weight, bias, to_stream=(residual, norm_weight))
         return PendingNorm(residual, scaled, squares, norm_weight, eps, out_dtype)
     return add_rmsnorm(residual, linear(x, weight, bias), norm_weight, eps, out_dtype)
 
@@ -1007,8 +1066,10 @@ def gate_up_swiglu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | N
     """``silu(x @ Wg.T + bg) * (x @ Wu.T + bu)`` where ``weight`` [2 I, K] holds gate and up rows alternating in
     runs of ``block``.  Small bfloat16 batches with runs of 64 do it in one kernel.  ``x`` may be a `PendingNorm`."""
     if isinstance(x, PendingNorm):
-        if block == 64 and weight.shape[0] % 128 == 0 and takes_pending_norm(x, weight.shape[0]):
-            return gemm_tcgen05(x, weight, bias, swiglu=True)
+        if block == 64 and weight.shape[0] % 128 == 0 and takes_pending_norm(x, weight.shape[0], swiglu=True):
+            if streams_weights(x.shape[0], weight.shape[0], x.shape[1], sm_count(x.device)):
+                return gemm_tcgen05(x, weight, bias, swiglu=True)
+            return gemm_tcgen05_many(x, weight, bias, swiglu=True)
         x = x.materialize()
     if x.dtype == torch.bfloat16 and block == 64 and weight.shape[0] % 128 == 0 and x.shape[1] % 8 == 0:
         sms = sm_count(x.device)

@@ -497,6 +497,74 @@ def test_projection_into_the_stream_and_the_norm_finished_by_the_next_product(to
     ops().check_errors(torch.device(DEV))
 
 
+@pytest.mark.parametrize("tokens, features, k, bias, w_f32", [(2048, 3584, 3584, False, False), (2300, 3600, 2048, True, True),
+                                                             (2048, 3584, 18944, False, False)])
+def test_long_prompt_portions_take_the_same_way_through_the_two_sm_kernel(tokens, features, k, bias, w_f32):
+    """`linear_add_rmsnorm` from 2,048 tokens: the persistent two-SM kernel adds its tiles to the stream (a row per
+    thread of its epilogue), and the products behind the norm scale their rows.  Same checks as for decode steps."""
+    torch.manual_seed(features + tokens)
+    assert not ops().adds_to_stream(tokens, features, k), "off unless asked for (it did not pay when measured)"
+    ops().set_norm_fusion(True, long_portions=True)
+    try:
+        check_long_portion(tokens, features, k, bias, w_f32)
+    finally:
+        ops().set_norm_fusion(True)
+
+
+def check_long_portion(tokens, features, k, bias, w_f32):
+    assert ops().adds_to_stream(tokens, features, k)
+    x = torch.randn(tokens, k, device=DEV).bfloat16()
+    w = (torch.randn(features, k, device=DEV) * 0.05).bfloat16()
+    b = torch.randn(features, device=DEV).bfloat16() if bias else None
+    nw = 1 + 0.1 * torch.randn(features, device=DEV)
+    nw = nw if w_f32 else nw.bfloat16()
+    stream0 = torch.randn(tokens, features, device=DEV) * 3
+    stream0[::7] *= 30
+    eps = 1e-6
+    delta = (x.double() @ w.double().T + (b.double() if bias else 0)).bfloat16().double()
+    stream_ref = (stream0.double() + delta).float()
+    launches = ops().launch_count()
+    stream = stream0.clone()
+    got = ops().linear_add_rmsnorm(x, w, b, stream, nw, eps, torch.bfloat16)
+    assert ops().launch_count() == launches + 1 and isinstance(got, ops().PendingNorm)
+    assert rel_err(stream, stream_ref) < 3e-3 and (stream - stream_ref).abs().max() <= 2 ** -6 * delta.abs().max()
+    assert torch.allclose(got.squares.double().sum(1), stream.double().pow(2).sum(1), rtol=1e-5)
+    assert torch.equal(got.scaled, (nw.float() * stream).bfloat16())
+    rstd = torch.rsqrt(stream.double().pow(2).mean(-1, keepdim=True) + eps)
+    exact = nw.double() * stream.double() * rstd
+    ops().set_norm_fusion(False)
+    try:
+        stream2 = stream0.clone()
+        two = ops().linear_add_rmsnorm(x, w, b, stream2, nw, eps, torch.bfloat16)
+        assert isinstance(two, torch.Tensor)
+    finally:
+        ops().set_norm_fusion(True, long_portions=True)
+    assert torch.equal(stream, stream2)
+    for features2, swiglu in ((4608, False), (37888, True)):
+        if swiglu and k > 4000:
+            continue
+        assert ops().takes_pending_norm(got, features2, swiglu=swiglu)
+        w2 = (torch.randn(features2, features, device=DEV) * 0.05).bfloat16()
+        b2 = torch.randn(features2, device=DEV).bfloat16()
+        same_roundings = (got.scaled.double() @ w2.double().T) * rstd + b2.double()
+        unrounded = exact @ w2.double().T + b2.double()
+        launches = ops().launch_count()
+        if swiglu:
+            inside, after = ops().gate_up_swiglu(got, w2, b2, 64), ops().gate_up_swiglu(two, w2, b2, 64)
+
+            def act(y):
+                g, u = (y.view(tokens, -1, 2, 64)[:, :, i].reshape(tokens, -1) for i in (0, 1))
+                return g * torch.sigmoid(g) * u
+            same_roundings, unrounded = act(same_roundings), act(unrounded)
+        else:
+            inside, after = ops().linear(got, w2, b2), ops().linear(two, w2, b2)
+        assert ops().launch_count() == launches + 2, "one launch each: no norm kernel"
+        assert rel_err(inside, same_roundings) < 6e-3, (features2, swiglu)
+        assert rel_err(inside, unrounded) <= max(rel_err(after, unrounded) * 1.2, 6e-3), (features2, swiglu)
+        del w2, same_roundings, unrounded
+    ops().check_errors(torch.device(DEV))
+
+
 def test_the_add_and_norm_stay_two_launches_where_the_product_is_not_a_cluster():
     """float32, many tokens, a width that is no multiple of 128: `linear` then `add_rmsnorm`, same result."""
     for dtype, tokens, features, k in ((torch.float32, 4, 128, 64), (torch.bfloat16, 40, 256, 128), (torch.bfloat16, 4, 200, 64)):
