@@ -177,7 +177,14 @@ __device__ __forceinline__ void store_out(const GemmArgs& g, int m, int n, float
     else ((bf16*)g.C)[at] = __float2bfloat16_rn(v);
 }
 
-template <int BN, int STAGES>
+// ENDS: 0 the plain product; 1 the output goes into the stream (GemmArgs::residual); 2 the output is scaled by the
+// norm in front (GemmArgs::in_squares).  Each is a kernel of its own, so that the plain product carries none of the
+// others' code: a block runs its epilogue once, from a cold instruction cache (with all three in one kernel a
+// decode step of 8 requests took 2.73 ms instead of 2.69 without using either).
+// PATH: 0 every form, chosen by the arguments; the forms of a decode step as kernels of their own (swapped, 16
+// columns): 1 K slices in a cluster, plain bfloat16 output (q/k/v, o, down); 2 one slice with SwiGLU (gate/up);
+// 3 one slice, plain output (the LM head).
+template <int BN, int STAGES, int ENDS, int PATH>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
     constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
@@ -193,10 +200,15 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     float* rstd_s = reinterpret_cast<float*>(tiles + STAGES * (A_BYTES + B_BYTES) + 256);  // [BN <= 64] (in_squares)
 
     pdl_launch_dependents();
+    // what the generic kernel (PATH 0) asks of its arguments, the others know: a decode step's kernels branch less
+    const bool f_swapped = PATH == 0 ? g.swapped != 0 : true;
+    const bool f_cluster = PATH == 0 ? g.cluster != 0 : PATH == 1;
+    const bool f_swiglu = PATH == 0 ? g.swiglu != 0 : PATH == 2;
+    const bool f_single = PATH == 0 ? g.slices == 1 : PATH != 1;  // one K slice
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // swapped: (token tile, weight tile); else the row tiles of the activations run fastest, so that the blocks
     // that are resident together share a weight tile and the weights are read from memory once
-    const int m0 = (g.swapped ? blockIdx.y : blockIdx.x) * TC_BM, n0 = (g.swapped ? blockIdx.x : blockIdx.y) * BN;
+    const int m0 = (f_swapped ? blockIdx.y : blockIdx.x) * TC_BM, n0 = (f_swapped ? blockIdx.x : blockIdx.y) * BN;
     const int k_iters_total = (g.K + TC_BK - 1) / TC_BK;
     const int per = (k_iters_total + g.slices - 1) / g.slices;
     const int k_begin = blockIdx.z * per, k_end = min(k_iters_total, k_begin + per);
@@ -223,13 +235,13 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // the bias of the four features a lane of the epilogue warps adds up in the cluster's reduction: it does not
     // depend on the kernels in front, so it is read before the wait for them, not behind the reduction
     float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (warp >= 2 && g.cluster && g.bias && !g.swiglu && m0 + lane * 4 + 3 < g.M)
+    if (warp >= 2 && f_cluster && g.bias && !f_swiglu && m0 + lane * 4 + 3 < g.M)
         bias4 = make_float4(bias_at(g, m0 + lane * 4), bias_at(g, m0 + lane * 4 + 1), bias_at(g, m0 + lane * 4 + 2),
                             bias_at(g, m0 + lane * 4 + 3));
     // likewise the weights of the norm behind a product into the stream, and (after the wait) the stream's values
     // that this block's first token column of the reduction is added to
     float4 nw4 = make_float4(0.f, 0.f, 0.f, 0.f), res0 = nw4;
-    if (warp >= 2 && g.residual) {
+    if (ENDS == 1 && warp >= 2) {
         const int f = m0 + lane * 4;
         if (g.norm_w_f32) nw4 = *reinterpret_cast<const float4*>((const float*)g.norm_weight + f);
         else {
@@ -242,7 +254,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (warp == 0 && lane == 0) {
         // ---- producer.  When the block runs swapped, A is the weight matrix: a constant, so its first
         // tiles are fetched before the kernels before this one have finished; B (activations) only after.
-        const int ahead = g.swapped ? min(STAGES, k_iters) : 0;
+        const int ahead = f_swapped ? min(STAGES, k_iters) : 0;
         const uint64_t once = l2_evict_first_policy();
         for (int it = 0; it < ahead; ++it) {
             mbar_expect_tx(&full[it], A_BYTES + B_BYTES);
@@ -256,7 +268,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, gave_up)) break;
             mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
             unsigned char* a_tile = tiles + s * (A_BYTES + B_BYTES);
-            if (g.swapped) tma_load_2d_once(a_tile, &map_a, (k_begin + it) * TC_BK, m0, &full[s], once);  // weights
+            if (f_swapped) tma_load_2d_once(a_tile, &map_a, (k_begin + it) * TC_BK, m0, &full[s], once);  // weights
             else tma_load_2d(a_tile, &map_a, (k_begin + it) * TC_BK, m0, &full[s]);
             tma_load_2d(a_tile + A_BYTES, &map_b, (k_begin + it) * TC_BK, n0, &full[s]);
         }
@@ -289,11 +301,11 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int quarter = warp & 3;
         const int m = m0 + quarter * 32 + lane;
         pdl_wait();  // the output, the scratch and the counters may still be in use by earlier kernels
-        if (g.residual) {
+        if (ENDS == 1) {
             const int c0 = (int)cluster_rank() + quarter * g.slices;
             if (c0 < min(BN, g.N - n0)) res0 = *reinterpret_cast<const float4*>(g.residual + (int64_t)(n0 + c0) * g.M + m0 + lane * 4);
         }
-        if constexpr (BN <= 64) if (g.in_squares != nullptr) {
+        if constexpr (ENDS == 2) {
             // 1 / rms of every token of the tile, while the products run: a warp takes tokens quarter, quarter + 4,
             // ...; its lanes read the tiles' sums (all loads of a warp in flight at once) and add them in a fixed order
             constexpr int PER_WARP = (BN + 3) / 4;
@@ -319,7 +331,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     rstd_s[quarter + 4 * j] = quarter + 4 * j < live ? 1.0f / sqrtf(ss / (float)g.K + g.in_eps) : 0.f;
             }
         }
-        const bool scaled_in = BN <= 64 && g.in_squares != nullptr;  // rstd_s is seen behind the barrier below
+        constexpr bool scaled_in = ENDS == 2;  // rstd_s is seen behind the barrier below
         if (k_iters > 0) mbar_wait(acc_ready, 0, gave_up);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         // one thread decides for all four epilogue warps whether the tile is good, so that the barriers
@@ -338,13 +350,13 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < 16; ++j) r[j] = 0u;
                 }
-                if (g.cluster || (g.slices == 1 && g.swiglu)) {
+                if (f_cluster || (f_single && f_swiglu)) {
                     // all stages have been consumed: the ring's memory is free to carry the tile across warps
                     float* xbuf = reinterpret_cast<float*>(tiles);
 #pragma unroll
                     for (int j = 0; j < 16; ++j) xbuf[(c + j) * TC_BM + quarter * 32 + lane] = __uint_as_float(r[j]);
-                } else if (g.slices == 1) {
-                    if (!g.swapped && !g.out_f32 && m < g.M && n0 + c + 16 <= g.N && (g.ldc % 8 == 0)) {
+                } else if (f_single) {
+                    if (!f_swapped && !g.out_f32 && m < g.M && n0 + c + 16 <= g.N && (g.ldc % 8 == 0)) {
                         // 16 consecutive bfloat16 of this thread's row: two 16-byte stores
                         uint32_t packed[8];
                         if (g.bias) {
@@ -374,7 +386,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     for (int j = 0; j < 16; ++j) dst[(int64_t)j * TC_BM] = __uint_as_float(r[j]);
                 }
             }
-            if (g.slices == 1 && g.swiglu) {
+            if (f_single && f_swiglu) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 const float* xbuf = reinterpret_cast<const float*>(tiles);
                 // all four warps: thread t takes gate/up pair t % 64 of the even (t < 64) or odd token columns
@@ -384,7 +396,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     store_swiglu(g, m0 + ml, n0 + c, xbuf[c * TC_BM + ml], xbuf[c * TC_BM + ml + 64],
                                  scaled_in ? rstd_s[c & 63] : 1.f);
             }
-            if (g.slices > 1 && !g.cluster) {
+            if (!f_single && !f_cluster) {
                 // the block that completes the tile last adds the slices, in slice order
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
@@ -407,7 +419,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                             for (int u = 0; u < 4; ++u) acc[u] += __ldcg(src + ((int64_t)s * BN + u) * TC_BM);
                         }
-                        if (g.swiglu && ml < 64) {
+                        if (f_swiglu && ml < 64) {
 #pragma unroll 4
                             for (int s = 0; s < g.slices; ++s) {
 #pragma unroll
@@ -417,7 +429,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
                             const float sc = scaled_in ? rstd_s[(c0 + u) & 63] : 1.f;
-                            if (!g.swiglu) store_out<BN>(g, m0 + ml, n0 + c0 + u, acc[u], sc);
+                            if (!f_swiglu) store_out<BN>(g, m0 + ml, n0 + c0 + u, acc[u], sc);
                             else if (ml < 64) store_swiglu(g, m0 + ml, n0 + c0 + u, acc[u], acc2[u], sc);
                         }
                     }
@@ -425,7 +437,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
         }
     }
-    if (g.cluster) {
+    if (f_cluster) {
         cluster_sync_all();  // every block's partial tile lies in its shared memory
         if (warp >= 2) {
             // a warp takes one token column at a time, a lane four consecutive features of it: 16-byte reads of
@@ -434,11 +446,11 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int n_live = min(BN, g.N - n0);
             const int rank = (int)cluster_rank(), q = warp & 3;
             const int mine = n_live > rank ? (n_live - 1 - rank) / g.slices + 1 : 0;  // columns rank, rank + slices, ...
-            const bool scaled_in = BN <= 64 && g.in_squares != nullptr;
+            constexpr bool scaled_in = ENDS == 2;
             for (int i = q; i < mine; i += 4) {
                 const int c = rank + i * g.slices;
                 const float sc = scaled_in ? rstd_s[c & 63] : 1.f;
-                if (!g.swiglu) {
+                if (!f_swiglu) {
                     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
                     for (int s = 0; s < g.slices; ++s) {
@@ -446,7 +458,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
                     }
                     const int m = m0 + lane * 4, n = n0 + c;
-                    if (g.residual != nullptr) {
+                    if constexpr (ENDS == 1) {
                         // (M is a multiple of 128.)  The stream takes this part of the branch's output, rounded as
                         // the output would have been; the norm behind it gets the stream times its weights, and
                         // the squares of the tile's 128 features in one sum
@@ -466,7 +478,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                         for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
                         if (lane == 0) g.tile_squares[(int64_t)n * gridDim.y + blockIdx.y] = sq;
-                    } else if (g.swapped && !g.out_f32 && m + 3 < g.M && (g.ldc & 3) == 0) {
+                    } else if (f_swapped && !g.out_f32 && m + 3 < g.M && (g.ldc & 3) == 0) {
                         acc.x = acc.x * sc + bias4.x; acc.y = acc.y * sc + bias4.y; acc.z = acc.z * sc + bias4.z; acc.w = acc.w * sc + bias4.w;
                         const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
                         uint2 packed;
@@ -859,16 +871,38 @@ static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K,
     return r == CUDA_SUCCESS ? 0 : -2002;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int ENDS = 0, int PATH = 0>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, dim3 grid, cudaStream_t stream) {
     constexpr int smem = STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024 + 512;
     static SsPerDevice opted;
-    if (int rc_smem = ss_opt_in_smem(gemm_tc5_kernel<BN, STAGES>, smem, opted)) return rc_smem;
+    if (int rc_smem = ss_opt_in_smem(gemm_tc5_kernel<BN, STAGES, ENDS, PATH>, smem, opted)) return rc_smem;
     if (g.cluster)
-        ss_launch_cluster(gemm_tc5_kernel<BN, STAGES>, dim3(grid), dim3(TC_THREADS), smem, stream, g.slices, ma, mb, g);
+        ss_launch_cluster(gemm_tc5_kernel<BN, STAGES, ENDS, PATH>, dim3(grid), dim3(TC_THREADS), smem, stream, g.slices, ma, mb, g);
     else
-        ss_launch(gemm_tc5_kernel<BN, STAGES>, dim3(grid), dim3(TC_THREADS), smem, stream, ma, mb, g);
+        ss_launch(gemm_tc5_kernel<BN, STAGES, ENDS, PATH>, dim3(grid), dim3(TC_THREADS), smem, stream, ma, mb, g);
     return SS_LAUNCH_CHECK();
+}
+
+// The 16-column kernels of a decode step: the form (PATH) and the ends (ENDS) as kernels of their own.
+template <int STAGES>
+static int launch16(int ends, const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, dim3 grid, cudaStream_t stream) {
+    const int path = !g.swapped ? 0 : (g.cluster && !g.swiglu && !g.out_f32) ? 1 : (g.slices == 1 && g.swiglu) ? 2
+                     : (g.slices == 1 && !g.swiglu) ? 3 : 0;
+    if (ends == 1) return path == 1 ? launch<16, STAGES, 1, 1>(ma, mb, g, grid, stream) : -2008;
+    if (ends == 2) {
+        switch (path) {
+            case 1: return launch<16, STAGES, 2, 1>(ma, mb, g, grid, stream);
+            case 2: return launch<16, STAGES, 2, 2>(ma, mb, g, grid, stream);
+            case 3: return launch<16, STAGES, 2, 3>(ma, mb, g, grid, stream);
+            default: return launch<16, STAGES, 2, 0>(ma, mb, g, grid, stream);
+        }
+    }
+    switch (path) {
+        case 1: return launch<16, STAGES, 0, 1>(ma, mb, g, grid, stream);
+        case 2: return launch<16, STAGES, 0, 2>(ma, mb, g, grid, stream);
+        case 3: return launch<16, STAGES, 0, 3>(ma, mb, g, grid, stream);
+        default: return launch<16, STAGES, 0, 0>(ma, mb, g, grid, stream);
+    }
 }
 
 // How many float32 the split-K scratch must hold, and how many counters, for a problem.
@@ -905,7 +939,8 @@ static int gemm_tc5(const void* A, const void* B, const void* bias, int bias_f32
     if (ends.residual && (!cluster || swiglu || M % TC_BM != 0 || !ends.tile_squares || !ends.scaled || !ends.norm_weight ||
                           ((uintptr_t)ends.residual & 15) || ((uintptr_t)ends.scaled & 7) || ((uintptr_t)ends.norm_weight & 15)))
         return -2008;
-    if (ends.in_squares && (!swapped || bn > 64 || ends.in_tiles < 1)) return -2009;
+    if (ends.in_squares && (!swapped || bn != 16 || ends.in_tiles < 1)) return -2009;
+    if (ends.residual && bn != 16) return -2008;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, M, K, lda, TC_BM);
     if (rc) return rc;
@@ -928,7 +963,10 @@ static int gemm_tc5(const void* A, const void* B, const void* bias, int bias_f32
         // bandwidth, gate/up with 296 blocks at 97 %).  A decode step of 8 requests: 2.79 ms instead of 2.84, of
         // one request 2.69 instead of 2.76.  With few K steps per block (q/k/v, o: 7) the fourth block an SM can
         // hold beside two of these matters more: six stages for every product took 2.96 ms.
-        case 16: return deep ? launch<16, 6>(ma, mb, g, grid, stream) : launch<16, 4>(ma, mb, g, grid, stream);
+        case 16: {
+            const int e = ends.residual ? 1 : ends.in_squares ? 2 : 0;
+            return deep ? launch16<6>(e, ma, mb, g, grid, stream) : launch16<4>(e, ma, mb, g, grid, stream);
+        }
         case 32: return launch<32, 4>(ma, mb, g, grid, stream);  // (five stages when deep: 3.27 ms instead of 3.24 at 32 requests)
         case 64: return launch<64, 4>(ma, mb, g, grid, stream);  // two blocks fit on an SM
         case 128: return launch<128, 6>(ma, mb, g, grid, stream);
@@ -945,7 +983,7 @@ extern "C" int ss_gemm_tc5(const void* A, const void* B, const void* bias, int b
 }
 
 // A branch's last projection into the float32 stream: the swapped product with its K slices as a thread-block
-// cluster (2..8 slices, N <= bn, M a multiple of 128).  residual [N, M] += the product (+ bias) rounded to bfloat16;
+// cluster (2..8 slices, N <= bn = 16, M a multiple of 128).  residual [N, M] += the product (+ bias) rounded to bfloat16;
 // scaled [N, M] (bfloat16) = norm_weight * the new stream; tile_squares [N, M / 128] = the sums of squares of the
 // new stream per tile of 128 features.  Other shapes are refused with -2008.
 extern "C" int ss_gemm_tc5_to_stream(const void* A, const void* B, const void* bias, int bias_f32, int M, int N, int K,
@@ -957,7 +995,7 @@ extern "C" int ss_gemm_tc5_to_stream(const void* A, const void* B, const void* b
     return gemm_tc5(A, B, bias, bias_f32, nullptr, M, N, K, lda, ldb, M, bn, 1, 0, slices, 0, nullptr, nullptr, ends, err, stream);
 }
 
-// The swapped product (bn <= 64) behind the RMS norm of that stream: B is `scaled`, and token n of the output is
+// The swapped product (bn 16) behind the RMS norm of that stream: B is `scaled`, and token n of the output is
 // multiplied, before the bias, by rsqrt(sum of in_squares[n][0 .. in_tiles) / K + eps); everything else as
 // ss_gemm_tc5.  Other shapes are refused with -2009.
 extern "C" int ss_gemm_tc5_scaled(const void* A, const void* B, const float* in_squares, int in_tiles, float eps,

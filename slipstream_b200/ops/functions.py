@@ -755,7 +755,7 @@ def takes_pending_norm(x: "torch.Tensor | PendingNorm", features: int, swiglu: b
     if not isinstance(x, PendingNorm) or x.dtype != torch.bfloat16:
         return False
     sms = sm_count(x.device)
-    if streams_weights(x.shape[0], features, x.shape[1], sms):
+    if x.shape[0] <= CLUSTER_BATCH and streams_weights(x.shape[0], features, x.shape[1], sms):
         return True
     if swiglu:
         return x.shape[1] % 8 == 0 and many_tokens_swiglu_fits(x.shape[0], features, sms)
@@ -796,8 +796,8 @@ def gemm_tcgen05(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: to
     ``to_stream`` = (float32 stream [tokens, features], weights of the norm behind it), where `adds_to_stream`:
     the product, rounded to bfloat16, is added to the stream in place instead of being returned, and the function
     returns (round(norm weights * new stream) in bfloat16, sums of squares [tokens, features / 128]).
-    ``x`` may be a `PendingNorm` (at most 64 tokens, swapped plan): the product runs on its ``scaled`` and applies
-    the scale of every token in the epilogue."""
+    ``x`` may be a `PendingNorm` (at most 16 tokens): the product runs on its ``scaled`` and applies the scale of
+    every token in the epilogue."""
     pending = x if isinstance(x, PendingNorm) else None
     if pending is not None:
         if pending.dtype != torch.bfloat16:
@@ -850,8 +850,8 @@ def gemm_tcgen05(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: to
         _check(rc, "gemm_tcgen05 into the stream")
         return scaled, squares
     if pending is not None:
-        if not swapped or bn > 64 or pending.weight.numel() != k or pending.squares.shape[0] != tokens:
-            raise KernelError("a pending norm feeds the swapped product of at most 64 tokens, over the stream's whole width")
+        if not swapped or bn != 16 or pending.weight.numel() != k or pending.squares.shape[0] != tokens:
+            raise KernelError("a pending norm feeds the swapped product of at most 16 tokens, over the stream's whole width")
         rc = gemm_library().ss_gemm_tc5_scaled(a.data_ptr(), b.data_ptr(), pending.squares.data_ptr(),
                                                pending.squares.shape[1], float(pending.eps), _ptr(bias), bias_f32,
                                                out.data_ptr(), a.shape[0], tokens, k, k, k, out.shape[1], bn,
@@ -990,7 +990,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     if isinstance(x, PendingNorm):
         if not takes_pending_norm(x, weight.shape[0]):
             x = x.materialize()
-        elif streams_weights(x.shape[0], weight.shape[0], x.shape[1], sm_count(x.device)):
+        elif x.shape[0] <= CLUSTER_BATCH:
             return gemm_tcgen05(x, weight, bias, out_dtype)
         else:
             return gemm_tcgen05_many(x, weight, bias, out_dtype)
@@ -1067,7 +1067,7 @@ def gate_up_swiglu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | N
     runs of ``block``.  Small bfloat16 batches with runs of 64 do it in one kernel.  ``x`` may be a `PendingNorm`."""
     if isinstance(x, PendingNorm):
         if block == 64 and weight.shape[0] % 128 == 0 and takes_pending_norm(x, weight.shape[0], swiglu=True):
-            if streams_weights(x.shape[0], weight.shape[0], x.shape[1], sm_count(x.device)):
+            if x.shape[0] <= CLUSTER_BATCH:
                 return gemm_tcgen05(x, weight, bias, swiglu=True)
             return gemm_tcgen05_many(x, weight, bias, swiglu=True)
         x = x.materialize()
