@@ -126,6 +126,21 @@ extern "C" int ss_attn_prefill_tc5(const void* q, int64_t q_stride, int n_tokens
 
 #include "attention_decode_tma.cuh"
 
+template <int NS, int FORM>
+static int launch_decode_tma(const CUtensorMap& map_kv, const DecodeTmaArgs& a, dim3 grid, int cluster, int smem,
+                             cudaStream_t stream) {
+    // the most a launch can ask for: 16 heads in a cluster of 7 are 3 x 7 records; the records a block receives from
+    // its cluster are sized by the heads it really has
+    static SsPerDevice opted;
+    if (int rc_smem = ss_opt_in_smem(attn_decode_tma<HEAD_DIM, NS, FORM>, decode_tma_smem_bytes<HEAD_DIM, NS>(24, 8), opted))
+        return rc_smem;
+    if (cluster > 1)
+        ss_launch_cluster(attn_decode_tma<HEAD_DIM, NS, FORM>, dim3(grid), dim3(DT_THREADS), smem, stream, cluster, map_kv, a);
+    else
+        ss_launch(attn_decode_tma<HEAD_DIM, NS, FORM>, dim3(grid), dim3(DT_THREADS), smem, stream, map_kv, a);
+    return SS_LAUNCH_CHECK();
+}
+
 // The decode kernel with TMA-fed tiles: arguments as ss_attn_decode_mma; page_size 8, 16, 32 or 64.  stages: 2 or 3
 // tiles of keys and values in the ring of a block (see the kernel).
 extern "C" int ss_attn_decode_tma(const void* q, int64_t q_stride, void* out, int64_t out_stride,
@@ -154,22 +169,14 @@ extern "C" int ss_attn_decode_tma(const void* q, int64_t q_stride, void* out, in
     a.part_o = part_o; a.part_lse = part_lse; a.counters = counters; a.err = err;
     const int G = n_q / n_kv;
     dim3 grid(n_requests, n_kv * ((G + 15) / 16), n_slices);
-    // the most a launch can ask for: 16 heads in a cluster of 7 are 3 x 7 records; the records a block receives from
-    // its cluster are sized by the heads it really has
-    if (stages == 3) {
-        static SsPerDevice opted3;
-        if (int rc_smem = ss_opt_in_smem(attn_decode_tma<HEAD_DIM, 3>, decode_tma_smem_bytes<HEAD_DIM, 3>(24, 8), opted3)) return rc_smem;
-        const int smem = decode_tma_smem_bytes<HEAD_DIM, 3>(G < 16 ? G : 16, cluster);
-        if (cluster > 1) ss_launch_cluster(attn_decode_tma<HEAD_DIM, 3>, dim3(grid), dim3(DT_THREADS), smem, stream, cluster, map_kv, a);
-        else ss_launch(attn_decode_tma<HEAD_DIM, 3>, dim3(grid), dim3(DT_THREADS), smem, stream, map_kv, a);
-        return SS_LAUNCH_CHECK();
-    }
-    static SsPerDevice opted;
-    if (int rc_smem = ss_opt_in_smem(attn_decode_tma<HEAD_DIM, 2>, decode_tma_smem_bytes<HEAD_DIM, 2>(24, 8), opted)) return rc_smem;
-    const int smem = decode_tma_smem_bytes<HEAD_DIM, 2>(G < 16 ? G : 16, cluster);
-    if (cluster > 1) ss_launch_cluster(attn_decode_tma<HEAD_DIM, 2>, dim3(grid), dim3(DT_THREADS), smem, stream, cluster, map_kv, a);
-    else ss_launch(attn_decode_tma<HEAD_DIM, 2>, dim3(grid), dim3(DT_THREADS), smem, stream, map_kv, a);
-    return SS_LAUNCH_CHECK();
+    // the usual decode step (rotation inside, no window, one cluster, a rotary size in steps of 16) has kernels of its own
+    const bool usual = fused && window == 0 && cluster == n_slices && cluster > 1 && rot_dim > 0 && rot_dim % 16 == 0;
+    const int smem3 = decode_tma_smem_bytes<HEAD_DIM, 3>(G < 16 ? G : 16, cluster);
+    const int smem2 = decode_tma_smem_bytes<HEAD_DIM, 2>(G < 16 ? G : 16, cluster);
+    if (stages == 3 && usual) return launch_decode_tma<3, 1>(map_kv, a, grid, cluster, smem3, stream);
+    if (stages == 3) return launch_decode_tma<3, 0>(map_kv, a, grid, cluster, smem3, stream);
+    if (usual) return launch_decode_tma<2, 1>(map_kv, a, grid, cluster, smem2, stream);
+    return launch_decode_tma<2, 0>(map_kv, a, grid, cluster, smem2, stream);
 }
 #else
 extern "C" int ss_attn_prefill_tc5_supported() { return 0; }

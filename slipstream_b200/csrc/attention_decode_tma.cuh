@@ -87,7 +87,10 @@ __device__ __forceinline__ void st_cluster_f32x2(float* local, uint32_t rank, fl
 }
 
 // (with three stages the registers are held to what lets two blocks share an SM, as the shared memory does)
-template <int D, int NS>
+// FORM 1 is the usual decode step as a kernel of its own: rotation and page write inside, no window, the slices one
+// cluster, a rotary size in steps of 16.  What FORM 0 asks of its arguments FORM 1 knows, and its blocks, which run
+// every part of the kernel once from a cold instruction cache, branch over less.
+template <int D, int NS, int FORM>
 __global__ void __launch_bounds__(DT_THREADS, NS == 3 ? 2 : 0)
 attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs a) {
     pdl_launch_dependents();
@@ -114,12 +117,15 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
     __shared__ int is_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int n_q = a.n_q, n_kv = a.n_kv, page_size = a.page_size, n_slices = a.n_slices, window = a.window;
+    const int n_q = a.n_q, n_kv = a.n_kv, page_size = a.page_size, n_slices = a.n_slices;
+    const int window = FORM == 0 ? a.window : 0;
+    const bool fused = FORM == 0 ? a.fused != 0 : true;
     const int G = n_q / n_kv, hblocks = (G + 15) / 16;
     const int r = blockIdx.x, kvh = blockIdx.y / hblocks, g0 = (blockIdx.y % hblocks) * 16;
     const int heads_here = min(16, G - g0);
     const int slice = blockIdx.z;
-    const int cs = a.cluster, n_groups = n_slices / cs, group = slice / cs;  // slices per cluster, clusters, this one
+    // slices per cluster, clusters, this one
+    const int cs = FORM == 0 ? a.cluster : n_slices, n_groups = FORM == 0 ? n_slices / cs : 1, group = FORM == 0 ? slice / cs : 0;
     const int row_q = a.q_start[r], seq_len = a.seq_lens[r];
     const int pos = seq_len - 1;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
@@ -129,7 +135,7 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
     const int kt_lo = kt_first + slice * per, kt_hi = min(kt_last, kt_lo + per - 1);
     const bool work = seq_len > 0 && kt_lo <= kt_hi;
     const int half = a.rot_dim / 2;
-    const bool has_newest = a.fused && work && kt_hi == kt_last;
+    const bool has_newest = fused && work && kt_hi == kt_last;
 
     if (tid == 0) {
         for (int s = 0; s < NB; ++s) { fa::mbar_init(&full[s], 1); fa::mbar_init(&empty[s], 2); }  // a pair of warps per tile
@@ -141,7 +147,7 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
     if (work) {
         table = stage_table(table_s, a.block_tables + (int64_t)r * a.max_blocks, max(lo, kt_lo * MMA_BN),
                             min(pos, kt_hi * MMA_BN + MMA_BN - 1), page_size, DT_TABLE_MAX);
-        if (a.fused) {
+        if (fused) {
             for (int i = tid; i < half; i += DT_THREADS) {
                 const float angle = __fmul_rn((float)pos, a.inv_freq[i]);
                 sincosf(angle, &sin_s[i], &cos_s[i]);
@@ -177,7 +183,7 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
                 // the tile that lay in this stage before (i - NS) has been used up
                 if (i >= NS) ok = __all_sync(0xffffffffu, fa::mbar_wait(&empty[bar_of(i - NS)], phase_of(i - NS) & 1, gave_up));
                 if (!ok) break;
-                if (!a.fused && kt == kt_last && !waited) {
+                if (!fused && kt == kt_last && !waited) {
                     pdl_wait();  // the newest key and value are written by the kernel before this one
                     waited = true;
                 }
@@ -249,8 +255,8 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
             }
             cp_async_wait<0>();
             asm volatile("bar.sync 1, 128;" ::: "memory");  // the four consumer warps: Q and the newest row are in place
-            if (a.fused && half > 0) {
-                if (half % 8 == 0) {
+            if (fused && (FORM == 1 || half > 0)) {
+                if (FORM == 1 || half % 8 == 0) {
                     // eight pairs a thread, 16-byte accesses (element by element this loop took 1,600 cycles, a
                     // fifth of the kernel at short contexts); the arithmetic and its rounding are the same
                     for (int idx = tid; idx < 16 * (half / 8); idx += MMA_THREADS) {
@@ -300,7 +306,7 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
                 // a wait that gives up makes every later wait give up at once
                 const bool ok = fa::mbar_wait(&full[bar_of(i)], phase_of(i) & 1, gave_up);
                 const int first_key = kt * MMA_BN + key_off;
-                if (a.fused && kt == kt_last && pos >= first_key && pos < first_key + 32) {
+                if (fused && kt == kt_last && pos >= first_key && pos < first_key + 32) {
                     // the newest token's row of this half comes from the projection output, not from the page
                     const int prow = pos - kt_last * MMA_BN;
                     for (int c = lane; c < 2 * (D / 8); c += 32) {
@@ -384,7 +390,7 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
             ll = fmaf(Lm[w * 16 + row], f, ll);
             mm = fmaxf(mm, Mm[w * 16 + row]);
         }
-        if (cs > 1) {
+        if (FORM == 1 || cs > 1) {
             // to the block of the cluster that owns this row: record [row / cs][this block] of its Recv
             float* rec = Recv + (((row / cs) * cs + rank) * (D + 2));
             st_cluster_f32x2(rec + d, (uint32_t)(row % cs), acc0, acc1);
@@ -403,9 +409,9 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
         }
     }
     if (*gave_up && tid == 0) atomicOr(a.err, SS_ERR_WAIT_LIMIT);
-    if (n_slices == 1) return;
+    if (FORM == 0 && n_slices == 1) return;
 
-    if (cs > 1) {
+    if (FORM == 1 || cs > 1) {
         // One barrier makes every block's pushes visible; then rank k combines rows k, k + cs, ... out of its OWN
         // shared memory (the records of the cs blocks, in block order) and is free to leave.
         cluster_sync_all();
