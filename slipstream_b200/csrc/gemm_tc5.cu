@@ -182,8 +182,8 @@ __device__ __forceinline__ void store_out(const GemmArgs& g, int m, int n, float
 // others' code: a block runs its epilogue once, from a cold instruction cache (with all three in one kernel a
 // decode step of 8 requests took 2.73 ms instead of 2.69 without using either).
 // PATH: 0 every form, chosen by the arguments; the forms of a decode step as kernels of their own (swapped, 16
-// columns): 1 K slices in a cluster, plain bfloat16 output (q/k/v, o, down); 2 one slice with SwiGLU (gate/up);
-// 3 one slice, plain output (the LM head).
+// columns): 1 K slices in a cluster, plain bfloat16 output (q/k/v, o, down), 4 the same with exactly 8 slices;
+// 2 one slice with SwiGLU (gate/up); 3 one slice, plain output (the LM head).
 template <int BN, int STAGES, int ENDS, int PATH>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
@@ -202,15 +202,16 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     pdl_launch_dependents();
     // what the generic kernel (PATH 0) asks of its arguments, the others know: a decode step's kernels branch less
     const bool f_swapped = PATH == 0 ? g.swapped != 0 : true;
-    const bool f_cluster = PATH == 0 ? g.cluster != 0 : PATH == 1;
+    const bool f_cluster = PATH == 0 ? g.cluster != 0 : (PATH == 1 || PATH == 4);
     const bool f_swiglu = PATH == 0 ? g.swiglu != 0 : PATH == 2;
-    const bool f_single = PATH == 0 ? g.slices == 1 : PATH != 1;  // one K slice
+    const bool f_single = PATH == 0 ? g.slices == 1 : (PATH == 2 || PATH == 3);  // one K slice
+    const int n_sl = PATH == 4 ? 8 : (PATH == 2 || PATH == 3) ? 1 : g.slices;    // K slices
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // swapped: (token tile, weight tile); else the row tiles of the activations run fastest, so that the blocks
     // that are resident together share a weight tile and the weights are read from memory once
     const int m0 = (f_swapped ? blockIdx.y : blockIdx.x) * TC_BM, n0 = (f_swapped ? blockIdx.x : blockIdx.y) * BN;
     const int k_iters_total = (g.K + TC_BK - 1) / TC_BK;
-    const int per = (k_iters_total + g.slices - 1) / g.slices;
+    const int per = (k_iters_total + n_sl - 1) / n_sl;
     const int k_begin = blockIdx.z * per, k_end = min(k_iters_total, k_begin + per);
     const int k_iters = max(0, k_end - k_begin);
 
@@ -302,7 +303,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int m = m0 + quarter * 32 + lane;
         pdl_wait();  // the output, the scratch and the counters may still be in use by earlier kernels
         if (ENDS == 1) {
-            const int c0 = (int)cluster_rank() + quarter * g.slices;
+            const int c0 = (int)cluster_rank() + quarter * n_sl;
             if (c0 < min(BN, g.N - n0)) res0 = *reinterpret_cast<const float4*>(g.residual + (int64_t)(n0 + c0) * g.M + m0 + lane * 4);
         }
         if constexpr (ENDS == 2) {
@@ -381,7 +382,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             store_out<BN>(g, m, n0 + c + j, __uint_as_float(r[j]), scaled_in ? rstd_s[(c + j) & 63] : 1.f);
                     }
                 } else {
-                    float* dst = g.partial + (((int64_t)tile * g.slices + blockIdx.z) * BN + c) * TC_BM + quarter * 32 + lane;
+                    float* dst = g.partial + (((int64_t)tile * n_sl + blockIdx.z) * BN + c) * TC_BM + quarter * 32 + lane;
 #pragma unroll
                     for (int j = 0; j < 16; ++j) dst[(int64_t)j * TC_BM] = __uint_as_float(r[j]);
                 }
@@ -402,8 +403,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
                 if (threadIdx.x == 64) {
                     const int seen = atomicAdd(&g.counters[tile], 1);
-                    *last_flag = (seen == g.slices - 1);
-                    if (seen == g.slices - 1) g.counters[tile] = 0;  // ready for the next call
+                    *last_flag = (seen == n_sl - 1);
+                    if (seen == n_sl - 1) g.counters[tile] = 0;  // ready for the next call
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (*last_flag) {
@@ -413,15 +414,15 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     for (int c0 = 0; c0 < n_live; c0 += 4) {
                         // four columns at a time so that many loads are in flight; slices are added in order
                         float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
-                        const float* src = g.partial + (((int64_t)tile * g.slices) * BN + c0) * TC_BM + ml;
+                        const float* src = g.partial + (((int64_t)tile * n_sl) * BN + c0) * TC_BM + ml;
 #pragma unroll 4
-                        for (int s = 0; s < g.slices; ++s) {
+                        for (int s = 0; s < n_sl; ++s) {
 #pragma unroll
                             for (int u = 0; u < 4; ++u) acc[u] += __ldcg(src + ((int64_t)s * BN + u) * TC_BM);
                         }
                         if (f_swiglu && ml < 64) {
 #pragma unroll 4
-                            for (int s = 0; s < g.slices; ++s) {
+                            for (int s = 0; s < n_sl; ++s) {
 #pragma unroll
                                 for (int u = 0; u < 4; ++u) acc2[u] += __ldcg(src + 64 + ((int64_t)s * BN + u) * TC_BM);
                             }
@@ -445,15 +446,15 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const float* xbuf = reinterpret_cast<const float*>(tiles);
             const int n_live = min(BN, g.N - n0);
             const int rank = (int)cluster_rank(), q = warp & 3;
-            const int mine = n_live > rank ? (n_live - 1 - rank) / g.slices + 1 : 0;  // columns rank, rank + slices, ...
+            const int mine = n_live > rank ? (n_live - 1 - rank) / n_sl + 1 : 0;  // columns rank, rank + slices, ...
             constexpr bool scaled_in = ENDS == 2;
             for (int i = q; i < mine; i += 4) {
-                const int c = rank + i * g.slices;
+                const int c = rank + i * n_sl;
                 const float sc = scaled_in ? rstd_s[c & 63] : 1.f;
                 if (!f_swiglu) {
                     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
-                    for (int s = 0; s < g.slices; ++s) {
+                    for (int s = 0; s < n_sl; ++s) {
                         const float4 v = ld_cluster_f32x4(xbuf + c * TC_BM + lane * 4, (uint32_t)s);
                         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
                     }
@@ -492,7 +493,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 } else if (lane < 16) {
                     float4 ga = make_float4(0.f, 0.f, 0.f, 0.f), ua = ga;
 #pragma unroll 8
-                    for (int s = 0; s < g.slices; ++s) {
+                    for (int s = 0; s < n_sl; ++s) {
                         const float4 v = ld_cluster_f32x4(xbuf + c * TC_BM + lane * 4, (uint32_t)s);
                         const float4 w = ld_cluster_f32x4(xbuf + c * TC_BM + 64 + lane * 4, (uint32_t)s);
                         ga.x += v.x; ga.y += v.y; ga.z += v.z; ga.w += v.w;
@@ -886,11 +887,14 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& 
 // The 16-column kernels of a decode step: the form (PATH) and the ends (ENDS) as kernels of their own.
 template <int STAGES>
 static int launch16(int ends, const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, dim3 grid, cudaStream_t stream) {
-    const int path = !g.swapped ? 0 : (g.cluster && !g.swiglu && !g.out_f32) ? 1 : (g.slices == 1 && g.swiglu) ? 2
-                     : (g.slices == 1 && !g.swiglu) ? 3 : 0;
-    if (ends == 1) return path == 1 ? launch<16, STAGES, 1, 1>(ma, mb, g, grid, stream) : -2008;
+    const int path = !g.swapped ? 0 : (g.cluster && !g.swiglu && !g.out_f32) ? (g.slices == 8 ? 4 : 1)
+                     : (g.slices == 1 && g.swiglu) ? 2 : (g.slices == 1 && !g.swiglu) ? 3 : 0;
+    if (ends == 1)
+        return path == 4 ? launch<16, STAGES, 1, 4>(ma, mb, g, grid, stream)
+                         : path == 1 ? launch<16, STAGES, 1, 1>(ma, mb, g, grid, stream) : -2008;
     if (ends == 2) {
         switch (path) {
+            case 4: return launch<16, STAGES, 2, 4>(ma, mb, g, grid, stream);
             case 1: return launch<16, STAGES, 2, 1>(ma, mb, g, grid, stream);
             case 2: return launch<16, STAGES, 2, 2>(ma, mb, g, grid, stream);
             case 3: return launch<16, STAGES, 2, 3>(ma, mb, g, grid, stream);
@@ -898,6 +902,7 @@ static int launch16(int ends, const CUtensorMap& ma, const CUtensorMap& mb, cons
         }
     }
     switch (path) {
+        case 4: return launch<16, STAGES, 0, 4>(ma, mb, g, grid, stream);
         case 1: return launch<16, STAGES, 0, 1>(ma, mb, g, grid, stream);
         case 2: return launch<16, STAGES, 0, 2>(ma, mb, g, grid, stream);
         case 3: return launch<16, STAGES, 0, 3>(ma, mb, g, grid, stream);
