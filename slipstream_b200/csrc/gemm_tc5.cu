@@ -592,6 +592,9 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(leader_addr(bar)) : "memory");
 }
 
+// ENDS as in gemm_tc5_kernel: 0 plain, 1 the output goes into the stream, 2 the output is scaled by the norm in
+// front; each a kernel of its own.
+template <int ENDS>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const ManyArgs g) {
     constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = TC_BM * TC_BK * 2, STAGES = PR_STAGES;  // this block's halves
@@ -683,7 +686,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             // while the tile's products run: the scale of this thread's row (the norm in front), or the first
             // chunks of the stream that the row is added to
             float rstd = 1.f;
-            if (g.in_squares != nullptr && m < g.M) {
+            if (ENDS == 2 && m < g.M) {
                 const float* sq = g.in_squares + (int64_t)m * g.in_tiles;
                 float ss = 0.f;
                 int i = 0;
@@ -703,7 +706,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     for (int q = 0; q < 4; ++q) dst[q] = __ldcs(p + q);
                 }
             };
-            if (g.residual != nullptr) {
+            if constexpr (ENDS == 1) {
 #pragma unroll
                 for (int u = 0; u < AHEAD; ++u) fetch(16 * u, ahead[u]);
             }
@@ -711,7 +714,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = tmem + ((uint32_t)(quarter * 32) << 16) + buf * MT_BN;
-            if (g.residual != nullptr) {
+            if constexpr (ENDS == 1) {
                 float sq = 0.f;
 #pragma unroll 1
                 for (int c0 = 0; c0 < bn; c0 += 16 * AHEAD) {
@@ -771,7 +774,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     uint32_t r[16];
                     tmem_ld16(acc + c, r);
                     if (m >= g.M || n0 + c >= g.N) continue;
-                    if (g.in_squares != nullptr) {
+                    if constexpr (ENDS == 2) {
 #pragma unroll
                         for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * rstd);
                     }
@@ -1035,6 +1038,15 @@ extern "C" int ss_gemm_tc5_many_tile_cols(int M, int N, int swiglu) {
     return bn;
 }
 
+template <int ENDS>
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const ManyArgs& g, int pairs, cudaStream_t stream) {
+    constexpr int smem_pair = PR_STAGES * (2 * TC_BM * TC_BK * 2) + 1024 + 256;
+    static SsPerDevice opted_pair;
+    if (int rc_smem = ss_opt_in_smem(gemm_tc5_pair_kernel<ENDS>, smem_pair, opted_pair)) return rc_smem;
+    ss_launch_cluster_x(gemm_tc5_pair_kernel<ENDS>, dim3(2 * pairs), dim3(TC_THREADS), smem_pair, stream, 2, ma, mb, g);
+    return SS_LAUNCH_CHECK();
+}
+
 static int gemm_tc5_many(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,
                          int64_t lda, int64_t ldb, int64_t ldc, int out_f32, int swiglu, int tile_cols,
                          const NormEnds& ends, int* err, cudaStream_t stream) {
@@ -1067,13 +1079,11 @@ static int gemm_tc5_many(const void* A, const void* B, const void* bias, int bia
     g.residual = ends.residual; g.tile_squares = ends.tile_squares; g.scaled = (bf16*)ends.scaled;
     g.norm_weight = ends.norm_weight; g.norm_w_f32 = ends.norm_w_f32;
     g.in_squares = ends.in_squares; g.in_tiles = ends.in_tiles; g.in_eps = ends.in_eps;
-    constexpr int smem_pair = PR_STAGES * (2 * TC_BM * TC_BK * 2) + 1024 + 256;
-    static SsPerDevice opted_pair;
-    if (int rc_smem = ss_opt_in_smem(gemm_tc5_pair_kernel, smem_pair, opted_pair)) return rc_smem;
     const int tiles2 = n_m * ((N + bn - 1) / bn);
     const int pairs = tiles2 < max_pairs ? tiles2 : max_pairs;
-    ss_launch_cluster_x(gemm_tc5_pair_kernel, dim3(2 * pairs), dim3(TC_THREADS), smem_pair, stream, 2, ma, mb, g);
-    return SS_LAUNCH_CHECK();
+    if (ends.residual) return launch_pair<1>(ma, mb, g, pairs, stream);
+    if (ends.in_squares) return launch_pair<2>(ma, mb, g, pairs, stream);
+    return launch_pair<0>(ma, mb, g, pairs, stream);
 }
 
 extern "C" int ss_gemm_tc5_many(const void* A, const void* B, const void* bias, int bias_f32, void* C, int M, int N, int K,

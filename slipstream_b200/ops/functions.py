@@ -1029,10 +1029,10 @@ def adds_to_stream(tokens: int, features: int, k: int, sms: int | None = None) -
 def set_norm_fusion(enabled: bool, long_portions: bool = False) -> None:
     """Whether `linear_add_rmsnorm` may leave the norm to the products around it (on by default; off for
     comparisons).  ``long_portions``: also in the two-SM kernel of prompt portions from 2,048 tokens.  That is off
-    unless asked for, by measurement at the 7B sizes: the o and down products with the add inside take 63.9 and
-    213.3 us where the product followed by the norm kernel takes 72.4 and 223.3, but q/k/v and gate/up with the
-    scale in their epilogue take 6 us longer each (57.8 against 51.9), and a whole 2,048-token step 21.7 ms
-    against 21.5."""
+    unless asked for, by measurement at the 7B sizes: the o and down products with the add inside take 71 and 225
+    us, as long as the product followed by the norm kernel (72 and 225: the read-modify-write of the stream from
+    an epilogue that holds a row per thread costs what the norm kernel cost), q/k/v and gate/up with the scale
+    in their epilogue take what they took, and a whole 2,048-token step 21.67 ms against 21.5 to 21.6."""
     _state["norm_rides_along"] = bool(enabled)
     _state["norm_rides_along_long"] = bool(enabled and long_portions)
 
