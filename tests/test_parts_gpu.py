@@ -175,3 +175,54 @@ def test_pre_norm_block(dtype):
     residual, pending = block.forward(x.to(DEV).clone(), None, ctx, LayerBinding(kv=store.kv[0][0], group=0))
     got = residual.double().cpu() + pending.double().cpu()  # the last add is left to the next norm
     assert rel(got, want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("n, fused", [(7, True), (40, False)])
+def test_pre_norm_block_chained_into_the_next_norm(n, fused):
+    """`forward_chained` with the first norm of the block that runs next: with few bfloat16 tokens and a width in
+    steps of 128 the branches' last projections add themselves to the stream and the norms come back pending (no
+    norm kernel but the first: 5 launches); with more tokens the same call runs product, add + norm (7 launches).
+    Both against the plain layer followed by the plain norm."""
+    from slipstream_b200 import ops
+    from slipstream_b200.cache import CacheManager, GroupLayout, PagedStore
+    from slipstream_b200.parts import (LayerBinding, PagedAttention, PreNormBlock, RMSNorm, RotaryEncoding,
+                                       SwiGLUFeedForward)
+    dtype = torch.bfloat16
+    hidden, heads, kv_heads, d, inter, eps, theta = 256, 4, 2, 64, 320, 1e-6, 1e4
+    prefix = "model.layers.0"
+    block = PreNormBlock(PagedAttention(f"{prefix}.self_attn", hidden, heads, kv_heads, d, RotaryEncoding(d, theta)),
+                         SwiGLUFeedForward(f"{prefix}.mlp", hidden, inter),
+                         RMSNorm(f"{prefix}.input_layernorm", hidden, eps),
+                         RMSNorm(f"{prefix}.post_attention_layernorm", hidden, eps))
+    following = RMSNorm("model.layers.1.input_layernorm", hidden, eps)
+    dev, ref = {}, {}
+    for k, child in enumerate(block.children() + [following]):
+        a, b = draw(child, dtype, seed=k, scale=0.2)  # sums over 256 and 320 terms of order one, as in the narrow block
+        dev.update(a); ref.update(b)
+    for child in block.children() + [following]:
+        child.bind(dev, runtime(dtype))
+    layouts = [GroupLayout(block.mixer.cache_spec(), 1)]
+    cache = CacheManager(layouts, 8, 8, 2, 64)
+    store = PagedStore(layouts, dtype, DEV, [[]], 2)
+    x = torch.randn(n, hidden, generator=torch.Generator().manual_seed(5))
+    s = {"n_q": heads, "n_kv": kv_heads, "head_dim": d, "theta": theta, "eps": eps}
+    out = plain.decoder_layer(x.double(), torch.arange(n), ref, 0, s)
+    want = plain.rms_norm(out, ref["model.layers.1.input_layernorm.weight"].double(), eps)
+    ctx = single_request_ctx(cache, "r", n)
+    launches = ops.launch_count()
+    residual, pending, normed = block.forward_chained(x.to(DEV).clone(), None, None, following, ctx,
+                                                      LayerBinding(kv=store.kv[0][0], group=0))
+    used = ops.launch_count() - launches
+    assert pending is None and normed is not None
+    assert isinstance(normed, ops.PendingNorm) == fused
+    if fused:
+        # norm, q/k/v, (rotation + pages), attention, o, gate/up, down: no norm kernel behind the first
+        assert used <= 7 and normed.stream.data_ptr() == residual.data_ptr()
+        got_norm = normed.materialize()
+        scaled_way = normed.scaled.double() * torch.rsqrt(normed.squares.double().sum(1, keepdim=True) / hidden + eps)
+        assert rel(scaled_way.cpu(), want) < TOL[dtype]
+    else:
+        got_norm = normed
+    errors = rel(residual.double().cpu(), out), rel(got_norm.double().cpu(), want)
+    assert errors[0] < TOL[dtype], errors  # the add is done: the stream is the layer's output
+    assert errors[1] < TOL[dtype], errors
