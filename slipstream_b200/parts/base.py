@@ -250,8 +250,9 @@ class Block(Part):
                         layer: "LayerBinding") -> tuple[torch.Tensor, torch.Tensor | None, torch.Tensor | None]:
         """``forward`` for a model that lets a block's last projection end in the next block's first norm.
         ``normed``: ``first_norm()`` of the stream, already computed by the block before, as a tensor or a pending
-        norm (then ``pending`` is None and added).  ``following``: the next block's first norm, or None.  Returns (stream, pending, normed): either
-        a pending output, or, if it applied ``following``, that norm's result.  The default chains nothing."""
+        norm (then ``pending`` is None and added).  ``following``: the next block's first norm, or None.  Returns
+        (stream, pending, normed): either a pending output, or, if it applied ``following``, that norm's result.
+        The default chains nothing."""
         assert normed is None
         residual, pending = self.forward(residual, pending, ctx, layer)
         return residual, pending, None
