@@ -211,10 +211,41 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
         // ---------------- consumers
         pdl_wait();
         if (work) {
-            for (int c = tid; c < 16 * (D / 8); c += MMA_THREADS) {
-                const int row = c / (D / 8), col = (c - row * (D / 8)) * 8;
-                const bool ok = row < heads_here;
-                cp_async16(Qs + row * KSTR + col, a.q + (int64_t)row_q * a.q_stride + (int64_t)(kvh * G + g0 + (ok ? row : 0)) * D + col, ok);
+            if constexpr (FORM == 1) {
+                // the queries are rotated on their way from global memory to shared memory: eight pairs a thread in
+                // registers, one pass and one barrier fewer than copying first and rotating in place (the arithmetic
+                // and its rounding are the same)
+                const bf16* q0 = a.q + (int64_t)row_q * a.q_stride + (int64_t)(kvh * G + g0) * D;
+                for (int idx = tid; idx < 16 * (half / 8); idx += MMA_THREADS) {
+                    const int row = idx / (half / 8), i0 = (idx - row * (half / 8)) * 8;
+                    uint4 lo4 = make_uint4(0u, 0u, 0u, 0u), hi4 = lo4;
+                    if (row < heads_here) {
+                        lo4 = *reinterpret_cast<const uint4*>(q0 + (int64_t)row * D + i0);
+                        hi4 = *reinterpret_cast<const uint4*>(q0 + (int64_t)row * D + i0 + half);
+                        bf16* x1 = reinterpret_cast<bf16*>(&lo4);
+                        bf16* x2 = reinterpret_cast<bf16*>(&hi4);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float a1 = to_float(x1[e]), a2 = to_float(x2[e]);
+                            const float c = cos_s[i0 + e], sn = sin_s[i0 + e];
+                            x1[e] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(a1, c), __fmul_rn(-a2, sn)));
+                            x2[e] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(a2, c), __fmul_rn(a1, sn)));
+                        }
+                    }
+                    *reinterpret_cast<uint4*>(Qs + row * KSTR + i0) = lo4;
+                    *reinterpret_cast<uint4*>(Qs + row * KSTR + i0 + half) = hi4;
+                }
+                for (int c = tid; c < 16 * ((D - 2 * half) / 8); c += MMA_THREADS) {  // behind the rotary size: as they are
+                    const int row = c / ((D - 2 * half) / 8), col = 2 * half + (c - row * ((D - 2 * half) / 8)) * 8;
+                    const bool ok = row < heads_here;
+                    cp_async16(Qs + row * KSTR + col, q0 + (int64_t)(ok ? row : 0) * D + col, ok);
+                }
+            } else {
+                for (int c = tid; c < 16 * (D / 8); c += MMA_THREADS) {
+                    const int row = c / (D / 8), col = (c - row * (D / 8)) * 8;
+                    const bool ok = row < heads_here;
+                    cp_async16(Qs + row * KSTR + col, a.q + (int64_t)row_q * a.q_stride + (int64_t)(kvh * G + g0 + (ok ? row : 0)) * D + col, ok);
+                }
             }
             cp_async_commit();
             if (has_newest) {
@@ -255,8 +286,8 @@ attn_decode_tma(const __grid_constant__ CUtensorMap map_kv, const DecodeTmaArgs 
             }
             cp_async_wait<0>();
             asm volatile("bar.sync 1, 128;" ::: "memory");  // the four consumer warps: Q and the newest row are in place
-            if (fused && (FORM == 1 || half > 0)) {
-                if (FORM == 1 || half % 8 == 0) {
+            if (FORM == 0 && fused && half > 0) {
+                if (half % 8 == 0) {
                     // eight pairs a thread, 16-byte accesses (element by element this loop took 1,600 cycles, a
                     // fifth of the kernel at short contexts); the arithmetic and its rounding are the same
                     for (int idx = tid; idx < 16 * (half / 8); idx += MMA_THREADS) {
