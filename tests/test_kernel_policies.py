@@ -53,3 +53,25 @@ def test_streaming_product_plan_and_routing():
         assert F.many_tokens_fits(2048, features, k, SMS) and not F.many_tokens_fits(2047, features, k, SMS)
     for features, k in ((1152, 896), (896, 4864), (2048, 1536), (3584, 3580)):
         assert not F.many_tokens_fits(4096, features, k, SMS)
+
+
+def test_where_a_projection_adds_itself_to_the_stream():
+    """The last projection of a branch takes over the add and prepares the norm behind it in decode steps of up to
+    16 tokens, where its K slices are a cluster and the width is a multiple of 128; for long prompt portions only
+    when asked for."""
+    for features, k in ((3584, 3584), (3584, 18944), (896, 4864), (5120, 13824), (128, 256)):
+        for tokens in (1, 8, 16):
+            assert F.adds_to_stream(tokens, features, k, SMS), (tokens, features, k)
+        assert not F.adds_to_stream(17, features, k, SMS) and not F.adds_to_stream(64, features, k, SMS)
+    assert not F.adds_to_stream(8, 3600, 3584, SMS)       # a width that is no multiple of 128
+    assert not F.adds_to_stream(8, 3584, 3580, SMS)       # K that the tensor-core product does not take
+    assert not F.adds_to_stream(8, 128, 64, SMS)          # one K step: nothing to cut into slices
+    assert not F.adds_to_stream(2048, 3584, 3584, SMS)    # the two-SM kernel could; it did not pay
+    try:
+        F.set_norm_fusion(True, long_portions=True)
+        assert F.adds_to_stream(2048, 3584, 3584, SMS) and not F.adds_to_stream(2047, 3584, 3584, SMS)
+        F.set_norm_fusion(False)
+        assert not F.adds_to_stream(8, 3584, 3584, SMS) and not F.adds_to_stream(2048, 3584, 3584, SMS)
+    finally:
+        F.set_norm_fusion(True)
+    assert F.adds_to_stream(8, 3584, 3584, SMS)
