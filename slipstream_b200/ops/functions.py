@@ -814,7 +814,8 @@ def gemm_tcgen05(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: to
     out_dtype = out_dtype or torch.bfloat16
     if swiglu and (tokens > 64 or features % 128):
         raise KernelError("the fused SwiGLU epilogue takes at most 64 tokens and a multiple of 128 weight rows")
-    out = torch.empty((tokens, features // 2 if swiglu else features), dtype=out_dtype, device=x.device)
+    out_shape = (tokens, features // 2 if swiglu else features)
+    out = None if to_stream is not None else torch.empty(out_shape, dtype=out_dtype, device=x.device)
     if tokens == 0:
         return out
     bias_f32 = 0
@@ -835,7 +836,7 @@ def gemm_tcgen05(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bias: to
         stream, norm_weight = to_stream
         _need(stream, torch.float32, "stream")
         _need(norm_weight, None, "norm weight")
-        if (swiglu or pending is not None or out_dtype != torch.bfloat16 or stream.shape != out.shape
+        if (swiglu or pending is not None or out_dtype != torch.bfloat16 or tuple(stream.shape) != out_shape
                 or not (swapped and 2 <= slices <= 8 and tokens <= bn) or features % 128
                 or norm_weight.numel() != features or norm_weight.dtype not in (torch.float32, torch.bfloat16)):
             raise KernelError("a product into the stream needs its plain bfloat16 output, K slices in a cluster, a "
@@ -892,7 +893,8 @@ def gemm_tcgen05_many(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bia
     out_dtype = out_dtype or torch.bfloat16
     if swiglu and (features % 128 or out_dtype != torch.bfloat16 or (features // 2) % 8):
         raise KernelError("the fused SwiGLU epilogue takes a multiple of 128 weight rows and writes bfloat16")
-    out = torch.empty((tokens, features // 2 if swiglu else features), dtype=out_dtype, device=x.device)
+    out_shape = (tokens, features // 2 if swiglu else features)
+    out = None if to_stream is not None else torch.empty(out_shape, dtype=out_dtype, device=x.device)
     if tokens == 0:
         return out
     bias_f32 = 0
@@ -905,7 +907,7 @@ def gemm_tcgen05_many(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, bia
         stream, norm_weight = to_stream
         _need(stream, torch.float32, "stream")
         _need(norm_weight, None, "norm weight")
-        if (swiglu or pending is not None or out_dtype != torch.bfloat16 or stream.shape != out.shape or features % 16
+        if (swiglu or pending is not None or out_dtype != torch.bfloat16 or tuple(stream.shape) != out_shape or features % 16
                 or norm_weight.numel() != features or norm_weight.dtype not in (torch.float32, torch.bfloat16)):
             raise KernelError("a product into the stream needs its plain bfloat16 output, a width in steps of 16 and a "
                               "stream of its shape")
@@ -1044,7 +1046,8 @@ def linear_add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor
     norm that follow it.  With few bfloat16 tokens the projection adds to the stream in its epilogue and the
     norm comes back as a `PendingNorm`, to be finished by the next product (no norm kernel); everything
     else is `linear` followed by `add_rmsnorm`."""
-    if x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and residual.shape == (x.shape[0], weight.shape[0]) \
+    if x.shape[0] > 0 and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 \
+            and residual.shape == (x.shape[0], weight.shape[0]) \
             and norm_weight.numel() == weight.shape[0] \
             and adds_to_stream(x.shape[0], weight.shape[0], x.shape[1], sm_count(x.device)):
         product = gemm_tcgen05 if x.shape[0] <= SMALL_BATCH else gemm_tcgen05_many
